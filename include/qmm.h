@@ -1,0 +1,173 @@
+/*
+ * qmm.h — C ABI of the B200 quantized-matmul kernel library (libqmm.so).
+ *
+ * This is the drop-in boundary for the quantized-matmul hot path of
+ * erfanzar/jax-metallib.  Every entry point takes plain device pointers, sizes
+ * and a CUDA stream (passed as void*, i.e. a cudaStream_t); nothing in the
+ * signatures depends on PyTorch, JAX or C++ types.  All tensors are dense and
+ * row-major unless a leading dimension is given.  Calls are asynchronous on
+ * the given stream and allocate nothing: scratch memory, where a kernel needs
+ * it, is passed in by the caller (see the *_workspace_bytes queries).
+ *
+ * Each function names the interface of the reference it stands in for
+ * (paths relative to the reference project root).
+ *
+ * Return value: 0 (QMM_OK) or a qmm_status error code; a human-readable
+ * message for the calling thread's last failure is available through
+ * qmm_last_error().  No function throws or aborts, and there is no CPU
+ * fallback: an unsupported shape or dtype is an error, as a missing op is in
+ * the reference's compile step (src/pjrt_plugin/api/pjrt_client.cc:211-220).
+ */
+#ifndef QMM_H_
+#define QMM_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(_WIN32)
+#define QMM_API
+#else
+#define QMM_API __attribute__((visibility("default")))
+#endif
+
+typedef enum qmm_status {
+  QMM_OK = 0,
+  QMM_ERR_INVALID_ARGUMENT = 1, /* null pointer, bad size, misaligned pointer */
+  QMM_ERR_UNSUPPORTED = 2,      /* shape / dtype / mode outside what the kernels cover */
+  QMM_ERR_CUDA = 3,             /* a CUDA runtime or driver call failed */
+  QMM_ERR_WORKSPACE = 4,        /* workspace missing or too small */
+  QMM_ERR_TIMEOUT = 5,          /* a bounded device-side wait gave up */
+  QMM_ERR_PARSE = 6             /* StableHLO text could not be read or matched */
+} qmm_status;
+
+/* Element type tags used by the entry points that take void* tensors. */
+typedef enum qmm_dtype {
+  QMM_F32 = 0,
+  QMM_F16 = 1,
+  QMM_BF16 = 2,
+  QMM_S8 = 3,
+  QMM_U8 = 4,
+  QMM_S32 = 5,
+  QMM_U4 = 6, /* two values per byte, low nibble first */
+  QMM_U32 = 7
+} qmm_dtype;
+
+/* MX microscaling modes of the operator API
+ * (src/jax_plugins/silicon/quantized.py:39-43). */
+typedef enum qmm_mx_mode { QMM_MXFP4 = 0, QMM_MXFP8 = 1, QMM_NVFP4 = 2 } qmm_mx_mode;
+
+QMM_API const char* qmm_version(void);
+QMM_API const char* qmm_status_name(int status);
+/* Copies the calling thread's last error message (NUL-terminated, truncated to
+ * cap) and returns its full length.  Mirrors the reference's error-as-value
+ * convention (src/pjrt_plugin/api/pjrt_memory.cc:22-57). */
+QMM_API size_t qmm_last_error(char* buf, size_t cap);
+
+/* Device-side waits (mbarrier / flag polls inside the kernels) are bounded: a
+ * kernel that gives up writes QMM_ERR_TIMEOUT plus a site tag into a
+ * host-visible status word and returns normally.  qmm_device_status() reads
+ * that word without synchronising (0 = healthy); entry points refuse further
+ * launches while it is set; qmm_clear_device_status() resets it.  The
+ * reference's counterpart is the bounded caller wait that returns
+ * DEADLINE_EXCEEDED (src/pjrt_plugin/core/completion_event.h:62-83,
+ * src/pjrt_plugin/api/pjrt_event.cc:46-59). */
+QMM_API int qmm_device_status(void);
+QMM_API void qmm_clear_device_status(void);
+
+/* ---------------------------------------------------------------------------
+ * Weight-only int8, per-output-channel scale, f32 activations.
+ *   y[M,N] = x[M,K] @ (float(w[K,N]) * scale[N])
+ * Replaces the un-fused chain HandleConvert -> HandleBroadcastInDim ->
+ * HandleMultiply -> HandleDotGeneral
+ * (src/pjrt_plugin/ops/shape_ops.mm:793-829, :93-153;
+ *  src/pjrt_plugin/ops/binary_ops.mm:165-193, :1006-1019).
+ * Exact f32 FMA arithmetic; the scale is applied once per output element. */
+QMM_API int qmm_w8a32_perchannel(const float* x, const int8_t* w, const float* scale, float* y,
+                                 int64_t M, int64_t N, int64_t K, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Weight-only int8, per-output-channel scale, bf16 activations, bf16 output.
+ *   y[M, ldy] (columns 0..N-1) = bf16( (x[M,K] @ float(w[K,N])) * scale[N] )
+ * Same chain as above with a bf16 lhs (src/pjrt_plugin/ops/binary_ops.mm:740-805:
+ * bf16 operands, f32 accumulation, one rounding to the declared result type).
+ * ldy is the row stride of y in elements (>= N), so that a rank holding a
+ * column shard can write straight into its slice of the gathered output.
+ * tcgen05 (kind::f16) GEMM with the int8->bf16 conversion done in shared
+ * memory; requires M % 128 == 0, N % 128 == 0, K % 64 == 0 for the tensor-core
+ * path, other shapes take a CUDA-core path. */
+QMM_API int qmm_w8a16_perchannel(const uint16_t* x_bf16, const int8_t* w, const float* scale,
+                                 uint16_t* y_bf16, int64_t M, int64_t N, int64_t K, int64_t ldy,
+                                 void* stream);
+/* Same, with the 16-bit format the weights are converted to chosen by the
+ * caller: 0 = bf16, 1 = f16 (int8 is exact in both; f16 needs fewer
+ * conversion instructions).  qmm_w8a16_perchannel uses 0 unless the
+ * environment variable QMM_W8A16_WEIGHT_F16=1 is set. */
+QMM_API int qmm_w8a16_perchannel_fmt(const uint16_t* x_bf16, const int8_t* w, const float* scale,
+                                     uint16_t* y_bf16, int64_t M, int64_t N, int64_t K,
+                                     int64_t ldy, int weight_format, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * int8 x int8 -> int32 dot with optional fused f32 rescale.
+ *   acc[M,N]  = a[M,K] . b[K,N]            (exact, int32)          if acc != NULL
+ *   out[M,N]  = float(acc) * row_scale[M] * col_scale[N]           if out != NULL
+ * Replaces IntegerMatMul (src/pjrt_plugin/ops/binary_ops.mm:433-475), which
+ * the reference emulates as an [M,K,N] broadcast product reduced over K, and
+ * the convert/multiply/multiply that follow it (ops/shape_ops.mm:793-829,
+ * ops/binary_ops.mm:165-193).  The multiplies happen in that order, each
+ * rounded to f32.  a_unsigned / b_unsigned select uint8 operands
+ * (tests/test_dot_preferred_dtype.py:61). */
+QMM_API int qmm_i8i8_i32(const void* a, const void* b, int32_t* acc, const float* row_scale,
+                         const float* col_scale, float* out, int64_t M, int64_t N, int64_t K,
+                         int a_unsigned, int b_unsigned, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * int4 asymmetric group-wise weight-only matmul at decode sizes (M <= 32).
+ *   w[k,n] = (q[k,n] - z[k/group, n]) * s[k/group, n]
+ *   y[M,N] = bf16( x[M,K] @ w[K,N] )
+ * wq is uint8 [K/2, N]: byte [kk, n] holds q[2kk, n] in its low nibble and
+ * q[2kk+1, n] in its high nibble (the reference's low-nibble-first packing,
+ * src/jax_plugins/silicon/quantized.py:189-191,264).  scales are bf16
+ * [K/group, N]; zeros are [K/group, N] one per byte (zeros_packed = 0) or
+ * [K/group, N/2] two per byte, low nibble = even n (zeros_packed = 1).
+ * Replaces and(…,15) / shift_right_logical(…,4) / convert / subtract /
+ * multiply / reshape / dot_general
+ * (src/pjrt_plugin/ops/bitwise_ops.mm:33-51,169-305; ops/shape_ops.mm:793-829;
+ *  ops/binary_ops.mm:66-193, :644-1245).
+ * Requires group == 128, K % 128 == 0, N % 128 == 0, 1 <= M <= 32.
+ * workspace: qmm_w4a16_g128_workspace_bytes(M, N, K) bytes, 256-byte aligned,
+ * zero-filled before its first use; the kernel leaves it zero-filled, so
+ * back-to-back calls on one stream may share it. */
+QMM_API size_t qmm_w4a16_g128_workspace_bytes(int64_t M, int64_t N, int64_t K);
+QMM_API int qmm_w4a16_g128(const uint16_t* x_bf16, const uint8_t* wq, const uint16_t* scales_bf16,
+                           const uint8_t* zeros, int zeros_packed, uint16_t* y_bf16, int64_t M,
+                           int64_t N, int64_t K, int64_t group, void* workspace,
+                           size_t workspace_bytes, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * Operator-API formats (weights stored transposed, [N, ...], K contiguous).
+ *
+ * qmm_affine_matmul replaces affine_quantized_matmul / _affine_matmul_gpu and
+ * the affine_qgemm_{4,8}bit_{f32,f16} kernels
+ * (src/jax_plugins/silicon/quantized.py:772-957, :1077-1152):
+ *   y[M,N] = dtype( sum_k float(x[m,k]) * (scales[n,k/gs] * q[n,k] + biases[n,k/gs]) )
+ * bits = 4: w_packed is uint32 [N, K/8], value j of a word at bits 4j;
+ * bits = 8: w_packed is uint8 [N, K].  dtype = QMM_F32 or QMM_F16 (x and y).
+ *
+ * qmm_mx_matmul replaces quantized_matmul / _quantized_matmul_gpu and the
+ * mx_qgemm_{mxfp4,mxfp8,nvfp4}_{f32,f16} kernels (quantized.py:528-753,
+ * :995-1074): E2M1 / E4M3 elements, E8M0 (group 32) or E4M3 (group 16) scales,
+ * NaN codes (E4M3 0x7F/0xFF, E8M0 0xFF) propagate. */
+QMM_API int qmm_affine_matmul(const void* x, const void* w_packed, const float* scales,
+                              const float* biases, void* y, int64_t M, int64_t N, int64_t K,
+                              int bits, int64_t group_size, int dtype, void* stream);
+QMM_API int qmm_mx_matmul(const void* x, const uint8_t* w_packed, const uint8_t* scales, void* y,
+                          int64_t M, int64_t N, int64_t K, int mode, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* QMM_H_ */

@@ -1,0 +1,89 @@
+"""ctypes binding of ``libqmm.so``.
+
+The library is the product: if it is missing or fails to load, every operator
+raises.  There is no CPU or framework fallback behind these calls.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+from ctypes import c_char_p, c_int, c_int64, c_size_t, c_void_p
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.environ.get("QMM_LIBRARY_PATH", os.path.join(HERE, "libqmm.so"))
+
+QMM_F32, QMM_F16, QMM_BF16, QMM_S8, QMM_U8, QMM_S32, QMM_U4, QMM_U32 = range(8)
+QMM_MXFP4, QMM_MXFP8, QMM_NVFP4 = range(3)
+MX_MODE_IDS = {"mxfp4": QMM_MXFP4, "mxfp8": QMM_MXFP8, "nvfp4": QMM_NVFP4}
+
+# name -> (restype, argtypes); mirrors include/qmm.h
+SIGNATURES = {
+    "qmm_version": (c_char_p, []),
+    "qmm_status_name": (c_char_p, [c_int]),
+    "qmm_last_error": (c_size_t, [c_char_p, c_size_t]),
+    "qmm_device_status": (c_int, []),
+    "qmm_clear_device_status": (None, []),
+    "qmm_w8a32_perchannel": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]),
+    "qmm_w8a16_perchannel": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p]),
+    "qmm_w8a16_perchannel_fmt": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int, c_void_p]),
+    "qmm_i8i8_i32": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int,
+                c_void_p]),
+    "qmm_w4a16_g128_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
+    "qmm_w4a16_g128": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p,
+                c_size_t, c_void_p]),
+    "qmm_affine_matmul": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int64, c_int,
+                c_void_p]),
+    "qmm_mx_matmul": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_void_p]),
+}
+
+
+class QmmError(RuntimeError):
+    def __init__(self, status: int, name: str, message: str):
+        super().__init__(f"{name} ({status}): {message}")
+        self.status = status
+        self.status_name = name
+
+
+_lib = None
+
+
+def load():
+    """Load the library once; raise loudly if the CUDA extension is absent."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python -m jax_metallib_b200.build` "
+            "(there is no CPU fallback for the quantized-matmul path)"
+        )
+    lib = ctypes.CDLL(LIB_PATH, mode=ctypes.RTLD_LOCAL)
+    for name, (res, args) in SIGNATURES.items():
+        try:
+            fn = getattr(lib, name)
+        except AttributeError as e:  # pragma: no cover
+            raise ImportError(f"{LIB_PATH} does not export {name}") from e
+        fn.restype = res
+        fn.argtypes = args
+    _lib = lib
+    return lib
+
+
+def last_error() -> str:
+    lib = load()
+    buf = ctypes.create_string_buffer(512)
+    lib.qmm_last_error(buf, 512)
+    return buf.value.decode("utf-8", "replace")
+
+
+def check(status: int) -> None:
+    if status != 0:
+        lib = load()
+        raise QmmError(status, lib.qmm_status_name(status).decode(), last_error())

@@ -1,0 +1,132 @@
+// Entry points whose work is routed between the tcgen05 GEMMs and plain
+// CUDA-core kernels.  The tensor-core kernels take every shape TMA can
+// describe (16-byte row pitches); anything else (the few-element shapes of the
+// reference's integer-dot tests, odd strides) runs on the simple kernels below.
+// Both routes are GPU code; there is no host fallback.
+#include <stdlib.h>
+#include <string.h>
+
+#include "common.cuh"
+
+namespace qmm {
+
+int i8gemm_tcgen05(const void* a, const void* b, int32_t* acc, const float* row_scale,
+                   const float* col_scale, float* out, int64_t M, int64_t N, int64_t K,
+                   int a_unsigned, int b_unsigned, cudaStream_t stream);
+int w8a16_tcgen05(const uint16_t* x, const int8_t* w, const float* scale, uint16_t* y, int64_t M,
+                  int64_t N, int64_t K, int64_t ldy, bool weights_f16, cudaStream_t stream);
+
+namespace simple {
+
+template <bool AU, bool BU>
+__global__ void i8dot_kernel(const uint8_t* __restrict__ a, const uint8_t* __restrict__ b,
+                             int32_t* __restrict__ acc, float* __restrict__ out,
+                             const float* __restrict__ rs, const float* __restrict__ cs, int M, int N,
+                             int K) {
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  const int m = blockIdx.y;
+  if (n >= N || m >= M) return;
+  int32_t s = 0;  // wraps mod 2^32 like the reference's int32 accumulator
+  for (int k = 0; k < K; ++k) {
+    const int av = AU ? static_cast<int>(a[static_cast<size_t>(m) * K + k])
+                      : static_cast<int>(static_cast<int8_t>(a[static_cast<size_t>(m) * K + k]));
+    const int bv = BU ? static_cast<int>(b[static_cast<size_t>(k) * N + n])
+                      : static_cast<int>(static_cast<int8_t>(b[static_cast<size_t>(k) * N + n]));
+    s = static_cast<int32_t>(static_cast<uint32_t>(s) + static_cast<uint32_t>(av * bv));
+  }
+  if (acc) acc[static_cast<size_t>(m) * N + n] = s;
+  if (out) out[static_cast<size_t>(m) * N + n] = static_cast<float>(s) * rs[m] * cs[n];
+}
+
+__global__ void w8a16_kernel(const uint16_t* __restrict__ x, const int8_t* __restrict__ w,
+                             const float* __restrict__ scale, uint16_t* __restrict__ y, int M, int N,
+                             int K, long long ldy) {
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  const int m = blockIdx.y;
+  if (n >= N || m >= M) return;
+  float s = 0.f;
+  for (int k = 0; k < K; ++k)
+    s = fmaf(dev::bf16_bits_to_float(x[static_cast<size_t>(m) * K + k]),
+             static_cast<float>(w[static_cast<size_t>(k) * N + n]), s);
+  y[static_cast<size_t>(m) * ldy + n] = dev::float_to_bf16_bits(s * scale[n]);
+}
+
+}  // namespace simple
+
+static int env_flag(const char* name, int dflt) {
+  const char* v = getenv(name);
+  if (!v || !*v) return dflt;
+  return atoi(v);
+}
+
+}  // namespace qmm
+
+extern "C" {
+
+int qmm_i8i8_i32(const void* a, const void* b, int32_t* acc, const float* row_scale,
+                 const float* col_scale, float* out, int64_t M, int64_t N, int64_t K,
+                 int a_unsigned, int b_unsigned, void* stream) {
+  using namespace qmm;
+  QMM_REQUIRE(a && b, QMM_ERR_INVALID_ARGUMENT, "qmm_i8i8_i32: null operand");
+  QMM_REQUIRE(acc || out, QMM_ERR_INVALID_ARGUMENT, "qmm_i8i8_i32: neither acc nor out requested");
+  QMM_REQUIRE(!out || (row_scale && col_scale), QMM_ERR_INVALID_ARGUMENT,
+              "qmm_i8i8_i32: out needs row_scale and col_scale");
+  QMM_REQUIRE(M >= 0 && N >= 0 && K >= 0 && M < (1ll << 30) && N < (1ll << 30) && K < (1ll << 30),
+              QMM_ERR_INVALID_ARGUMENT, "qmm_i8i8_i32: bad shape");
+  if (M == 0 || N == 0) return QMM_OK;
+  if (int st = read_device_status())
+    return set_error(QMM_ERR_TIMEOUT, "a previous kernel gave up waiting (status word 0x%x)", st);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool tma_ok = K > 0 && K % 16 == 0 && N % 16 == 0 && aligned(a, 16) && aligned(b, 16) &&
+                      (!acc || aligned(acc, 16)) && (!out || (aligned(out, 16) && aligned(col_scale, 16)));
+  if (tma_ok && M * N >= 128 * 128 && !env_flag("QMM_FORCE_SIMPLE", 0))
+    return i8gemm_tcgen05(a, b, acc, row_scale, col_scale, out, M, N, K, a_unsigned, b_unsigned, s);
+  QMM_REQUIRE(M <= 65535, QMM_ERR_UNSUPPORTED, "qmm_i8i8_i32: unaligned shape with M > 65535");
+  dim3 grid(static_cast<unsigned>((N + 127) / 128), static_cast<unsigned>(M));
+  const uint8_t* ap = static_cast<const uint8_t*>(a);
+  const uint8_t* bp = static_cast<const uint8_t*>(b);
+  const int m = (int)M, n = (int)N, k = (int)K;
+  if (a_unsigned && b_unsigned)
+    simple::i8dot_kernel<true, true><<<grid, 128, 0, s>>>(ap, bp, acc, out, row_scale, col_scale, m, n, k);
+  else if (a_unsigned)
+    simple::i8dot_kernel<true, false><<<grid, 128, 0, s>>>(ap, bp, acc, out, row_scale, col_scale, m, n, k);
+  else if (b_unsigned)
+    simple::i8dot_kernel<false, true><<<grid, 128, 0, s>>>(ap, bp, acc, out, row_scale, col_scale, m, n, k);
+  else
+    simple::i8dot_kernel<false, false><<<grid, 128, 0, s>>>(ap, bp, acc, out, row_scale, col_scale, m, n, k);
+  QMM_CHECK_LAUNCH("i8dot_kernel");
+  return QMM_OK;
+}
+
+/* weight_format: 0 = convert weights to bf16 (default), 1 = convert to f16
+ * (fewer conversion instructions; products with bf16 activations stay exact). */
+int qmm_w8a16_perchannel_fmt(const uint16_t* x, const int8_t* w, const float* scale, uint16_t* y,
+                             int64_t M, int64_t N, int64_t K, int64_t ldy, int weight_format,
+                             void* stream) {
+  using namespace qmm;
+  QMM_REQUIRE(x && w && scale && y, QMM_ERR_INVALID_ARGUMENT, "qmm_w8a16_perchannel: null pointer");
+  QMM_REQUIRE(M >= 0 && N >= 0 && K >= 0 && M < (1ll << 30) && N < (1ll << 30) && K < (1ll << 30) &&
+                  ldy >= N,
+              QMM_ERR_INVALID_ARGUMENT, "qmm_w8a16_perchannel: bad shape (ldy must be >= N)");
+  if (M == 0 || N == 0) return QMM_OK;
+  if (int st = read_device_status())
+    return set_error(QMM_ERR_TIMEOUT, "a previous kernel gave up waiting (status word 0x%x)", st);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool tma_ok = K > 0 && K % 8 == 0 && N % 16 == 0 && ldy % 2 == 0 && aligned(x, 16) &&
+                      aligned(w, 16) && aligned(y, 4);
+  if (tma_ok && M * N >= 128 * 128 && !env_flag("QMM_FORCE_SIMPLE", 0))
+    return w8a16_tcgen05(x, w, scale, y, M, N, K, ldy, weight_format == 1, s);
+  QMM_REQUIRE(M <= 65535, QMM_ERR_UNSUPPORTED, "qmm_w8a16_perchannel: unaligned shape with M > 65535");
+  dim3 grid(static_cast<unsigned>((N + 127) / 128), static_cast<unsigned>(M));
+  simple::w8a16_kernel<<<grid, 128, 0, s>>>(x, w, scale, y, (int)M, (int)N, (int)K, (long long)ldy);
+  QMM_CHECK_LAUNCH("w8a16_kernel(simple)");
+  return QMM_OK;
+}
+
+int qmm_w8a16_perchannel(const uint16_t* x, const int8_t* w, const float* scale, uint16_t* y,
+                         int64_t M, int64_t N, int64_t K, int64_t ldy, void* stream) {
+  static const int fmt = qmm::env_flag("QMM_W8A16_WEIGHT_F16", 0);
+  return qmm_w8a16_perchannel_fmt(x, w, scale, y, M, N, K, ldy, fmt, stream);
+}
+
+}  // extern "C"

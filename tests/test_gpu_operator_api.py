@@ -1,0 +1,95 @@
+"""The operator API on the GPU, against the reference's own outputs (golden
+fixtures) and the known answers of the reference's tests/test_quantized.py."""
+
+import numpy as np
+import pytest
+import torch
+
+from jax_metallib_b200 import quantized as Q
+from oracle import qmm_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.mark.parametrize("mode", ["mxfp4", "mxfp8", "nvfp4"])
+@pytest.mark.parametrize("shape", ["4x8x64", "8x16x64", "16x32x128"])
+def test_mx_matmul_matches_reference_outputs(cuda, golden, mode, shape):
+    tag = f"mx_{mode}_{shape}"
+    x, p, s = golden[tag + "_x"], golden[tag + "_packed"], golden[tag + "_scales"]
+    K = x.shape[1]
+    out = Q.quantized_matmul(x, p, s, mode=mode, K=K)
+    assert isinstance(out, np.ndarray) and out.dtype == np.float32
+    np.testing.assert_allclose(out, golden[tag + "_matmul_f32"], rtol=1e-5, atol=1e-6)
+    out16 = Q.quantized_matmul(x.astype(np.float16), p, s, mode=mode, K=K)
+    assert out16.dtype == np.float16
+    np.testing.assert_allclose(out16.astype(np.float32), O.mx_qmm(x.astype(np.float16), p, s, mode=mode, K=K)
+                               .astype(np.float32), rtol=2e-3, atol=1e-3)
+    # tolerance of the reference's own test against the float matmul (tests/test_quantized.py:228-253)
+    ref = x @ golden[tag + "_w"].T
+    np.testing.assert_allclose(out, ref, rtol=0.5, atol=0.1 if "fp4" in mode else 0.06)
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+@pytest.mark.parametrize("gs", [32, 64, 128])
+def test_affine_matmul_matches_reference_outputs(cuda, golden, bits, gs):
+    tag = f"affine_b{bits}_g{gs}"
+    x, p, s, b = golden[tag + "_x"], golden[tag + "_packed"], golden[tag + "_scales"], golden[tag + "_biases"]
+    out = Q.affine_quantized_matmul(x, p, s, b, bits=bits, group_size=gs, K=128)
+    np.testing.assert_allclose(out, golden[tag + "_matmul_f32"], rtol=1e-5, atol=1e-6)
+    out16 = Q.affine_quantized_matmul(x.astype(np.float16), p, s, b, bits=bits, group_size=gs, K=128)
+    assert out16.dtype == np.float16
+    np.testing.assert_allclose(out16.astype(np.float32), golden[tag + "_matmul_f16"].astype(np.float32),
+                               rtol=4e-3, atol=2e-3)
+
+
+def test_known_answers_of_the_reference_tests(cuda):
+    # all-ones 4-bit affine: exactly [[64, 64]] (tests/test_quantized.py:528-541)
+    p, s, b = Q.affine_quantize(np.ones((2, 64), np.float32), bits=4, group_size=64)
+    out = Q.affine_quantized_matmul(np.ones((1, 64), np.float16), p, s, b, bits=4, group_size=64, K=64,
+                                    out_dtype=np.float32)
+    assert out.dtype == np.float32
+    np.testing.assert_array_equal(out, [[64.0, 64.0]])
+    # NaN propagation (tests/test_quantized.py:303-335)
+    x = np.ones((1, 32), np.float32)
+    out = Q.quantized_matmul(x, np.array([[0x7F] + [0] * 31], np.uint8), np.array([[127]], np.uint8), mode="mxfp8", K=32)
+    assert np.isnan(out[0, 0])
+    for mode, nb in (("mxfp4", 16), ("mxfp8", 32)):
+        out = Q.quantized_matmul(x, np.full((1, nb), 0x11, np.uint8), np.array([[0xFF]], np.uint8), mode=mode, K=32)
+        assert np.isnan(out[0, 0])
+    out = Q.quantized_matmul(np.ones((1, 16), np.float32), np.full((1, 8), 0x11, np.uint8),
+                             np.array([[0x7F]], np.uint8), mode="nvfp4", K=16)
+    assert np.isnan(out[0, 0])
+    # f16 activations widened to an f32 result (tests/test_quantized.py:510-526)
+    w = np.ones((2, 64), np.float32)
+    p, s = Q.mx_quantize(w, mode="mxfp8")
+    out = Q.quantized_matmul(np.ones((1, 64), np.float16), p, s, mode="mxfp8", K=64, out_dtype=np.float32)
+    assert out.dtype == np.float32
+    np.testing.assert_allclose(out, np.ones((1, 64), np.float32) @ Q.mx_dequantize(p, s, mode="mxfp8", shape=w.shape).T,
+                               atol=0.1, rtol=0.01)
+
+
+@pytest.mark.parametrize("mode", ["mxfp4", "mxfp8", "nvfp4"])
+def test_larger_and_batched_shapes(cuda, mode):
+    rng = np.random.default_rng(42)
+    M, N, K = 64, 128, 256
+    x = rng.standard_normal((2, 3, M, K)).astype(np.float32) * 0.1
+    w = rng.standard_normal((N, K)).astype(np.float32) * 0.1
+    p, s = Q.mx_quantize(w, mode=mode)
+    xt = torch.from_numpy(x).cuda()
+    out = Q.quantized_matmul(xt, torch.from_numpy(p).cuda(), torch.from_numpy(s).cuda(), mode=mode, K=K)
+    assert isinstance(out, torch.Tensor) and out.shape == (2, 3, M, N) and out.is_cuda
+    ref = O.mx_qmm(x, p, s, mode=mode, K=K)
+    np.testing.assert_allclose(out.cpu().numpy(), ref, rtol=1e-4, atol=1e-5)
+    assert not np.isnan(out.cpu().numpy()).any() and np.any(out.cpu().numpy() != 0)
+
+
+def test_affine_large_k_and_rows(cuda):
+    rng = np.random.default_rng(7)
+    M, N, K = 19, 96, 4096
+    x = rng.standard_normal((M, K)).astype(np.float32)
+    w = rng.standard_normal((N, K)).astype(np.float32) * 0.05
+    for bits in (4, 8):
+        p, s, b = Q.affine_quantize(w, bits=bits, group_size=128)
+        out = Q.affine_quantized_matmul(x, p, s, b, bits=bits, group_size=128, K=K)
+        ref = O.affine_qmm(x, p, s, b, bits=bits, group_size=128, K=K)
+        assert O.max_rel_err(out, ref) <= 1e-5

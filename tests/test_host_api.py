@@ -1,0 +1,122 @@
+"""Host-side logic of the operator API and the C-ABI library (no GPU needed)."""
+
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+
+from jax_metallib_b200 import _lib
+from jax_metallib_b200 import quantized as Q
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_loads_and_exports_every_declared_symbol():
+    header = open(os.path.join(ROOT, "include", "qmm.h")).read()
+    declared = set(re.findall(r"QMM_API\s+[\w\s\*]+?\b(qmm_\w+)\s*\(", header))
+    assert len(declared) >= 12
+    lib = ctypes.CDLL(_lib.LIB_PATH)
+    for name in sorted(declared):
+        assert hasattr(lib, name), f"{name} is declared in include/qmm.h but not exported"
+    assert declared <= set(_lib.SIGNATURES), "every declared entry point has a ctypes signature"
+    assert b"sm_100a" in _lib.load().qmm_version()
+
+
+def test_error_reporting_without_a_gpu():
+    lib = _lib.load()
+    # argument validation happens before any CUDA call
+    st = lib.qmm_w4a16_g128(None, None, None, None, 0, None, 1, 128, 128, 128, None, 0, None)
+    assert st == 1 and lib.qmm_status_name(st) == b"QMM_ERR_INVALID_ARGUMENT"
+    assert "null" in _lib.last_error()
+    buf = ctypes.create_string_buffer(8)
+    full = lib.qmm_last_error(buf, 8)
+    assert full > 7 and len(buf.value) == 7  # truncated, NUL-terminated
+    assert lib.qmm_w4a16_g128_workspace_bytes(1, 100, 4096) == 0  # N not a multiple of 128
+    assert lib.qmm_w4a16_g128_workspace_bytes(1, 14336, 4096) > 0
+    with pytest.raises(_lib.QmmError) as e:
+        _lib.check(lib.qmm_affine_matmul(1, 1, 1, 1, 1, 1, 1, 64, 3, 64, 0, None))
+    assert e.value.status_name == "QMM_ERR_UNSUPPORTED"
+
+
+def test_codecs_match_reference_fixtures(golden):
+    p = golden["codec_probe"]
+    np.testing.assert_array_equal(Q._fp4_e2m1_quantize(p), golden["e2m1_encode_probe"])
+    np.testing.assert_array_equal(Q._fp8_e4m3_quantize(p), golden["e4m3_encode_probe"])
+    np.testing.assert_array_equal(Q._fp8_e8m0_quantize(np.abs(p)), golden["e8m0_encode_probe"])
+    codes = np.arange(256, dtype=np.uint8)
+    np.testing.assert_array_equal(Q._fp8_e4m3_dequantize(codes), golden["e4m3_decode_table"])
+    np.testing.assert_array_equal(Q._fp8_e8m0_dequantize(codes), golden["e8m0_decode_table"])
+    np.testing.assert_array_equal(Q._fp4_e2m1_dequantize(codes[:16]), golden["e2m1_decode_table"])
+
+
+@pytest.mark.parametrize("mode", ["mxfp4", "mxfp8", "nvfp4"])
+def test_mx_roundtrip_shapes_and_fixtures(golden, mode):
+    for shape in ("4x8x64", "8x16x64", "16x32x128"):
+        tag = f"mx_{mode}_{shape}"
+        w = golden[tag + "_w"]
+        p, s = Q.mx_quantize(w, mode=mode)
+        assert p.dtype == np.uint8 and s.dtype == np.uint8
+        np.testing.assert_array_equal(p, golden[tag + "_packed"])
+        np.testing.assert_array_equal(s, golden[tag + "_scales"])
+        np.testing.assert_array_equal(Q.mx_dequantize(p, s, mode=mode, shape=w.shape), golden[tag + "_dequant"])
+    cfg = Q._MX_MODES[mode]
+    p, s = Q.mx_quantize(np.ones((16, 128), np.float32), mode=mode)
+    assert p.shape == (16, 128 // (2 if cfg["bits"] == 4 else 1)) and s.shape == (16, 128 // cfg["group_size"])
+    p, s = Q.mx_quantize(np.zeros((2, 64), np.float32), mode=mode)
+    np.testing.assert_array_equal(Q.mx_dequantize(p, s, mode=mode, shape=(2, 64)), 0.0)
+    # roundtrip tolerance of tests/test_quantized.py:167-186
+    w = np.random.default_rng(42).standard_normal((4, 64)).astype(np.float32) * 0.1
+    p, s = Q.mx_quantize(w, mode=mode)
+    np.testing.assert_allclose(Q.mx_dequantize(p, s, mode=mode, shape=w.shape), w,
+                               atol=0.15 if "fp4" in mode else 0.1, rtol=0.8)
+
+
+@pytest.mark.parametrize("bits", [2, 3, 4, 8])
+def test_affine_roundtrip_and_fixtures(golden, bits):
+    for gs in (32, 64, 128):
+        tag = f"affine_b{bits}_g{gs}"
+        w = golden[tag + "_w"]
+        p, s, b = Q.affine_quantize(w, bits=bits, group_size=gs)
+        assert p.dtype == golden[tag + "_packed"].dtype
+        np.testing.assert_array_equal(p, golden[tag + "_packed"])
+        np.testing.assert_array_equal(s, golden[tag + "_scales"])
+        np.testing.assert_array_equal(b, golden[tag + "_biases"])
+        np.testing.assert_array_equal(Q.affine_dequantize(p, s, b, bits=bits, group_size=gs, shape=w.shape),
+                                      golden[tag + "_dequant"])
+    if bits in (4, 8):
+        p, s, b = Q.affine_quantize(np.ones((16, 128), np.float32), bits=bits, group_size=64)
+        assert p.shape == ((16, 16) if bits == 4 else (16, 128))
+        assert p.dtype == (np.uint32 if bits == 4 else np.uint8)
+        assert s.shape == (16, 2) and b.shape == (16, 2)
+
+
+def test_value_errors_match_reference_behaviour():
+    w = np.ones((2, 48), np.float32)
+    with pytest.raises(ValueError, match="Unknown mode"):
+        Q.mx_quantize(w, mode="fp3")
+    with pytest.raises(ValueError, match="divisible by group_size"):
+        Q.mx_quantize(w, mode="mxfp4")
+    with pytest.raises(ValueError, match="shape is required"):
+        Q.mx_dequantize(np.zeros((2, 16), np.uint8), np.zeros((2, 1), np.uint8), mode="mxfp4")
+    with pytest.raises(ValueError, match="bits must be"):
+        Q.affine_quantize(w, bits=5)
+    with pytest.raises(ValueError, match="divisible by group_size"):
+        Q.affine_quantize(w, bits=4, group_size=64)
+    with pytest.raises(ValueError, match="shape is required"):
+        Q.affine_dequantize(np.zeros((2, 8), np.uint32), np.ones((2, 1)), np.zeros((2, 1)), bits=4)
+    with pytest.raises(ValueError, match="Unknown mode"):
+        Q.quantized_matmul(np.ones((1, 32), np.float32), np.zeros((1, 16), np.uint8), np.zeros((1, 1), np.uint8),
+                           mode="bogus", K=32)
+
+
+def test_matmul_refuses_to_run_without_cuda():
+    import torch
+
+    if torch.cuda.is_available():
+        pytest.skip("a CUDA device is present")
+    w = np.ones((2, 64), np.float32)
+    p, s, b = Q.affine_quantize(w, bits=4, group_size=64)
+    with pytest.raises(RuntimeError, match="no CPU fallback"):
+        Q.affine_quantized_matmul(np.ones((1, 64), np.float32), p, s, b, bits=4, group_size=64, K=64)
