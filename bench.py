@@ -1,0 +1,512 @@
+#!/usr/bin/env python
+"""Benchmark of the quantized-matmul hot path on B200.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+Headline workload (every N): the tensor-parallel int8 per-channel weight-only
+linears with Llama-3-70B shapes — 80 layers of QKV 8192->10240, O 8192->8192,
+gate+up 8192->2x28672, down 28672->8192 on bf16 activations [4096, 8192]
+(random-init weights, seeded synthetic inputs).  One step = one pass over all
+320 linears.  With N ranks the weights are column-sharded along N, every rank
+computes its [4096, N/P] slice and the slices are all-gathered with NCCL
+(strong scaling: total work is fixed).  ``value`` is prefill TFLOP/s of the
+whole job, timed on the device with inputs resident in HBM; ``e2e`` is the same
+metric with the step's activations copied from pinned host memory and the
+last layer's result copied back inside the timed region.
+
+At N = 1 the JSON line also carries, under ``detail``, the other workloads of
+the path (decode int4 GEMV in GB/s, int8 x int8 GEMM in TOP/s, the small f32
+case in microseconds), each with its own roofline fraction, and a CPU baseline
+(the NumPy oracle timed on the host cores on a bounded sample).
+
+``--impl reference`` times the reference's CPU route for this path — the
+oracle restatement, since neither jaxlib's CPU backend nor the Metal plugin
+can be installed here — on the same metric.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+M_TOKENS = 4096
+D_MODEL, FFN, QKV = 8192, 28672, 10240
+N_LAYERS = 80
+METRIC = "prefill_tflops_int8_weight_only_linears"
+
+
+def layer_shapes():
+    """(name, K, N, activation) for the four linears of a layer."""
+    return [("qkv", D_MODEL, QKV, "x"), ("o", D_MODEL, D_MODEL, "x"), ("gate_up", D_MODEL, 2 * FFN, "x"),
+            ("down", FFN, D_MODEL, "h")]
+
+
+def flops_per_layer(m=M_TOKENS):
+    return sum(2.0 * m * k * n for _, k, n, _ in layer_shapes())
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            d = json.load(open(path))
+            return dict(hbm_gbs=float(d["hbm_gbs"]), bf16_tflops=float(d["bf16_tflops"]),
+                        bf16_tflops_sustained=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                        source="measured")
+        except Exception:
+            pass
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+# ----------------------------------------------------------------------------
+# clocks sampled during the timed region
+# ----------------------------------------------------------------------------
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu_index = gpu_index
+        self.proc = None
+        self.lines = []
+        self.thread = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100",
+                 "-i", str(self.gpu_index)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
+            return
+
+        def reader():
+            for line in self.proc.stdout:
+                self.lines.append((time.time(), line.strip()))
+
+        self.thread = threading.Thread(target=reader, daemon=True)
+        self.thread.start()
+
+    def stop(self, t0: float, t1: float):
+        if self.proc is None:
+            return None
+        time.sleep(0.15)
+        self.proc.terminate()  # the exact child this object started
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, smax, reasons = [], [], set()
+        for ts, line in self.lines:
+            if ts < t0 or ts > t1 + 0.2:
+                continue
+            f = [p.strip() for p in line.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                smax.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        if not sm:
+            return None
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(smax), "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+# ----------------------------------------------------------------------------
+# CPU baseline (oracle port) — also the --impl reference arm
+# ----------------------------------------------------------------------------
+def cpu_linears_tflops(budget_s: float, m_rows: int = 256):
+    """Time the NumPy oracle of the weight-only int8 linears on the host cores.
+
+    Sample: the four linears of one layer at m_rows activation rows (full K and
+    N), repeated until budget_s seconds of CPU work have been spent."""
+    import numpy as np
+
+    from jax_metallib_b200 import synthetic
+    from oracle import qmm_oracle as O
+
+    rng = np.random.default_rng(5000)
+    problems = []
+    for _name, k, n, _act in layer_shapes():
+        x = synthetic.bf16_bits_to_f32(synthetic.to_bf16_bits(rng.standard_normal((m_rows, k)).astype(np.float32)))
+        w = rng.integers(-127, 128, size=(k, n), dtype=np.int64).astype(np.int8)
+        s = rng.uniform(0.005, 0.02, size=(n,)).astype(np.float32)
+        problems.append((x, w, s))
+    flops = sum(2.0 * m_rows * w.shape[0] * w.shape[1] for _, w, _ in problems)
+
+    def one_pass():
+        for x, w, s in problems:
+            wf = O.w8_perchannel_dequant(w, s)  # fp32 dequantise
+            y = x @ wf                            # f32 dot (BLAS, all host threads)
+            O.f32_to_bf16_bits(y)                 # round to the declared result type
+
+    one_pass()  # warm-up
+    t0 = time.perf_counter()
+    reps = 0
+    while True:
+        one_pass()
+        reps += 1
+        if time.perf_counter() - t0 >= budget_s:
+            break
+    dt = (time.perf_counter() - t0) / reps
+    cores = os.cpu_count() or 1
+    return dict(value=flops / dt / 1e12, unit="TFLOP/s", cores=cores, kind="port",
+                sample=f"one layer's four linears at M={m_rows} rows (full K, N), fp32 dequantise + NumPy "
+                       f"matmul + bf16 rounding, {reps} passes, {dt:.3f} s each"), dt
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    budget = 20.0
+    # --steps/--warmup are honoured as repetitions of the bounded sample
+    base, dt = cpu_linears_tflops(budget_s=max(5.0, min(60.0, budget)))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": base["value"], "unit": "TFLOP/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "int8 per-channel weight-only linears, Llama-3-70B shapes (80 layers), "
+                               "bf16 activations [4096,8192]; CPU arm runs a bounded sample of one layer",
+                   "parallelism": f"tp{args.gpus}", "note": "reference CPU route = NumPy oracle port "
+                   "(jaxlib CPU backend and the Metal plugin are not installable offline)"},
+        "cpu_baseline": base,
+        "e2e": {"value": base["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+# ----------------------------------------------------------------------------
+# GPU arm
+# ----------------------------------------------------------------------------
+def build_weights(torch, synthetic, device, rank, world, layers):
+    """Column shard of every layer's four weights, generated on the device."""
+    gen = synthetic.torch_generator(device, 5, rank)
+    weights = []
+    for _l in range(layers):
+        layer = []
+        for name, k, n, act in layer_shapes():
+            assert n % world == 0
+            ns = n // world
+            w = synthetic.device_int8((k, ns), device, gen)
+            s = synthetic.device_uniform((ns,), 0.005, 0.02, device, gen)
+            layer.append((name, k, n, ns, act, w, s))
+        weights.append(layer)
+    return weights
+
+
+def run_gpu(args):
+    import torch
+    import torch.distributed as dist
+
+    from jax_metallib_b200 import _lib, ops, synthetic
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        if world == 1 and args.gpus > 1:
+            raise SystemExit("launch with torch.distributed.run for --gpus > 1")
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    lib = _lib.load()
+    peaks = measured_peaks()
+    layers = args.layers
+
+    weights = build_weights(torch, synthetic, device, rank, world, layers)
+    gen = synthetic.torch_generator(device, 5, 1000)
+    x_host = torch.randn((M_TOKENS, D_MODEL), dtype=torch.float32).to(torch.bfloat16).pin_memory()
+    h_host = torch.randn((M_TOKENS, FFN), dtype=torch.float32).to(torch.bfloat16).pin_memory()
+    acts = {"x": x_host.to(device), "h": h_host.to(device)}
+    # gathered outputs, one buffer per linear kind (reused by every layer)
+    outs = {}
+    for name, k, n, act in layer_shapes():
+        if world == 1:
+            outs[name] = torch.empty((M_TOKENS, n), dtype=torch.bfloat16, device=device)
+        else:
+            # all_gather_into_tensor concatenates rank buffers: [P, M, N/P]; a consumer
+            # addresses it as a 3-D tensor (rank, row, column-in-shard)
+            outs[name] = torch.empty((world, M_TOKENS, n // world), dtype=torch.bfloat16, device=device)
+    shard_out = {name: torch.empty((M_TOKENS, n // world), dtype=torch.bfloat16, device=device)
+                 for name, k, n, act in layer_shapes()} if world > 1 else None
+    result_host = torch.empty((M_TOKENS, D_MODEL), dtype=torch.bfloat16).pin_memory()
+
+    compute = torch.cuda.current_stream()
+    comm = torch.cuda.Stream() if world > 1 else None
+    launches = [0]
+    kernel_events = []
+
+    def step(record_kernels=False):
+        prev_done = None
+        for layer in weights:
+            for name, k, n, ns, act, w, s in layer:
+                xin = acts[act]
+                if world == 1:
+                    if record_kernels:
+                        e0 = torch.cuda.Event(enable_timing=True)
+                        e1 = torch.cuda.Event(enable_timing=True)
+                        e0.record()
+                    ops.w8a16_perchannel(xin, w, s, out=outs[name])
+                    if record_kernels:
+                        e1.record()
+                        kernel_events.append((e0, e1, 2.0 * M_TOKENS * k * ns))
+                else:
+                    # the gather of the previous use of this buffer must be finished
+                    if prev_done is not None and name in prev_done:
+                        compute.wait_event(prev_done[name])
+                    if record_kernels:
+                        e0 = torch.cuda.Event(enable_timing=True)
+                        e1 = torch.cuda.Event(enable_timing=True)
+                        e0.record()
+                    ops.w8a16_perchannel(xin, w, s, out=shard_out[name])
+                    if record_kernels:
+                        e1.record()
+                        kernel_events.append((e0, e1, 2.0 * M_TOKENS * k * ns))
+                    ready = torch.cuda.Event()
+                    ready.record(compute)
+                    comm.wait_event(ready)
+                    with torch.cuda.stream(comm):
+                        dist.all_gather_into_tensor(outs[name].view(-1), shard_out[name].view(-1))
+                        done = torch.cuda.Event()
+                        done.record(comm)
+                    prev_done = prev_done or {}
+                    prev_done[name] = done
+                launches[0] += 1
+        if world > 1:
+            compute.wait_stream(comm)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- resident-input timing -------------------------------------------------
+    for _ in range(args.warmup):
+        step()
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+        time.sleep(0.3)
+    barrier()
+    launches[0] = 0
+    t_wall0 = time.time()
+    ev0 = torch.cuda.Event(enable_timing=True)
+    ev1 = torch.cuda.Event(enable_timing=True)
+    ev0.record()
+    for _ in range(args.steps):
+        step(record_kernels=True)
+    ev1.record()
+    barrier()
+    t_wall1 = time.time()
+    clocks = sampler.stop(t_wall0, t_wall1) if rank == 0 else None
+    ms = ev0.elapsed_time(ev1)
+    timed_launches = launches[0]
+    kern_ms = sum(a.elapsed_time(b) for a, b, _ in kernel_events)
+    kern_flops = sum(f for _, _, f in kernel_events)
+    if world > 1:
+        t = torch.tensor([ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms_per_step = ms / args.steps
+    total_flops = flops_per_layer() * layers
+    value = total_flops / (ms_per_step * 1e-3) / 1e12
+
+    # ---- end-to-end timing (host activations in, last result out) ---------------
+    def e2e_step():
+        acts["x"].copy_(x_host, non_blocking=True)
+        acts["h"].copy_(h_host, non_blocking=True)
+        step()
+        last = outs["down"]
+        if world == 1:
+            result_host.copy_(last, non_blocking=True)
+        else:
+            result_host.view(world, M_TOKENS, D_MODEL // world).copy_(last, non_blocking=True)
+
+    e2e_step()
+    barrier()
+    ee0 = torch.cuda.Event(enable_timing=True)
+    ee1 = torch.cuda.Event(enable_timing=True)
+    ee0.record()
+    for _ in range(args.steps):
+        e2e_step()
+    ee1.record()
+    barrier()
+    e2e_ms = ee0.elapsed_time(ee1)
+    if world > 1:
+        t = torch.tensor([e2e_ms], dtype=torch.float64, device=device)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t.item())
+    e2e_value = total_flops / (e2e_ms / args.steps * 1e-3) / 1e12
+    h2d = x_host.numel() * 2 + h_host.numel() * 2
+    d2h = result_host.numel() * 2
+
+    status = lib.qmm_device_status()
+    if status != 0:
+        raise SystemExit(f"device status word is 0x{status:x}: a kernel gave up waiting")
+
+    line = None
+    if rank == 0:
+        peak = peaks["bf16_tflops_sustained"]
+        achieved = kern_flops / (kern_ms * 1e-3) / 1e12 if kern_ms > 0 else 0.0
+        line = {
+            "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"int8 per-channel weight-only linears, Llama-3-70B shapes, {layers} layers x "
+                                   "(qkv 8192->10240, o 8192->8192, gate_up 8192->57344, down 28672->8192), "
+                                   "bf16 activations [4096,8192]",
+                       "parallelism": f"tp{world} (weights column-sharded along N, NCCL all-gather of outputs "
+                                      "into [P, M, N/P], overlapped on a second stream)" if world > 1 else "tp1",
+                       "l2": "every launch reads a different weight matrix (>= 67 MB each), inputs exceed L2",
+                       "layers": layers},
+            "roofline": {"bound": "tensor", "kernel": "w8a16_kernel (tcgen05 kind::f16, in-kernel int8->bf16)",
+                         "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
+                         "peak_source": f"{peaks['source']} bf16_tflops_sustained (burst {peaks['bf16_tflops']})",
+                         "traffic": None},
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": timed_launches,
+            "clocks": clocks,
+        }
+    if world == 1 and rank == 0 and not args.no_detail:
+        line["detail"] = run_detail(torch, ops, synthetic, lib, device, peaks)
+        base, _ = cpu_linears_tflops(budget_s=12.0)
+        line["cpu_baseline"] = base
+    if rank == 0:
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+def run_detail(torch, ops, synthetic, lib, device, peaks):
+    """The other workloads of the path.  The kernels here run for microseconds,
+    so a sequence of launches is captured in a CUDA graph and the graph is
+    replayed: the device time per launch is then free of host launch overhead.
+    Timing is by CUDA events on the replaying stream."""
+    detail = {}
+    hbm = peaks["hbm_gbs"]
+    stream = torch.cuda.Stream()
+
+    def graph_time(launch, n_launches, replays=20, warm_replays=3):
+        """launch(i) issues the i-th kernel; returns mean microseconds per kernel."""
+        with torch.cuda.stream(stream):
+            launch(0)  # first call outside capture (function attributes, lazy init)
+            stream.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g, stream=stream):
+                for i in range(n_launches):
+                    launch(i)
+            for _ in range(warm_replays):
+                g.replay()
+            stream.synchronize()
+            e0 = torch.cuda.Event(enable_timing=True)
+            e1 = torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for _ in range(replays):
+                g.replay()
+            e1.record(stream)
+            stream.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / (replays * n_launches)
+
+    # decode int4 g128 GEMV: rotate through enough weight copies that no launch finds its weights in L2
+    K, N, G = 4096, 14336, 32
+    copies = 12  # 12 x 30.5 MB > 2 x L2
+    gen = synthetic.torch_generator(device, 3, 0)
+    wqs = [torch.randint(0, 256, (K // 2, N), dtype=torch.uint8, device=device, generator=gen) for _ in range(copies)]
+    sc = synthetic.device_uniform((G, N), 0.002, 0.01, device, gen, torch.bfloat16)
+    zp = torch.randint(0, 256, (G, N // 2), dtype=torch.uint8, device=device, generator=gen)
+    ws = torch.zeros(lib.qmm_w4a16_g128_workspace_bytes(16, N, K), dtype=torch.uint8, device=device)
+    for M in (1, 4, 16):
+        x = synthetic.device_normal((M, K), device, gen, torch.bfloat16)
+        y = torch.empty((M, N), dtype=torch.bfloat16, device=device)
+        us = graph_time(lambda i: ops.w4a16_g128(x, wqs[i % copies], sc, zp, zeros_packed=True, out=y, workspace=ws),
+                        copies * 2)
+        us_warm = graph_time(lambda i: ops.w4a16_g128(x, wqs[0], sc, zp, zeros_packed=True, out=y, workspace=ws),
+                             copies * 2)
+        nbytes = K * N // 2 + G * N * 2 + G * N // 2 + M * K * 2 + M * N * 2
+        gbs = nbytes / (us * 1e-6) / 1e9
+        detail[f"int4_g128_decode_M{M}"] = {
+            "us": us, "bytes": nbytes, "GB/s": gbs, "frac_of_measured_hbm": gbs / hbm, "frac_of_8TBs": gbs / 8000.0,
+            "us_warm_l2_single_copy": us_warm,
+            "note": f"{copies} rotating weight copies (cold L2), zero points packed 4-bit, CUDA-graph replay"}
+    del wqs
+
+    # int8 x int8 -> int32 with fused rescale
+    Mi, Ki, Ni = 2048, 4096, 4096
+    gen = synthetic.torch_generator(device, 2, 0)
+    a = synthetic.device_int8((Mi, Ki), device, gen)
+    bs = [synthetic.device_int8((Ki, Ni), device, gen) for _ in range(10)]  # 160 MB of B operands
+    row = synthetic.device_uniform((Mi,), 0.01, 0.05, device, gen)
+    col = synthetic.device_uniform((Ni,), 0.005, 0.02, device, gen)
+    out = torch.empty((Mi, Ni), dtype=torch.float32, device=device)
+
+    def run_i8(i):
+        st = lib.qmm_i8i8_i32(a.data_ptr(), bs[i % 10].data_ptr(), None, row.data_ptr(), col.data_ptr(),
+                              out.data_ptr(), Mi, Ni, Ki, 0, 0, torch.cuda.current_stream().cuda_stream)
+        assert st == 0
+
+    us = graph_time(run_i8, 20, replays=10)
+    tops = 2.0 * Mi * Ni * Ki / (us * 1e-6) / 1e12
+    detail["int8_dot_2048x4096x4096_f32_rescale"] = {
+        "us": us, "TOP/s": tops, "frac_of_2x_measured_bf16_burst": tops / (2 * peaks["bf16_tflops"]),
+        "note": "fused float(acc)*row*col epilogue, f32 output only; 10 rotating B operands; the int8 peak is "
+                "not in MEASURED_PEAKS.json, 2 x the measured bf16 burst stands in for it"}
+    del bs
+
+    # small f32 case (launch-latency bound)
+    c = synthetic.config1()
+    x1 = torch.from_numpy(c["x"]).to(device)
+    w1 = torch.from_numpy(c["w"]).to(device)
+    s1 = torch.from_numpy(c["scale"]).to(device)
+    y1 = torch.empty((32, 1024), dtype=torch.float32, device=device)
+
+    def run_c1(i):
+        st = lib.qmm_w8a32_perchannel(x1.data_ptr(), w1.data_ptr(), s1.data_ptr(), y1.data_ptr(), 32, 1024, 1024,
+                                      torch.cuda.current_stream().cuda_stream)
+        assert st == 0
+
+    us = graph_time(run_c1, 50)
+    nbytes = 32 * 1024 * 4 * 2 + 1024 * 1024 + 4096
+    detail["int8_weight_only_f32_32x1024x1024"] = {
+        "us": us, "GB/s": nbytes / (us * 1e-6) / 1e9, "frac_of_measured_hbm": nbytes / (us * 1e-6) / 1e9 / hbm,
+        "note": "1.3 MB problem (fits L2): back-to-back launches in a CUDA graph; latency bound"}
+    return detail
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--layers", type=int, default=N_LAYERS, help="layers in the pass (the workload names 80)")
+    ap.add_argument("--no-detail", action="store_true", help="skip the per-workload detail and the CPU baseline")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference(args)
+    return run_gpu(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

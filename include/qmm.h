@@ -97,19 +97,12 @@ QMM_API int qmm_w8a32_perchannel(const float* x, const int8_t* w, const float* s
  * ldy is the row stride of y in elements (>= N), so that a rank holding a
  * column shard can write straight into its slice of the gathered output.
  * tcgen05 (kind::f16) GEMM with the int8->bf16 conversion done in shared
- * memory; requires M % 128 == 0, N % 128 == 0, K % 64 == 0 for the tensor-core
- * path, other shapes take a CUDA-core path. */
+ * memory.  The tensor-core route needs K % 8 == 0, N % 16 == 0, an even ldy
+ * and 16-byte aligned x and w (what TMA can address); any other shape runs on
+ * a plain CUDA-core kernel. */
 QMM_API int qmm_w8a16_perchannel(const uint16_t* x_bf16, const int8_t* w, const float* scale,
                                  uint16_t* y_bf16, int64_t M, int64_t N, int64_t K, int64_t ldy,
                                  void* stream);
-/* Same, with the 16-bit format the weights are converted to chosen by the
- * caller: 0 = bf16, 1 = f16 (int8 is exact in both; f16 needs fewer
- * conversion instructions).  qmm_w8a16_perchannel uses 0 unless the
- * environment variable QMM_W8A16_WEIGHT_F16=1 is set. */
-QMM_API int qmm_w8a16_perchannel_fmt(const uint16_t* x_bf16, const int8_t* w, const float* scale,
-                                     uint16_t* y_bf16, int64_t M, int64_t N, int64_t K,
-                                     int64_t ldy, int weight_format, void* stream);
-
 /* ---------------------------------------------------------------------------
  * int8 x int8 -> int32 dot with optional fused f32 rescale.
  *   acc[M,N]  = a[M,K] . b[K,N]            (exact, int32)          if acc != NULL

@@ -14,7 +14,7 @@ int i8gemm_tcgen05(const void* a, const void* b, int32_t* acc, const float* row_
                    const float* col_scale, float* out, int64_t M, int64_t N, int64_t K,
                    int a_unsigned, int b_unsigned, cudaStream_t stream);
 int w8a16_tcgen05(const uint16_t* x, const int8_t* w, const float* scale, uint16_t* y, int64_t M,
-                  int64_t N, int64_t K, int64_t ldy, bool weights_f16, cudaStream_t stream);
+                  int64_t N, int64_t K, int64_t ldy, cudaStream_t stream);
 
 namespace simple {
 
@@ -67,13 +67,13 @@ int qmm_i8i8_i32(const void* a, const void* b, int32_t* acc, const float* row_sc
                  const float* col_scale, float* out, int64_t M, int64_t N, int64_t K,
                  int a_unsigned, int b_unsigned, void* stream) {
   using namespace qmm;
+  QMM_REQUIRE(M >= 0 && N >= 0 && K >= 0 && M < (1ll << 30) && N < (1ll << 30) && K < (1ll << 30),
+              QMM_ERR_INVALID_ARGUMENT, "qmm_i8i8_i32: bad shape");
+  if (M == 0 || N == 0) return QMM_OK;  // empty result
   QMM_REQUIRE(a && b, QMM_ERR_INVALID_ARGUMENT, "qmm_i8i8_i32: null operand");
   QMM_REQUIRE(acc || out, QMM_ERR_INVALID_ARGUMENT, "qmm_i8i8_i32: neither acc nor out requested");
   QMM_REQUIRE(!out || (row_scale && col_scale), QMM_ERR_INVALID_ARGUMENT,
               "qmm_i8i8_i32: out needs row_scale and col_scale");
-  QMM_REQUIRE(M >= 0 && N >= 0 && K >= 0 && M < (1ll << 30) && N < (1ll << 30) && K < (1ll << 30),
-              QMM_ERR_INVALID_ARGUMENT, "qmm_i8i8_i32: bad shape");
-  if (M == 0 || N == 0) return QMM_OK;
   if (int st = read_device_status())
     return set_error(QMM_ERR_TIMEOUT, "a previous kernel gave up waiting (status word 0x%x)", st);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
@@ -98,35 +98,26 @@ int qmm_i8i8_i32(const void* a, const void* b, int32_t* acc, const float* row_sc
   return QMM_OK;
 }
 
-/* weight_format: 0 = convert weights to bf16 (default), 1 = convert to f16
- * (fewer conversion instructions; products with bf16 activations stay exact). */
-int qmm_w8a16_perchannel_fmt(const uint16_t* x, const int8_t* w, const float* scale, uint16_t* y,
-                             int64_t M, int64_t N, int64_t K, int64_t ldy, int weight_format,
-                             void* stream) {
+int qmm_w8a16_perchannel(const uint16_t* x, const int8_t* w, const float* scale, uint16_t* y,
+                         int64_t M, int64_t N, int64_t K, int64_t ldy, void* stream) {
   using namespace qmm;
-  QMM_REQUIRE(x && w && scale && y, QMM_ERR_INVALID_ARGUMENT, "qmm_w8a16_perchannel: null pointer");
   QMM_REQUIRE(M >= 0 && N >= 0 && K >= 0 && M < (1ll << 30) && N < (1ll << 30) && K < (1ll << 30) &&
                   ldy >= N,
               QMM_ERR_INVALID_ARGUMENT, "qmm_w8a16_perchannel: bad shape (ldy must be >= N)");
-  if (M == 0 || N == 0) return QMM_OK;
+  if (M == 0 || N == 0) return QMM_OK;  // empty result
+  QMM_REQUIRE(x && w && scale && y, QMM_ERR_INVALID_ARGUMENT, "qmm_w8a16_perchannel: null pointer");
   if (int st = read_device_status())
     return set_error(QMM_ERR_TIMEOUT, "a previous kernel gave up waiting (status word 0x%x)", st);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool tma_ok = K > 0 && K % 8 == 0 && N % 16 == 0 && ldy % 2 == 0 && aligned(x, 16) &&
                       aligned(w, 16) && aligned(y, 4);
   if (tma_ok && M * N >= 128 * 128 && !env_flag("QMM_FORCE_SIMPLE", 0))
-    return w8a16_tcgen05(x, w, scale, y, M, N, K, ldy, weight_format == 1, s);
+    return w8a16_tcgen05(x, w, scale, y, M, N, K, ldy, s);
   QMM_REQUIRE(M <= 65535, QMM_ERR_UNSUPPORTED, "qmm_w8a16_perchannel: unaligned shape with M > 65535");
   dim3 grid(static_cast<unsigned>((N + 127) / 128), static_cast<unsigned>(M));
   simple::w8a16_kernel<<<grid, 128, 0, s>>>(x, w, scale, y, (int)M, (int)N, (int)K, (long long)ldy);
   QMM_CHECK_LAUNCH("w8a16_kernel(simple)");
   return QMM_OK;
-}
-
-int qmm_w8a16_perchannel(const uint16_t* x, const int8_t* w, const float* scale, uint16_t* y,
-                         int64_t M, int64_t N, int64_t K, int64_t ldy, void* stream) {
-  static const int fmt = qmm::env_flag("QMM_W8A16_WEIGHT_F16", 0);
-  return qmm_w8a16_perchannel_fmt(x, w, scale, y, M, N, K, ldy, fmt, stream);
 }
 
 }  // extern "C"

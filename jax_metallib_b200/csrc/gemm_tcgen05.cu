@@ -201,41 +201,29 @@ constexpr int kStageBytes = kRawBytes + kCvtBytes + kXBytes;  // 56 KB
 constexpr int kThreads = (2 + kEpiWarps + kCvtWarps) * 32;
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 1024;
 
-// Sixteen int8 (one 16-byte read) -> sixteen 16-bit floats, exactly.
-//  WF16 = false: bf16 through f32 (2^23 + 128 + v, minus the constant, packed RNE)
-//  WF16 = true : f16 (1024 + 128 + v as 0x64xx, minus 1152)
-template <bool WF16>
+// Sixteen int8 (one 16-byte read) -> sixteen bf16, exactly: the byte, biased to
+// unsigned, becomes the low mantissa bits of 2^23 (an f32 holding 2^23 + 128 + v),
+// the constant is subtracted and pairs are packed with round-to-nearest (exact,
+// |v| <= 128 fits bf16's 8 significant bits).  The MMA needs both operands in
+// one 16-bit format (an f16 weight operand against bf16 activations raises an
+// illegal-instruction error on sm_100a), so the weights follow the activations.
 __device__ __forceinline__ void convert16(const uint4& in, uint4& lo8, uint4& hi8) {
   const uint32_t w[4] = {in.x ^ 0x80808080u, in.y ^ 0x80808080u, in.z ^ 0x80808080u,
                          in.w ^ 0x80808080u};
   uint32_t o[8];
-  if (WF16) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const uint32_t p01 = __byte_perm(w[i], 0x64646464u, 0x4140);
-      const uint32_t p23 = __byte_perm(w[i], 0x64646464u, 0x4342);
-      const __half2 m = __halves2half2(__ushort_as_half(0x6480), __ushort_as_half(0x6480));
-      __half2 a = __hsub2(*reinterpret_cast<const __half2*>(&p01), m);
-      __half2 b = __hsub2(*reinterpret_cast<const __half2*>(&p23), m);
-      o[2 * i] = *reinterpret_cast<uint32_t*>(&a);
-      o[2 * i + 1] = *reinterpret_cast<uint32_t*>(&b);
-    }
-  } else {
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float f0 = __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7440)) - 8388736.f;
-      const float f1 = __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7441)) - 8388736.f;
-      const float f2 = __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7442)) - 8388736.f;
-      const float f3 = __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7443)) - 8388736.f;
-      o[2 * i] = dev::pack_bf16x2(f0, f1);
-      o[2 * i + 1] = dev::pack_bf16x2(f2, f3);
-    }
+  for (int i = 0; i < 4; ++i) {
+    const float f0 = __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7440)) - 8388736.f;
+    const float f1 = __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7441)) - 8388736.f;
+    const float f2 = __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7442)) - 8388736.f;
+    const float f3 = __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7443)) - 8388736.f;
+    o[2 * i] = dev::pack_bf16x2(f0, f1);
+    o[2 * i + 1] = dev::pack_bf16x2(f2, f3);
   }
   lo8 = make_uint4(o[0], o[1], o[2], o[3]);
   hi8 = make_uint4(o[4], o[5], o[6], o[7]);
 }
 
-template <bool WF16>
 __global__ void __launch_bounds__(kThreads, 1)
 w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
              const float* __restrict__ scale, uint16_t* __restrict__ y, int M, int N, int K,
@@ -387,7 +375,7 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
           const int r = (p * kCvtWarps + cw) * 4 + rsub;  // k-row 0..63
           const uint4 in = *reinterpret_cast<const uint4*>(raw + r * 128 + ((seg ^ (r & 7)) << 4));
           uint4 lo8, hi8;
-          convert16<WF16>(in, lo8, hi8);
+          convert16(in, lo8, hi8);
           uint8_t* rowp = dst + (seg >> 2) * (BK * 128) + r * 128;
           const int c0 = 2 * (seg & 3), c1 = c0 + 1;
           uint4* p0 = reinterpret_cast<uint4*>(rowp + ((c0 ^ (r & 7)) << 4));
@@ -449,7 +437,7 @@ int i8gemm_tcgen05(const void* a, const void* b, int32_t* acc, const float* row_
 }
 
 int w8a16_tcgen05(const uint16_t* x, const int8_t* w, const float* scale, uint16_t* y, int64_t M,
-                  int64_t N, int64_t K, int64_t ldy, bool weights_f16, cudaStream_t stream) {
+                  int64_t N, int64_t K, int64_t ldy, cudaStream_t stream) {
   using namespace tc::w8;
   CUtensorMap wmap, xmap;
   if (int rc = make_tensor_map_2d(&wmap, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)K,
@@ -460,23 +448,17 @@ int w8a16_tcgen05(const uint16_t* x, const int8_t* w, const float* scale, uint16
     return rc;
   static bool configured = false;
   if (!configured) {
-    QMM_CUDA_TRY(cudaFuncSetAttribute(w8a16_kernel<false>,
-                                      cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
-    QMM_CUDA_TRY(cudaFuncSetAttribute(w8a16_kernel<true>,
-                                      cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    QMM_CUDA_TRY(cudaFuncSetAttribute(w8a16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                      kSmemBytes));
     configured = true;
   }
-  // operand "a" of the MMA = weights (f16 or bf16, MN-major), "b" = activations (bf16, K-major)
-  const uint32_t idesc = dev::make_idesc(/*c=f32*/ 1, weights_f16 ? 0 : 1, /*bf16*/ 1,
+  // operand "a" of the MMA = weights (bf16, MN-major), "b" = activations (bf16, K-major)
+  const uint32_t idesc = dev::make_idesc(/*c=f32*/ 1, /*bf16*/ 1, /*bf16*/ 1,
                                          /*a MN-major*/ 1, /*b K-major*/ 0, BNW, BMX);
   const int tiles = static_cast<int>(((N + BNW - 1) / BNW) * ((M + BMX - 1) / BMX));
   const int grid = tiles < num_sms() ? tiles : num_sms();
-  if (weights_f16)
-    w8a16_kernel<true><<<grid, kThreads, kSmemBytes, stream>>>(
-        wmap, xmap, scale, y, (int)M, (int)N, (int)K, (long long)ldy, idesc, device_status_word());
-  else
-    w8a16_kernel<false><<<grid, kThreads, kSmemBytes, stream>>>(
-        wmap, xmap, scale, y, (int)M, (int)N, (int)K, (long long)ldy, idesc, device_status_word());
+  w8a16_kernel<<<grid, kThreads, kSmemBytes, stream>>>(wmap, xmap, scale, y, (int)M, (int)N, (int)K,
+                                                       (long long)ldy, idesc, device_status_word());
   QMM_CHECK_LAUNCH("w8a16_kernel");
   return QMM_OK;
 }

@@ -101,10 +101,10 @@ extern "C" int qmm_w8a32_perchannel(const float* x, const int8_t* w, const float
                                     int64_t M, int64_t N, int64_t K, void* stream) {
   using namespace qmm;
   using namespace qmm::w8a32;
-  QMM_REQUIRE(x && w && scale && y, QMM_ERR_INVALID_ARGUMENT, "qmm_w8a32_perchannel: null pointer");
   QMM_REQUIRE(M >= 0 && N >= 0 && K >= 0 && M < (1ll << 30) && N < (1ll << 30) && K < (1ll << 30),
               QMM_ERR_INVALID_ARGUMENT, "qmm_w8a32_perchannel: bad shape");
-  if (M == 0 || N == 0) return QMM_OK;
+  if (M == 0 || N == 0) return QMM_OK;  // empty result: nothing to launch, pointers may be null
+  QMM_REQUIRE(x && w && scale && y, QMM_ERR_INVALID_ARGUMENT, "qmm_w8a32_perchannel: null pointer");
   const unsigned gx = static_cast<unsigned>((N + TN - 1) / TN);
   const unsigned gy = static_cast<unsigned>((M + TM - 1) / TM);
   QMM_REQUIRE(gy <= 65535, QMM_ERR_UNSUPPORTED, "qmm_w8a32_perchannel: M too large");

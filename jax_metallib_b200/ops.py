@@ -51,7 +51,7 @@ def w8a32_perchannel(x: torch.Tensor, w: torch.Tensor, scale: torch.Tensor) -> t
 
 
 def w8a16_perchannel(x: torch.Tensor, w: torch.Tensor, scale: torch.Tensor, out: torch.Tensor | None = None,
-                     out_col_offset: int = 0, weight_format: int | None = None) -> torch.Tensor:
+                     out_col_offset: int = 0) -> torch.Tensor:
     """bf16 ``x[M,K]`` times int8 ``w[K,N]`` with per-channel f32 ``scale[N]`` -> bf16.
 
     ``out`` may be a wider ``[M, N_total]`` buffer; the result is written to
@@ -72,13 +72,8 @@ def w8a16_perchannel(x: torch.Tensor, w: torch.Tensor, scale: torch.Tensor, out:
         raise ValueError("bad output buffer")
     ldy = out.shape[1]
     yptr = out.data_ptr() + 2 * out_col_offset
-    lib = _lib.load()
-    if weight_format is None:
-        st = lib.qmm_w8a16_perchannel(x.data_ptr(), w.data_ptr(), scale.data_ptr(), yptr, M, N, K, ldy, _stream_ptr())
-    else:
-        st = lib.qmm_w8a16_perchannel_fmt(x.data_ptr(), w.data_ptr(), scale.data_ptr(), yptr, M, N, K, ldy,
-                                          int(weight_format), _stream_ptr())
-    _lib.check(st)
+    _lib.check(_lib.load().qmm_w8a16_perchannel(x.data_ptr(), w.data_ptr(), scale.data_ptr(), yptr, M, N, K, ldy,
+                                                _stream_ptr()))
     return out
 
 
