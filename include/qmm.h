@@ -141,6 +141,36 @@ QMM_API int qmm_w4a16_g128(const uint16_t* x_bf16, const uint8_t* wq, const uint
                            size_t workspace_bytes, void* stream);
 
 /* ---------------------------------------------------------------------------
+ * The same matmul for callers that cannot allocate device memory.
+ *
+ * This entry point has no counterpart in the reference; it exists for hosts
+ * of this library that must not (or cannot) call cudaMalloc around a matmul:
+ * an executable running under a runtime that already owns nearly all of HBM
+ * (a PJRT/XLA client preallocates its pool, so a later cudaMalloc can simply
+ * fail), and decode loops in which an allocation or free would synchronise
+ * the whole device in the middle of a token.  Such a caller has nowhere to
+ * get the split-K workspace of qmm_w4a16_g128 from, so this variant brings its
+ * own: a fixed array of QMM_STATIC_SCRATCH_BYTES inside the library's device
+ * image (each GPU that loads the library holds it until the process exits).
+ *
+ * Arguments and result are those of qmm_w4a16_g128 without the workspace.
+ * The call allocates nothing and frees nothing.  Limits and rules:
+ *  - shapes whose scratch need (qmm_w4a16_g128_workspace_bytes) exceeds
+ *    QMM_STATIC_SCRATCH_BYTES are refused with QMM_ERR_WORKSPACE — 4 MiB covers
+ *    M <= 16 at 4096 x 14336 (3.7 MB) and M <= 8 at 14336 x 4096;
+ *  - the first call on each device resolves the array's device address; make
+ *    that call before starting any stream capture;
+ *  - the array is shared by every call on the device and keeps what the last
+ *    call wrote; the part that must start at zero is cleared on the stream by
+ *    each call, but two calls that may run at the same time on one GPU race
+ *    on it — keep them on one stream or order them yourself. */
+#define QMM_STATIC_SCRATCH_BYTES (4u << 20)
+QMM_API int qmm_w4a16_g128_static_scratch(const uint16_t* x_bf16, const uint8_t* wq,
+                                          const uint16_t* scales_bf16, const uint8_t* zeros,
+                                          int zeros_packed, uint16_t* y_bf16, int64_t M, int64_t N,
+                                          int64_t K, int64_t group, void* stream);
+
+/* ---------------------------------------------------------------------------
  * Operator-API formats (weights stored transposed, [N, ...], K contiguous).
  *
  * qmm_affine_matmul replaces affine_quantized_matmul / _affine_matmul_gpu and

@@ -34,6 +34,9 @@ SIGNATURES = {
     "qmm_w4a16_g128": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p,
                 c_size_t, c_void_p]),
+    "qmm_w4a16_g128_static_scratch": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int64, c_int64, c_int64,
+                c_void_p]),
     "qmm_affine_matmul": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int64, c_int,
                 c_void_p]),

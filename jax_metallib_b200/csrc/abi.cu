@@ -44,6 +44,8 @@ int* device_status_word() {
   std::call_once(g_status_once, init_status_word);
   return g_status_dev;
 }
+// The status word if it has been created already, else null.  Never allocates.
+int* device_status_word_if_ready() { return g_status_dev; }
 int read_device_status() {
   std::call_once(g_status_once, init_status_word);
   return g_status_host ? *reinterpret_cast<volatile int*>(g_status_host) : 0;

@@ -43,6 +43,7 @@ int set_error(int status, const char* fmt, ...) __attribute__((format(printf, 2,
 // give up (code in the low 16 bits, a site tag above).  Allocated once per
 // process; readable by the host without synchronising.
 int* device_status_word();   // device-visible pointer (may be null on failure)
+int* device_status_word_if_ready();  // same, but never creates it (null until someone has)
 int read_device_status();    // current value (0 = healthy)
 void clear_device_status();
 int num_sms();               // of the current device (cached)

@@ -19,6 +19,8 @@
 // Partial sums of CTAs sharing a column block meet in the caller's workspace;
 // the last CTA to arrive adds them in a fixed order (deterministic result) and
 // writes bf16.  The workspace counters are left at zero.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace qmm {
@@ -367,6 +369,60 @@ static int slots_for(int G, int U, int P) {
 }
 static int rows_padded(int M) { return M <= 8 ? 8 : (M <= 16 ? 16 : 32); }
 
+// ---------------------------------------------------------------------------
+// Built-in scratch for callers that must not allocate.
+//
+// The array lives in the library's device image: every GPU that loads the
+// library holds these bytes until the process exits.  On the host its name is
+// only a handle, not an address a kernel can use; the device address is
+// looked up once per device with cudaGetSymbolAddress while that device is
+// current, and that pointer is what gets passed to the kernel.
+// ---------------------------------------------------------------------------
+constexpr size_t kStaticScratchBytes = QMM_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+static void* g_static_scratch_addr[kMaxDevices] = {nullptr};
+static std::mutex g_static_scratch_mutex;
+
+// Device address of g_static_scratch on the current device (looked up on the
+// first call per device, cached afterwards).
+static int static_scratch_address(void** out) {
+  int dev = -1;
+  QMM_CUDA_TRY(cudaGetDevice(&dev));
+  QMM_REQUIRE(dev >= 0 && dev < kMaxDevices, QMM_ERR_UNSUPPORTED, "device ordinal %d out of range", dev);
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch_addr[dev] == nullptr) {
+    void* p = nullptr;
+    QMM_CUDA_TRY(cudaGetSymbolAddress(&p, g_static_scratch));
+    QMM_REQUIRE(p != nullptr && aligned(p, 256), QMM_ERR_CUDA,
+                "cudaGetSymbolAddress returned an unusable address for the built-in scratch");
+    g_static_scratch_addr[dev] = p;
+  }
+  *out = g_static_scratch_addr[dev];
+  return QMM_OK;
+}
+
+// Same launch as launch<MT, ZP>() but with the status pointer supplied by the
+// caller instead of created on demand (creating it would allocate).
+template <int MT, bool ZP>
+static int launch_no_alloc(const CUtensorMap& wmap, const uint16_t* x, const uint16_t* scales,
+                           const uint8_t* zeros, uint16_t* y, float* ws_partial, int* ws_counter,
+                           int M, int N, int K, int G, int U, int P, int max_slots, int* status,
+                           cudaStream_t stream) {
+  using L = Smem<MT>;
+  static bool configured = false;
+  auto kern = w4a16_decode_kernel<MT, ZP>;
+  if (!configured) {
+    QMM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
+    configured = true;
+  }
+  kern<<<P, kThreads, L::kTotal, stream>>>(wmap, x, scales, zeros, y, ws_partial, ws_counter, M, N,
+                                           K, G, U, max_slots, status);
+  QMM_CHECK_LAUNCH("w4a16_decode_kernel");
+  return QMM_OK;
+}
+
 }  // namespace w4
 }  // namespace qmm
 
@@ -438,6 +494,82 @@ int qmm_w4a16_g128(const uint16_t* x, const uint8_t* wq, const uint16_t* scales,
   if (M <= 16) return QMM_W4_LAUNCH(2);
   return QMM_W4_LAUNCH(4);
 #undef QMM_W4_LAUNCH
+}
+
+
+// qmm_w4a16_g128 for callers that cannot allocate: the split-K scratch is the
+// library's own fixed array instead of a caller-provided workspace.
+//
+// Nothing here calls cudaMalloc, cudaFree, a host allocator of the CUDA
+// runtime or any library routine that allocates.  The first call on a device
+// looks up the array's device address (cudaGetSymbolAddress, with that device
+// current); make that first call outside any stream capture.  The arrival
+// counters at the head of the array are cleared on the stream before every
+// launch, so a call never depends on what an earlier call (possibly one that
+// was cut short) left behind; the partial tiles behind them are overwritten
+// before they are read.  All calls on a device share the one array: two calls
+// that can overlap on the GPU (different streams without an ordering between
+// them) race on it and must be serialised by the caller.
+int qmm_w4a16_g128_static_scratch(const uint16_t* x, const uint8_t* wq, const uint16_t* scales,
+                                  const uint8_t* zeros, int zeros_packed, uint16_t* y, int64_t M,
+                                  int64_t N, int64_t K, int64_t group, void* stream) {
+  using namespace qmm;
+  using namespace qmm::w4;
+  QMM_REQUIRE(x && wq && scales && zeros && y, QMM_ERR_INVALID_ARGUMENT,
+              "qmm_w4a16_g128_static_scratch: null tensor pointer");
+  QMM_REQUIRE(group == kGroup, QMM_ERR_UNSUPPORTED,
+              "qmm_w4a16_g128_static_scratch: group must be 128, got %lld", (long long)group);
+  QMM_REQUIRE(M >= 1 && M <= 32, QMM_ERR_UNSUPPORTED,
+              "qmm_w4a16_g128_static_scratch: covers 1 <= M <= 32, got %lld", (long long)M);
+  QMM_REQUIRE(N >= kColsPerBlock && N % kColsPerBlock == 0 && K >= kGroup && K % kGroup == 0,
+              QMM_ERR_UNSUPPORTED,
+              "qmm_w4a16_g128_static_scratch: N (%lld) and K (%lld) must be positive multiples of 128",
+              (long long)N, (long long)K);
+  QMM_REQUIRE(N * (K / kGroup) < (1ll << 30), QMM_ERR_UNSUPPORTED,
+              "qmm_w4a16_g128_static_scratch: problem too large");
+  QMM_REQUIRE(aligned(x, 16) && aligned(wq, 16) && aligned(scales, 16) && aligned(zeros, 16) &&
+                  aligned(y, 4),
+              QMM_ERR_INVALID_ARGUMENT,
+              "qmm_w4a16_g128_static_scratch: tensors must be 16-byte aligned");
+  const size_t need = qmm_w4a16_g128_workspace_bytes(M, N, K);
+  QMM_REQUIRE(need > 0 && need <= kStaticScratchBytes, QMM_ERR_WORKSPACE,
+              "qmm_w4a16_g128_static_scratch: this shape needs %zu bytes of scratch but the built-in "
+              "array holds %zu; use qmm_w4a16_g128 with a caller-provided workspace",
+              need, kStaticScratchBytes);
+  void* scratch = nullptr;
+  if (int rc = static_scratch_address(&scratch)) return rc;
+
+  const int G = static_cast<int>(K / kGroup);
+  const int C = static_cast<int>(N / kColsPerBlock);
+  const int U = G * C;
+  const int P = grid_size(U);
+  const int slots = slots_for(G, U, P);
+  const size_t counters = (static_cast<size_t>(C) * sizeof(int) + 255) / 256 * 256;
+  int* ws_counter = static_cast<int*>(scratch);
+  float* ws_partial = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + counters);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  QMM_CUDA_TRY(cudaMemsetAsync(ws_counter, 0, counters, st));
+
+  CUtensorMap wmap;
+  if (int rc = make_tensor_map_2d(&wmap, wq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1,
+                                  static_cast<uint64_t>(K / 2), static_cast<uint64_t>(N),
+                                  static_cast<uint64_t>(N), kRowsPerUnit, kColsPerBlock,
+                                  CU_TENSOR_MAP_SWIZZLE_128B))
+    return rc;
+  // A wait that gives up is reported through the library's status word when
+  // that word exists already (any other entry point, or qmm_device_status(),
+  // creates it); this call will not create it, because that allocates.
+  int* status = device_status_word_if_ready();
+  const int m = static_cast<int>(M), n = static_cast<int>(N), k = static_cast<int>(K);
+#define QMM_W4_LAUNCH_NA(MT)                                                                       \
+  (zeros_packed ? launch_no_alloc<MT, true>(wmap, x, scales, zeros, y, ws_partial, ws_counter, m, \
+                                            n, k, G, U, P, slots, status, st)                     \
+                : launch_no_alloc<MT, false>(wmap, x, scales, zeros, y, ws_partial, ws_counter, m, \
+                                             n, k, G, U, P, slots, status, st))
+  if (M <= 8) return QMM_W4_LAUNCH_NA(1);
+  if (M <= 16) return QMM_W4_LAUNCH_NA(2);
+  return QMM_W4_LAUNCH_NA(4);
+#undef QMM_W4_LAUNCH_NA
 }
 
 }  // extern "C"
