@@ -502,9 +502,20 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--layers", type=int, default=N_LAYERS, help="layers in the pass (the workload names 80)")
     ap.add_argument("--no-detail", action="store_true", help="skip the per-workload detail and the CPU baseline")
+    ap.add_argument("--detail-only", action="store_true",
+                    help="run only the per-workload detail (small case for profiling) and print it as JSON")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    if args.detail_only:
+        import torch
+
+        from jax_metallib_b200 import _lib, ops, synthetic
+
+        device = torch.device("cuda", 0)
+        torch.cuda.set_device(device)
+        print(json.dumps({"detail": run_detail(torch, ops, synthetic, _lib.load(), device, measured_peaks())}))
+        return 0
     return run_gpu(args)
 
 

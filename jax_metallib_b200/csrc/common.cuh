@@ -119,12 +119,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // phase did not complete within kWaitLimitNs; callers then stop issuing work
 // and fall through to their teardown (free TMEM, return).
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int tag) {
-  for (int i = 0; i < 64; ++i) {
+  for (int i = 0; i < 128; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
   }
   const uint64_t t0 = globaltimer_ns();
   while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
+#pragma unroll 1
+    for (int i = 0; i < 32; ++i) {
+      if (mbar_try_wait(bar, parity)) return true;
+    }
     if (globaltimer_ns() - t0 > kWaitLimitNs) break;
   }
   if (status) atomicExch(status, (tag << 16) | QMM_ERR_TIMEOUT);

@@ -5,17 +5,25 @@
 // HBM-bound: the packed weights (K*N/2 bytes) are read exactly once.  The work
 // is cut into units of one 128-column block x one 128-k group (a 64-row x
 // 128-byte tile, 8 KB); consecutive units are dealt evenly to a grid of
-// resident CTAs (2 per SM), so every SM streams the same number of bytes.
+// resident CTAs, so every SM streams the same number of bytes.
 //
-// Per CTA: a producer warp issues TMA loads (packed weights with the 128-byte
-// swizzle, scales and zero points as bulk copies) into an 8-deep ring and
-// stages the activations of the group (k-permuted to match the MMA fragment,
-// plus the per-row group sums); eight consumer warps each own 16 columns.
-// A consumer reads the tile with ldmatrix.trans, turns nibbles into bf16
-// (128 + q) with one logic op each, and feeds mma.sync.m16n8k16 with the
-// weights as the 16-row operand and the activations as the 8-column operand.
-// Per group the accumulator is corrected and scaled:
-//   y += s[g,n] * (acc - (128 + z[g,n]) * sum_k x[m,k])
+// Per CTA: a producer warp issues the loads of a unit (TMA tile of packed
+// weights with the 128-byte swizzle, bulk copies of scales and zero points, a
+// TMA box of the group's activations) into an mbarrier ring, and two units
+// later turns those activations into the MMA's operand: f16, scaled per (row,
+// group) by a power of two so that any bf16 magnitude fits, odd k divided by
+// 16, every four k permuted to fragment order, written back in place.
+// Eight consumer warps each own 16 columns.  A consumer reads the tile with
+// ldmatrix.trans, which turns the k-pair-per-byte layout into registers that
+// hold (same column, two k) in their 16-bit halves; one logic op per register
+// makes the f16 pair 1024+q (low nibbles) or 1024+16q (high nibbles, no shift
+// needed: the factor 16 is what the activations of odd k were divided by), one
+// packed subtract removes 1024+z resp. 1024+16z, and mma.sync.m16n8k16 (f16,
+// f32 accumulate) takes the weights as its 16-row operand and the activations
+// as its 8-column operand: one MMA per 256 weights for M <= 8.  The integer
+// ALU pipe, the narrow one on this SM, sees five instructions per eight
+// weights; the subtracts go to the FMA pipe.  Per group:
+//   y += s[g,n] * 2^e[m,g] * acc.
 // Partial sums of CTAs sharing a column block meet in the caller's workspace;
 // the last CTA to arrive adds them in a fixed order (deterministic result) and
 // writes bf16.  The workspace counters are left at zero.
@@ -31,23 +39,26 @@ constexpr int kGroup = 128;          // k per unit
 constexpr int kRowsPerUnit = 64;     // packed byte-rows per unit
 constexpr int kConsumerWarps = 8;
 constexpr int kThreads = (kConsumerWarps + 1) * 32;
-constexpr int kXRowBytes = 288;      // 128 bf16 + 32 B pad: conflict-free 8-byte fragment reads
+constexpr int kXRowBytes = 256;      // 128 16-bit activations; 16-byte chunks XOR-swizzled by (row & 3) << 1
+constexpr int kXLag = 2;             // units between issuing a group's loads and converting its activations
 
 template <int MT>
 struct Smem {
   static constexpr int kW = kRowsPerUnit * kColsPerBlock;  // 8192
   static constexpr int kS = kColsPerBlock * 2;             // 256
   static constexpr int kZ = kColsPerBlock;                 // 128 (64 used when packed)
-  static constexpr int kSx = 128;                          // MT*8 floats, padded
-  static constexpr int kX = MT * 8 * kXRowBytes;
+  static constexpr int kF = 128;                           // per-row power-of-two factors (MT*8 floats)
+  static constexpr int kX = MT * 8 * kXRowBytes;           // also the byte count of the TMA box
   static constexpr int kOffS = kW;
   static constexpr int kOffZ = kOffS + kS;
-  static constexpr int kOffSx = kOffZ + kZ;
-  static constexpr int kOffX = kOffSx + kSx;
+  static constexpr int kOffF = kOffZ + kZ;
+  static constexpr int kOffX = 9216;                       // multiple of 256 (the swizzle uses address bits 5-7)
   static constexpr int kStage = ((kOffX + kX + 1023) / 1024) * 1024;
-  static constexpr int kStages = (MT <= 2) ? 8 : 6;
+  static constexpr int kMinBlocks = (MT == 1) ? 3 : 2;     // resident CTAs per SM
+  static constexpr int kStages = (MT == 1) ? 6 : (MT == 2 ? 8 : 6);
   static constexpr int kBarBytes = 1024;
   static constexpr int kTotal = kStages * kStage + kBarBytes + 1024;  // + alignment slack
+  static_assert(kOffF + kF <= kOffX, "stage layout overlaps");
 };
 
 __device__ __forceinline__ void bulk_copy_g2s(void* smem_dst, const void* gsrc, uint32_t bytes,
@@ -65,14 +76,29 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4
                : "r"(addr));
 }
 
-__device__ __forceinline__ void mma_bf16_16816(float (&d)[4], uint32_t a0, uint32_t a1,
-                                               uint32_t a2, uint32_t a3, uint32_t b0,
-                                               uint32_t b1) {
+__device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
+                                              uint32_t a3, uint32_t b0, uint32_t b1) {
   asm volatile(
-      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
       "{%8, %9}, {%0, %1, %2, %3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t mask, uint32_t orv) {
+  uint32_t r;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(mask), "r"(orv));  // (a & b) | c
+  return r;
+}
+__device__ __forceinline__ uint32_t hsub2_u32(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+__device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
+  uint32_t r;
+  asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
 }
 
 // CTA that owns unit u when U units are dealt to P CTAs as [i*U/P, (i+1)*U/P).
@@ -81,8 +107,8 @@ __device__ __forceinline__ int cta_of_unit(long long u, int P, int U) {
 }
 
 template <int MT, bool ZP_PACKED>
-__global__ void __launch_bounds__(kThreads, 2)
-w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const uint16_t* __restrict__ x,
+__global__ void __launch_bounds__(kThreads, Smem<MT>::kMinBlocks)
+w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
                     const uint16_t* __restrict__ scales, const uint8_t* __restrict__ zeros,
                     uint16_t* __restrict__ y, float* __restrict__ ws_partial,
                     int* __restrict__ ws_counter, int M, int N, int K, int G, int U, int max_slots,
@@ -94,7 +120,8 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const uint16_t* __
                                              ~static_cast<uintptr_t>(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + S * L::kStage);
   uint64_t* empty = full + S;
-  uint64_t* sync_bar = empty + S;  // consumer-only rendezvous with a bounded wait
+  uint64_t* xraw = empty + S;      // raw activations of the group have landed
+  uint64_t* sync_bar = xraw + S;   // consumer-only rendezvous with a bounded wait
   int* flag = reinterpret_cast<int*>(sync_bar + 1);
 
   const int warp = threadIdx.x >> 5;
@@ -102,11 +129,13 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const uint16_t* __
   const int P = gridDim.x;
   const int u_begin = static_cast<int>((static_cast<long long>(blockIdx.x) * U) / P);
   const int u_end = static_cast<int>((static_cast<long long>(blockIdx.x + 1) * U) / P);
+  const int n_units = u_end - u_begin;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       dev::mbar_init(&full[s], 2);                // TMA transaction arrive + activation staging
       dev::mbar_init(&empty[s], kConsumerWarps);  // one arrive per consumer warp
+      dev::mbar_init(&xraw[s], 1);
     }
     dev::mbar_init(sync_bar, kConsumerWarps);
     dev::fence_mbar_init();
@@ -115,72 +144,105 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const uint16_t* __
 
   if (warp == kConsumerWarps) {
     // ------------------------------ producer ------------------------------
-    if (lane == 0) dev::tma_prefetch_desc(&wmap);
+    // Iteration `it` issues every load of unit `it` (one elected lane) and, kXLag
+    // units later, the whole warp converts that unit's activations in place, so
+    // the loads of several units are always in flight while it works.
+    if (lane == 0) {
+      dev::tma_prefetch_desc(&wmap);
+      dev::tma_prefetch_desc(&xmap);
+    }
     const uint64_t policy = dev::policy_evict_first();
     constexpr int kPasses = MT * 4;  // a pass = 2 rows x 16 lanes x 16 bytes
-    uint4 xr[kPasses];
-    auto load_x = [&](int u) {
-      const int g = u % G;
-#pragma unroll
-      for (int p = 0; p < kPasses; ++p) {
-        const int row = p * 2 + (lane >> 4);
-        if (row < M) {
-          const uint16_t* src = x + static_cast<size_t>(row) * K + g * kGroup + (lane & 15) * 8;
-          xr[p] = __ldg(reinterpret_cast<const uint4*>(src));
-        } else {
-          xr[p] = make_uint4(0, 0, 0, 0);
+    int c = (n_units > 0) ? u_begin / G : 0;
+    int g = (n_units > 0) ? u_begin - c * G : 0;
+    int s_issue = 0, s_conv = 0;
+    uint32_t ph_issue = 0, ph_conv = 0;
+    for (int it = 0; it < n_units + kXLag; ++it) {
+      if (it < n_units) {
+        if (!dev::mbar_wait(&empty[s_issue], ph_issue ^ 1, status, 1)) break;
+        if (lane == 0) {
+          uint8_t* st = smem + s_issue * L::kStage;
+          const uint32_t zbytes = ZP_PACKED ? 64 : 128;
+          dev::mbar_expect_tx(&full[s_issue], L::kW + L::kS + zbytes);
+          dev::tma_load_2d_hint(st, &wmap, &full[s_issue], c * kColsPerBlock, g * kRowsPerUnit,
+                                policy);
+          bulk_copy_g2s(st + L::kOffS, scales + static_cast<size_t>(g) * N + c * kColsPerBlock,
+                        L::kS, &full[s_issue]);
+          const uint8_t* zsrc =
+              ZP_PACKED ? zeros + static_cast<size_t>(g) * (N / 2) + c * (kColsPerBlock / 2)
+                        : zeros + static_cast<size_t>(g) * N + c * kColsPerBlock;
+          bulk_copy_g2s(st + L::kOffZ, zsrc, zbytes, &full[s_issue]);
+          // activations of the group: rows beyond M are zero-filled by the TMA unit
+          dev::mbar_expect_tx(&xraw[s_issue], L::kX);
+          dev::tma_load_2d(st + L::kOffX, &xmap, &xraw[s_issue], g * kGroup, 0);
         }
+        if (++g == G) { g = 0; ++c; }
+        if (++s_issue == S) { s_issue = 0; ph_issue ^= 1; }
       }
-    };
-    if (u_begin < u_end) load_x(u_begin);
-    int it = 0;
-    for (int u = u_begin; u < u_end; ++u, ++it) {
-      const int s = it % S;
-      const uint32_t ph = (it / S) & 1;
-      if (!dev::mbar_wait(&empty[s], ph ^ 1, status, 1)) break;
-      uint8_t* st = smem + s * L::kStage;
-      const int c = u / G, g = u % G;
-      if (lane == 0) {
-        const uint32_t zbytes = ZP_PACKED ? 64 : 128;
-        dev::mbar_expect_tx(&full[s], L::kW + L::kS + zbytes);
-        dev::tma_load_2d_hint(st, &wmap, &full[s], c * kColsPerBlock, g * kRowsPerUnit, policy);
-        bulk_copy_g2s(st + L::kOffS, scales + static_cast<size_t>(g) * N + c * kColsPerBlock,
-                      L::kS, &full[s]);
-        const uint8_t* zsrc = ZP_PACKED
-                                  ? zeros + static_cast<size_t>(g) * (N / 2) + c * (kColsPerBlock / 2)
-                                  : zeros + static_cast<size_t>(g) * N + c * kColsPerBlock;
-        bulk_copy_g2s(st + L::kOffZ, zsrc, zbytes, &full[s]);
-      }
-      // activations of this group: permute every 4 consecutive k from (0,1,2,3)
-      // to (0,2,1,3) and sum each row over the group
-      float* sx = reinterpret_cast<float*>(st + L::kOffSx);
+      if (it >= kXLag) {
+        if (!dev::mbar_wait(&xraw[s_conv], ph_conv, status, 4)) break;
+        uint8_t* st = smem + s_conv * L::kStage;
+        float* fac = reinterpret_cast<float*>(st + L::kOffF);
+        uint4 v[kPasses];
 #pragma unroll
-      for (int p = 0; p < kPasses; ++p) {
-        const int row = p * 2 + (lane >> 4);
-        const uint4 v = xr[p];
-        uint4 o;
-        o.x = __byte_perm(v.x, v.y, 0x5410);
-        o.y = __byte_perm(v.x, v.y, 0x7632);
-        o.z = __byte_perm(v.z, v.w, 0x5410);
-        o.w = __byte_perm(v.z, v.w, 0x7632);
-        *reinterpret_cast<uint4*>(st + L::kOffX + row * kXRowBytes + (lane & 15) * 16) = o;
-        float sum = __uint_as_float(v.x << 16) + __uint_as_float(v.x & 0xFFFF0000u) +
-                    __uint_as_float(v.y << 16) + __uint_as_float(v.y & 0xFFFF0000u) +
-                    __uint_as_float(v.z << 16) + __uint_as_float(v.z & 0xFFFF0000u) +
-                    __uint_as_float(v.w << 16) + __uint_as_float(v.w & 0xFFFF0000u);
+        for (int p = 0; p < kPasses; ++p) {
+          const int row = p * 2 + (lane >> 4);
+          v[p] = *reinterpret_cast<const uint4*>(st + L::kOffX + row * kXRowBytes + (lane & 15) * 16);
+        }
+        __syncwarp();  // every raw chunk is in registers before any is overwritten
 #pragma unroll
-        for (int off = 8; off >= 1; off >>= 1) sum += __shfl_xor_sync(0xFFFFFFFFu, sum, off);
-        if ((lane & 15) == 0) sx[row] = sum;
+        for (int p = 0; p < kPasses; ++p) {
+          const int row = p * 2 + (lane >> 4);
+          // largest magnitude of the row's 128 values, from the bf16 bit patterns
+          uint32_t mx = __vmaxu2(__vmaxu2(v[p].x & 0x7FFF7FFFu, v[p].y & 0x7FFF7FFFu),
+                                 __vmaxu2(v[p].z & 0x7FFF7FFFu, v[p].w & 0x7FFF7FFFu));
+          mx = max(mx & 0xFFFFu, mx >> 16);
+#pragma unroll
+          for (int off = 8; off >= 1; off >>= 1) mx = max(mx, __shfl_xor_sync(0xFFFFFFFFu, mx, off));
+          // scale the row by 2^(135 - e) so that |x| < 2^9 in f16 whatever its bf16
+          // exponent e was; the inverse goes to the consumers.  Degenerate rows
+          // (all tiny, or inf/NaN present) are passed through unscaled.
+          const uint32_t e8 = mx >> 7;
+          const bool scaled = (e8 >= 16u) && (e8 < 255u);
+          const float mul = scaled ? __uint_as_float((262u - e8) << 23) : 1.0f;
+          const float inv = scaled ? __uint_as_float((e8 - 8u) << 23) : 1.0f;
+          const float mul_odd = mul * 0.0625f;
+          const uint32_t w0 = pack_f16x2(__uint_as_float(v[p].x << 16) * mul,
+                                         __uint_as_float(v[p].x & 0xFFFF0000u) * mul_odd);
+          const uint32_t w1 = pack_f16x2(__uint_as_float(v[p].y << 16) * mul,
+                                         __uint_as_float(v[p].y & 0xFFFF0000u) * mul_odd);
+          const uint32_t w2 = pack_f16x2(__uint_as_float(v[p].z << 16) * mul,
+                                         __uint_as_float(v[p].z & 0xFFFF0000u) * mul_odd);
+          const uint32_t w3 = pack_f16x2(__uint_as_float(v[p].w << 16) * mul,
+                                         __uint_as_float(v[p].w & 0xFFFF0000u) * mul_odd);
+          // every 4 consecutive k go from (0,1,2,3) to (0,2,1,3): the order the
+          // MMA fragments of the consumers read them in
+          uint4 o;
+          o.x = __byte_perm(w0, w1, 0x5410);
+          o.y = __byte_perm(w0, w1, 0x7632);
+          o.z = __byte_perm(w2, w3, 0x5410);
+          o.w = __byte_perm(w2, w3, 0x7632);
+          const int chunk = (lane & 15) ^ ((row & 3) << 1);
+          *reinterpret_cast<uint4*>(st + L::kOffX + row * kXRowBytes + chunk * 16) = o;
+          if ((lane & 15) == 0) fac[row] = inv;
+        }
+        __syncwarp();
+        if (lane == 0) dev::mbar_arrive(&full[s_conv]);
+        if (++s_conv == S) { s_conv = 0; ph_conv ^= 1; }
       }
-      __syncwarp();
-      if (lane == 0) dev::mbar_arrive(&full[s]);
-      if (u + 1 < u_end) load_x(u + 1);
     }
   } else {
     // ------------------------------ consumers -----------------------------
     const int g8 = lane >> 2;  // 0..7
     const int t4 = lane & 3;   // 0..3
     const int ctid = threadIdx.x;  // 0..255
+    // ldmatrix: lane l addresses row 32h + l of the tile, this warp's 16-byte chunk
+    const uint32_t ld_off = lane * 128 + ((warp ^ (lane & 7)) << 4);
+    // activation fragment: row g8 (+8 per tile), chunk 2*slab + t4/2 swizzled by the row,
+    // 8-byte half t4 & 1.  Address bits 5-7 carry the chunk, so the slab is XOR-ed in.
+    const uint32_t x_off = L::kOffX + g8 * kXRowBytes + ((t4 >> 1) << 4) + ((t4 & 1) << 3) +
+                           ((g8 & 3) << 5);
+    const int lc = warp * 16 + 2 * g8;  // this thread's column pair inside the block
     float yacc[MT][4];
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
@@ -203,7 +265,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const uint16_t* __
       const int first = cta_of_unit(static_cast<long long>(c) * G, P, U);
       const int last = cta_of_unit(static_cast<long long>(c) * G + G - 1, P, U);
       const int nslots = last - first + 1;
-      const int col = c * kColsPerBlock + warp * 16 + 2 * g8;
+      const int col = c * kColsPerBlock + lc;
       if (nslots == 1) {
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
@@ -224,7 +286,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const uint16_t* __
         for (int r = 0; r < 2; ++r) {
           const int m = mt * 8 + 2 * t4 + r;
           if (m < M)
-            __stcg(reinterpret_cast<float2*>(part + m * kColsPerBlock + warp * 16 + 2 * g8),
+            __stcg(reinterpret_cast<float2*>(part + m * kColsPerBlock + lc),
                    make_float2(yacc[mt][r], yacc[mt][2 + r]));
         }
       __threadfence();
@@ -257,90 +319,100 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const uint16_t* __
       consumer_sync();
     };
 
-    int cur_c = (u_begin < u_end) ? u_begin / G : 0;
-    int it = 0;
+    int c = (n_units > 0) ? u_begin / G : 0;
+    int g = (n_units > 0) ? u_begin - c * G : 0;
+    int s = 0;
+    uint32_t ph = 0;
     bool ok = true;
-    for (int u = u_begin; u < u_end; ++u, ++it) {
-      const int s = it % S;
-      const uint32_t ph = (it / S) & 1;
-      const int c = u / G;
-      if (c != cur_c) {
-        flush(cur_c);
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-          for (int i = 0; i < 4; ++i) yacc[mt][i] = 0.f;
-        cur_c = c;
-      }
+    for (int it = 0; it < n_units; ++it) {
       if (!dev::mbar_wait(&full[s], ph, status, 2)) {
         ok = false;
         break;
       }
       const uint8_t* st = smem + s * L::kStage;
       const uint32_t st_addr = dev::smem_u32(st);
+
+      // per-group constants of this thread's two columns
+      const uint32_t s2 = *reinterpret_cast<const uint32_t*>(st + L::kOffS + lc * 2);
+      const float sc0 = __uint_as_float(s2 << 16);
+      const float sc1 = __uint_as_float(s2 & 0xFFFF0000u);
+      uint32_t z0, z1;
+      if (ZP_PACKED) {
+        const uint32_t zb = st[L::kOffZ + (lc >> 1)];
+        z0 = zb & 0xFu;
+        z1 = zb >> 4;
+      } else {
+        const uint32_t zb = *reinterpret_cast<const uint16_t*>(st + L::kOffZ + lc);
+        z0 = zb & 0xFFu;
+        z1 = zb >> 8;
+      }
+      // f16 pairs 1024 + z (low nibbles) and 1024 + 16 z (high nibbles)
+      const uint32_t zlo0 = (0x6400u | z0) * 0x00010001u, zhi0 = (0x6400u | (z0 << 4)) * 0x00010001u;
+      const uint32_t zlo1 = (0x6400u | z1) * 0x00010001u, zhi1 = (0x6400u | (z1 << 4)) * 0x00010001u;
+
       float acc[MT][4];
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
         for (int i = 0; i < 4; ++i) acc[mt][i] = 0.f;
+      const uint32_t xb = st_addr + x_off;
 
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        // four 8-row matrices: rows 32h + 8j + (lane % 8), this warp's 16-byte chunk
-        const int row = 32 * h + lane;
         uint32_t wreg[4];
-        ldmatrix_x4_trans(st_addr + row * 128 + ((warp ^ (row & 7)) << 4), wreg);
+        ldmatrix_x4_trans(st_addr + ld_off + h * 4096, wreg);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           const uint32_t w = wreg[j];
-          const uint32_t r0 = (w & 0x000F000Fu) | 0x43004300u;          // col 2g,   k 4t, 4t+2
-          const uint32_t r1 = ((w >> 4) & 0x000F000Fu) | 0x43004300u;   // col 2g,   k 4t+1, 4t+3
-          const uint32_t r2 = ((w >> 8) & 0x000F000Fu) | 0x43004300u;   // col 2g+1, k 4t, 4t+2
-          const uint32_t r3 = ((w >> 12) & 0x000F000Fu) | 0x43004300u;  // col 2g+1, k 4t+1, 4t+3
+          const uint32_t t = w >> 8;
+          // bytes 0/2 of the register: column 2g, rows 2t and 2t+1 of the slab
+          const uint32_t r0 = hsub2_u32(lop3_and_or(w, 0x000F000Fu, 0x64006400u), zlo0);  // k 4t, 4t+2
+          const uint32_t r1 = hsub2_u32(lop3_and_or(w, 0x00F000F0u, 0x64006400u), zhi0);  // k 4t+1, 4t+3 (x16)
+          // bytes 1/3: column 2g+1
+          const uint32_t r2 = hsub2_u32(lop3_and_or(t, 0x000F000Fu, 0x64006400u), zlo1);
+          const uint32_t r3 = hsub2_u32(lop3_and_or(t, 0x00F000F0u, 0x64006400u), zhi1);
           const int slab = 4 * h + j;
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
-            const uint2 xf = *reinterpret_cast<const uint2*>(
-                st + L::kOffX + (mt * 8 + g8) * kXRowBytes + slab * 32 + t4 * 8);
-            mma_bf16_16816(acc[mt], r0, r2, r1, r3, xf.x, xf.y);
+            uint32_t x0, x1;
+            asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];"
+                         : "=r"(x0), "=r"(x1)
+                         : "r"((xb ^ (slab << 5)) + mt * 8 * kXRowBytes));
+            mma_f16_16816(acc[mt], r0, r2, r1, r3, x0, x1);
           }
         }
       }
       // group epilogue: this thread holds columns (2g, 2g+1) of its warp's
       // chunk for rows (2t, 2t+1) of each 8-row tile
-      const int lc = warp * 16 + 2 * g8;
-      const uint32_t s2 = *reinterpret_cast<const uint32_t*>(st + L::kOffS + lc * 2);
-      const float sc0 = __uint_as_float(s2 << 16);
-      const float sc1 = __uint_as_float(s2 & 0xFFFF0000u);
-      float z0, z1;
-      if (ZP_PACKED) {
-        const uint32_t zb = st[L::kOffZ + (lc >> 1)];
-        z0 = static_cast<float>(zb & 0xF);
-        z1 = static_cast<float>(zb >> 4);
-      } else {
-        const uint32_t zb = *reinterpret_cast<const uint16_t*>(st + L::kOffZ + lc);
-        z0 = static_cast<float>(zb & 0xFF);
-        z1 = static_cast<float>(zb >> 8);
-      }
-      const float off0 = -(128.f + z0), off1 = -(128.f + z1);
-      const float* sx = reinterpret_cast<const float*>(st + L::kOffSx);
+      const float* fac = reinterpret_cast<const float*>(st + L::kOffF);
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
-        const float2 sxm = *reinterpret_cast<const float2*>(sx + mt * 8 + 2 * t4);
-        yacc[mt][0] = fmaf(sc0, fmaf(off0, sxm.x, acc[mt][0]), yacc[mt][0]);
-        yacc[mt][1] = fmaf(sc0, fmaf(off0, sxm.y, acc[mt][1]), yacc[mt][1]);
-        yacc[mt][2] = fmaf(sc1, fmaf(off1, sxm.x, acc[mt][2]), yacc[mt][2]);
-        yacc[mt][3] = fmaf(sc1, fmaf(off1, sxm.y, acc[mt][3]), yacc[mt][3]);
+        const float2 f = *reinterpret_cast<const float2*>(fac + mt * 8 + 2 * t4);
+        yacc[mt][0] = fmaf(sc0 * f.x, acc[mt][0], yacc[mt][0]);
+        yacc[mt][1] = fmaf(sc0 * f.y, acc[mt][1], yacc[mt][1]);
+        yacc[mt][2] = fmaf(sc1 * f.x, acc[mt][2], yacc[mt][2]);
+        yacc[mt][3] = fmaf(sc1 * f.y, acc[mt][3], yacc[mt][3]);
       }
       __syncwarp();
       if (lane == 0) dev::mbar_arrive(&empty[s]);
+      if (++s == S) { s = 0; ph ^= 1; }
+      if (++g == G) {
+        // the column block is complete as far as this CTA is concerned
+        g = 0;
+        flush(c);
+        ++c;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) yacc[mt][i] = 0.f;
+      }
     }
-    if (ok && u_begin < u_end) flush(cur_c);
+    if (ok && n_units > 0 && g != 0) flush(c);
   }
 }
 
 template <int MT, bool ZP>
-static int launch(const CUtensorMap& wmap, const uint16_t* x, const uint16_t* scales,
+static int launch(const CUtensorMap& wmap, const CUtensorMap& xmap, const uint16_t* scales,
                   const uint8_t* zeros, uint16_t* y, float* ws_partial, int* ws_counter, int M, int N,
                   int K, int G, int U, int P, int max_slots, cudaStream_t stream) {
   using L = Smem<MT>;
@@ -350,16 +422,17 @@ static int launch(const CUtensorMap& wmap, const uint16_t* x, const uint16_t* sc
     QMM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
     configured = true;
   }
-  kern<<<P, kThreads, L::kTotal, stream>>>(wmap, x, scales, zeros, y, ws_partial, ws_counter, M, N,
-                                           K, G, U, max_slots, device_status_word());
+  kern<<<P, kThreads, L::kTotal, stream>>>(wmap, xmap, scales, zeros, y, ws_partial, ws_counter, M,
+                                           N, K, G, U, max_slots, device_status_word());
   QMM_CHECK_LAUNCH("w4a16_decode_kernel");
   return QMM_OK;
 }
 
-static int grid_size(int U) {
-  // two resident CTAs per SM; small problems get at least two units per CTA so
-  // that few CTAs share a column block
-  const int p = 2 * num_sms();
+static int blocks_per_sm(int M) { return M <= 8 ? Smem<1>::kMinBlocks : Smem<2>::kMinBlocks; }
+static int grid_size(int U, int M) {
+  // every CTA resident at once; small problems get at least two units per CTA
+  // so that few CTAs share a column block
+  const int p = blocks_per_sm(M) * num_sms();
   const int q = (U + 1) / 2;
   return q < p ? q : p;
 }
@@ -406,7 +479,7 @@ static int static_scratch_address(void** out) {
 // Same launch as launch<MT, ZP>() but with the status pointer supplied by the
 // caller instead of created on demand (creating it would allocate).
 template <int MT, bool ZP>
-static int launch_no_alloc(const CUtensorMap& wmap, const uint16_t* x, const uint16_t* scales,
+static int launch_no_alloc(const CUtensorMap& wmap, const CUtensorMap& xmap, const uint16_t* scales,
                            const uint8_t* zeros, uint16_t* y, float* ws_partial, int* ws_counter,
                            int M, int N, int K, int G, int U, int P, int max_slots, int* status,
                            cudaStream_t stream) {
@@ -417,8 +490,8 @@ static int launch_no_alloc(const CUtensorMap& wmap, const uint16_t* x, const uin
     QMM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
     configured = true;
   }
-  kern<<<P, kThreads, L::kTotal, stream>>>(wmap, x, scales, zeros, y, ws_partial, ws_counter, M, N,
-                                           K, G, U, max_slots, status);
+  kern<<<P, kThreads, L::kTotal, stream>>>(wmap, xmap, scales, zeros, y, ws_partial, ws_counter, M,
+                                           N, K, G, U, max_slots, status);
   QMM_CHECK_LAUNCH("w4a16_decode_kernel");
   return QMM_OK;
 }
@@ -434,7 +507,7 @@ size_t qmm_w4a16_g128_workspace_bytes(int64_t M, int64_t N, int64_t K) {
   const int G = static_cast<int>(K / kGroup);
   const int C = static_cast<int>(N / kColsPerBlock);
   const int U = G * C;
-  const int P = grid_size(U);
+  const int P = grid_size(U, static_cast<int>(M));
   const int slots = slots_for(G, U, P);
   const size_t counters = (static_cast<size_t>(C) * sizeof(int) + 255) / 256 * 256;
   return counters + static_cast<size_t>(C) * slots * rows_padded(static_cast<int>(M)) * kColsPerBlock *
@@ -471,7 +544,7 @@ int qmm_w4a16_g128(const uint16_t* x, const uint8_t* wq, const uint16_t* scales,
   const int G = static_cast<int>(K / kGroup);
   const int C = static_cast<int>(N / kColsPerBlock);
   const int U = G * C;
-  const int P = grid_size(U);
+  const int P = grid_size(U, static_cast<int>(M));
   const int slots = slots_for(G, U, P);
   const size_t counters = (static_cast<size_t>(C) * sizeof(int) + 255) / 256 * 256;
   int* ws_counter = static_cast<int*>(workspace);
@@ -483,13 +556,20 @@ int qmm_w4a16_g128(const uint16_t* x, const uint8_t* wq, const uint16_t* scales,
                                   static_cast<uint64_t>(N), kRowsPerUnit, kColsPerBlock,
                                   CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
+  // activations: [M, K] bf16, one box = (8, 16 or 32 rows) x one 128-k group, rows past M read as zero
+  CUtensorMap xmap;
+  if (int rc = make_tensor_map_2d(&xmap, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                                  static_cast<uint64_t>(M), static_cast<uint64_t>(K),
+                                  static_cast<uint64_t>(K) * 2, rows_padded(static_cast<int>(M)),
+                                  kGroup, CU_TENSOR_MAP_SWIZZLE_NONE))
+    return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   const int m = static_cast<int>(M), n = static_cast<int>(N), k = static_cast<int>(K);
 #define QMM_W4_LAUNCH(MT)                                                                        \
-  (zeros_packed ? launch<MT, true>(wmap, x, scales, zeros, y, ws_partial, ws_counter, m, n, k, G, \
-                                   U, P, slots, st)                                              \
-                : launch<MT, false>(wmap, x, scales, zeros, y, ws_partial, ws_counter, m, n, k,  \
-                                    G, U, P, slots, st))
+  (zeros_packed ? launch<MT, true>(wmap, xmap, scales, zeros, y, ws_partial, ws_counter, m, n, k, \
+                                   G, U, P, slots, st)                                           \
+                : launch<MT, false>(wmap, xmap, scales, zeros, y, ws_partial, ws_counter, m, n,  \
+                                    k, G, U, P, slots, st))
   if (M <= 8) return QMM_W4_LAUNCH(1);
   if (M <= 16) return QMM_W4_LAUNCH(2);
   return QMM_W4_LAUNCH(4);
@@ -542,7 +622,7 @@ int qmm_w4a16_g128_static_scratch(const uint16_t* x, const uint8_t* wq, const ui
   const int G = static_cast<int>(K / kGroup);
   const int C = static_cast<int>(N / kColsPerBlock);
   const int U = G * C;
-  const int P = grid_size(U);
+  const int P = grid_size(U, static_cast<int>(M));
   const int slots = slots_for(G, U, P);
   const size_t counters = (static_cast<size_t>(C) * sizeof(int) + 255) / 256 * 256;
   int* ws_counter = static_cast<int*>(scratch);
@@ -559,13 +639,19 @@ int qmm_w4a16_g128_static_scratch(const uint16_t* x, const uint8_t* wq, const ui
   // A wait that gives up is reported through the library's status word when
   // that word exists already (any other entry point, or qmm_device_status(),
   // creates it); this call will not create it, because that allocates.
+  CUtensorMap xmap;
+  if (int rc = make_tensor_map_2d(&xmap, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                                  static_cast<uint64_t>(M), static_cast<uint64_t>(K),
+                                  static_cast<uint64_t>(K) * 2, rows_padded(static_cast<int>(M)),
+                                  kGroup, CU_TENSOR_MAP_SWIZZLE_NONE))
+    return rc;
   int* status = device_status_word_if_ready();
   const int m = static_cast<int>(M), n = static_cast<int>(N), k = static_cast<int>(K);
-#define QMM_W4_LAUNCH_NA(MT)                                                                       \
-  (zeros_packed ? launch_no_alloc<MT, true>(wmap, x, scales, zeros, y, ws_partial, ws_counter, m, \
-                                            n, k, G, U, P, slots, status, st)                     \
-                : launch_no_alloc<MT, false>(wmap, x, scales, zeros, y, ws_partial, ws_counter, m, \
-                                             n, k, G, U, P, slots, status, st))
+#define QMM_W4_LAUNCH_NA(MT)                                                                      \
+  (zeros_packed ? launch_no_alloc<MT, true>(wmap, xmap, scales, zeros, y, ws_partial, ws_counter, \
+                                            m, n, k, G, U, P, slots, status, st)                  \
+                : launch_no_alloc<MT, false>(wmap, xmap, scales, zeros, y, ws_partial,            \
+                                             ws_counter, m, n, k, G, U, P, slots, status, st))
   if (M <= 8) return QMM_W4_LAUNCH_NA(1);
   if (M <= 16) return QMM_W4_LAUNCH_NA(2);
   return QMM_W4_LAUNCH_NA(4);
