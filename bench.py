@@ -440,9 +440,11 @@ def run_detail(torch, ops, synthetic, lib, device, peaks):
     for M in (1, 4, 16):
         x = synthetic.device_normal((M, K), device, gen, torch.bfloat16)
         y = torch.empty((M, N), dtype=torch.bfloat16, device=device)
-        us = graph_time(lambda i: ops.w4a16_g128(x, wqs[i % copies], sc, zp, zeros_packed=True, out=y, workspace=ws),
+        us = graph_time(lambda i: ops.w4a16_g128(x, wqs[i % copies], sc, zp, zeros_packed=True, out=y, workspace=ws,
+                                                   static_weights=True),
                         copies * 2)
-        us_warm = graph_time(lambda i: ops.w4a16_g128(x, wqs[0], sc, zp, zeros_packed=True, out=y, workspace=ws),
+        us_warm = graph_time(lambda i: ops.w4a16_g128(x, wqs[0], sc, zp, zeros_packed=True, out=y, workspace=ws,
+                                                        static_weights=True),
                              copies * 2)
         nbytes = K * N // 2 + G * N * 2 + G * N // 2 + M * K * 2 + M * N * 2
         gbs = nbytes / (us * 1e-6) / 1e9

@@ -130,15 +130,24 @@ QMM_API int qmm_i8i8_i32(const void* a, const void* b, int32_t* acc, const float
  * multiply / reshape / dot_general
  * (src/pjrt_plugin/ops/bitwise_ops.mm:33-51,169-305; ops/shape_ops.mm:793-829;
  *  ops/binary_ops.mm:66-193, :644-1245).
+ * Zero points are 4-bit values (0..15) in either form.
  * Requires group == 128, K % 128 == 0, N % 128 == 0, 1 <= M <= 32.
  * workspace: qmm_w4a16_g128_workspace_bytes(M, N, K) bytes, 256-byte aligned,
  * zero-filled before its first use; the kernel leaves it zero-filled, so
- * back-to-back calls on one stream may share it. */
+ * back-to-back calls on one stream may share it.
+ * flags: 0, or QMM_W4_STATIC_WEIGHTS when wq, scales and zeros are not written
+ * by any work queued earlier on the stream (the usual case for model weights).
+ * The kernel is launched with programmatic stream serialization: its blocks
+ * may start while the previous kernel on the stream drains.  x, y and the
+ * workspace are only touched once that kernel has finished; with
+ * QMM_W4_STATIC_WEIGHTS the first weight tiles are fetched before that point,
+ * which hides the launch gap in a decode loop. */
+#define QMM_W4_STATIC_WEIGHTS 1u
 QMM_API size_t qmm_w4a16_g128_workspace_bytes(int64_t M, int64_t N, int64_t K);
 QMM_API int qmm_w4a16_g128(const uint16_t* x_bf16, const uint8_t* wq, const uint16_t* scales_bf16,
                            const uint8_t* zeros, int zeros_packed, uint16_t* y_bf16, int64_t M,
                            int64_t N, int64_t K, int64_t group, void* workspace,
-                           size_t workspace_bytes, void* stream);
+                           size_t workspace_bytes, unsigned flags, void* stream);
 
 /* ---------------------------------------------------------------------------
  * The same matmul for callers that cannot allocate device memory.
@@ -156,15 +165,15 @@ QMM_API int qmm_w4a16_g128(const uint16_t* x_bf16, const uint8_t* wq, const uint
  * Arguments and result are those of qmm_w4a16_g128 without the workspace.
  * The call allocates nothing and frees nothing.  Limits and rules:
  *  - shapes whose scratch need (qmm_w4a16_g128_workspace_bytes) exceeds
- *    QMM_STATIC_SCRATCH_BYTES are refused with QMM_ERR_WORKSPACE — 4 MiB covers
- *    M <= 16 at 4096 x 14336 (3.7 MB) and M <= 8 at 14336 x 4096;
+ *    QMM_STATIC_SCRATCH_BYTES are refused with QMM_ERR_WORKSPACE — 8 MiB covers
+ *    M <= 16 at 4096 x 14336 (6.4 MB) and at 14336 x 4096;
  *  - the first call on each device resolves the array's device address; make
  *    that call before starting any stream capture;
  *  - the array is shared by every call on the device and keeps what the last
  *    call wrote; the part that must start at zero is cleared on the stream by
  *    each call, but two calls that may run at the same time on one GPU race
  *    on it — keep them on one stream or order them yourself. */
-#define QMM_STATIC_SCRATCH_BYTES (4u << 20)
+#define QMM_STATIC_SCRATCH_BYTES (8u << 20)
 QMM_API int qmm_w4a16_g128_static_scratch(const uint16_t* x_bf16, const uint8_t* wq,
                                           const uint16_t* scales_bf16, const uint8_t* zeros,
                                           int zeros_packed, uint16_t* y_bf16, int64_t M, int64_t N,
@@ -189,6 +198,36 @@ QMM_API int qmm_affine_matmul(const void* x, const void* w_packed, const float* 
                               int bits, int64_t group_size, int dtype, void* stream);
 QMM_API int qmm_mx_matmul(const void* x, const uint8_t* w_packed, const uint8_t* scales, void* y,
                           int64_t M, int64_t N, int64_t K, int mode, int dtype, void* stream);
+
+/* ---------------------------------------------------------------------------
+ * StableHLO front end: text in, launch plan out.
+ *
+ * qmm_plan_compile reads the textual StableHLO of a module (the form
+ * jax.jit(f).lower(...).as_text() prints), matches every dot_general with the
+ * dequantisation chain that feeds it and builds one kernel launch per match;
+ * it stands where the reference parses and plans a program
+ * (src/pjrt_plugin/core/stablehlo_parser.mm:521-586,
+ *  src/pjrt_plugin/core/mps_executable.mm:7627-9008; pattern fusions
+ *  :1214-1326).  An op that is not part of a supported pattern makes
+ * compilation fail with QMM_ERR_UNSUPPORTED and a message naming the op and
+ * its line, as the reference reports unsupported ops
+ * (src/pjrt_plugin/api/pjrt_client.cc:211-220); nothing is executed on the CPU.
+ * qmm_plan_trace returns one JSON line per decision ("QMM_PLAN_JSON:{...}",
+ * also written to stderr when QMM_TRACE_PLAN is set), the counterpart of the
+ * reference's JAX_METALLIB_TRACE_PLAN output (mps_executable.mm:7925-7961).
+ * qmm_plan_execute takes the device pointers of @main's arguments and results
+ * in declaration order. */
+typedef struct qmm_plan qmm_plan;
+QMM_API int qmm_plan_compile(const char* stablehlo_text, size_t length, qmm_plan** plan);
+QMM_API void qmm_plan_destroy(qmm_plan* plan);
+QMM_API int qmm_plan_num_steps(const qmm_plan* plan);
+QMM_API int qmm_plan_num_args(const qmm_plan* plan);
+QMM_API int qmm_plan_num_results(const qmm_plan* plan);
+QMM_API size_t qmm_plan_workspace_bytes(const qmm_plan* plan);
+QMM_API size_t qmm_plan_trace(const qmm_plan* plan, char* buf, size_t cap);
+QMM_API int qmm_plan_execute(const qmm_plan* plan, const void* const* args, int num_args,
+                             void* const* results, int num_results, void* workspace,
+                             size_t workspace_bytes, void* stream);
 
 #ifdef __cplusplus
 }

@@ -8,13 +8,14 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import c_char_p, c_int, c_int64, c_size_t, c_void_p
+from ctypes import c_char_p, c_int, c_int64, c_size_t, c_uint, c_void_p
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 LIB_PATH = os.environ.get("QMM_LIBRARY_PATH", os.path.join(HERE, "libqmm.so"))
 
 QMM_F32, QMM_F16, QMM_BF16, QMM_S8, QMM_U8, QMM_S32, QMM_U4, QMM_U32 = range(8)
 QMM_MXFP4, QMM_MXFP8, QMM_NVFP4 = range(3)
+QMM_W4_STATIC_WEIGHTS = 1
 MX_MODE_IDS = {"mxfp4": QMM_MXFP4, "mxfp8": QMM_MXFP8, "nvfp4": QMM_NVFP4}
 
 # name -> (restype, argtypes); mirrors include/qmm.h
@@ -33,12 +34,22 @@ SIGNATURES = {
     "qmm_w4a16_g128_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64]),
     "qmm_w4a16_g128": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p,
-                c_size_t, c_void_p]),
+                c_size_t, c_uint, c_void_p]),
     "qmm_w4a16_g128_static_scratch": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int64, c_int64, c_int64, c_int64,
                 c_void_p]),
     "qmm_affine_matmul": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int64, c_int,
+                c_void_p]),
+    "qmm_plan_compile": (c_int, [c_char_p, c_size_t, ctypes.POINTER(c_void_p)]),
+    "qmm_plan_destroy": (None, [c_void_p]),
+    "qmm_plan_num_steps": (c_int, [c_void_p]),
+    "qmm_plan_num_args": (c_int, [c_void_p]),
+    "qmm_plan_num_results": (c_int, [c_void_p]),
+    "qmm_plan_workspace_bytes": (c_size_t, [c_void_p]),
+    "qmm_plan_trace": (c_size_t, [c_void_p, c_char_p, c_size_t]),
+    "qmm_plan_execute": (
+        c_int, [c_void_p, ctypes.POINTER(c_void_p), c_int, ctypes.POINTER(c_void_p), c_int, c_void_p, c_size_t,
                 c_void_p]),
     "qmm_mx_matmul": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_void_p]),

@@ -3,17 +3,18 @@
 //   y[M,N] = bf16( x[M,K] @ ((q[K,N] - z[K/128,N]) * s[K/128,N]) )
 //
 // HBM-bound: the packed weights (K*N/2 bytes) are read exactly once.  The work
-// is cut into units of one 128-column block x one 128-k group (a 64-row x
-// 128-byte tile, 8 KB); consecutive units are dealt evenly to a grid of
-// resident CTAs, so every SM streams the same number of bytes.
+// is cut into units of one 256-column block x one 128-k group (two 64-row x
+// 128-byte TMA boxes side by side, 16 KB: 256 contiguous bytes per DRAM row
+// stream measurably faster than 128); consecutive units are dealt evenly to a
+// grid of resident CTAs (two per SM).
 //
-// Per CTA: a producer warp issues the loads of a unit (TMA tile of packed
-// weights with the 128-byte swizzle, bulk copies of scales and zero points, a
-// TMA box of the group's activations) into an mbarrier ring, and two units
-// later turns those activations into the MMA's operand: f16, scaled per (row,
-// group) by a power of two so that any bf16 magnitude fits, odd k divided by
-// 16, every four k permuted to fragment order, written back in place.
-// Eight consumer warps each own 16 columns.  A consumer reads the tile with
+// Per CTA: a producer warp issues the loads of a unit (packed weights with the
+// 128-byte swizzle, bulk copies of scales and zero points, a TMA box of the
+// group's activations) into an mbarrier ring, and two units later turns those
+// activations into the MMA's operand: f16, scaled per (row, group) by a power
+// of two so that any bf16 magnitude fits, odd k divided by 16, every four k
+// permuted to fragment order, written back in place.
+// Eight consumer warps each own 32 columns.  A consumer reads the tile with
 // ldmatrix.trans, which turns the k-pair-per-byte layout into registers that
 // hold (same column, two k) in their 16-bit halves; one logic op per register
 // makes the f16 pair 1024+q (low nibbles) or 1024+16q (high nibbles, no shift
@@ -27,6 +28,12 @@
 // Partial sums of CTAs sharing a column block meet in the caller's workspace;
 // the last CTA to arrive adds them in a fixed order (deterministic result) and
 // writes bf16.  The workspace counters are left at zero.
+//
+// Launch overlap: the kernel is launched with programmatic stream
+// serialization, so its CTAs may start while the previous kernel on the stream
+// drains.  Everything that can depend on earlier work (activations, output,
+// workspace) is touched only after griddepcontrol.wait; when the caller states
+// that the weights are static, their first loads are issued before that wait.
 #include <mutex>
 
 #include "common.cuh"
@@ -34,28 +41,29 @@
 namespace qmm {
 namespace w4 {
 
-constexpr int kColsPerBlock = 128;   // columns per unit (= bytes per TMA row)
+constexpr int kColsPerBlock = 256;   // columns per unit: two 128-byte TMA boxes
 constexpr int kGroup = 128;          // k per unit
 constexpr int kRowsPerUnit = 64;     // packed byte-rows per unit
-constexpr int kConsumerWarps = 8;
+constexpr int kConsumerWarps = 8;    // 32 columns (two 16-byte chunks) each
 constexpr int kThreads = (kConsumerWarps + 1) * 32;
 constexpr int kXRowBytes = 256;      // 128 16-bit activations; 16-byte chunks XOR-swizzled by (row & 3) << 1
 constexpr int kXLag = 2;             // units between issuing a group's loads and converting its activations
+constexpr int kBoxBytes = kRowsPerUnit * 128;  // 8192
 
 template <int MT>
 struct Smem {
-  static constexpr int kW = kRowsPerUnit * kColsPerBlock;  // 8192
-  static constexpr int kS = kColsPerBlock * 2;             // 256
-  static constexpr int kZ = kColsPerBlock;                 // 128 (64 used when packed)
+  static constexpr int kW = 2 * kBoxBytes;                 // 16384
+  static constexpr int kS = kColsPerBlock * 2;             // 512
+  static constexpr int kZ = kColsPerBlock;                 // 256 (128 used when packed)
   static constexpr int kF = 128;                           // per-row power-of-two factors (MT*8 floats)
   static constexpr int kX = MT * 8 * kXRowBytes;           // also the byte count of the TMA box
   static constexpr int kOffS = kW;
   static constexpr int kOffZ = kOffS + kS;
   static constexpr int kOffF = kOffZ + kZ;
-  static constexpr int kOffX = 9216;                       // multiple of 256 (the swizzle uses address bits 5-7)
+  static constexpr int kOffX = 17408;                      // multiple of 256 (the swizzle uses address bits 5-7)
   static constexpr int kStage = ((kOffX + kX + 1023) / 1024) * 1024;
-  static constexpr int kMinBlocks = (MT == 1) ? 3 : 2;     // resident CTAs per SM
-  static constexpr int kStages = (MT == 1) ? 6 : (MT == 2 ? 8 : 6);
+  static constexpr int kMinBlocks = (MT <= 2) ? 2 : 1;     // resident CTAs per SM
+  static constexpr int kStages = (MT <= 2) ? 5 : 8;
   static constexpr int kBarBytes = 1024;
   static constexpr int kTotal = kStages * kStage + kBarBytes + 1024;  // + alignment slack
   static_assert(kOffF + kF <= kOffX, "stage layout overlaps");
@@ -100,10 +108,28 @@ __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
   asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
   return r;
 }
+__device__ __forceinline__ void grid_dependency_wait() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void grid_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
 
 // CTA that owns unit u when U units are dealt to P CTAs as [i*U/P, (i+1)*U/P).
 __device__ __forceinline__ int cta_of_unit(long long u, int P, int U) {
   return static_cast<int>(((u + 1) * P - 1) / U);
+}
+
+// Eight packed weights of one register -> four f16x2 MMA operand registers
+// (columns c and c+1, k pairs (4t, 4t+2) and (4t+1, 4t+3) of the slab), zero
+// point removed.
+__device__ __forceinline__ void dequant8(uint32_t w, uint32_t zlo0, uint32_t zhi0, uint32_t zlo1,
+                                         uint32_t zhi1, uint32_t (&r)[4]) {
+  const uint32_t t = w >> 8;
+  r[0] = hsub2_u32(lop3_and_or(w, 0x000F000Fu, 0x64006400u), zlo0);  // bytes 0/2, low nibbles
+  r[1] = hsub2_u32(lop3_and_or(w, 0x00F000F0u, 0x64006400u), zhi0);  // bytes 0/2, high nibbles (x16)
+  r[2] = hsub2_u32(lop3_and_or(t, 0x000F000Fu, 0x64006400u), zlo1);  // bytes 1/3
+  r[3] = hsub2_u32(lop3_and_or(t, 0x00F000F0u, 0x64006400u), zhi1);
 }
 
 template <int MT, bool ZP_PACKED>
@@ -112,7 +138,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
                     const uint16_t* __restrict__ scales, const uint8_t* __restrict__ zeros,
                     uint16_t* __restrict__ y, float* __restrict__ ws_partial,
                     int* __restrict__ ws_counter, int M, int N, int K, int G, int U, int max_slots,
-                    int* status) {
+                    int static_weights, int* status) {
   using L = Smem<MT>;
   constexpr int S = L::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -123,6 +149,8 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
   uint64_t* xraw = empty + S;      // raw activations of the group have landed
   uint64_t* sync_bar = xraw + S;   // consumer-only rendezvous with a bounded wait
   int* flag = reinterpret_cast<int*>(sync_bar + 1);
+
+  grid_launch_dependents();  // the next kernel on the stream may start its own prologue
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
@@ -144,38 +172,57 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
 
   if (warp == kConsumerWarps) {
     // ------------------------------ producer ------------------------------
-    // Iteration `it` issues every load of unit `it` (one elected lane) and, kXLag
-    // units later, the whole warp converts that unit's activations in place, so
-    // the loads of several units are always in flight while it works.
     if (lane == 0) {
       dev::tma_prefetch_desc(&wmap);
       dev::tma_prefetch_desc(&xmap);
     }
     const uint64_t policy = dev::policy_evict_first();
     constexpr int kPasses = MT * 4;  // a pass = 2 rows x 16 lanes x 16 bytes
+    // weights, scales and zero points of a unit (one elected lane)
+    auto issue_weights = [&](int s, int c, int g) {
+      uint8_t* st = smem + s * L::kStage;
+      const int col0 = c * kColsPerBlock;
+      const int cols = min(kColsPerBlock, N - col0);  // 128 in a trailing half block
+      const uint32_t sbytes = cols * 2;
+      const uint32_t zbytes = ZP_PACKED ? cols / 2 : cols;
+      dev::mbar_expect_tx(&full[s], L::kW + sbytes + zbytes);
+      dev::tma_load_2d_hint(st, &wmap, &full[s], col0, g * kRowsPerUnit, policy);
+      dev::tma_load_2d_hint(st + kBoxBytes, &wmap, &full[s], col0 + 128, g * kRowsPerUnit, policy);
+      bulk_copy_g2s(st + L::kOffS, scales + static_cast<size_t>(g) * N + col0, sbytes, &full[s]);
+      const uint8_t* zsrc = ZP_PACKED ? zeros + static_cast<size_t>(g) * (N / 2) + col0 / 2
+                                      : zeros + static_cast<size_t>(g) * N + col0;
+      bulk_copy_g2s(st + L::kOffZ, zsrc, zbytes, &full[s]);
+    };
+    auto issue_x = [&](int s, int g) {
+      uint8_t* st = smem + s * L::kStage;
+      dev::mbar_expect_tx(&xraw[s], L::kX);  // rows beyond M are zero-filled by the TMA unit
+      dev::tma_load_2d(st + L::kOffX, &xmap, &xraw[s], g * kGroup, 0);
+    };
     int c = (n_units > 0) ? u_begin / G : 0;
     int g = (n_units > 0) ? u_begin - c * G : 0;
+    // Static weights do not depend on earlier kernels: fill the ring with them
+    // before waiting for those kernels to finish.
+    int prefetched = 0;
+    if (static_weights) {
+      prefetched = n_units < S ? n_units : S;
+      if (lane == 0) {
+        int cc = c, gg = g;
+        for (int i = 0; i < prefetched; ++i) {
+          issue_weights(i, cc, gg);
+          if (++gg == G) { gg = 0; ++cc; }
+        }
+      }
+    }
+    grid_dependency_wait();
     int s_issue = 0, s_conv = 0;
     uint32_t ph_issue = 0, ph_conv = 0;
     for (int it = 0; it < n_units + kXLag; ++it) {
       if (it < n_units) {
-        if (!dev::mbar_wait(&empty[s_issue], ph_issue ^ 1, status, 1)) break;
-        if (lane == 0) {
-          uint8_t* st = smem + s_issue * L::kStage;
-          const uint32_t zbytes = ZP_PACKED ? 64 : 128;
-          dev::mbar_expect_tx(&full[s_issue], L::kW + L::kS + zbytes);
-          dev::tma_load_2d_hint(st, &wmap, &full[s_issue], c * kColsPerBlock, g * kRowsPerUnit,
-                                policy);
-          bulk_copy_g2s(st + L::kOffS, scales + static_cast<size_t>(g) * N + c * kColsPerBlock,
-                        L::kS, &full[s_issue]);
-          const uint8_t* zsrc =
-              ZP_PACKED ? zeros + static_cast<size_t>(g) * (N / 2) + c * (kColsPerBlock / 2)
-                        : zeros + static_cast<size_t>(g) * N + c * kColsPerBlock;
-          bulk_copy_g2s(st + L::kOffZ, zsrc, zbytes, &full[s_issue]);
-          // activations of the group: rows beyond M are zero-filled by the TMA unit
-          dev::mbar_expect_tx(&xraw[s_issue], L::kX);
-          dev::tma_load_2d(st + L::kOffX, &xmap, &xraw[s_issue], g * kGroup, 0);
+        if (it >= prefetched) {
+          if (!dev::mbar_wait(&empty[s_issue], ph_issue ^ 1, status, 1)) break;
+          if (lane == 0) issue_weights(s_issue, c, g);
         }
+        if (lane == 0) issue_x(s_issue, g);
         if (++g == G) { g = 0; ++c; }
         if (++s_issue == S) { s_issue = 0; ph_issue ^= 1; }
       }
@@ -233,21 +280,27 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
     }
   } else {
     // ------------------------------ consumers -----------------------------
+    grid_dependency_wait();    // before anything is written to the output or the workspace
     const int g8 = lane >> 2;  // 0..7
     const int t4 = lane & 3;   // 0..3
     const int ctid = threadIdx.x;  // 0..255
-    // ldmatrix: lane l addresses row 32h + l of the tile, this warp's 16-byte chunk
-    const uint32_t ld_off = lane * 128 + ((warp ^ (lane & 7)) << 4);
+    // ldmatrix: lane l addresses row 32h + l of this warp's box, 16-byte chunk ch (swizzled by the row)
+    const int ch0 = 2 * (warp & 3);
+    const uint32_t ld_base = (warp >> 2) * kBoxBytes + lane * 128;
+    const uint32_t ld_off0 = ld_base + ((ch0 ^ (lane & 7)) << 4);
+    const uint32_t ld_off1 = ld_base + (((ch0 + 1) ^ (lane & 7)) << 4);
     // activation fragment: row g8 (+8 per tile), chunk 2*slab + t4/2 swizzled by the row,
     // 8-byte half t4 & 1.  Address bits 5-7 carry the chunk, so the slab is XOR-ed in.
     const uint32_t x_off = L::kOffX + g8 * kXRowBytes + ((t4 >> 1) << 4) + ((t4 & 1) << 3) +
                            ((g8 & 3) << 5);
-    const int lc = warp * 16 + 2 * g8;  // this thread's column pair inside the block
-    float yacc[MT][4];
+    const int lc = warp * 32 + 2 * g8;  // first column pair of this thread inside the block (second: +16)
+    float yacc[2][MT][4];
 #pragma unroll
-    for (int mt = 0; mt < MT; ++mt)
+    for (int j = 0; j < 2; ++j)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) yacc[mt][i] = 0.f;
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) yacc[j][mt][i] = 0.f;
 
     uint32_t sync_phase = 0;
     // Rendezvous of the eight consumer warps.  An mbarrier with a bounded wait
@@ -265,30 +318,35 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
       const int first = cta_of_unit(static_cast<long long>(c) * G, P, U);
       const int last = cta_of_unit(static_cast<long long>(c) * G + G - 1, P, U);
       const int nslots = last - first + 1;
-      const int col = c * kColsPerBlock + lc;
+      const int col0 = c * kColsPerBlock;
       if (nslots == 1) {
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+              const int m = mt * 8 + 2 * t4 + r;
+              const int col = col0 + lc + 16 * j;
+              if (m < M && col < N)
+                *reinterpret_cast<uint32_t*>(y + static_cast<size_t>(m) * N + col) =
+                    dev::pack_bf16x2(yacc[j][mt][r], yacc[j][mt][2 + r]);
+            }
+        return;
+      }
+      const int slot = static_cast<int>(blockIdx.x) - first;
+      float* part = ws_partial + (static_cast<size_t>(c) * max_slots + slot) * (MT * 8) * kColsPerBlock;
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
 #pragma unroll
         for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
           for (int r = 0; r < 2; ++r) {
             const int m = mt * 8 + 2 * t4 + r;
             if (m < M)
-              *reinterpret_cast<uint32_t*>(y + static_cast<size_t>(m) * N + col) =
-                  dev::pack_bf16x2(yacc[mt][r], yacc[mt][2 + r]);
+              __stcg(reinterpret_cast<float2*>(part + m * kColsPerBlock + lc + 16 * j),
+                     make_float2(yacc[j][mt][r], yacc[j][mt][2 + r]));
           }
-        return;
-      }
-      const int slot = static_cast<int>(blockIdx.x) - first;
-      float* part = ws_partial + (static_cast<size_t>(c) * max_slots + slot) * (MT * 8) * kColsPerBlock;
-#pragma unroll
-      for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-        for (int r = 0; r < 2; ++r) {
-          const int m = mt * 8 + 2 * t4 + r;
-          if (m < M)
-            __stcg(reinterpret_cast<float2*>(part + m * kColsPerBlock + lc),
-                   make_float2(yacc[mt][r], yacc[mt][2 + r]));
-        }
       __threadfence();
       if (!consumer_sync()) return;
       if (ctid == 0) {
@@ -303,6 +361,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
         for (int idx = ctid; idx < M * (kColsPerBlock / 2); idx += 256) {
           const int m = idx / (kColsPerBlock / 2);
           const int cp = (idx % (kColsPerBlock / 2)) * 2;
+          if (col0 + cp >= N) continue;
           float a = 0.f, b = 0.f;
           for (int sl = 0; sl < nslots; ++sl) {
             const float2 v = __ldcg(reinterpret_cast<const float2*>(
@@ -310,7 +369,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
             a += v.x;
             b += v.y;
           }
-          *reinterpret_cast<uint32_t*>(y + static_cast<size_t>(m) * N + c * kColsPerBlock + cp) =
+          *reinterpret_cast<uint32_t*>(y + static_cast<size_t>(m) * N + col0 + cp) =
               dev::pack_bf16x2(a, b);
         }
         if (ctid == 0) ws_counter[c] = 0;
@@ -332,66 +391,78 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
       const uint8_t* st = smem + s * L::kStage;
       const uint32_t st_addr = dev::smem_u32(st);
 
-      // per-group constants of this thread's two columns
-      const uint32_t s2 = *reinterpret_cast<const uint32_t*>(st + L::kOffS + lc * 2);
-      const float sc0 = __uint_as_float(s2 << 16);
-      const float sc1 = __uint_as_float(s2 & 0xFFFF0000u);
-      uint32_t z0, z1;
-      if (ZP_PACKED) {
-        const uint32_t zb = st[L::kOffZ + (lc >> 1)];
-        z0 = zb & 0xFu;
-        z1 = zb >> 4;
-      } else {
-        const uint32_t zb = *reinterpret_cast<const uint16_t*>(st + L::kOffZ + lc);
-        z0 = zb & 0xFFu;
-        z1 = zb >> 8;
+      // per-group constants of this thread's four columns (pairs lc, lc+16)
+      float sc[2][2];
+      uint32_t zc[2][4];  // per pair: 1024+z and 1024+16z as f16x2, for both columns
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int col = lc + 16 * j;
+        const uint32_t s2 = *reinterpret_cast<const uint32_t*>(st + L::kOffS + col * 2);
+        sc[j][0] = __uint_as_float(s2 << 16);
+        sc[j][1] = __uint_as_float(s2 & 0xFFFF0000u);
+        uint32_t z0, z1;
+        if (ZP_PACKED) {
+          const uint32_t zb = st[L::kOffZ + (col >> 1)];
+          z0 = zb & 0xFu;
+          z1 = zb >> 4;
+        } else {
+          const uint32_t zb = *reinterpret_cast<const uint16_t*>(st + L::kOffZ + col);
+          z0 = zb & 0xFFu;
+          z1 = zb >> 8;
+        }
+        zc[j][0] = (0x6400u | z0) * 0x00010001u;
+        zc[j][1] = (0x6400u | (z0 << 4)) * 0x00010001u;
+        zc[j][2] = (0x6400u | z1) * 0x00010001u;
+        zc[j][3] = (0x6400u | (z1 << 4)) * 0x00010001u;
       }
-      // f16 pairs 1024 + z (low nibbles) and 1024 + 16 z (high nibbles)
-      const uint32_t zlo0 = (0x6400u | z0) * 0x00010001u, zhi0 = (0x6400u | (z0 << 4)) * 0x00010001u;
-      const uint32_t zlo1 = (0x6400u | z1) * 0x00010001u, zhi1 = (0x6400u | (z1 << 4)) * 0x00010001u;
 
-      float acc[MT][4];
+      float acc[2][MT][4];
 #pragma unroll
-      for (int mt = 0; mt < MT; ++mt)
+      for (int j = 0; j < 2; ++j)
 #pragma unroll
-        for (int i = 0; i < 4; ++i) acc[mt][i] = 0.f;
+        for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+          for (int i = 0; i < 4; ++i) acc[j][mt][i] = 0.f;
       const uint32_t xb = st_addr + x_off;
 
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        uint32_t wreg[4];
-        ldmatrix_x4_trans(st_addr + ld_off + h * 4096, wreg);
+        uint32_t wa[4], wb[4];
+        ldmatrix_x4_trans(st_addr + ld_off0 + h * 4096, wa);
+        ldmatrix_x4_trans(st_addr + ld_off1 + h * 4096, wb);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const uint32_t w = wreg[j];
-          const uint32_t t = w >> 8;
-          // bytes 0/2 of the register: column 2g, rows 2t and 2t+1 of the slab
-          const uint32_t r0 = hsub2_u32(lop3_and_or(w, 0x000F000Fu, 0x64006400u), zlo0);  // k 4t, 4t+2
-          const uint32_t r1 = hsub2_u32(lop3_and_or(w, 0x00F000F0u, 0x64006400u), zhi0);  // k 4t+1, 4t+3 (x16)
-          // bytes 1/3: column 2g+1
-          const uint32_t r2 = hsub2_u32(lop3_and_or(t, 0x000F000Fu, 0x64006400u), zlo1);
-          const uint32_t r3 = hsub2_u32(lop3_and_or(t, 0x00F000F0u, 0x64006400u), zhi1);
-          const int slab = 4 * h + j;
+        for (int q = 0; q < 4; ++q) {
+          const int slab = 4 * h + q;
+          uint32_t xf[MT][2];
 #pragma unroll
-          for (int mt = 0; mt < MT; ++mt) {
-            uint32_t x0, x1;
+          for (int mt = 0; mt < MT; ++mt)
             asm volatile("ld.shared.v2.u32 {%0, %1}, [%2];"
-                         : "=r"(x0), "=r"(x1)
+                         : "=r"(xf[mt][0]), "=r"(xf[mt][1])
                          : "r"((xb ^ (slab << 5)) + mt * 8 * kXRowBytes));
-            mma_f16_16816(acc[mt], r0, r2, r1, r3, x0, x1);
-          }
+          uint32_t r[4];
+          dequant8(wa[q], zc[0][0], zc[0][1], zc[0][2], zc[0][3], r);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt)
+            mma_f16_16816(acc[0][mt], r[0], r[2], r[1], r[3], xf[mt][0], xf[mt][1]);
+          dequant8(wb[q], zc[1][0], zc[1][1], zc[1][2], zc[1][3], r);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt)
+            mma_f16_16816(acc[1][mt], r[0], r[2], r[1], r[3], xf[mt][0], xf[mt][1]);
         }
       }
-      // group epilogue: this thread holds columns (2g, 2g+1) of its warp's
-      // chunk for rows (2t, 2t+1) of each 8-row tile
+      // group epilogue: per pair this thread holds columns (c, c+1) for rows
+      // (2t, 2t+1) of each 8-row tile
       const float* fac = reinterpret_cast<const float*>(st + L::kOffF);
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
         const float2 f = *reinterpret_cast<const float2*>(fac + mt * 8 + 2 * t4);
-        yacc[mt][0] = fmaf(sc0 * f.x, acc[mt][0], yacc[mt][0]);
-        yacc[mt][1] = fmaf(sc0 * f.y, acc[mt][1], yacc[mt][1]);
-        yacc[mt][2] = fmaf(sc1 * f.x, acc[mt][2], yacc[mt][2]);
-        yacc[mt][3] = fmaf(sc1 * f.y, acc[mt][3], yacc[mt][3]);
+#pragma unroll
+        for (int j = 0; j < 2; ++j) {
+          yacc[j][mt][0] = fmaf(sc[j][0] * f.x, acc[j][mt][0], yacc[j][mt][0]);
+          yacc[j][mt][1] = fmaf(sc[j][0] * f.y, acc[j][mt][1], yacc[j][mt][1]);
+          yacc[j][mt][2] = fmaf(sc[j][1] * f.x, acc[j][mt][2], yacc[j][mt][2]);
+          yacc[j][mt][3] = fmaf(sc[j][1] * f.y, acc[j][mt][3], yacc[j][mt][3]);
+        }
       }
       __syncwarp();
       if (lane == 0) dev::mbar_arrive(&empty[s]);
@@ -402,19 +473,24 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
         flush(c);
         ++c;
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt)
+        for (int j = 0; j < 2; ++j)
 #pragma unroll
-          for (int i = 0; i < 4; ++i) yacc[mt][i] = 0.f;
+          for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) yacc[j][mt][i] = 0.f;
       }
     }
     if (ok && n_units > 0 && g != 0) flush(c);
   }
 }
 
+// One launch path for both entry points: `status` is where a bounded wait that
+// gives up is recorded (may be null).
 template <int MT, bool ZP>
 static int launch(const CUtensorMap& wmap, const CUtensorMap& xmap, const uint16_t* scales,
                   const uint8_t* zeros, uint16_t* y, float* ws_partial, int* ws_counter, int M, int N,
-                  int K, int G, int U, int P, int max_slots, cudaStream_t stream) {
+                  int K, int G, int U, int P, int max_slots, int static_weights, int* status,
+                  cudaStream_t stream) {
   using L = Smem<MT>;
   static bool configured = false;
   auto kern = w4a16_decode_kernel<MT, ZP>;
@@ -422,13 +498,22 @@ static int launch(const CUtensorMap& wmap, const CUtensorMap& xmap, const uint16
     QMM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
     configured = true;
   }
-  kern<<<P, kThreads, L::kTotal, stream>>>(wmap, xmap, scales, zeros, y, ws_partial, ws_counter, M,
-                                           N, K, G, U, max_slots, device_status_word());
-  QMM_CHECK_LAUNCH("w4a16_decode_kernel");
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(P);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = L::kTotal;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  QMM_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, wmap, xmap, scales, zeros, y, ws_partial, ws_counter, M,
+                                  N, K, G, U, max_slots, static_weights, status));
   return QMM_OK;
 }
 
-static int blocks_per_sm(int M) { return M <= 8 ? Smem<1>::kMinBlocks : Smem<2>::kMinBlocks; }
+static int blocks_per_sm(int M) { return M <= 16 ? 2 : 1; }
 static int grid_size(int U, int M) {
   // every CTA resident at once; small problems get at least two units per CTA
   // so that few CTAs share a column block
@@ -441,6 +526,64 @@ static int slots_for(int G, int U, int P) {
   return static_cast<int>((static_cast<long long>(G) * P + U - 1) / U) + 1;
 }
 static int rows_padded(int M) { return M <= 8 ? 8 : (M <= 16 ? 16 : 32); }
+static int col_blocks(int64_t N) { return static_cast<int>((N + kColsPerBlock - 1) / kColsPerBlock); }
+
+// Shared body of the two entry points: argument checks, tensor maps, launch.
+static int run(const char* name, const uint16_t* x, const uint8_t* wq, const uint16_t* scales,
+               const uint8_t* zeros, int zeros_packed, uint16_t* y, int64_t M, int64_t N, int64_t K,
+               void* workspace, unsigned flags, int* status, cudaStream_t st) {
+  const int G = static_cast<int>(K / kGroup);
+  const int C = col_blocks(N);
+  const int U = G * C;
+  const int P = grid_size(U, static_cast<int>(M));
+  const int slots = slots_for(G, U, P);
+  const size_t counters = (static_cast<size_t>(C) * sizeof(int) + 255) / 256 * 256;
+  int* ws_counter = static_cast<int*>(workspace);
+  float* ws_partial = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + counters);
+
+  CUtensorMap wmap, xmap;
+  if (int rc = make_tensor_map_2d(&wmap, wq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1,
+                                  static_cast<uint64_t>(K / 2), static_cast<uint64_t>(N),
+                                  static_cast<uint64_t>(N), kRowsPerUnit, 128,
+                                  CU_TENSOR_MAP_SWIZZLE_128B))
+    return rc;
+  // activations: [M, K] bf16, one box = (8, 16 or 32 rows) x one 128-k group, rows past M read as zero
+  if (int rc = make_tensor_map_2d(&xmap, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                                  static_cast<uint64_t>(M), static_cast<uint64_t>(K),
+                                  static_cast<uint64_t>(K) * 2, rows_padded(static_cast<int>(M)),
+                                  kGroup, CU_TENSOR_MAP_SWIZZLE_NONE))
+    return rc;
+  const int m = static_cast<int>(M), n = static_cast<int>(N), k = static_cast<int>(K);
+  const int sw = (flags & QMM_W4_STATIC_WEIGHTS) ? 1 : 0;
+  (void)name;
+#define QMM_W4_LAUNCH(MT)                                                                         \
+  (zeros_packed ? launch<MT, true>(wmap, xmap, scales, zeros, y, ws_partial, ws_counter, m, n, k, \
+                                   G, U, P, slots, sw, status, st)                                \
+                : launch<MT, false>(wmap, xmap, scales, zeros, y, ws_partial, ws_counter, m, n,   \
+                                    k, G, U, P, slots, sw, status, st))
+  if (M <= 8) return QMM_W4_LAUNCH(1);
+  if (M <= 16) return QMM_W4_LAUNCH(2);
+  return QMM_W4_LAUNCH(4);
+#undef QMM_W4_LAUNCH
+}
+
+static int check_args(const char* name, const void* x, const void* wq, const void* scales,
+                      const void* zeros, const void* y, int64_t M, int64_t N, int64_t K,
+                      int64_t group) {
+  QMM_REQUIRE(x && wq && scales && zeros && y, QMM_ERR_INVALID_ARGUMENT, "%s: null tensor pointer", name);
+  QMM_REQUIRE(group == kGroup, QMM_ERR_UNSUPPORTED, "%s: group must be 128, got %lld", name,
+              (long long)group);
+  QMM_REQUIRE(M >= 1 && M <= 32, QMM_ERR_UNSUPPORTED, "%s: decode kernel covers 1 <= M <= 32, got %lld",
+              name, (long long)M);
+  QMM_REQUIRE(N >= 128 && N % 128 == 0 && K >= kGroup && K % kGroup == 0, QMM_ERR_UNSUPPORTED,
+              "%s: N (%lld) and K (%lld) must be positive multiples of 128", name, (long long)N,
+              (long long)K);
+  QMM_REQUIRE(N * (K / kGroup) < (1ll << 30), QMM_ERR_UNSUPPORTED, "%s: problem too large", name);
+  QMM_REQUIRE(aligned(x, 16) && aligned(wq, 16) && aligned(scales, 16) && aligned(zeros, 16) &&
+                  aligned(y, 4),
+              QMM_ERR_INVALID_ARGUMENT, "%s: tensors must be 16-byte aligned", name);
+  return QMM_OK;
+}
 
 // ---------------------------------------------------------------------------
 // Built-in scratch for callers that must not allocate.
@@ -476,26 +619,6 @@ static int static_scratch_address(void** out) {
   return QMM_OK;
 }
 
-// Same launch as launch<MT, ZP>() but with the status pointer supplied by the
-// caller instead of created on demand (creating it would allocate).
-template <int MT, bool ZP>
-static int launch_no_alloc(const CUtensorMap& wmap, const CUtensorMap& xmap, const uint16_t* scales,
-                           const uint8_t* zeros, uint16_t* y, float* ws_partial, int* ws_counter,
-                           int M, int N, int K, int G, int U, int P, int max_slots, int* status,
-                           cudaStream_t stream) {
-  using L = Smem<MT>;
-  static bool configured = false;
-  auto kern = w4a16_decode_kernel<MT, ZP>;
-  if (!configured) {
-    QMM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
-    configured = true;
-  }
-  kern<<<P, kThreads, L::kTotal, stream>>>(wmap, xmap, scales, zeros, y, ws_partial, ws_counter, M,
-                                           N, K, G, U, max_slots, status);
-  QMM_CHECK_LAUNCH("w4a16_decode_kernel");
-  return QMM_OK;
-}
-
 }  // namespace w4
 }  // namespace qmm
 
@@ -503,9 +626,9 @@ extern "C" {
 
 size_t qmm_w4a16_g128_workspace_bytes(int64_t M, int64_t N, int64_t K) {
   using namespace qmm::w4;
-  if (M < 1 || M > 32 || N < kColsPerBlock || K < kGroup || N % kColsPerBlock || K % kGroup) return 0;
+  if (M < 1 || M > 32 || N < 128 || K < kGroup || N % 128 || K % kGroup) return 0;
   const int G = static_cast<int>(K / kGroup);
-  const int C = static_cast<int>(N / kColsPerBlock);
+  const int C = col_blocks(N);
   const int U = G * C;
   const int P = grid_size(U, static_cast<int>(M));
   const int slots = slots_for(G, U, P);
@@ -517,65 +640,19 @@ size_t qmm_w4a16_g128_workspace_bytes(int64_t M, int64_t N, int64_t K) {
 int qmm_w4a16_g128(const uint16_t* x, const uint8_t* wq, const uint16_t* scales,
                    const uint8_t* zeros, int zeros_packed, uint16_t* y, int64_t M, int64_t N,
                    int64_t K, int64_t group, void* workspace, size_t workspace_bytes,
-                   void* stream) {
+                   unsigned flags, void* stream) {
   using namespace qmm;
   using namespace qmm::w4;
-  QMM_REQUIRE(x && wq && scales && zeros && y, QMM_ERR_INVALID_ARGUMENT,
-              "qmm_w4a16_g128: null tensor pointer");
-  QMM_REQUIRE(group == kGroup, QMM_ERR_UNSUPPORTED, "qmm_w4a16_g128: group must be 128, got %lld",
-              (long long)group);
-  QMM_REQUIRE(M >= 1 && M <= 32, QMM_ERR_UNSUPPORTED,
-              "qmm_w4a16_g128: decode kernel covers 1 <= M <= 32, got %lld", (long long)M);
-  QMM_REQUIRE(N >= kColsPerBlock && N % kColsPerBlock == 0 && K >= kGroup && K % kGroup == 0,
-              QMM_ERR_UNSUPPORTED,
-              "qmm_w4a16_g128: N (%lld) and K (%lld) must be positive multiples of 128", (long long)N,
-              (long long)K);
-  QMM_REQUIRE(N * (K / kGroup) < (1ll << 30), QMM_ERR_UNSUPPORTED, "qmm_w4a16_g128: problem too large");
-  QMM_REQUIRE(aligned(x, 16) && aligned(wq, 16) && aligned(scales, 16) && aligned(zeros, 16) &&
-                  aligned(y, 4),
-              QMM_ERR_INVALID_ARGUMENT, "qmm_w4a16_g128: tensors must be 16-byte aligned");
+  if (int rc = check_args("qmm_w4a16_g128", x, wq, scales, zeros, y, M, N, K, group)) return rc;
   const size_t need = qmm_w4a16_g128_workspace_bytes(M, N, K);
   QMM_REQUIRE(workspace != nullptr && workspace_bytes >= need && aligned(workspace, 256),
               QMM_ERR_WORKSPACE, "qmm_w4a16_g128: workspace of %zu bytes (256-byte aligned) required",
               need);
   if (int st = read_device_status())
     return set_error(QMM_ERR_TIMEOUT, "a previous kernel gave up waiting (status word 0x%x)", st);
-
-  const int G = static_cast<int>(K / kGroup);
-  const int C = static_cast<int>(N / kColsPerBlock);
-  const int U = G * C;
-  const int P = grid_size(U, static_cast<int>(M));
-  const int slots = slots_for(G, U, P);
-  const size_t counters = (static_cast<size_t>(C) * sizeof(int) + 255) / 256 * 256;
-  int* ws_counter = static_cast<int*>(workspace);
-  float* ws_partial = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + counters);
-
-  CUtensorMap wmap;
-  if (int rc = make_tensor_map_2d(&wmap, wq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1,
-                                  static_cast<uint64_t>(K / 2), static_cast<uint64_t>(N),
-                                  static_cast<uint64_t>(N), kRowsPerUnit, kColsPerBlock,
-                                  CU_TENSOR_MAP_SWIZZLE_128B))
-    return rc;
-  // activations: [M, K] bf16, one box = (8, 16 or 32 rows) x one 128-k group, rows past M read as zero
-  CUtensorMap xmap;
-  if (int rc = make_tensor_map_2d(&xmap, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
-                                  static_cast<uint64_t>(M), static_cast<uint64_t>(K),
-                                  static_cast<uint64_t>(K) * 2, rows_padded(static_cast<int>(M)),
-                                  kGroup, CU_TENSOR_MAP_SWIZZLE_NONE))
-    return rc;
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const int m = static_cast<int>(M), n = static_cast<int>(N), k = static_cast<int>(K);
-#define QMM_W4_LAUNCH(MT)                                                                        \
-  (zeros_packed ? launch<MT, true>(wmap, xmap, scales, zeros, y, ws_partial, ws_counter, m, n, k, \
-                                   G, U, P, slots, st)                                           \
-                : launch<MT, false>(wmap, xmap, scales, zeros, y, ws_partial, ws_counter, m, n,  \
-                                    k, G, U, P, slots, st))
-  if (M <= 8) return QMM_W4_LAUNCH(1);
-  if (M <= 16) return QMM_W4_LAUNCH(2);
-  return QMM_W4_LAUNCH(4);
-#undef QMM_W4_LAUNCH
+  return run("qmm_w4a16_g128", x, wq, scales, zeros, zeros_packed, y, M, N, K, workspace, flags,
+             device_status_word(), static_cast<cudaStream_t>(stream));
 }
-
 
 // qmm_w4a16_g128 for callers that cannot allocate: the split-K scratch is the
 // library's own fixed array instead of a caller-provided workspace.
@@ -595,22 +672,8 @@ int qmm_w4a16_g128_static_scratch(const uint16_t* x, const uint8_t* wq, const ui
                                   int64_t N, int64_t K, int64_t group, void* stream) {
   using namespace qmm;
   using namespace qmm::w4;
-  QMM_REQUIRE(x && wq && scales && zeros && y, QMM_ERR_INVALID_ARGUMENT,
-              "qmm_w4a16_g128_static_scratch: null tensor pointer");
-  QMM_REQUIRE(group == kGroup, QMM_ERR_UNSUPPORTED,
-              "qmm_w4a16_g128_static_scratch: group must be 128, got %lld", (long long)group);
-  QMM_REQUIRE(M >= 1 && M <= 32, QMM_ERR_UNSUPPORTED,
-              "qmm_w4a16_g128_static_scratch: covers 1 <= M <= 32, got %lld", (long long)M);
-  QMM_REQUIRE(N >= kColsPerBlock && N % kColsPerBlock == 0 && K >= kGroup && K % kGroup == 0,
-              QMM_ERR_UNSUPPORTED,
-              "qmm_w4a16_g128_static_scratch: N (%lld) and K (%lld) must be positive multiples of 128",
-              (long long)N, (long long)K);
-  QMM_REQUIRE(N * (K / kGroup) < (1ll << 30), QMM_ERR_UNSUPPORTED,
-              "qmm_w4a16_g128_static_scratch: problem too large");
-  QMM_REQUIRE(aligned(x, 16) && aligned(wq, 16) && aligned(scales, 16) && aligned(zeros, 16) &&
-                  aligned(y, 4),
-              QMM_ERR_INVALID_ARGUMENT,
-              "qmm_w4a16_g128_static_scratch: tensors must be 16-byte aligned");
+  if (int rc = check_args("qmm_w4a16_g128_static_scratch", x, wq, scales, zeros, y, M, N, K, group))
+    return rc;
   const size_t need = qmm_w4a16_g128_workspace_bytes(M, N, K);
   QMM_REQUIRE(need > 0 && need <= kStaticScratchBytes, QMM_ERR_WORKSPACE,
               "qmm_w4a16_g128_static_scratch: this shape needs %zu bytes of scratch but the built-in "
@@ -618,44 +681,14 @@ int qmm_w4a16_g128_static_scratch(const uint16_t* x, const uint8_t* wq, const ui
               need, kStaticScratchBytes);
   void* scratch = nullptr;
   if (int rc = static_scratch_address(&scratch)) return rc;
-
-  const int G = static_cast<int>(K / kGroup);
-  const int C = static_cast<int>(N / kColsPerBlock);
-  const int U = G * C;
-  const int P = grid_size(U, static_cast<int>(M));
-  const int slots = slots_for(G, U, P);
-  const size_t counters = (static_cast<size_t>(C) * sizeof(int) + 255) / 256 * 256;
-  int* ws_counter = static_cast<int*>(scratch);
-  float* ws_partial = reinterpret_cast<float*>(static_cast<uint8_t*>(scratch) + counters);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  QMM_CUDA_TRY(cudaMemsetAsync(ws_counter, 0, counters, st));
-
-  CUtensorMap wmap;
-  if (int rc = make_tensor_map_2d(&wmap, wq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1,
-                                  static_cast<uint64_t>(K / 2), static_cast<uint64_t>(N),
-                                  static_cast<uint64_t>(N), kRowsPerUnit, kColsPerBlock,
-                                  CU_TENSOR_MAP_SWIZZLE_128B))
-    return rc;
+  const size_t counters = (static_cast<size_t>(col_blocks(N)) * sizeof(int) + 255) / 256 * 256;
+  QMM_CUDA_TRY(cudaMemsetAsync(scratch, 0, counters, st));
   // A wait that gives up is reported through the library's status word when
   // that word exists already (any other entry point, or qmm_device_status(),
   // creates it); this call will not create it, because that allocates.
-  CUtensorMap xmap;
-  if (int rc = make_tensor_map_2d(&xmap, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
-                                  static_cast<uint64_t>(M), static_cast<uint64_t>(K),
-                                  static_cast<uint64_t>(K) * 2, rows_padded(static_cast<int>(M)),
-                                  kGroup, CU_TENSOR_MAP_SWIZZLE_NONE))
-    return rc;
-  int* status = device_status_word_if_ready();
-  const int m = static_cast<int>(M), n = static_cast<int>(N), k = static_cast<int>(K);
-#define QMM_W4_LAUNCH_NA(MT)                                                                      \
-  (zeros_packed ? launch_no_alloc<MT, true>(wmap, xmap, scales, zeros, y, ws_partial, ws_counter, \
-                                            m, n, k, G, U, P, slots, status, st)                  \
-                : launch_no_alloc<MT, false>(wmap, xmap, scales, zeros, y, ws_partial,            \
-                                             ws_counter, m, n, k, G, U, P, slots, status, st))
-  if (M <= 8) return QMM_W4_LAUNCH_NA(1);
-  if (M <= 16) return QMM_W4_LAUNCH_NA(2);
-  return QMM_W4_LAUNCH_NA(4);
-#undef QMM_W4_LAUNCH_NA
+  return run("qmm_w4a16_g128_static_scratch", x, wq, scales, zeros, zeros_packed, y, M, N, K, scratch,
+             0u, device_status_word_if_ready(), st);
 }
 
 }  // extern "C"

@@ -130,12 +130,14 @@ _w4_workspaces: dict = {}
 
 def w4a16_g128(x: torch.Tensor, wq: torch.Tensor, scales: torch.Tensor, zeros: torch.Tensor, *,
                zeros_packed: bool = False, group: int = 128, out: torch.Tensor | None = None,
-               workspace: torch.Tensor | None = None) -> torch.Tensor:
+               workspace: torch.Tensor | None = None, static_weights: bool = False) -> torch.Tensor:
     """int4 group-wise asymmetric weight-only matmul at decode sizes.
 
     x bf16 ``[M,K]`` (M <= 32); wq uint8 ``[K/2,N]`` (low nibble = even k);
     scales bf16 ``[K/group,N]``; zeros uint8 ``[K/group,N]`` or packed
-    ``[K/group,N/2]``; returns bf16 ``[M,N]``.
+    ``[K/group,N/2]``; returns bf16 ``[M,N]``.  ``static_weights=True`` tells
+    the kernel that nothing queued earlier on the stream writes the weights,
+    so it may fetch them while the previous kernel is still finishing.
     """
     _need_cuda(x, wq, scales, zeros, out, workspace)
     if x.dtype != torch.bfloat16 or wq.dtype != torch.uint8 or scales.dtype != torch.bfloat16 or zeros.dtype != torch.uint8:
@@ -159,5 +161,6 @@ def w4a16_g128(x: torch.Tensor, wq: torch.Tensor, scales: torch.Tensor, zeros: t
         out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
     _lib.check(lib.qmm_w4a16_g128(x.data_ptr(), wq.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
                                   1 if zeros_packed else 0, out.data_ptr(), M, N, K, group, workspace.data_ptr(),
-                                  workspace.numel(), _stream_ptr()))
+                                  workspace.numel(), _lib.QMM_W4_STATIC_WEIGHTS if static_weights else 0,
+                                  _stream_ptr()))
     return out

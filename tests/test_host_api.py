@@ -27,7 +27,7 @@ def test_library_loads_and_exports_every_declared_symbol():
 def test_error_reporting_without_a_gpu():
     lib = _lib.load()
     # argument validation happens before any CUDA call
-    st = lib.qmm_w4a16_g128(None, None, None, None, 0, None, 1, 128, 128, 128, None, 0, None)
+    st = lib.qmm_w4a16_g128(None, None, None, None, 0, None, 1, 128, 128, 128, None, 0, 0, None)
     assert st == 1 and lib.qmm_status_name(st) == b"QMM_ERR_INVALID_ARGUMENT"
     assert "null" in _lib.last_error()
     buf = ctypes.create_string_buffer(8)

@@ -1,0 +1,103 @@
+"""The StableHLO reader and dequant-chain matcher (host logic, no GPU).
+
+Mirrors the reference's plan-shape tests, which parse the planner's JSON trace
+to assert which route was chosen (tests/test_reduce_routing.py:55-62).
+"""
+
+import os
+
+import pytest
+
+from jax_metallib_b200 import _lib
+from jax_metallib_b200.stablehlo import Executable
+
+FIX = os.path.join(os.path.dirname(os.path.abspath(__file__)), "fixtures")
+
+
+def load(name):
+    return open(os.path.join(FIX, name)).read()
+
+
+def fused(exe):
+    return [t for t in exe.trace() if t["event"] == "fused"]
+
+
+def test_config1_chain_becomes_one_kernel():
+    exe = Executable(load("cfg1_w8a32.mlir"))
+    assert (exe.num_args, exe.num_results, exe.num_steps) == (3, 1, 1)
+    (f,) = fused(exe)
+    assert f["kernel"] == "qmm_w8a32_perchannel" and (f["M"], f["N"], f["K"]) == (32, 1024, 1024)
+    assert f["ops_fused"] == 5  # convert, two broadcasts, multiply, dot_general
+    assert exe.workspace_bytes == 0
+
+
+def test_config1_spelling_variants_and_rank3_lhs():
+    exe = Executable(load("cfg1_variant_reshape_swapped.mlir"))
+    (f,) = fused(exe)
+    assert f["kernel"] == "qmm_w8a32_perchannel" and (f["M"], f["N"], f["K"]) == (32, 128, 256)
+
+
+def test_config2_integer_dot_with_and_without_rescale():
+    exe = Executable(load("cfg2_i8dot_rescale.mlir"))
+    (f,) = fused(exe)
+    assert f["kernel"] == "qmm_i8i8_i32" and f["rescale"] is True and f["ops_fused"] == 8
+    assert (f["M"], f["N"], f["K"]) == (2048, 4096, 4096) and exe.num_results == 2
+    exe = Executable(load("cfg2_i8dot_only.mlir"))
+    (f,) = fused(exe)
+    assert f["kernel"] == "qmm_i8i8_i32" and f["rescale"] is False
+    # multiply order swapped (column scale first) is the same fused step
+    text = load("cfg2_i8dot_rescale.mlir").replace("%4 = stablehlo.multiply %1, %3", "%4 = stablehlo.multiply %1, %6x") \
+        .replace("%7 = stablehlo.multiply %4, %6 ", "%7 = stablehlo.multiply %4, %3 ").replace("%6x", "%6")
+    lines = text.splitlines()
+    # move the column broadcasts above the first multiply so that SSA order stays valid
+    i4 = next(i for i, l in enumerate(lines) if l.strip().startswith("%4 ="))
+    i5 = next(i for i, l in enumerate(lines) if l.strip().startswith("%5 ="))
+    lines[i4], lines[i5], lines[i5 + 1] = lines[i5], lines[i5 + 1], lines[i4]
+    (f,) = fused(Executable("\n".join(lines)))
+    assert f["rescale"] is True
+
+
+def test_config3_int4_chain():
+    exe = Executable(load("cfg3_w4a16.mlir"))
+    (f,) = fused(exe)
+    assert f["kernel"] == "qmm_w4a16_g128" and (f["M"], f["N"], f["K"]) == (4, 14336, 4096)
+    assert f["ops_fused"] == 19
+    assert exe.workspace_bytes == _lib.load().qmm_w4a16_g128_workspace_bytes(4, 14336, 4096)
+
+
+def test_config5_bf16_activations():
+    (f,) = fused(Executable(load("cfg5_w8a16.mlir")))
+    assert f["kernel"] == "qmm_w8a16_perchannel" and (f["M"], f["N"], f["K"]) == (4096, 1024, 8192)
+
+
+@pytest.mark.parametrize("name,needle", [
+    ("reject_unfused_add.mlir", "stablehlo.tanh"),
+    ("reject_escaping_intermediate.mlir", "also used on line"),
+])
+def test_unsupported_programs_fail_at_compile_time_naming_the_op(name, needle):
+    with pytest.raises(_lib.QmmError) as e:
+        Executable(load(name))
+    assert e.value.status_name == "QMM_ERR_UNSUPPORTED" and needle in str(e.value)
+
+
+def test_malformed_and_foreign_programs():
+    with pytest.raises(_lib.QmmError) as e:
+        Executable("module { }")
+    assert e.value.status_name == "QMM_ERR_PARSE"
+    with pytest.raises(_lib.QmmError) as e:
+        Executable(load("cfg1_w8a32.mlir").replace("tensor<1024x1024xi8>) ->", "tensor<1024x1024xi8> ->"))
+    assert e.value.status_name in ("QMM_ERR_PARSE", "QMM_ERR_UNSUPPORTED")
+    # plain float dot: not on the path
+    text = """module {
+  func.func public @main(%arg0: tensor<8x16xf32>, %arg1: tensor<16x4xf32>) -> tensor<8x4xf32> {
+    %0 = stablehlo.dot_general %arg0, %arg1, contracting_dims = [1] x [0] : (tensor<8x16xf32>, tensor<16x4xf32>) -> tensor<8x4xf32>
+    return %0 : tensor<8x4xf32>
+  }
+}"""
+    with pytest.raises(_lib.QmmError) as e:
+        Executable(text)
+    assert e.value.status_name == "QMM_ERR_UNSUPPORTED" and "plain float" in str(e.value)
+    # group size other than 128
+    with pytest.raises(_lib.QmmError) as e:
+        Executable(load("cfg3_w4a16.mlir").replace("32x128x14336", "64x64x14336").replace("32x14336", "64x14336"))
+    assert "group 128" in str(e.value)
