@@ -44,11 +44,13 @@ namespace w4 {
 constexpr int kColsPerBlock = 256;   // columns per unit: two 128-byte TMA boxes
 constexpr int kGroup = 128;          // k per unit
 constexpr int kRowsPerUnit = 64;     // packed byte-rows per unit
+constexpr int kRowsPerHalf = 32;     // a CTA's first and last unit may be half units (TMA boxes are 32 rows)
 constexpr int kConsumerWarps = 8;    // 32 columns (two 16-byte chunks) each
 constexpr int kThreads = (kConsumerWarps + 1) * 32;
 constexpr int kXRowBytes = 256;      // 128 16-bit activations; 16-byte chunks XOR-swizzled by (row & 3) << 1
 constexpr int kXLag = 2;             // units between issuing a group's loads and converting its activations
-constexpr int kBoxBytes = kRowsPerUnit * 128;  // 8192
+constexpr int kBoxBytes = kRowsPerUnit * 128;  // 8192: one 128-column half of a unit
+constexpr int kHalfBoxBytes = kRowsPerHalf * 128;
 
 template <int MT>
 struct Smem {
@@ -115,6 +117,11 @@ __device__ __forceinline__ void grid_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
+#ifdef QMM_W4_PROFILE
+__device__ unsigned long long g_w4_prof[2048 * 8];
+__device__ unsigned long long g_w4_span[64 * 4];  // per launch: min start, max first-data, max loop end, max exit
+#endif
+
 // CTA that owns unit u when U units are dealt to P CTAs as [i*U/P, (i+1)*U/P).
 __device__ __forceinline__ int cta_of_unit(long long u, int P, int U) {
   return static_cast<int>(((u + 1) * P - 1) / U);
@@ -138,7 +145,11 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
                     const uint16_t* __restrict__ scales, const uint8_t* __restrict__ zeros,
                     uint16_t* __restrict__ y, float* __restrict__ ws_partial,
                     int* __restrict__ ws_counter, int M, int N, int K, int G, int U, int max_slots,
-                    int static_weights, int* status) {
+                    int static_weights, int* status
+#ifdef QMM_W4_PROFILE
+                    , int launch_id
+#endif
+                    ) {
   using L = Smem<MT>;
   constexpr int S = L::kStages;
   extern __shared__ uint8_t smem_raw[];
@@ -147,17 +158,21 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + S * L::kStage);
   uint64_t* empty = full + S;
   uint64_t* xraw = empty + S;      // raw activations of the group have landed
-  uint64_t* sync_bar = xraw + S;   // consumer-only rendezvous with a bounded wait
-  int* flag = reinterpret_cast<int*>(sync_bar + 1);
 
   grid_launch_dependents();  // the next kernel on the stream may start its own prologue
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int P = gridDim.x;
-  const int u_begin = static_cast<int>((static_cast<long long>(blockIdx.x) * U) / P);
-  const int u_end = static_cast<int>((static_cast<long long>(blockIdx.x + 1) * U) / P);
+  // The range of this CTA in half units (64 k); whole units in between.
+  const int h_begin = static_cast<int>((static_cast<long long>(blockIdx.x) * 2 * U) / P);
+  const int h_end = static_cast<int>((static_cast<long long>(blockIdx.x + 1) * 2 * U) / P);
+  const int u_begin = h_begin >> 1;
+  const int u_end = (h_end + 1) >> 1;
   const int n_units = u_end - u_begin;
+  // halves of unit number `it` of this CTA that belong to it: [first, last)
+  auto half_lo = [&](int it) { return (it == 0) ? (h_begin & 1) : 0; };
+  auto half_hi = [&](int it) { return (it == n_units - 1 && (h_end & 1)) ? 1 : 2; };
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
@@ -165,7 +180,6 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
       dev::mbar_init(&empty[s], kConsumerWarps);  // one arrive per consumer warp
       dev::mbar_init(&xraw[s], 1);
     }
-    dev::mbar_init(sync_bar, kConsumerWarps);
     dev::fence_mbar_init();
   }
   __syncthreads();
@@ -179,15 +193,19 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
     const uint64_t policy = dev::policy_evict_first();
     constexpr int kPasses = MT * 4;  // a pass = 2 rows x 16 lanes x 16 bytes
     // weights, scales and zero points of a unit (one elected lane)
-    auto issue_weights = [&](int s, int c, int g) {
+    auto issue_weights = [&](int s, int c, int g, int it) {
       uint8_t* st = smem + s * L::kStage;
       const int col0 = c * kColsPerBlock;
       const int cols = min(kColsPerBlock, N - col0);  // 128 in a trailing half block
       const uint32_t sbytes = cols * 2;
       const uint32_t zbytes = ZP_PACKED ? cols / 2 : cols;
-      dev::mbar_expect_tx(&full[s], L::kW + sbytes + zbytes);
-      dev::tma_load_2d_hint(st, &wmap, &full[s], col0, g * kRowsPerUnit, policy);
-      dev::tma_load_2d_hint(st + kBoxBytes, &wmap, &full[s], col0 + 128, g * kRowsPerUnit, policy);
+      const int hl = half_lo(it), hh = half_hi(it);
+      dev::mbar_expect_tx(&full[s], (hh - hl) * 2 * kHalfBoxBytes + sbytes + zbytes);
+      for (int h = hl; h < hh; ++h) {
+        const int row = g * kRowsPerUnit + h * kRowsPerHalf;
+        dev::tma_load_2d_hint(st + h * kHalfBoxBytes, &wmap, &full[s], col0, row, policy);
+        dev::tma_load_2d_hint(st + kBoxBytes + h * kHalfBoxBytes, &wmap, &full[s], col0 + 128, row, policy);
+      }
       bulk_copy_g2s(st + L::kOffS, scales + static_cast<size_t>(g) * N + col0, sbytes, &full[s]);
       const uint8_t* zsrc = ZP_PACKED ? zeros + static_cast<size_t>(g) * (N / 2) + col0 / 2
                                       : zeros + static_cast<size_t>(g) * N + col0;
@@ -208,7 +226,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
       if (lane == 0) {
         int cc = c, gg = g;
         for (int i = 0; i < prefetched; ++i) {
-          issue_weights(i, cc, gg);
+          issue_weights(i, cc, gg, i);
           if (++gg == G) { gg = 0; ++cc; }
         }
       }
@@ -220,7 +238,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
       if (it < n_units) {
         if (it >= prefetched) {
           if (!dev::mbar_wait(&empty[s_issue], ph_issue ^ 1, status, 1)) break;
-          if (lane == 0) issue_weights(s_issue, c, g);
+          if (lane == 0) issue_weights(s_issue, c, g, it);
         }
         if (lane == 0) issue_x(s_issue, g);
         if (++g == G) { g = 0; ++c; }
@@ -283,7 +301,6 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
     grid_dependency_wait();    // before anything is written to the output or the workspace
     const int g8 = lane >> 2;  // 0..7
     const int t4 = lane & 3;   // 0..3
-    const int ctid = threadIdx.x;  // 0..255
     // ldmatrix: lane l addresses row 32h + l of this warp's box, 16-byte chunk ch (swizzled by the row)
     const int ch0 = 2 * (warp & 3);
     const uint32_t ld_base = (warp >> 2) * kBoxBytes + lane * 128;
@@ -302,21 +319,14 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
 #pragma unroll
         for (int i = 0; i < 4; ++i) yacc[j][mt][i] = 0.f;
 
-    uint32_t sync_phase = 0;
-    // Rendezvous of the eight consumer warps.  An mbarrier with a bounded wait
-    // rather than bar.sync, so that a warp that gave up earlier cannot leave
-    // the others waiting for ever.
-    auto consumer_sync = [&]() -> bool {
-      __syncwarp();
-      if (lane == 0) dev::mbar_arrive(sync_bar);
-      const bool r = dev::mbar_wait(sync_bar, sync_phase, status, 3);
-      sync_phase ^= 1;
-      __syncwarp();
-      return r;
-    };
+    // Hand this warp's 32 columns of the finished column block over.  CTAs that
+    // share the block each write a partial tile; every warp counts arrivals on
+    // its own counter, and the warp that arrives last adds the partial tiles of
+    // its columns in slot order (so the result does not depend on arrival
+    // order) and writes bf16.  No CTA-wide rendezvous is involved.
     auto flush = [&](int c) {
-      const int first = cta_of_unit(static_cast<long long>(c) * G, P, U);
-      const int last = cta_of_unit(static_cast<long long>(c) * G + G - 1, P, U);
+      const int first = cta_of_unit(static_cast<long long>(c) * 2 * G, P, 2 * U);
+      const int last = cta_of_unit(static_cast<long long>(c) * 2 * G + 2 * G - 1, P, 2 * U);
       const int nslots = last - first + 1;
       const int col0 = c * kColsPerBlock;
       if (nslots == 1) {
@@ -347,35 +357,45 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
               __stcg(reinterpret_cast<float2*>(part + m * kColsPerBlock + lc + 16 * j),
                      make_float2(yacc[j][mt][r], yacc[j][mt][2 + r]));
           }
-      __threadfence();
-      if (!consumer_sync()) return;
-      if (ctid == 0) {
-        const int old = atomicAdd(&ws_counter[c], 1);
-        *reinterpret_cast<volatile int*>(flag) = (old + 1 == nslots) ? 1 : 0;
+      __syncwarp();
+      int is_last = 0;
+      if (lane == 0) {
+        __threadfence();  // the warp's partial tile is visible before its arrival is
+        is_last = (atomicAdd(&ws_counter[c * kConsumerWarps + warp], 1) + 1 == nslots);
+        if (is_last) __threadfence();
       }
-      if (!consumer_sync()) return;
-      const bool is_last = (*reinterpret_cast<volatile int*>(flag) != 0);
-      if (is_last) {
-        __threadfence();
-        const float* base = ws_partial + static_cast<size_t>(c) * max_slots * (MT * 8) * kColsPerBlock;
-        for (int idx = ctid; idx < M * (kColsPerBlock / 2); idx += 256) {
-          const int m = idx / (kColsPerBlock / 2);
-          const int cp = (idx % (kColsPerBlock / 2)) * 2;
-          if (col0 + cp >= N) continue;
-          float a = 0.f, b = 0.f;
-          for (int sl = 0; sl < nslots; ++sl) {
-            const float2 v = __ldcg(reinterpret_cast<const float2*>(
-                base + (static_cast<size_t>(sl) * (MT * 8) + m) * kColsPerBlock + cp));
-            a += v.x;
-            b += v.y;
-          }
-          *reinterpret_cast<uint32_t*>(y + static_cast<size_t>(m) * N + col0 + cp) =
-              dev::pack_bf16x2(a, b);
+      is_last = __shfl_sync(0xFFFFFFFFu, is_last, 0);
+      if (!is_last) return;
+      const float* base = ws_partial + static_cast<size_t>(c) * max_slots * (MT * 8) * kColsPerBlock;
+      const int wcol = warp * 32 + lane;  // one column per lane
+      // four rows x four slots of loads in flight; slots are always added in
+      // ascending order, so the rounding does not depend on who arrived last
+      for (int m0 = 0; m0 < M; m0 += 4) {
+        float a[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int sl0 = 0; sl0 < nslots; sl0 += 4) {
+          float v[4][4];
+#pragma unroll
+          for (int ds = 0; ds < 4; ++ds)
+#pragma unroll
+            for (int r = 0; r < 4; ++r)
+              v[ds][r] = (sl0 + ds < nslots && m0 + r < M)
+                             ? __ldcg(base + (static_cast<size_t>(sl0 + ds) * (MT * 8) + m0 + r) * kColsPerBlock + wcol)
+                             : 0.f;
+#pragma unroll
+          for (int ds = 0; ds < 4; ++ds)
+#pragma unroll
+            for (int r = 0; r < 4; ++r) a[r] += v[ds][r];
         }
-        if (ctid == 0) ws_counter[c] = 0;
+#pragma unroll
+        for (int r = 0; r < 4; ++r) {
+          const float b = __shfl_down_sync(0xFFFFFFFFu, a[r], 1);
+          if (m0 + r < M && !(lane & 1) && col0 + wcol < N)
+            *reinterpret_cast<uint32_t*>(y + static_cast<size_t>(m0 + r) * N + col0 + wcol) =
+                dev::pack_bf16x2(a[r], b);
+        }
       }
-      // the flag word is reused by the next flush of this CTA
-      consumer_sync();
+      __syncwarp();
+      if (lane == 0) ws_counter[c * kConsumerWarps + warp] = 0;
     };
 
     int c = (n_units > 0) ? u_begin / G : 0;
@@ -383,11 +403,22 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
     int s = 0;
     uint32_t ph = 0;
     bool ok = true;
+#ifdef QMM_W4_PROFILE
+    unsigned long long p_start = dev::globaltimer_ns(), p_first = 0, p_wait = 0, p_comp = 0, p_flush = 0;
+#endif
     for (int it = 0; it < n_units; ++it) {
+#ifdef QMM_W4_PROFILE
+      long long c0 = clock64();
+#endif
       if (!dev::mbar_wait(&full[s], ph, status, 2)) {
         ok = false;
         break;
       }
+#ifdef QMM_W4_PROFILE
+      long long c1 = clock64();
+      p_wait += c1 - c0;
+      if (it == 0) p_first = dev::globaltimer_ns();
+#endif
       const uint8_t* st = smem + s * L::kStage;
       const uint32_t st_addr = dev::smem_u32(st);
 
@@ -425,8 +456,10 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
           for (int i = 0; i < 4; ++i) acc[j][mt][i] = 0.f;
       const uint32_t xb = st_addr + x_off;
 
+      const int hl = half_lo(it), hh = half_hi(it);
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
+        if (h < hl || h >= hh) continue;  // the other half of a boundary unit belongs to a neighbour CTA
         uint32_t wa[4], wb[4];
         ldmatrix_x4_trans(st_addr + ld_off0 + h * 4096, wa);
         ldmatrix_x4_trans(st_addr + ld_off1 + h * 4096, wb);
@@ -466,11 +499,21 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
       }
       __syncwarp();
       if (lane == 0) dev::mbar_arrive(&empty[s]);
+#ifdef QMM_W4_PROFILE
+      long long c2 = clock64();
+      p_comp += c2 - c1;
+#endif
       if (++s == S) { s = 0; ph ^= 1; }
       if (++g == G) {
         // the column block is complete as far as this CTA is concerned
         g = 0;
+#ifdef QMM_W4_PROFILE
+        long long f0 = clock64();
         flush(c);
+        p_flush += clock64() - f0;
+#else
+        flush(c);
+#endif
         ++c;
 #pragma unroll
         for (int j = 0; j < 2; ++j)
@@ -480,7 +523,24 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
             for (int i = 0; i < 4; ++i) yacc[j][mt][i] = 0.f;
       }
     }
+#ifdef QMM_W4_PROFILE
+    unsigned long long p_loop_end = dev::globaltimer_ns();
+    long long f0 = clock64();
+#endif
     if (ok && n_units > 0 && g != 0) flush(c);
+#ifdef QMM_W4_PROFILE
+    p_flush += clock64() - f0;
+    if (warp == 0 && lane == 0 && blockIdx.x < 2048) {
+      unsigned long long* o = g_w4_prof + blockIdx.x * 8;
+      o[0] = p_start; o[1] = p_first; o[2] = p_loop_end; o[3] = dev::globaltimer_ns();
+      o[4] = p_wait; o[5] = p_comp; o[6] = p_flush; { unsigned smid; asm("mov.u32 %0, %%smid;" : "=r"(smid)); o[7] = n_units | ((unsigned long long)smid << 32); }
+      unsigned long long* sp = g_w4_span + (launch_id & 63) * 4;
+      atomicMin(sp + 0, p_start);
+      atomicMax(sp + 1, p_first);
+      atomicMax(sp + 2, p_loop_end);
+      atomicMax(sp + 3, dev::globaltimer_ns());
+    }
+#endif
   }
 }
 
@@ -508,8 +568,14 @@ static int launch(const CUtensorMap& wmap, const CUtensorMap& xmap, const uint16
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
+#ifdef QMM_W4_PROFILE
+  static int launch_id = 0;
+  QMM_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, wmap, xmap, scales, zeros, y, ws_partial, ws_counter, M,
+                                  N, K, G, U, max_slots, static_weights, status, launch_id++));
+#else
   QMM_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, wmap, xmap, scales, zeros, y, ws_partial, ws_counter, M,
                                   N, K, G, U, max_slots, static_weights, status));
+#endif
   return QMM_OK;
 }
 
@@ -525,6 +591,12 @@ static int slots_for(int G, int U, int P) {
   // a column block of G units is shared by at most ceil(G*P/U) + 1 CTAs
   return static_cast<int>((static_cast<long long>(G) * P + U - 1) / U) + 1;
 }
+// One arrival counter per (column block, consumer warp).  The counters occupy a
+// fixed-size header of the workspace so that calls with different shapes can
+// share one workspace: only this header has to be zero between calls, and every
+// call leaves it zero.
+constexpr int kMaxColBlocks = 2048;
+static size_t counter_bytes(int /*C*/) { return static_cast<size_t>(kMaxColBlocks) * kConsumerWarps * sizeof(int); }
 static int rows_padded(int M) { return M <= 8 ? 8 : (M <= 16 ? 16 : 32); }
 static int col_blocks(int64_t N) { return static_cast<int>((N + kColsPerBlock - 1) / kColsPerBlock); }
 
@@ -537,14 +609,14 @@ static int run(const char* name, const uint16_t* x, const uint8_t* wq, const uin
   const int U = G * C;
   const int P = grid_size(U, static_cast<int>(M));
   const int slots = slots_for(G, U, P);
-  const size_t counters = (static_cast<size_t>(C) * sizeof(int) + 255) / 256 * 256;
+  const size_t counters = counter_bytes(C);
   int* ws_counter = static_cast<int*>(workspace);
   float* ws_partial = reinterpret_cast<float*>(static_cast<uint8_t*>(workspace) + counters);
 
   CUtensorMap wmap, xmap;
   if (int rc = make_tensor_map_2d(&wmap, wq, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1,
                                   static_cast<uint64_t>(K / 2), static_cast<uint64_t>(N),
-                                  static_cast<uint64_t>(N), kRowsPerUnit, 128,
+                                  static_cast<uint64_t>(N), kRowsPerHalf, 128,
                                   CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
   // activations: [M, K] bf16, one box = (8, 16 or 32 rows) x one 128-k group, rows past M read as zero
@@ -578,7 +650,8 @@ static int check_args(const char* name, const void* x, const void* wq, const voi
   QMM_REQUIRE(N >= 128 && N % 128 == 0 && K >= kGroup && K % kGroup == 0, QMM_ERR_UNSUPPORTED,
               "%s: N (%lld) and K (%lld) must be positive multiples of 128", name, (long long)N,
               (long long)K);
-  QMM_REQUIRE(N * (K / kGroup) < (1ll << 30), QMM_ERR_UNSUPPORTED, "%s: problem too large", name);
+  QMM_REQUIRE(N * (K / kGroup) < (1ll << 30) && N <= static_cast<int64_t>(kMaxColBlocks) * kColsPerBlock,
+              QMM_ERR_UNSUPPORTED, "%s: problem too large", name);
   QMM_REQUIRE(aligned(x, 16) && aligned(wq, 16) && aligned(scales, 16) && aligned(zeros, 16) &&
                   aligned(y, 4),
               QMM_ERR_INVALID_ARGUMENT, "%s: tensors must be 16-byte aligned", name);
@@ -622,6 +695,20 @@ static int static_scratch_address(void** out) {
 }  // namespace w4
 }  // namespace qmm
 
+#ifdef QMM_W4_PROFILE
+extern "C" __attribute__((visibility("default"))) int qmm_w4_profile_read(unsigned long long* dst, int n) {
+  return (int)cudaMemcpyFromSymbol(dst, qmm::w4::g_w4_prof, sizeof(unsigned long long) * n);
+}
+extern "C" __attribute__((visibility("default"))) int qmm_w4_span_read(unsigned long long* dst) {
+  return (int)cudaMemcpyFromSymbol(dst, qmm::w4::g_w4_span, sizeof(unsigned long long) * 256);
+}
+extern "C" __attribute__((visibility("default"))) int qmm_w4_span_reset() {
+  unsigned long long h[256];
+  for (int i = 0; i < 64; ++i) { h[i * 4] = ~0ull; h[i * 4 + 1] = h[i * 4 + 2] = h[i * 4 + 3] = 0; }
+  return (int)cudaMemcpyToSymbol(qmm::w4::g_w4_span, h, sizeof(h));
+}
+#endif
+
 extern "C" {
 
 size_t qmm_w4a16_g128_workspace_bytes(int64_t M, int64_t N, int64_t K) {
@@ -632,7 +719,7 @@ size_t qmm_w4a16_g128_workspace_bytes(int64_t M, int64_t N, int64_t K) {
   const int U = G * C;
   const int P = grid_size(U, static_cast<int>(M));
   const int slots = slots_for(G, U, P);
-  const size_t counters = (static_cast<size_t>(C) * sizeof(int) + 255) / 256 * 256;
+  const size_t counters = counter_bytes(C);
   return counters + static_cast<size_t>(C) * slots * rows_padded(static_cast<int>(M)) * kColsPerBlock *
                         sizeof(float);
 }
@@ -682,8 +769,7 @@ int qmm_w4a16_g128_static_scratch(const uint16_t* x, const uint8_t* wq, const ui
   void* scratch = nullptr;
   if (int rc = static_scratch_address(&scratch)) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  const size_t counters = (static_cast<size_t>(col_blocks(N)) * sizeof(int) + 255) / 256 * 256;
-  QMM_CUDA_TRY(cudaMemsetAsync(scratch, 0, counters, st));
+  QMM_CUDA_TRY(cudaMemsetAsync(scratch, 0, counter_bytes(col_blocks(N)), st));
   // A wait that gives up is reported through the library's status word when
   // that word exists already (any other entry point, or qmm_device_status(),
   // creates it); this call will not create it, because that allocates.
