@@ -1,0 +1,577 @@
+// The non-matmul operators of a Llama-shaped decode step (bf16 activations):
+// embedding row gather, (residual add +) RMSNorm, rotary embedding, SwiGLU
+// gating, grouped-query decode attention over a read-only KV cache, and a
+// bf16 matmul for a few activation rows (the unquantized lm_head).
+// They are small next to the int4 linears; each is one launch, written to be
+// captured in a CUDA graph together with the quantized matmuls.
+//
+// Reference semantics kept where the reference pins them: take-rows wraps
+// negative indices and fills out-of-range rows
+// (README.md:200-202, core/mps_executable.mm:1149-1160); the new K/V rows are
+// returned separately and the cache is a read-only input, because the
+// reference has no buffer donation (api/pjrt_api.cc:310) and a
+// dynamic_update_slice of the whole cache per token would copy 2 GB.
+#include <math.h>
+
+#include "common.cuh"
+
+namespace qmm {
+namespace dec {
+
+__device__ __forceinline__ float2 bf2_to_f2(uint32_t v) {
+  return make_float2(__uint_as_float(v << 16), __uint_as_float(v & 0xFFFF0000u));
+}
+
+// ---------------------------------------------------------------------------
+// take rows: out[b, :] = table[wrap(ids[b]), :] or fill
+// ---------------------------------------------------------------------------
+__global__ void take_rows_kernel(const uint16_t* __restrict__ table, const int32_t* __restrict__ ids,
+                                 uint16_t* __restrict__ out, int V, int D, uint16_t fill_bits) {
+  const int b = blockIdx.x;
+  int id = ids[b];
+  if (id < 0) id += V;  // negative indices count from the end
+  const bool valid = id >= 0 && id < V;
+  const uint4* src = reinterpret_cast<const uint4*>(table + static_cast<size_t>(valid ? id : 0) * D);
+  uint4* dst = reinterpret_cast<uint4*>(out + static_cast<size_t>(b) * D);
+  const uint32_t f2 = fill_bits | (static_cast<uint32_t>(fill_bits) << 16);
+  for (int i = threadIdx.x; i < D / 8; i += blockDim.x) dst[i] = valid ? __ldg(src + i) : make_uint4(f2, f2, f2, f2);
+}
+
+// ---------------------------------------------------------------------------
+// h = x (+ r);  y = bf16( float(bf16(h * rsqrt(mean(h^2) + eps))) * w )
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+add_rmsnorm_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ r,
+                   const uint16_t* __restrict__ w, uint16_t* __restrict__ sum_out,
+                   uint16_t* __restrict__ norm_out, int D, float eps) {
+  const int row = blockIdx.x;
+  const uint32_t* xp = reinterpret_cast<const uint32_t*>(x + static_cast<size_t>(row) * D);
+  const uint32_t* rp = r ? reinterpret_cast<const uint32_t*>(r + static_cast<size_t>(row) * D) : nullptr;
+  const uint32_t* wp = reinterpret_cast<const uint32_t*>(w);
+  extern __shared__ float hbuf[];  // D floats: the (rounded) sum row
+  __shared__ float red[8];
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < D / 2; i += blockDim.x) {
+    float2 a = bf2_to_f2(xp[i]);
+    if (rp) {
+      const float2 b = bf2_to_f2(rp[i]);
+      // the residual stream is kept in bf16: round the sum once
+      const uint32_t s = dev::pack_bf16x2(a.x + b.x, a.y + b.y);
+      if (sum_out) reinterpret_cast<uint32_t*>(sum_out + static_cast<size_t>(row) * D)[i] = s;
+      a = bf2_to_f2(s);
+    }
+    hbuf[2 * i] = a.x;
+    hbuf[2 * i + 1] = a.y;
+    ss += a.x * a.x + a.y * a.y;
+  }
+  for (int off = 16; off >= 1; off >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, off);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
+  __syncthreads();
+  float tot = 0.f;
+  for (int i = 0; i < (blockDim.x >> 5); ++i) tot += red[i];
+  const float inv = rsqrtf(tot / static_cast<float>(D) + eps);
+  for (int i = threadIdx.x; i < D / 2; i += blockDim.x) {
+    const float2 g = bf2_to_f2(wp[i]);
+    const float2 n = bf2_to_f2(dev::pack_bf16x2(hbuf[2 * i] * inv, hbuf[2 * i + 1] * inv));
+    reinterpret_cast<uint32_t*>(norm_out + static_cast<size_t>(row) * D)[i] = dev::pack_bf16x2(n.x * g.x, n.y * g.y);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// rotary embedding, rotate-half pairing (i, i + hd/2), in place on q and k
+// ---------------------------------------------------------------------------
+__global__ void rope_kernel(uint16_t* __restrict__ q, uint16_t* __restrict__ k,
+                            const int32_t* __restrict__ pos, int Hq, int Hkv, int hd, float theta) {
+  const int b = blockIdx.x;
+  const int half = hd / 2;
+  const float p = static_cast<float>(pos[b]);
+  const int total = (Hq + Hkv) * half;
+  for (int i = threadIdx.x; i < total; i += blockDim.x) {
+    const int h = i / half, j = i % half;
+    uint16_t* base = (h < Hq) ? q + (static_cast<size_t>(b) * Hq + h) * hd
+                              : k + (static_cast<size_t>(b) * Hkv + (h - Hq)) * hd;
+    const float freq = powf(theta, -2.0f * static_cast<float>(j) / static_cast<float>(hd));
+    float sn, cs;
+    sincosf(p * freq, &sn, &cs);
+    const float a = dev::bf16_bits_to_float(base[j]), c = dev::bf16_bits_to_float(base[j + half]);
+    base[j] = dev::float_to_bf16_bits(a * cs - c * sn);
+    base[j + half] = dev::float_to_bf16_bits(c * cs + a * sn);
+  }
+}
+
+// ---------------------------------------------------------------------------
+// out = bf16( silu(gate) * up ), silu(x) = x * sigmoid(x); gate/up may be the
+// two halves of one [B, 2F] buffer (ld = row stride in elements)
+// ---------------------------------------------------------------------------
+__global__ void silu_mul_kernel(const uint16_t* __restrict__ gate, const uint16_t* __restrict__ up,
+                                uint16_t* __restrict__ out, int F, long long ld_in) {
+  const int row = blockIdx.y;
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= F / 2) return;
+  const float2 g = bf2_to_f2(reinterpret_cast<const uint32_t*>(gate + static_cast<size_t>(row) * ld_in)[i]);
+  const float2 u = bf2_to_f2(reinterpret_cast<const uint32_t*>(up + static_cast<size_t>(row) * ld_in)[i]);
+  // the activation is rounded to bf16 before the product, as an un-fused bf16 graph does
+  const float2 s = bf2_to_f2(dev::pack_bf16x2(g.x / (1.f + __expf(-g.x)), g.y / (1.f + __expf(-g.y))));
+  reinterpret_cast<uint32_t*>(out + static_cast<size_t>(row) * F)[i] = dev::pack_bf16x2(s.x * u.x, s.y * u.y);
+}
+
+// ---------------------------------------------------------------------------
+// decode attention, grouped-query, head dim 128.
+//   cache k/v: [B, Hkv, L, 128] bf16 (read only); new row knew/vnew [B, Hkv, 128]
+//   q [B, Hq, 128] -> out [B, Hq, 128]; the new row is the (L+1)-th key.
+// Pass 1 (attn_partial): one CTA per (b, kv head, 128-row chunk of the cache).
+// TMA brings the K and V chunks (two 64-wide boxes each, 128-byte swizzle);
+// thread r owns cache row r for the scores of the R = Hq/Hkv query heads that
+// share the kv head; softmax statistics per chunk; thread pairs own two output
+// dims for P.V.  Pass 2 (attn_combine) merges the chunks and the new row.
+// ---------------------------------------------------------------------------
+constexpr int kHd = 128, kChunk = 128, kMaxR = 8;
+
+template <int R>
+__global__ void __launch_bounds__(128)
+attn_partial_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
+                    const uint16_t* __restrict__ q, float* __restrict__ part, int Hq, int Hkv, int L,
+                    int nchunks, float scale, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint8_t* ks = smem;              // 2 boxes x 16 KB
+  uint8_t* vs = smem + 32768;      // 2 boxes x 16 KB
+  float* qs = reinterpret_cast<float*>(smem + 65536);          // [R][128]
+  float* ps = qs + R * kHd;                                    // [128 rows][R] probabilities
+  float* red = ps + kChunk * R;                                // [4 warps][R]
+  float* ored = red + 4 * R;                                   // [64 d pairs][R][2] from the upper row half
+  uint64_t* bars = reinterpret_cast<uint64_t*>(ored + 64 * R * 2);
+
+  const int chunk = blockIdx.x, bh = blockIdx.y;  // bh = b * Hkv + kvh
+  const int b = bh / Hkv, kvh = bh % Hkv;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int row0 = chunk * kChunk;
+
+  if (tid == 0) {
+    dev::mbar_init(&bars[0], 1);
+    dev::mbar_init(&bars[1], 1);
+    dev::fence_mbar_init();
+  }
+  __syncthreads();
+  if (tid == 0) {
+    const int grow = bh * L + row0;  // row in the [B*Hkv*L, 128] view
+    dev::mbar_expect_tx(&bars[0], 32768);
+    dev::tma_load_2d(ks, &kmap, &bars[0], 0, grow);
+    dev::tma_load_2d(ks + 16384, &kmap, &bars[0], 64, grow);
+    dev::mbar_expect_tx(&bars[1], 32768);
+    dev::tma_load_2d(vs, &vmap, &bars[1], 0, grow);
+    dev::tma_load_2d(vs + 16384, &vmap, &bars[1], 64, grow);
+  }
+  // q of the R heads of this kv head, pre-multiplied by the softmax scale
+  for (int i = tid; i < R * kHd; i += 128) {
+    const int h = i / kHd, d = i % kHd;
+    qs[i] = dev::bf16_bits_to_float(q[(static_cast<size_t>(b) * Hq + kvh * R + h) * kHd + d]) * scale;
+  }
+  __syncthreads();
+  if (!dev::mbar_wait(&bars[0], 0, status, 31)) return;
+
+  // scores: thread = cache row
+  float sc[R];
+#pragma unroll
+  for (int h = 0; h < R; ++h) sc[h] = 0.f;
+  const int r = tid;
+#pragma unroll
+  for (int box = 0; box < 2; ++box) {
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      const uint4 kv = *reinterpret_cast<const uint4*>(ks + box * 16384 + r * 128 + ((c ^ (r & 7)) << 4));
+      const uint32_t w[4] = {kv.x, kv.y, kv.z, kv.w};
+      const int d0 = box * 64 + c * 8;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 kk = bf2_to_f2(w[j]);
+#pragma unroll
+        for (int h = 0; h < R; ++h) {
+          const float2 qq = *reinterpret_cast<const float2*>(qs + h * kHd + d0 + 2 * j);
+          sc[h] = fmaf(kk.x, qq.x, fmaf(kk.y, qq.y, sc[h]));
+        }
+      }
+    }
+  }
+  const bool valid = row0 + r < L;
+  // chunk max per head
+  float mx[R];
+#pragma unroll
+  for (int h = 0; h < R; ++h) {
+    float v = valid ? sc[h] : -INFINITY;
+    for (int off = 16; off >= 1; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, off));
+    if (lane == 0) red[warp * R + h] = v;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int h = 0; h < R; ++h) mx[h] = fmaxf(fmaxf(red[h], red[R + h]), fmaxf(red[2 * R + h], red[3 * R + h]));
+  __syncthreads();
+  float sm[R];
+#pragma unroll
+  for (int h = 0; h < R; ++h) {
+    const float p = valid ? __expf(sc[h] - mx[h]) : 0.f;
+    ps[r * R + h] = p;
+    float v = p;
+    for (int off = 16; off >= 1; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
+    if (lane == 0) red[warp * R + h] = v;
+  }
+  __syncthreads();
+#pragma unroll
+  for (int h = 0; h < R; ++h) sm[h] = red[h] + red[R + h] + red[2 * R + h] + red[3 * R + h];
+
+  // P.V: thread = (d pair, row half)
+  if (!dev::mbar_wait(&bars[1], 0, status, 32)) return;
+  const int dp = tid & 63, half = tid >> 6;
+  const int box = dp >> 5, cc = (dp & 31) >> 2, within = (dp & 3) * 4;  // 16-byte chunk and byte offset in it
+  float2 o[R];
+#pragma unroll
+  for (int h = 0; h < R; ++h) o[h] = make_float2(0.f, 0.f);
+  for (int i = 0; i < 64; ++i) {
+    const int l = half * 64 + i;
+    const uint32_t vv = *reinterpret_cast<const uint32_t*>(vs + box * 16384 + l * 128 + ((cc ^ (l & 7)) << 4) + within);
+    const float2 vf = bf2_to_f2(vv);
+#pragma unroll
+    for (int h = 0; h < R; ++h) {
+      const float p = ps[l * R + h];
+      o[h].x = fmaf(p, vf.x, o[h].x);
+      o[h].y = fmaf(p, vf.y, o[h].y);
+    }
+  }
+  if (half == 1) {
+#pragma unroll
+    for (int h = 0; h < R; ++h) *reinterpret_cast<float2*>(ored + (dp * R + h) * 2) = o[h];
+  }
+  __syncthreads();
+  if (half == 0) {
+    // part layout: [bh][chunk][head][2 + 128] = (max, sum, o[128])
+#pragma unroll
+    for (int h = 0; h < R; ++h) {
+      const float2 u = *reinterpret_cast<const float2*>(ored + (dp * R + h) * 2);
+      float* dst = part + ((static_cast<size_t>(bh) * nchunks + chunk) * R + h) * (kHd + 2);
+      *reinterpret_cast<float2*>(dst + 2 + 2 * dp) = make_float2(o[h].x + u.x, o[h].y + u.y);
+      if (dp == 0) {
+        dst[0] = mx[h];
+        dst[1] = sm[h];
+      }
+    }
+  }
+}
+
+// one block per (b, q head): merge the chunks and the new key/value row
+__global__ void __launch_bounds__(128)
+attn_combine_kernel(const float* __restrict__ part, const uint16_t* __restrict__ q,
+                    const uint16_t* __restrict__ knew, const uint16_t* __restrict__ vnew,
+                    uint16_t* __restrict__ out, int Hq, int Hkv, int R, int nchunks, float scale) {
+  const int b = blockIdx.x / Hq, hq = blockIdx.x % Hq;
+  const int kvh = hq / R, h = hq % R;
+  const int bh = b * Hkv + kvh;
+  const int d = threadIdx.x;
+  __shared__ float red[4];
+  // score of the new row
+  const float qd = dev::bf16_bits_to_float(q[(static_cast<size_t>(b) * Hq + hq) * kHd + d]) * scale;
+  const float kd = dev::bf16_bits_to_float(knew[static_cast<size_t>(bh) * kHd + d]);
+  float s = qd * kd;
+  for (int off = 16; off >= 1; off >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, off);
+  if ((d & 31) == 0) red[d >> 5] = s;
+  __syncthreads();
+  const float s_new = red[0] + red[1] + red[2] + red[3];
+  float m = s_new;
+  const float* base = part + (static_cast<size_t>(bh) * nchunks * R + h) * (kHd + 2);
+  const size_t stride = static_cast<size_t>(R) * (kHd + 2);
+  for (int c = 0; c < nchunks; ++c) m = fmaxf(m, base[c * stride]);
+  float denom = __expf(s_new - m);
+  float acc = denom * dev::bf16_bits_to_float(vnew[static_cast<size_t>(bh) * kHd + d]);
+  for (int c = 0; c < nchunks; ++c) {
+    const float* p = base + c * stride;
+    const float wgt = __expf(p[0] - m);
+    denom = fmaf(wgt, p[1], denom);
+    acc = fmaf(wgt, p[2 + d], acc);
+  }
+  out[(static_cast<size_t>(b) * Hq + hq) * kHd + d] = dev::float_to_bf16_bits(acc / denom);
+}
+
+// ---------------------------------------------------------------------------
+// y[M,N] = x[M,K] @ w[K,N], bf16 in, f32 accumulate, bf16 out, M <= 16.
+// HBM-bound on w (read once).  One CTA owns 128 columns and all of K; a
+// producer thread streams 64-k tiles (two 64-column boxes, 128-byte swizzle)
+// plus the matching activation tile; four consumer warps own 32 columns each:
+// ldmatrix.trans makes the [k][n] tile the 16-row MMA operand, the activations
+// are the 8-column operand (mma.sync.m16n8k16).
+// ---------------------------------------------------------------------------
+namespace gemv {
+constexpr int BN = 128, BK = 64, kStages = 5;
+constexpr int kWBytes = BK * BN * 2;  // 16 KB: two [64 k][64 n] boxes
+constexpr int kXBytes = 16 * BK * 2;  // 2 KB: [16 rows][64 k]
+constexpr int kStage = kWBytes + kXBytes;  // 18 KB, a multiple of 1024
+constexpr int kSmem = kStages * kStage + 1024 + 1024;
+
+__device__ __forceinline__ void ldsm_x4_trans(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
+      "{%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+template <int MT>
+__global__ void __launch_bounds__(160)
+bf16_small_m_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
+                    uint16_t* __restrict__ y, int M, int N, int K, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~static_cast<uintptr_t>(1023));
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * kStage);
+  uint64_t* empty = full + kStages;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n0 = blockIdx.x * BN;
+  const int kblocks = K / BK;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      dev::mbar_init(&full[s], 1);
+      dev::mbar_init(&empty[s], 4);
+    }
+    dev::fence_mbar_init();
+  }
+  __syncthreads();
+  if (warp == 4) {
+    if (lane == 0) {
+      const uint64_t policy = dev::policy_evict_first();
+      int s = 0;
+      uint32_t ph = 0;
+      for (int kb = 0; kb < kblocks; ++kb) {
+        if (!dev::mbar_wait(&empty[s], ph ^ 1, status, 41)) break;
+        uint8_t* st = smem + s * kStage;
+        dev::mbar_expect_tx(&full[s], kWBytes + MT * 8 * BK * 2);
+        dev::tma_load_2d_hint(st, &wmap, &full[s], n0, kb * BK, policy);
+        dev::tma_load_2d_hint(st + kWBytes / 2, &wmap, &full[s], n0 + 64, kb * BK, policy);
+        dev::tma_load_2d(st + kWBytes, &xmap, &full[s], kb * BK, 0);
+        if (++s == kStages) { s = 0; ph ^= 1; }
+      }
+    }
+    return;
+  }
+  // consumers: warp w owns columns [32w, 32w+32) = box w/2, 16-byte chunks 4(w%2) .. 4(w%2)+3
+  const int g8 = lane >> 2, t4 = lane & 3;
+  float acc[2][MT][4];
+#pragma unroll
+  for (int j = 0; j < 2; ++j)
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) acc[j][mt][i] = 0.f;
+  // ldmatrix.x4.trans over a [16 k][16 n] block: matrices (k 0-7, n 0-7), (k 0-7, n 8-15),
+  // (k 8-15, n 0-7), (k 8-15, n 8-15) -> a0..a3 of the 16(n) x 16(k) operand
+  const int lrow = (lane & 7) + ((lane >> 4) << 3);  // k row inside the 16-k slab
+  const int lchunk = (lane >> 3) & 1;                // which 8-column half of the 16 columns
+  int s = 0;
+  uint32_t ph = 0;
+  for (int kb = 0; kb < kblocks; ++kb) {
+    if (!dev::mbar_wait(&full[s], ph, status, 42)) return;
+    const uint32_t st = dev::smem_u32(smem + s * kStage);
+    const uint32_t wbase = st + (warp >> 1) * (kWBytes / 2);
+    const uint32_t xbase = st + kWBytes;
+#pragma unroll
+    for (int ks = 0; ks < BK / 16; ++ks) {
+      // activations: B fragment b0 = x[m = g8][k = 16 ks + 2 t4 .. +1], b1 = same + 8
+      uint32_t xb[MT][2];
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        // the activation tile is swizzled like the weights: 16-byte chunk c of row m sits at c ^ (m & 7)
+        const uint32_t xrow = xbase + (mt * 8 + g8) * (BK * 2) + t4 * 4;
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(xb[mt][0]) : "r"(xrow + (((2 * ks) ^ g8) << 4)));
+        asm volatile("ld.shared.u32 %0, [%1];" : "=r"(xb[mt][1]) : "r"(xrow + (((2 * ks + 1) ^ g8) << 4)));
+      }
+#pragma unroll
+      for (int j = 0; j < 2; ++j) {
+        const int krow = ks * 16 + lrow;
+        const int chunk = (warp & 1) * 4 + j * 2 + lchunk;
+        uint32_t a[4];
+        ldsm_x4_trans(wbase + krow * 128 + ((chunk ^ (krow & 7)) << 4), a);
+        // matrices arrive as (k lo, n lo), (k lo, n hi), (k hi, n lo), (k hi, n hi); the MMA wants
+        // a0 = (n lo, k lo), a1 = (n hi, k lo), a2 = (n lo, k hi), a3 = (n hi, k hi): same order
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) mma_bf16(acc[j][mt], a, xb[mt][0], xb[mt][1]);
+      }
+    }
+    __syncwarp();
+    if (lane == 0) dev::mbar_arrive(&empty[s]);
+    if (++s == kStages) { s = 0; ph ^= 1; }
+  }
+  // D fragment: d0,d1 = (n = g8, m = 2 t4, 2 t4 + 1), d2,d3 = (n = g8 + 8, same m)
+#pragma unroll
+  for (int j = 0; j < 2; ++j)
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int n = n0 + warp * 32 + j * 16 + g8 + ((i >> 1) << 3);
+        const int m = mt * 8 + 2 * t4 + (i & 1);
+        if (m < M && n < N) y[static_cast<size_t>(m) * N + n] = dev::float_to_bf16_bits(acc[j][mt][i]);
+      }
+}
+}  // namespace gemv
+
+}  // namespace dec
+}  // namespace qmm
+
+extern "C" {
+
+int qmm_take_rows_bf16(const uint16_t* table, const int32_t* ids, uint16_t* out, int64_t V, int64_t D,
+                       int64_t B, uint16_t fill_bits, void* stream) {
+  using namespace qmm;
+  QMM_REQUIRE(table && ids && out, QMM_ERR_INVALID_ARGUMENT, "qmm_take_rows_bf16: null pointer");
+  QMM_REQUIRE(V > 0 && D > 0 && D % 8 == 0 && B >= 0 && V < (1ll << 31), QMM_ERR_INVALID_ARGUMENT,
+              "qmm_take_rows_bf16: bad shape (D must be a multiple of 8)");
+  QMM_REQUIRE(aligned(table, 16) && aligned(out, 16), QMM_ERR_INVALID_ARGUMENT, "qmm_take_rows_bf16: 16-byte alignment");
+  if (B == 0) return QMM_OK;
+  dec::take_rows_kernel<<<(unsigned)B, 256, 0, (cudaStream_t)stream>>>(table, ids, out, (int)V, (int)D, fill_bits);
+  QMM_CHECK_LAUNCH("take_rows_kernel");
+  return QMM_OK;
+}
+
+int qmm_add_rmsnorm_bf16(const uint16_t* x, const uint16_t* residual, const uint16_t* weight, uint16_t* sum_out,
+                         uint16_t* norm_out, int64_t B, int64_t D, float eps, void* stream) {
+  using namespace qmm;
+  QMM_REQUIRE(x && weight && norm_out, QMM_ERR_INVALID_ARGUMENT, "qmm_add_rmsnorm_bf16: null pointer");
+  QMM_REQUIRE(B >= 0 && D > 0 && D % 2 == 0 && D <= 16384, QMM_ERR_UNSUPPORTED,
+              "qmm_add_rmsnorm_bf16: D must be even and <= 16384");
+  if (B == 0) return QMM_OK;
+  static bool configured = false;
+  if (!configured) {
+    QMM_CUDA_TRY(cudaFuncSetAttribute(dec::add_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536));
+    configured = true;
+  }
+  dec::add_rmsnorm_kernel<<<(unsigned)B, 256, D * sizeof(float), (cudaStream_t)stream>>>(x, residual, weight, sum_out,
+                                                                                       norm_out, (int)D, eps);
+  QMM_CHECK_LAUNCH("add_rmsnorm_kernel");
+  return QMM_OK;
+}
+
+int qmm_rope_bf16(uint16_t* q, uint16_t* k, const int32_t* positions, int64_t B, int64_t Hq, int64_t Hkv,
+                  int64_t head_dim, float theta, void* stream) {
+  using namespace qmm;
+  QMM_REQUIRE(q && k && positions, QMM_ERR_INVALID_ARGUMENT, "qmm_rope_bf16: null pointer");
+  QMM_REQUIRE(B >= 0 && Hq > 0 && Hkv > 0 && head_dim > 0 && head_dim % 2 == 0, QMM_ERR_INVALID_ARGUMENT,
+              "qmm_rope_bf16: bad shape");
+  if (B == 0) return QMM_OK;
+  dec::rope_kernel<<<(unsigned)B, 256, 0, (cudaStream_t)stream>>>(q, k, positions, (int)Hq, (int)Hkv, (int)head_dim, theta);
+  QMM_CHECK_LAUNCH("rope_kernel");
+  return QMM_OK;
+}
+
+int qmm_silu_mul_bf16(const uint16_t* gate, const uint16_t* up, uint16_t* out, int64_t B, int64_t F, int64_t ld_in,
+                      void* stream) {
+  using namespace qmm;
+  QMM_REQUIRE(gate && up && out, QMM_ERR_INVALID_ARGUMENT, "qmm_silu_mul_bf16: null pointer");
+  QMM_REQUIRE(B >= 0 && F > 0 && F % 2 == 0 && ld_in >= F && ld_in % 2 == 0 && B <= 65535, QMM_ERR_INVALID_ARGUMENT,
+              "qmm_silu_mul_bf16: bad shape");
+  if (B == 0) return QMM_OK;
+  dim3 grid((unsigned)((F / 2 + 255) / 256), (unsigned)B);
+  dec::silu_mul_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(gate, up, out, (int)F, (long long)ld_in);
+  QMM_CHECK_LAUNCH("silu_mul_kernel");
+  return QMM_OK;
+}
+
+size_t qmm_attention_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t L) {
+  if (B <= 0 || Hq <= 0 || Hkv <= 0 || L < 0 || Hq % Hkv) return 0;
+  const int64_t nchunks = (L + qmm::dec::kChunk - 1) / qmm::dec::kChunk;
+  return static_cast<size_t>(B * Hq * (nchunks > 0 ? nchunks : 1)) * (qmm::dec::kHd + 2) * sizeof(float);
+}
+
+int qmm_attention_decode_bf16(const uint16_t* q, const uint16_t* kcache, const uint16_t* vcache,
+                              const uint16_t* knew, const uint16_t* vnew, uint16_t* out, int64_t B, int64_t Hq,
+                              int64_t Hkv, int64_t L, int64_t head_dim, float scale, void* workspace,
+                              size_t workspace_bytes, void* stream) {
+  using namespace qmm;
+  using namespace qmm::dec;
+  QMM_REQUIRE(q && knew && vnew && out && (L == 0 || (kcache && vcache)), QMM_ERR_INVALID_ARGUMENT,
+              "qmm_attention_decode_bf16: null pointer");
+  QMM_REQUIRE(head_dim == kHd, QMM_ERR_UNSUPPORTED, "qmm_attention_decode_bf16: head_dim must be 128");
+  QMM_REQUIRE(B > 0 && Hkv > 0 && Hq % Hkv == 0 && L >= 0 && B * Hkv <= 65535 && B * Hkv * L < (1ll << 31),
+              QMM_ERR_INVALID_ARGUMENT, "qmm_attention_decode_bf16: bad shape");
+  const int R = static_cast<int>(Hq / Hkv);
+  QMM_REQUIRE(R == 1 || R == 2 || R == 4 || R == 8, QMM_ERR_UNSUPPORTED,
+              "qmm_attention_decode_bf16: %d query heads per kv head (supported: 1, 2, 4, 8)", R);
+  const int nchunks = static_cast<int>((L + kChunk - 1) / kChunk);
+  const size_t need = qmm_attention_decode_workspace_bytes(B, Hq, Hkv, L);
+  QMM_REQUIRE(workspace && workspace_bytes >= need, QMM_ERR_WORKSPACE,
+              "qmm_attention_decode_bf16: %zu bytes of workspace required", need);
+  if (int st = read_device_status())
+    return set_error(QMM_ERR_TIMEOUT, "a previous kernel gave up waiting (status word 0x%x)", st);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  float* part = static_cast<float*>(workspace);
+  if (nchunks > 0) {
+    CUtensorMap kmap, vmap;
+    const uint64_t rows = static_cast<uint64_t>(B * Hkv * L);
+    if (int rc = make_tensor_map_2d(&kmap, kcache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows, kHd, kHd * 2, kChunk, 64,
+                                    CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+    if (int rc = make_tensor_map_2d(&vmap, vcache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows, kHd, kHd * 2, kChunk, 64,
+                                    CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+    const size_t smem = 65536 + (R * kHd + kChunk * R + 4 * R + 64 * R * 2) * sizeof(float) + 64 + 1024;
+    dim3 grid(nchunks, static_cast<unsigned>(B * Hkv));
+#define QMM_ATTN(RR)                                                                                         \
+  {                                                                                                          \
+    static bool configured = false;                                                                          \
+    if (!configured) {                                                                                       \
+      QMM_CUDA_TRY(cudaFuncSetAttribute(attn_partial_kernel<RR>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                                        (int)(65536 + (RR * kHd + kChunk * RR + 4 * RR + 64 * RR * 2) * 4 + 64 + 1024))); \
+      configured = true;                                                                                     \
+    }                                                                                                        \
+    attn_partial_kernel<RR><<<grid, 128, smem, s>>>(kmap, vmap, q, part, (int)Hq, (int)Hkv, (int)L, nchunks, scale, \
+                                                    device_status_word());                                   \
+  }
+    if (R == 1) QMM_ATTN(1) else if (R == 2) QMM_ATTN(2) else if (R == 4) QMM_ATTN(4) else QMM_ATTN(8)
+#undef QMM_ATTN
+    QMM_CHECK_LAUNCH("attn_partial_kernel");
+  }
+  attn_combine_kernel<<<static_cast<unsigned>(B * Hq), 128, 0, s>>>(part, q, knew, vnew, out, (int)Hq, (int)Hkv, R, nchunks,
+                                                                    scale);
+  QMM_CHECK_LAUNCH("attn_combine_kernel");
+  return QMM_OK;
+}
+
+int qmm_bf16_matmul_small_m(const uint16_t* x, const uint16_t* w, uint16_t* y, int64_t M, int64_t N, int64_t K,
+                            void* stream) {
+  using namespace qmm;
+  using namespace qmm::dec::gemv;
+  QMM_REQUIRE(x && w && y, QMM_ERR_INVALID_ARGUMENT, "qmm_bf16_matmul_small_m: null pointer");
+  QMM_REQUIRE(M >= 1 && M <= 16, QMM_ERR_UNSUPPORTED, "qmm_bf16_matmul_small_m: covers 1 <= M <= 16, got %lld",
+              (long long)M);
+  QMM_REQUIRE(N >= 64 && N % 64 == 0 && K >= BK && K % BK == 0 && N < (1ll << 30) && K < (1ll << 30),
+              QMM_ERR_UNSUPPORTED, "qmm_bf16_matmul_small_m: N and K must be positive multiples of 64");
+  QMM_REQUIRE(aligned(x, 16) && aligned(w, 16), QMM_ERR_INVALID_ARGUMENT, "qmm_bf16_matmul_small_m: 16-byte alignment");
+  if (int st = read_device_status())
+    return set_error(QMM_ERR_TIMEOUT, "a previous kernel gave up waiting (status word 0x%x)", st);
+  CUtensorMap wmap, xmap;
+  if (int rc = make_tensor_map_2d(&wmap, w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)K, (uint64_t)N, (uint64_t)N * 2,
+                                  BK, 64, CU_TENSOR_MAP_SWIZZLE_128B))
+    return rc;
+  const int MT = M <= 8 ? 1 : 2;
+  if (int rc = make_tensor_map_2d(&xmap, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)K, (uint64_t)K * 2,
+                                  MT * 8, BK, CU_TENSOR_MAP_SWIZZLE_128B))
+    return rc;
+  static bool configured = false;
+  if (!configured) {
+    QMM_CUDA_TRY(cudaFuncSetAttribute(bf16_small_m_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+    QMM_CUDA_TRY(cudaFuncSetAttribute(bf16_small_m_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+    configured = true;
+  }
+  const unsigned grid = static_cast<unsigned>((N + BN - 1) / BN);
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (MT == 1)
+    bf16_small_m_kernel<1><<<grid, 160, kSmem, s>>>(wmap, xmap, y, (int)M, (int)N, (int)K, device_status_word());
+  else
+    bf16_small_m_kernel<2><<<grid, 160, kSmem, s>>>(wmap, xmap, y, (int)M, (int)N, (int)K, device_status_word());
+  QMM_CHECK_LAUNCH("bf16_small_m_kernel");
+  return QMM_OK;
+}
+
+}  // extern "C"
