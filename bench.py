@@ -476,6 +476,45 @@ def run_detail(torch, ops, synthetic, lib, device, peaks):
                 "not in MEASURED_PEAKS.json, 2 x the measured bf16 burst stands in for it"}
     del bs
 
+    # Llama-3-8B-shaped int4 decode step, batch 8, KV context 2048 (random weights and cache)
+    from jax_metallib_b200.decode_stack import DecodeStep, LlamaShape, random_model
+
+    shape = LlamaShape()
+    B, L = 8, 2048
+    model = random_model(shape, device, seed=4000)
+    gen = synthetic.torch_generator(device, 4, 1)
+    kc = [torch.randn((B, shape.n_kv_heads, L, shape.head_dim), device=device, generator=gen).to(torch.bfloat16)
+          for _ in range(shape.n_layers)]
+    vc = [torch.randn((B, shape.n_kv_heads, L, shape.head_dim), device=device, generator=gen).to(torch.bfloat16)
+          for _ in range(shape.n_layers)]
+    step = DecodeStep(shape, model, B, L, device)
+    step.ids.copy_(torch.randint(0, shape.vocab, (B,), device=device, generator=gen).to(torch.int32))
+    g = step.capture(kc, vc)
+    with torch.cuda.stream(stream):
+        for _ in range(3):
+            g.replay()
+        stream.synchronize()
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        reps = 20
+        for _ in range(reps):
+            g.replay()
+        e1.record(stream)
+        stream.synchronize()
+    ms = e0.elapsed_time(e1) / reps
+    step_bytes = shape.weight_bytes_per_step(B, L)
+    detail["llama3_8b_int4_decode_b8_ctx2048"] = {
+        "ms_per_step": ms, "tokens_per_s": B / (ms * 1e-3), "launches_per_step": step.launches_per_step,
+        "bytes_per_step": step_bytes, "GB/s": step_bytes / (ms * 1e-3) / 1e9,
+        "frac_of_measured_hbm": step_bytes / (ms * 1e-3) / 1e9 / hbm,
+        "ceiling_tokens_per_s_at_measured_hbm": B / (step_bytes / (hbm * 1e9)),
+        "note": "one CUDA-graph replay per step: embedding gather, 32 layers (7 int4 g128 linears, RMSNorm, RoPE, "
+                "GQA attention over a read-only bf16 KV cache, SwiGLU), final norm and bf16 lm_head all inside the "
+                "timed step; the step returns logits and the new K/V rows; 6.8 GB touched per step exceeds L2"}
+    del model, kc, vc, step, g
+    torch.cuda.empty_cache()
+
     # small f32 case (launch-latency bound)
     c = synthetic.config1()
     x1 = torch.from_numpy(c["x"]).to(device)

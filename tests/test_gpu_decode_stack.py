@@ -33,8 +33,8 @@ def test_take_rows_wraps_and_fills(cuda):
     table = O.round_to_bf16(rng.standard_normal((50, 64)).astype(np.float32))
     ids = np.array([0, 49, -1, -50, 50, -51, 7], dtype=np.int32)
     out = torch.empty((len(ids), 64), dtype=torch.bfloat16, device=cuda)
-    _lib.check(lib.qmm_take_rows_bf16(bft(table, cuda).data_ptr(), torch.from_numpy(ids).to(cuda).data_ptr(),
-                                      out.data_ptr(), 50, 64, len(ids), 0, stream()))
+    tt, it = bft(table, cuda), torch.from_numpy(ids).to(cuda)  # keep the device copies alive across the launch
+    _lib.check(lib.qmm_take_rows_bf16(tt.data_ptr(), it.data_ptr(), out.data_ptr(), 50, 64, len(ids), 0, stream()))
     np.testing.assert_array_equal(f32(out), D.take_rows(table, ids))
 
 
@@ -65,8 +65,8 @@ def test_rope(cuda):
     q = O.round_to_bf16(rng.standard_normal((B, Hq, hd)).astype(np.float32))
     k = O.round_to_bf16(rng.standard_normal((B, Hkv, hd)).astype(np.float32))
     pos = np.array([0, 1, 2047, 100000], dtype=np.int32)
-    qt, kt = bft(q, cuda), bft(k, cuda)
-    _lib.check(lib.qmm_rope_bf16(qt.data_ptr(), kt.data_ptr(), torch.from_numpy(pos).to(cuda).data_ptr(), B, Hq, Hkv, hd,
+    qt, kt, pt = bft(q, cuda), bft(k, cuda), torch.from_numpy(pos).to(cuda)
+    _lib.check(lib.qmm_rope_bf16(qt.data_ptr(), kt.data_ptr(), pt.data_ptr(), B, Hq, Hkv, hd,
                                  ctypes.c_float(500000.0), stream()))
     assert O.max_rel_err(f32(qt), D.rope(q, pos, 500000.0)) <= 1e-2
     assert O.max_rel_err(f32(kt), D.rope(k, pos, 500000.0)) <= 1e-2
@@ -80,7 +80,8 @@ def test_silu_mul(cuda):
     g = O.round_to_bf16(rng.standard_normal((B, F)).astype(np.float32) * 4)
     u = O.round_to_bf16(rng.standard_normal((B, F)).astype(np.float32))
     out = torch.empty((B, F), dtype=torch.bfloat16, device=cuda)
-    _lib.check(lib.qmm_silu_mul_bf16(bft(g, cuda).data_ptr(), bft(u, cuda).data_ptr(), out.data_ptr(), B, F, F, stream()))
+    gt, ut = bft(g, cuda), bft(u, cuda)
+    _lib.check(lib.qmm_silu_mul_bf16(gt.data_ptr(), ut.data_ptr(), out.data_ptr(), B, F, F, stream()))
     assert O.max_rel_err(f32(out), D.silu_mul(g, u)) <= 1e-2
 
 
@@ -98,8 +99,9 @@ def test_attention_decode(cuda, B, Hq, Hkv, L):
     ws = torch.empty(max(1, lib.qmm_attention_decode_workspace_bytes(B, Hq, Hkv, L)), dtype=torch.uint8, device=cuda)
     kct = bft(kc, cuda) if L else torch.empty(1, dtype=torch.bfloat16, device=cuda)
     vct = bft(vc, cuda) if L else torch.empty(1, dtype=torch.bfloat16, device=cuda)
-    _lib.check(lib.qmm_attention_decode_bf16(bft(q, cuda).data_ptr(), kct.data_ptr(), vct.data_ptr(), bft(kn, cuda).data_ptr(),
-                                             bft(vn, cuda).data_ptr(), out.data_ptr(), B, Hq, Hkv, L, hd,
+    qt, knt, vnt = bft(q, cuda), bft(kn, cuda), bft(vn, cuda)
+    _lib.check(lib.qmm_attention_decode_bf16(qt.data_ptr(), kct.data_ptr(), vct.data_ptr(), knt.data_ptr(),
+                                             vnt.data_ptr(), out.data_ptr(), B, Hq, Hkv, L, hd,
                                              ctypes.c_float(1 / np.sqrt(hd)), ws.data_ptr(), ws.numel(), stream()))
     torch.cuda.synchronize()
     assert lib.qmm_device_status() == 0
@@ -113,7 +115,8 @@ def test_bf16_matmul_small_m(cuda, M, K, N):
     x = O.round_to_bf16(rng.standard_normal((M, K)).astype(np.float32))
     w = O.round_to_bf16(rng.standard_normal((K, N)).astype(np.float32) * 0.05)
     y = torch.empty((M, N), dtype=torch.bfloat16, device=cuda)
-    _lib.check(lib.qmm_bf16_matmul_small_m(bft(x, cuda).data_ptr(), bft(w, cuda).data_ptr(), y.data_ptr(), M, N, K, stream()))
+    xt, wt = bft(x, cuda), bft(w, cuda)
+    _lib.check(lib.qmm_bf16_matmul_small_m(xt.data_ptr(), wt.data_ptr(), y.data_ptr(), M, N, K, stream()))
     torch.cuda.synchronize()
     assert lib.qmm_device_status() == 0
     ref = (x.astype(np.float64) @ w.astype(np.float64)).astype(np.float32)
