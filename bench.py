@@ -199,13 +199,15 @@ def run_reference(args):
 # ----------------------------------------------------------------------------
 def build_weights(torch, synthetic, device, rank, world, layers):
     """Column shard of every layer's four weights, generated on the device."""
+    from jax_metallib_b200 import tp
+
     gen = synthetic.torch_generator(device, 5, rank)
     weights = []
     for _l in range(layers):
         layer = []
         for name, k, n, act in layer_shapes():
-            assert n % world == 0
-            ns = n // world
+            lo, hi = tp.shard_bounds(n, world, rank)
+            ns = hi - lo
             w = synthetic.device_int8((k, ns), device, gen)
             s = synthetic.device_uniform((ns,), 0.005, 0.02, device, gen)
             layer.append((name, k, n, ns, act, w, s))

@@ -19,8 +19,9 @@ namespace cg = cooperative_groups;
 namespace qmm {
 namespace w8a32 {
 
-constexpr int TM = 32, TN = 32, KC = 64;  // tile and k-chunk staged per iteration
-constexpr int kThreads = 128;
+constexpr int TM = 32, TN = 32;
+constexpr int KC = 256;  // k staged per pass: one global round trip per 256 k
+constexpr int kThreads = 256;
 
 __global__ void __launch_bounds__(kThreads)
 w8a32_kernel(const float* __restrict__ x, const int8_t* __restrict__ w,
@@ -29,59 +30,73 @@ w8a32_kernel(const float* __restrict__ x, const int8_t* __restrict__ w,
   cg::cluster_group cluster = cg::this_cluster();
   const int ks = cluster.block_rank();       // k-slice of this CTA
   const int KS = cluster.num_blocks();
-  __shared__ __align__(16) float xs[KC][TM];  // transposed: xs[k][m]
-  __shared__ float wsm[KC][TN + 1];
+  __shared__ __align__(16) float xs[KC][TM];   // transposed: xs[k][m]
+  __shared__ __align__(16) int8_t wsm[KC][TN];
   __shared__ __align__(16) float part[TM][TN];
 
   const int n0 = blockIdx.x * TN, m0 = blockIdx.y * TM;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;  // warp: rows 4w..4w+3, lane: column
   const int k_begin = ks * k_per_cta;
   const int k_end = min(K, k_begin + k_per_cta);
+  const bool vec_ok = (K % 4 == 0) && (N % 16 == 0) && ((reinterpret_cast<uintptr_t>(x) & 15) == 0) &&
+                      ((reinterpret_cast<uintptr_t>(w) & 15) == 0);
 
-  float acc[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
-
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
   for (int k0 = k_begin; k0 < k_end; k0 += KC) {
-    // stage x (transposed) and w (converted to f32); out-of-range -> 0
-    for (int idx = threadIdx.x; idx < TM * KC; idx += kThreads) {
-      const int m = idx / KC, kk = idx % KC;
-      const int gm = m0 + m, gk = k0 + kk;
-      xs[kk][m] = (gm < M && gk < k_end) ? __ldg(x + static_cast<size_t>(gm) * K + gk) : 0.f;
-    }
-    for (int idx = threadIdx.x; idx < KC * TN; idx += kThreads) {
-      const int kk = idx / TN, n = idx % TN;
-      const int gk = k0 + kk, gn = n0 + n;
-      wsm[kk][n] = (gk < k_end && gn < N)
-                       ? static_cast<float>(__ldg(w + static_cast<size_t>(gk) * N + gn))
-                       : 0.f;
+    // stage x (transposed) and w; everything out of range reads as 0.  All loads of
+    // a pass are independent, so the pass costs one memory round trip.
+    if (vec_ok) {
+      for (int idx = threadIdx.x; idx < TM * (KC / 4); idx += kThreads) {
+        const int m = idx % TM, kq = idx / TM;  // lanes along m: conflict-free transposed stores
+        const int gm = m0 + m, gk = k0 + 4 * kq;
+        float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (gm < M && gk < k_end) v = __ldg(reinterpret_cast<const float4*>(x + static_cast<size_t>(gm) * K + gk));
+        xs[4 * kq + 0][m] = v.x;
+        xs[4 * kq + 1][m] = (gk + 1 < k_end) ? v.y : 0.f;
+        xs[4 * kq + 2][m] = (gk + 2 < k_end) ? v.z : 0.f;
+        xs[4 * kq + 3][m] = (gk + 3 < k_end) ? v.w : 0.f;
+      }
+      for (int idx = threadIdx.x; idx < KC * (TN / 16); idx += kThreads) {
+        const int kk = idx / (TN / 16), h = idx % (TN / 16);
+        const int gk = k0 + kk, gn = n0 + 16 * h;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (gk < k_end && gn < N) v = __ldg(reinterpret_cast<const uint4*>(w + static_cast<size_t>(gk) * N + gn));
+        *reinterpret_cast<uint4*>(&wsm[kk][16 * h]) = v;
+      }
+    } else {
+      for (int idx = threadIdx.x; idx < TM * KC; idx += kThreads) {
+        const int m = idx % TM, kk = idx / TM;
+        const int gm = m0 + m, gk = k0 + kk;
+        xs[kk][m] = (gm < M && gk < k_end) ? __ldg(x + static_cast<size_t>(gm) * K + gk) : 0.f;
+      }
+      for (int idx = threadIdx.x; idx < KC * TN; idx += kThreads) {
+        const int kk = idx / TN, n = idx % TN;
+        const int gk = k0 + kk, gn = n0 + n;
+        wsm[kk][n] = (gk < k_end && gn < N) ? __ldg(w + static_cast<size_t>(gk) * N + gn) : static_cast<int8_t>(0);
+      }
     }
     __syncthreads();
+    const int kmax = min(KC, k_end - k0);
 #pragma unroll 8
-    for (int kk = 0; kk < KC; ++kk) {
-      const float wv = wsm[kk][lane];
-      const float4 a = *reinterpret_cast<const float4*>(&xs[kk][warp * 8]);
-      const float4 b = *reinterpret_cast<const float4*>(&xs[kk][warp * 8 + 4]);
+    for (int kk = 0; kk < kmax; ++kk) {
+      const float wv = static_cast<float>(wsm[kk][lane]);
+      const float4 a = *reinterpret_cast<const float4*>(&xs[kk][warp * 4]);
       acc[0] = fmaf(a.x, wv, acc[0]);
       acc[1] = fmaf(a.y, wv, acc[1]);
       acc[2] = fmaf(a.z, wv, acc[2]);
       acc[3] = fmaf(a.w, wv, acc[3]);
-      acc[4] = fmaf(b.x, wv, acc[4]);
-      acc[5] = fmaf(b.y, wv, acc[5]);
-      acc[6] = fmaf(b.z, wv, acc[6]);
-      acc[7] = fmaf(b.w, wv, acc[7]);
     }
     __syncthreads();
   }
 #pragma unroll
-  for (int i = 0; i < 8; ++i) part[warp * 8 + i][lane] = acc[i];
+  for (int i = 0; i < 4; ++i) part[warp * 4 + i][lane] = acc[i];
   cluster.sync();
   if (ks == 0) {
     const int gn = n0 + lane;
     const float sc = (gn < N) ? __ldg(scale + gn) : 0.f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int m = warp * 8 + i;
+    for (int i = 0; i < 4; ++i) {
+      const int m = warp * 4 + i;
       float v = acc[i];
       for (int r = 1; r < KS; ++r) {
         const float* remote = cluster.map_shared_rank(&part[0][0], r);
@@ -111,10 +126,10 @@ extern "C" int qmm_w8a32_perchannel(const float* x, const int8_t* w, const float
   // split K over a cluster until the grid covers the machine (at most 8 CTAs per cluster)
   int KS = 1;
   const int target = num_sms();
-  while (KS < 8 && static_cast<long long>(gx) * gy * KS < target && K / (KS * 2) >= KC) KS *= 2;
+  while (KS < 8 && static_cast<long long>(gx) * gy * KS < target && K / (KS * 2) >= 128) KS *= 2;
   int k_per_cta = static_cast<int>((K + KS - 1) / KS);
-  k_per_cta = (k_per_cta + KC - 1) / KC * KC;
-  if (k_per_cta == 0) k_per_cta = KC;
+  k_per_cta = (k_per_cta + 3) / 4 * 4;  // keeps every k-slice 16-byte aligned for the vector loads
+  if (k_per_cta == 0) k_per_cta = 4;
 
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(gx, gy, KS);
