@@ -385,7 +385,10 @@ def run_gpu(args):
             "roofline": {"bound": "tensor", "kernel": "w8a16_kernel (tcgen05 kind::f16, in-kernel int8->bf16)",
                          "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                          "peak_source": f"{peaks['source']} bf16_tflops_sustained (burst {peaks['bf16_tflops']})",
-                         "traffic": None},
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture (qkv and o launches,
+                         # 1.09 bytes per kFLOP), scaled by FLOPs to this run's mean launch
+                         "traffic": 1.09e-3 * kern_flops / max(1, len(kernel_events)),
+                         "traffic_unit": "bytes per launch (mean)"},
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": timed_launches,
             "clocks": clocks,
@@ -401,7 +404,7 @@ def run_gpu(args):
     return 0
 
 
-def run_detail(torch, ops, synthetic, lib, device, peaks):
+def run_detail(torch, ops, synthetic, lib, device, peaks, items=None):
     """The other workloads of the path.  The kernels here run for microseconds,
     so a sequence of launches is captured in a CUDA graph and the graph is
     replayed: the device time per launch is then free of host launch overhead.
@@ -409,6 +412,7 @@ def run_detail(torch, ops, synthetic, lib, device, peaks):
     detail = {}
     hbm = peaks["hbm_gbs"]
     stream = torch.cuda.Stream()
+    want = (lambda name: True) if not items else (lambda name: name in items)
 
     def graph_time(launch, n_launches, replays=20, warm_replays=3):
         """launch(i) issues the i-th kernel; returns mean microseconds per kernel."""
@@ -431,6 +435,18 @@ def run_detail(torch, ops, synthetic, lib, device, peaks):
             stream.synchronize()
         return e0.elapsed_time(e1) * 1e3 / (replays * n_launches)
 
+    if want("int4_decode"):
+        _detail_int4_decode(torch, ops, synthetic, lib, device, hbm, graph_time, detail)
+    if want("int8_dot"):
+        _detail_int8_dot(torch, synthetic, lib, device, peaks, graph_time, detail)
+    if want("llama_decode"):
+        _detail_llama_decode(torch, synthetic, device, hbm, stream, detail)
+    if want("small_f32"):
+        _detail_small_f32(torch, synthetic, lib, device, hbm, graph_time, detail)
+    return detail
+
+
+def _detail_int4_decode(torch, ops, synthetic, lib, device, hbm, graph_time, detail):
     # decode int4 g128 GEMV: rotate through enough weight copies that no launch finds its weights in L2
     K, N, G = 4096, 14336, 32
     copies = 12  # 12 x 30.5 MB > 2 x L2
@@ -456,6 +472,8 @@ def run_detail(torch, ops, synthetic, lib, device, peaks):
             "note": f"{copies} rotating weight copies (cold L2), zero points packed 4-bit, CUDA-graph replay"}
     del wqs
 
+
+def _detail_int8_dot(torch, synthetic, lib, device, peaks, graph_time, detail):
     # int8 x int8 -> int32 with fused rescale
     Mi, Ki, Ni = 2048, 4096, 4096
     gen = synthetic.torch_generator(device, 2, 0)
@@ -478,6 +496,8 @@ def run_detail(torch, ops, synthetic, lib, device, peaks):
                 "not in MEASURED_PEAKS.json, 2 x the measured bf16 burst stands in for it"}
     del bs
 
+
+def _detail_llama_decode(torch, synthetic, device, hbm, stream, detail):
     # Llama-3-8B-shaped int4 decode step, batch 8, KV context 2048 (random weights and cache)
     from jax_metallib_b200.decode_stack import DecodeStep, LlamaShape, random_model
 
@@ -517,6 +537,8 @@ def run_detail(torch, ops, synthetic, lib, device, peaks):
     del model, kc, vc, step, g
     torch.cuda.empty_cache()
 
+
+def _detail_small_f32(torch, synthetic, lib, device, hbm, graph_time, detail):
     # small f32 case (launch-latency bound)
     c = synthetic.config1()
     x1 = torch.from_numpy(c["x"]).to(device)
@@ -534,7 +556,6 @@ def run_detail(torch, ops, synthetic, lib, device, peaks):
     detail["int8_weight_only_f32_32x1024x1024"] = {
         "us": us, "GB/s": nbytes / (us * 1e-6) / 1e9, "frac_of_measured_hbm": nbytes / (us * 1e-6) / 1e9 / hbm,
         "note": "1.3 MB problem (fits L2): back-to-back launches in a CUDA graph; latency bound"}
-    return detail
 
 
 def main():
@@ -547,6 +568,8 @@ def main():
     ap.add_argument("--no-detail", action="store_true", help="skip the per-workload detail and the CPU baseline")
     ap.add_argument("--detail-only", action="store_true",
                     help="run only the per-workload detail (small case for profiling) and print it as JSON")
+    ap.add_argument("--detail-items", default="",
+                    help="comma-separated subset of int4_decode,int8_dot,llama_decode,small_f32")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
@@ -557,7 +580,8 @@ def main():
 
         device = torch.device("cuda", 0)
         torch.cuda.set_device(device)
-        print(json.dumps({"detail": run_detail(torch, ops, synthetic, _lib.load(), device, measured_peaks())}))
+        items = [x for x in args.detail_items.split(",") if x] or None
+        print(json.dumps({"detail": run_detail(torch, ops, synthetic, _lib.load(), device, measured_peaks(), items)}))
         return 0
     return run_gpu(args)
 
