@@ -192,27 +192,29 @@ namespace w8 {
 constexpr int BNW = 128;   // output channels per tile (MMA M)
 constexpr int BMX = 256;   // activation rows per tile (MMA N)
 constexpr int BK = 64;
-constexpr int kStages = 3;
+constexpr int kStages = 4;     // TMA ring: raw weights + activations
+constexpr int kCvtBufs = 2;    // converted-weight buffers between the converter warps and the MMA
 constexpr int kCvtWarps = 8;
 constexpr int kRawBytes = BK * BNW;        // 8 KB  int8 [k][n]
 constexpr int kCvtBytes = BK * BNW * 2;    // 16 KB bf16, two 64-channel blocks of [k][128 B]
 constexpr int kXBytes = BMX * BK * 2;      // 32 KB bf16 [m][k]
-constexpr int kStageBytes = kRawBytes + kCvtBytes + kXBytes;  // 56 KB
+constexpr int kStageBytes = kRawBytes + kXBytes;  // 40 KB
+constexpr int kCvtBase = kStages * kStageBytes;   // 160 KB
 constexpr int kThreads = (2 + kEpiWarps + kCvtWarps) * 32;
-constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 1024;
+constexpr int kSmemBytes = kCvtBase + kCvtBufs * kCvtBytes + 1024 + 1024;
+constexpr int kPanelTiles = 8;  // activation tiles swept together so that they stay in L2
 
-// Sixteen int8 (one 16-byte read) -> sixteen bf16, exactly: the byte, biased to
+// Eight int8 (one 8-byte read) -> eight bf16, exactly: the byte, biased to
 // unsigned, becomes the low mantissa bits of 2^23 (an f32 holding 2^23 + 128 + v),
 // the constant is subtracted and pairs are packed with round-to-nearest (exact,
 // |v| <= 128 fits bf16's 8 significant bits).  The MMA needs both operands in
 // one 16-bit format (an f16 weight operand against bf16 activations raises an
 // illegal-instruction error on sm_100a), so the weights follow the activations.
-__device__ __forceinline__ void convert16(const uint4& in, uint4& lo8, uint4& hi8) {
-  const uint32_t w[4] = {in.x ^ 0x80808080u, in.y ^ 0x80808080u, in.z ^ 0x80808080u,
-                         in.w ^ 0x80808080u};
-  uint32_t o[8];
+__device__ __forceinline__ uint4 convert8(const uint2& in) {
+  const uint32_t w[2] = {in.x ^ 0x80808080u, in.y ^ 0x80808080u};
+  uint32_t o[4];
 #pragma unroll
-  for (int i = 0; i < 4; ++i) {
+  for (int i = 0; i < 2; ++i) {
     const float f0 = __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7440)) - 8388736.f;
     const float f1 = __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7441)) - 8388736.f;
     const float f2 = __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7442)) - 8388736.f;
@@ -220,8 +222,18 @@ __device__ __forceinline__ void convert16(const uint4& in, uint4& lo8, uint4& hi
     o[2 * i] = dev::pack_bf16x2(f0, f1);
     o[2 * i + 1] = dev::pack_bf16x2(f2, f3);
   }
-  lo8 = make_uint4(o[0], o[1], o[2], o[3]);
-  hi8 = make_uint4(o[4], o[5], o[6], o[7]);
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+// Tile order: activation tiles are swept in panels of kPanelTiles; inside a
+// panel the weight tile changes slowest, so the CTAs that run together share
+// one panel of activations (it stays in L2) and a handful of weight tiles.
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
+  const int per_panel = kPanelTiles * tiles_n;
+  const int p = tile / per_panel, r = tile - p * per_panel;
+  const int rows = min(kPanelTiles, tiles_m - p * kPanelTiles);  // the last panel may be short
+  tn = r / rows;
+  tm = p * kPanelTiles + r % rows;
 }
 
 __global__ void __launch_bounds__(kThreads, 1)
@@ -231,10 +243,11 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);  // TMA landed
-  uint64_t* cvt = full + kStages;                                              // weights converted
-  uint64_t* empty = cvt + kStages;                                             // MMAs retired
-  uint64_t* tfull = empty + kStages;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kCvtBase + kCvtBufs * kCvtBytes);  // TMA landed
+  uint64_t* empty = full + kStages;     // MMAs that read the stage's activations retired
+  uint64_t* cfull = empty + kStages;    // weights converted
+  uint64_t* cempty = cfull + kCvtBufs;  // MMAs that read the converted buffer retired
+  uint64_t* tfull = cempty + kCvtBufs;
   uint64_t* tempty = tfull + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
 
@@ -246,8 +259,11 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       dev::mbar_init(&full[s], 1);
-      dev::mbar_init(&cvt[s], kCvtWarps);
       dev::mbar_init(&empty[s], 1);
+    }
+    for (int i = 0; i < kCvtBufs; ++i) {
+      dev::mbar_init(&cfull[i], kCvtWarps);
+      dev::mbar_init(&cempty[i], 1);
     }
     for (int i = 0; i < 2; ++i) {
       dev::mbar_init(&tfull[i], 1);
@@ -269,39 +285,39 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
     if (lane == 0) {
       dev::tma_prefetch_desc(&wmap);
       dev::tma_prefetch_desc(&xmap);
-      int it = 0;
+      int s = 0;
+      uint32_t ph = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int tm = tile % tiles_m, tn = tile / tiles_m;  // activation tiles fastest
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          const int s = it % kStages;
-          const uint32_t ph = (it / kStages) & 1;
+        int tm, tn;
+        tile_coords(tile, tiles_m, tiles_n, tm, tn);
+        for (int kb = 0; kb < kblocks; ++kb) {
           if (!dev::mbar_wait(&empty[s], ph ^ 1, status, 21)) { ok = false; break; }
           uint8_t* st = smem + s * kStageBytes;
           dev::mbar_expect_tx(&full[s], kRawBytes + kXBytes);
           dev::tma_load_2d(st, &wmap, &full[s], tn * BNW, kb * BK);
-          dev::tma_load_2d(st + kRawBytes + kCvtBytes, &xmap, &full[s], kb * BK, tm * BMX);
+          dev::tma_load_2d(st + kRawBytes, &xmap, &full[s], kb * BK, tm * BMX);
+          if (++s == kStages) { s = 0; ph ^= 1; }
         }
       }
     }
   } else if (warp == 1) {
     // ------------------------------ MMA issuer -----------------------------
     if (lane == 0) {
-      int it = 0, tcount = 0;
+      int s = 0, c = 0, tcount = 0;
+      uint32_t ph = 0, cph = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
         const int as = tcount & 1;
         if (!dev::mbar_wait(&tempty[as], ((tcount >> 1) & 1) ^ 1, status, 22)) { ok = false; break; }
         dev::tc_fence_after();
         const uint32_t d_tmem = tmem_base + as * BMX;
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          const int s = it % kStages;
-          const uint32_t ph = (it / kStages) & 1;
+        for (int kb = 0; kb < kblocks; ++kb) {
           if (!dev::mbar_wait(&full[s], ph, status, 23) ||
-              !dev::mbar_wait(&cvt[s], ph, status, 24)) { ok = false; break; }
+              !dev::mbar_wait(&cfull[c], cph, status, 24)) { ok = false; break; }
           dev::tc_fence_after();
-          const uint32_t w_addr = dev::smem_u32(smem + s * kStageBytes + kRawBytes);
-          const uint32_t x_addr = w_addr + kCvtBytes;
+          const uint32_t w_addr = dev::smem_u32(smem + kCvtBase + c * kCvtBytes);
+          const uint32_t x_addr = dev::smem_u32(smem + s * kStageBytes + kRawBytes);
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
             // weights: MN-major, 16 k-rows (2 KB) per instruction, 64-channel blocks 8 KB apart
@@ -311,7 +327,10 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
             const uint64_t bdesc = dev::make_smem_desc(x_addr + k * 32, 16, 1024, kSwizzle128);
             dev::umma_f16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0);
           }
-          dev::tc_commit(&empty[s]);
+          dev::tc_commit(&empty[s]);    // frees the TMA stage (raw weights were consumed earlier)
+          dev::tc_commit(&cempty[c]);   // frees the converted buffer
+          if (++s == kStages) { s = 0; ph ^= 1; }
+          if (++c == kCvtBufs) { c = 0; cph ^= 1; }
         }
         if (ok) dev::tc_commit(&tfull[as]);
       }
@@ -321,7 +340,8 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
     const int q = warp & 3;
     int tcount = 0;
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcount) {
-      const int tm = tile % tiles_m, tn = tile / tiles_m;
+      int tm, tn;
+      tile_coords(tile, tiles_m, tiles_n, tm, tn);
       const int as = tcount & 1;
       if (!dev::mbar_wait(&tfull[as], (tcount >> 1) & 1, status, 25)) break;
       dev::tc_fence_after();
@@ -354,43 +374,39 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
     }
   } else {
     // ------------------------------ converters -----------------------------
-    // A quarter-warp reads one 128-byte raw row (any permutation of its eight
-    // 16-byte chunks is conflict-free) and writes sixteen 16-byte chunks of the
-    // bf16 tile; lanes 4-7 write their upper chunk first so that the eight
-    // lanes of a store touch eight different chunk positions.
+    // A half-warp reads one 128-byte raw row, 8 bytes per lane (conflict-free
+    // in any permutation); each lane writes the 16-byte bf16 chunk it made, so
+    // a quarter-warp store covers the eight chunks of one 128-byte row of one
+    // 64-channel block: conflict-free as well, with no divergence.
     const int cw = warp - (2 + kEpiWarps);  // 0..7
-    const int seg = lane & 7;               // 16 channels: [16*seg, 16*seg+16)
-    const int rsub = lane >> 3;             // row within a group of 4
-    int it = 0;
+    const int piece = lane & 15;            // 8 channels: [8*piece, 8*piece+8)
+    const int rsub = lane >> 4;             // row within a pair
+    int s = 0, c = 0;
+    uint32_t ph = 0, cph = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      for (int kb = 0; kb < kblocks; ++kb, ++it) {
-        const int s = it % kStages;
-        const uint32_t ph = (it / kStages) & 1;
-        if (!dev::mbar_wait(&full[s], ph, status, 26)) { ok = false; break; }
+      for (int kb = 0; kb < kblocks; ++kb) {
+        if (!dev::mbar_wait(&full[s], ph, status, 26) ||
+            !dev::mbar_wait(&cempty[c], cph ^ 1, status, 27)) { ok = false; break; }
         const uint8_t* raw = smem + s * kStageBytes;
-        uint8_t* dst = smem + s * kStageBytes + kRawBytes;
+        uint8_t* dst = smem + kCvtBase + c * kCvtBytes + (piece >> 3) * (BK * 128);
+        uint2 in[BK / (2 * kCvtWarps)];
 #pragma unroll
-        for (int p = 0; p < BK / (4 * kCvtWarps); ++p) {
-          const int r = (p * kCvtWarps + cw) * 4 + rsub;  // k-row 0..63
-          const uint4 in = *reinterpret_cast<const uint4*>(raw + r * 128 + ((seg ^ (r & 7)) << 4));
-          uint4 lo8, hi8;
-          convert16(in, lo8, hi8);
-          uint8_t* rowp = dst + (seg >> 2) * (BK * 128) + r * 128;
-          const int c0 = 2 * (seg & 3), c1 = c0 + 1;
-          uint4* p0 = reinterpret_cast<uint4*>(rowp + ((c0 ^ (r & 7)) << 4));
-          uint4* p1 = reinterpret_cast<uint4*>(rowp + ((c1 ^ (r & 7)) << 4));
-          if (seg & 4) {
-            *p1 = hi8;
-            *p0 = lo8;
-          } else {
-            *p0 = lo8;
-            *p1 = hi8;
-          }
+        for (int p = 0; p < BK / (2 * kCvtWarps); ++p) {
+          const int r = (p * kCvtWarps + cw) * 2 + rsub;  // k-row 0..63
+          in[p] = *reinterpret_cast<const uint2*>(raw + r * 128 + (((piece >> 1) ^ (r & 7)) << 4) +
+                                                  ((piece & 1) << 3));
+        }
+#pragma unroll
+        for (int p = 0; p < BK / (2 * kCvtWarps); ++p) {
+          const int r = (p * kCvtWarps + cw) * 2 + rsub;
+          *reinterpret_cast<uint4*>(dst + r * 128 + (((piece & 7) ^ (r & 7)) << 4)) = convert8(in[p]);
         }
         dev::fence_proxy_async();
         __syncwarp();
-        if (lane == 0) dev::mbar_arrive(&cvt[s]);
+        if (lane == 0) dev::mbar_arrive(&cfull[c]);
+        if (++s == kStages) { s = 0; ph ^= 1; }
+        if (++c == kCvtBufs) { c = 0; cph ^= 1; }
       }
     }
   }
