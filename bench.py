@@ -531,7 +531,7 @@ def _detail_llama_decode(torch, synthetic, device, hbm, stream, detail):
         "bytes_per_step": step_bytes, "GB/s": step_bytes / (ms * 1e-3) / 1e9,
         "frac_of_measured_hbm": step_bytes / (ms * 1e-3) / 1e9 / hbm,
         "ceiling_tokens_per_s_at_measured_hbm": B / (step_bytes / (hbm * 1e9)),
-        "note": "one CUDA-graph replay per step: embedding gather, 32 layers (7 int4 g128 linears, RMSNorm, RoPE, "
+        "note": "one CUDA-graph replay per step: embedding gather, 32 layers (7 int4 g128 linears as 4 launches: q|k|v and gate|up side by side along N; RMSNorm, RoPE, "
                 "GQA attention over a read-only bf16 KV cache, SwiGLU), final norm and bf16 lm_head all inside the "
                 "timed step; the step returns logits and the new K/V rows; 6.8 GB touched per step exceeds L2"}
     del model, kc, vc, step, g

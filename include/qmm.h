@@ -213,12 +213,15 @@ QMM_API int qmm_mx_matmul(const void* x, const uint8_t* w_packed, const uint8_t*
  *   bf16 and stored to sum_out if given; norm_out =
  *   bf16(bf16(h * rsqrt(mean(h^2) + eps)) * weight), statistics in f32.
  * qmm_rope_bf16: rotary embedding in place on q [B,Hq,hd] and k [B,Hkv,hd],
- *   pairs (i, i + hd/2), angle = position * theta^(-2i/hd).
+ *   pairs (i, i + hd/2), angle = position * theta^(-2i/hd); batch rows of q / k
+ *   are q_ld / k_ld elements apart (slices of a fused q|k|v projection output).
  * qmm_silu_mul_bf16: out = bf16(bf16(silu(gate)) * up); gate/up rows are ld_in
  *   elements apart (so they may be the two halves of one buffer).
  * qmm_attention_decode_bf16: grouped-query attention of one new token per
  *   sequence over a read-only cache [B,Hkv,L,128] plus the new key/value row
- *   [B,Hkv,128]; softmax in f32; two launches (per-chunk partials, merge).
+ *   [B,Hkv,128]; batch rows of q are q_ld elements apart, those of knew / vnew
+ *   new_ld; scores and P.V on the tensor cores (bf16 operands, f32 accumulate),
+ *   softmax in f32; two launches (per-split partials, merge).
  * qmm_bf16_matmul_small_m: y[M,N] = bf16(x[M,K] @ w[K,N]), bf16 operands, f32
  *   accumulate, M <= 16 (the unquantized lm_head of the decode step). */
 QMM_API int qmm_take_rows_bf16(const uint16_t* table, const int32_t* ids, uint16_t* out, int64_t V,
@@ -227,7 +230,8 @@ QMM_API int qmm_add_rmsnorm_bf16(const uint16_t* x, const uint16_t* residual, co
                                  uint16_t* sum_out, uint16_t* norm_out, int64_t B, int64_t D,
                                  float eps, void* stream);
 QMM_API int qmm_rope_bf16(uint16_t* q, uint16_t* k, const int32_t* positions, int64_t B, int64_t Hq,
-                          int64_t Hkv, int64_t head_dim, float theta, void* stream);
+                          int64_t Hkv, int64_t head_dim, float theta, int64_t q_ld, int64_t k_ld,
+                          void* stream);
 QMM_API int qmm_silu_mul_bf16(const uint16_t* gate, const uint16_t* up, uint16_t* out, int64_t B,
                               int64_t F, int64_t ld_in, void* stream);
 QMM_API size_t qmm_attention_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t L);
@@ -235,7 +239,8 @@ QMM_API int qmm_attention_decode_bf16(const uint16_t* q, const uint16_t* kcache,
                                       const uint16_t* vcache, const uint16_t* knew,
                                       const uint16_t* vnew, uint16_t* out, int64_t B, int64_t Hq,
                                       int64_t Hkv, int64_t L, int64_t head_dim, float scale,
-                                      void* workspace, size_t workspace_bytes, void* stream);
+                                      int64_t q_ld, int64_t new_ld, void* workspace,
+                                      size_t workspace_bytes, void* stream);
 QMM_API int qmm_bf16_matmul_small_m(const uint16_t* x, const uint16_t* w, uint16_t* y, int64_t M,
                                     int64_t N, int64_t K, void* stream);
 

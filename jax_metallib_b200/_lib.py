@@ -44,12 +44,13 @@ SIGNATURES = {
     "qmm_take_rows_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, ctypes.c_uint16, c_void_p]),
     "qmm_add_rmsnorm_bf16": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, ctypes.c_float, c_void_p]),
-    "qmm_rope_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, ctypes.c_float, c_void_p]),
+    "qmm_rope_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, ctypes.c_float, c_int64,
+                              c_int64, c_void_p]),
     "qmm_silu_mul_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]),
     "qmm_attention_decode_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int64]),
     "qmm_attention_decode_bf16": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
-                ctypes.c_float, c_void_p, c_size_t, c_void_p]),
+                ctypes.c_float, c_int64, c_int64, c_void_p, c_size_t, c_void_p]),
     "qmm_bf16_matmul_small_m": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]),
     "qmm_plan_compile": (c_int, [c_char_p, c_size_t, ctypes.POINTER(c_void_p)]),
     "qmm_plan_destroy": (None, [c_void_p]),

@@ -78,25 +78,28 @@ add_rmsnorm_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ 
 }
 
 // ---------------------------------------------------------------------------
-// rotary embedding, rotate-half pairing (i, i + hd/2), in place on q and k
+// rotary embedding, rotate-half pairing (i, i + hd/2), in place on q and k;
+// one thread per (batch row, head, pair); q / k batch rows are q_ld / k_ld
+// elements apart (they may be slices of one fused projection output)
 // ---------------------------------------------------------------------------
-__global__ void rope_kernel(uint16_t* __restrict__ q, uint16_t* __restrict__ k,
-                            const int32_t* __restrict__ pos, int Hq, int Hkv, int hd, float theta) {
-  const int b = blockIdx.x;
+__global__ void __launch_bounds__(256)
+rope_kernel(uint16_t* __restrict__ q, uint16_t* __restrict__ k, const int32_t* __restrict__ pos, int B, int Hq,
+            int Hkv, int hd, float theta, long long q_ld, long long k_ld) {
   const int half = hd / 2;
+  const int per_row = (Hq + Hkv) * half;
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= B * per_row) return;
+  const int b = idx / per_row, i = idx % per_row;
+  const int h = i / half, j = i % half;
+  uint16_t* base = (h < Hq) ? q + static_cast<size_t>(b) * q_ld + static_cast<size_t>(h) * hd
+                            : k + static_cast<size_t>(b) * k_ld + static_cast<size_t>(h - Hq) * hd;
   const float p = static_cast<float>(pos[b]);
-  const int total = (Hq + Hkv) * half;
-  for (int i = threadIdx.x; i < total; i += blockDim.x) {
-    const int h = i / half, j = i % half;
-    uint16_t* base = (h < Hq) ? q + (static_cast<size_t>(b) * Hq + h) * hd
-                              : k + (static_cast<size_t>(b) * Hkv + (h - Hq)) * hd;
-    const float freq = powf(theta, -2.0f * static_cast<float>(j) / static_cast<float>(hd));
-    float sn, cs;
-    sincosf(p * freq, &sn, &cs);
-    const float a = dev::bf16_bits_to_float(base[j]), c = dev::bf16_bits_to_float(base[j + half]);
-    base[j] = dev::float_to_bf16_bits(a * cs - c * sn);
-    base[j + half] = dev::float_to_bf16_bits(c * cs + a * sn);
-  }
+  const float freq = powf(theta, -2.0f * static_cast<float>(j) / static_cast<float>(hd));
+  float sn, cs;
+  sincosf(p * freq, &sn, &cs);
+  const float a = dev::bf16_bits_to_float(base[j]), c = dev::bf16_bits_to_float(base[j + half]);
+  base[j] = dev::float_to_bf16_bits(a * cs - c * sn);
+  base[j + half] = dev::float_to_bf16_bits(c * cs + a * sn);
 }
 
 // ---------------------------------------------------------------------------
@@ -119,170 +122,252 @@ __global__ void silu_mul_kernel(const uint16_t* __restrict__ gate, const uint16_
 // decode attention, grouped-query, head dim 128.
 //   cache k/v: [B, Hkv, L, 128] bf16 (read only); new row knew/vnew [B, Hkv, 128]
 //   q [B, Hq, 128] -> out [B, Hq, 128]; the new row is the (L+1)-th key.
-// Pass 1 (attn_partial): one CTA per (b, kv head, 128-row chunk of the cache).
-// TMA brings the K and V chunks (two 64-wide boxes each, 128-byte swizzle);
-// thread r owns cache row r for the scores of the R = Hq/Hkv query heads that
-// share the kv head; softmax statistics per chunk; thread pairs own two output
-// dims for P.V.  Pass 2 (attn_combine) merges the chunks and the new row.
+// Pass 1 (attn_partial): the cache rows of one (b, kv head) are cut into
+// `nsplit` contiguous runs of 64-row tiles; one CTA streams a run through a
+// three-stage TMA ring (K and V tile, 16 KB each, 128-byte swizzle).  Four
+// consumer warps each own 16 rows of every tile and keep their own running
+// softmax (max, sum, 128-dim accumulator) for the R = Hq/Hkv query heads that
+// share the kv head, on the tensor cores (mma.sync m16n8k16, bf16):
+//   S^T[head, row] = Q[head, d] . K[row, d]     (heads padded to 16, A = Q in registers)
+//   O[head, d]    += P[head, row] . V[row, d]   (P straight from the S^T accumulators)
+// so the kernel does ~32 MMAs per 8 KB of cache and stays HBM-bound.  The
+// warps merge through shared memory and write one (max, sum, O) partial per
+// (b, head, split).  Pass 2 (attn_combine) merges the splits and the new row.
 // ---------------------------------------------------------------------------
-constexpr int kHd = 128, kChunk = 128, kMaxR = 8;
+constexpr int kHd = 128, kTileRows = 64, kAttnStages = 3, kAttnWarps = 4;
+constexpr int kAttnStageBytes = 2 * kTileRows * kHd * 2;  // K tile + V tile = 32 KB
+constexpr int kAttnSmem = kAttnStages * kAttnStageBytes + 128 + 1024;
+constexpr int kAttnThreads = (kAttnWarps + 1) * 32;
 
-template <int R>
-__global__ void __launch_bounds__(128)
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t (&r)[4]) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+               : "r"(addr));
+}
+// D += A.B with the lower eight rows of A (a1, a3) zero: only query heads 0..7 exist
+__device__ __forceinline__ void mma_heads(float (&d)[4], uint32_t a0, uint32_t a2, uint32_t b0, uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %5}, "
+      "{%7, %8}, {%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(0u), "r"(a2), "r"(b0), "r"(b1));
+}
+
+// tiles [begin, end) of split `s` out of `nsplit` over `ntiles`
+__host__ __device__ inline int split_begin(int s, int nsplit, int ntiles) {
+  return static_cast<int>(static_cast<long long>(s) * ntiles / nsplit);
+}
+
+__global__ void __launch_bounds__(kAttnThreads)
 attn_partial_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
-                    const uint16_t* __restrict__ q, float* __restrict__ part, int Hq, int Hkv, int L,
-                    int nchunks, float scale, int* status) {
+                    const uint16_t* __restrict__ q, float* __restrict__ part, int Hq, int Hkv, int R, int L,
+                    int nsplit, float scale, long long q_ld, int* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint8_t* ks = smem;              // 2 boxes x 16 KB
-  uint8_t* vs = smem + 32768;      // 2 boxes x 16 KB
-  float* qs = reinterpret_cast<float*>(smem + 65536);          // [R][128]
-  float* ps = qs + R * kHd;                                    // [128 rows][R] probabilities
-  float* red = ps + kChunk * R;                                // [4 warps][R]
-  float* ored = red + 4 * R;                                   // [64 d pairs][R][2] from the upper row half
-  uint64_t* bars = reinterpret_cast<uint64_t*>(ored + 64 * R * 2);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kAttnStages * kAttnStageBytes);
+  uint64_t* empty = full + kAttnStages;
 
-  const int chunk = blockIdx.x, bh = blockIdx.y;  // bh = b * Hkv + kvh
+  const int split = blockIdx.x, bh = blockIdx.y;  // bh = b * Hkv + kvh
   const int b = bh / Hkv, kvh = bh % Hkv;
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int row0 = chunk * kChunk;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int ntiles = (L + kTileRows - 1) / kTileRows;
+  const int t_begin = split_begin(split, nsplit, ntiles), t_end = split_begin(split + 1, nsplit, ntiles);
 
-  if (tid == 0) {
-    dev::mbar_init(&bars[0], 1);
-    dev::mbar_init(&bars[1], 1);
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kAttnStages; ++s) {
+      dev::mbar_init(&full[s], 1);
+      dev::mbar_init(&empty[s], kAttnWarps);
+    }
     dev::fence_mbar_init();
   }
   __syncthreads();
-  if (tid == 0) {
-    const int grow = bh * L + row0;  // row in the [B*Hkv*L, 128] view
-    dev::mbar_expect_tx(&bars[0], 32768);
-    dev::tma_load_2d(ks, &kmap, &bars[0], 0, grow);
-    dev::tma_load_2d(ks + 16384, &kmap, &bars[0], 64, grow);
-    dev::mbar_expect_tx(&bars[1], 32768);
-    dev::tma_load_2d(vs, &vmap, &bars[1], 0, grow);
-    dev::tma_load_2d(vs + 16384, &vmap, &bars[1], 64, grow);
-  }
-  // q of the R heads of this kv head, pre-multiplied by the softmax scale
-  for (int i = tid; i < R * kHd; i += 128) {
-    const int h = i / kHd, d = i % kHd;
-    qs[i] = dev::bf16_bits_to_float(q[(static_cast<size_t>(b) * Hq + kvh * R + h) * kHd + d]) * scale;
-  }
-  __syncthreads();
-  if (!dev::mbar_wait(&bars[0], 0, status, 31)) return;
 
-  // scores: thread = cache row
-  float sc[R];
-#pragma unroll
-  for (int h = 0; h < R; ++h) sc[h] = 0.f;
-  const int r = tid;
-#pragma unroll
-  for (int box = 0; box < 2; ++box) {
-#pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      const uint4 kv = *reinterpret_cast<const uint4*>(ks + box * 16384 + r * 128 + ((c ^ (r & 7)) << 4));
-      const uint32_t w[4] = {kv.x, kv.y, kv.z, kv.w};
-      const int d0 = box * 64 + c * 8;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 kk = bf2_to_f2(w[j]);
-#pragma unroll
-        for (int h = 0; h < R; ++h) {
-          const float2 qq = *reinterpret_cast<const float2*>(qs + h * kHd + d0 + 2 * j);
-          sc[h] = fmaf(kk.x, qq.x, fmaf(kk.y, qq.y, sc[h]));
-        }
+  if (warp == kAttnWarps) {
+    // ------------------------------ producer -------------------------------
+    if (lane == 0) {
+      const uint64_t policy = dev::policy_evict_first();
+      int s = 0;
+      uint32_t ph = 0;
+      for (int t = t_begin; t < t_end; ++t) {
+        if (!dev::mbar_wait(&empty[s], ph ^ 1, status, 31)) break;
+        uint8_t* st = smem + s * kAttnStageBytes;
+        const int grow = bh * L + t * kTileRows;  // row in the [B*Hkv*L, 128] view
+        dev::mbar_expect_tx(&full[s], kAttnStageBytes);
+        dev::tma_load_2d_hint(st, &kmap, &full[s], 0, grow, policy);
+        dev::tma_load_2d_hint(st + 8192, &kmap, &full[s], 64, grow, policy);
+        dev::tma_load_2d_hint(st + 16384, &vmap, &full[s], 0, grow, policy);
+        dev::tma_load_2d_hint(st + 24576, &vmap, &full[s], 64, grow, policy);
+        if (++s == kAttnStages) { s = 0; ph ^= 1; }
       }
     }
+    return;
   }
-  const bool valid = row0 + r < L;
-  // chunk max per head
-  float mx[R];
-#pragma unroll
-  for (int h = 0; h < R; ++h) {
-    float v = valid ? sc[h] : -INFINITY;
-    for (int off = 16; off >= 1; off >>= 1) v = fmaxf(v, __shfl_xor_sync(0xFFFFFFFFu, v, off));
-    if (lane == 0) red[warp * R + h] = v;
-  }
-  __syncthreads();
-#pragma unroll
-  for (int h = 0; h < R; ++h) mx[h] = fmaxf(fmaxf(red[h], red[R + h]), fmaxf(red[2 * R + h], red[3 * R + h]));
-  __syncthreads();
-  float sm[R];
-#pragma unroll
-  for (int h = 0; h < R; ++h) {
-    const float p = valid ? __expf(sc[h] - mx[h]) : 0.f;
-    ps[r * R + h] = p;
-    float v = p;
-    for (int off = 16; off >= 1; off >>= 1) v += __shfl_xor_sync(0xFFFFFFFFu, v, off);
-    if (lane == 0) red[warp * R + h] = v;
-  }
-  __syncthreads();
-#pragma unroll
-  for (int h = 0; h < R; ++h) sm[h] = red[h] + red[R + h] + red[2 * R + h] + red[3 * R + h];
 
-  // P.V: thread = (d pair, row half)
-  if (!dev::mbar_wait(&bars[1], 0, status, 32)) return;
-  const int dp = tid & 63, half = tid >> 6;
-  const int box = dp >> 5, cc = (dp & 31) >> 2, within = (dp & 3) * 4;  // 16-byte chunk and byte offset in it
-  float2 o[R];
+  // -------------------------------- consumers -------------------------------
+  const int g8 = lane >> 2, t4 = lane & 3;  // this thread's head (if g8 < R) and column pair
+  // Q fragments of the A operand: head g8, d = 16 ks + 2 t4 (+1) and + 8
+  uint32_t qa[8][2];
+  {
+    const uint16_t* qrow = q + static_cast<size_t>(b) * q_ld + static_cast<size_t>(kvh * R + g8) * kHd;
 #pragma unroll
-  for (int h = 0; h < R; ++h) o[h] = make_float2(0.f, 0.f);
-  for (int i = 0; i < 64; ++i) {
-    const int l = half * 64 + i;
-    const uint32_t vv = *reinterpret_cast<const uint32_t*>(vs + box * 16384 + l * 128 + ((cc ^ (l & 7)) << 4) + within);
-    const float2 vf = bf2_to_f2(vv);
-#pragma unroll
-    for (int h = 0; h < R; ++h) {
-      const float p = ps[l * R + h];
-      o[h].x = fmaf(p, vf.x, o[h].x);
-      o[h].y = fmaf(p, vf.y, o[h].y);
+    for (int ks = 0; ks < 8; ++ks) {
+      qa[ks][0] = g8 < R ? *reinterpret_cast<const uint32_t*>(qrow + 16 * ks + 2 * t4) : 0u;
+      qa[ks][1] = g8 < R ? *reinterpret_cast<const uint32_t*>(qrow + 16 * ks + 2 * t4 + 8) : 0u;
     }
   }
-  if (half == 1) {
+  const float sl2 = scale * 1.4426950408889634f;  // scores in log2 units
+  float m_run = -INFINITY, l_run = 0.f;
+  float o[16][4];
 #pragma unroll
-    for (int h = 0; h < R; ++h) *reinterpret_cast<float2*>(ored + (dp * R + h) * 2) = o[h];
-  }
-  __syncthreads();
-  if (half == 0) {
-    // part layout: [bh][chunk][head][2 + 128] = (max, sum, o[128])
+  for (int nt = 0; nt < 16; ++nt)
 #pragma unroll
-    for (int h = 0; h < R; ++h) {
-      const float2 u = *reinterpret_cast<const float2*>(ored + (dp * R + h) * 2);
-      float* dst = part + ((static_cast<size_t>(bh) * nchunks + chunk) * R + h) * (kHd + 2);
-      *reinterpret_cast<float2*>(dst + 2 + 2 * dp) = make_float2(o[h].x + u.x, o[h].y + u.y);
-      if (dp == 0) {
-        dst[0] = mx[h];
-        dst[1] = sm[h];
+    for (int i = 0; i < 4; ++i) o[nt][i] = 0.f;
+
+  // ldmatrix lane roles
+  const int mi = lane >> 3, rin = lane & 7;
+  const int krow = warp * 16 + (mi >> 1) * 8 + rin;  // K: matrices (rows lo, d lo), (rows lo, d hi), (rows hi, d lo), (rows hi, d hi)
+  const int kchunk = mi & 1;
+  const int vrow = warp * 16 + (mi & 1) * 8 + rin;   // V: (rows lo, d), (rows hi, d), (rows lo, d + 8), (rows hi, d + 8)
+  const int vchunk = mi >> 1;
+
+  int s = 0;
+  uint32_t ph = 0;
+  for (int t = t_begin; t < t_end; ++t) {
+    if (!dev::mbar_wait(&full[s], ph, status, 32)) return;
+    const uint32_t kb = dev::smem_u32(smem + s * kAttnStageBytes);
+    const uint32_t vb = kb + 16384;
+    float sacc[2][4];
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) sacc[nt][i] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < 8; ++ks) {
+      const int c16 = 2 * ks + kchunk;  // 16-byte chunk of the 256-byte row
+      uint32_t r[4];
+      ldsm_x4(kb + (c16 >> 3) * 8192 + krow * 128 + (((c16 & 7) ^ (krow & 7)) << 4), r);
+      mma_heads(sacc[0], qa[ks][0], qa[ks][1], r[0], r[1]);
+      mma_heads(sacc[1], qa[ks][0], qa[ks][1], r[2], r[3]);
+    }
+    // sacc[nt][0..1] = scores of head g8 against rows 16 warp + 8 nt + 2 t4 (+1)
+    const int row0 = t * kTileRows + warp * 16 + 2 * t4;
+    float tv[2][2], tmax = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        tv[nt][i] = (row0 + 8 * nt + i < L) ? sacc[nt][i] * sl2 : -INFINITY;
+        tmax = fmaxf(tmax, tv[nt][i]);
       }
+    tmax = fmaxf(tmax, __shfl_xor_sync(0xFFFFFFFFu, tmax, 1));
+    tmax = fmaxf(tmax, __shfl_xor_sync(0xFFFFFFFFu, tmax, 2));
+    const float m_new = fmaxf(m_run, tmax);
+    const float m_use = (m_new == -INFINITY) ? 0.f : m_new;  // a slab with no valid row yet
+    const float alpha = exp2f(m_run - m_use);
+    float p[2][2], psum = 0.f;
+#pragma unroll
+    for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        p[nt][i] = exp2f(tv[nt][i] - m_use);
+        psum += p[nt][i];
+      }
+    psum += __shfl_xor_sync(0xFFFFFFFFu, psum, 1);
+    psum += __shfl_xor_sync(0xFFFFFFFFu, psum, 2);
+    l_run = l_run * alpha + psum;
+    m_run = m_new;
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt) {
+      o[nt][0] *= alpha;
+      o[nt][1] *= alpha;
+    }
+    const uint32_t pa0 = dev::pack_bf16x2(p[0][0], p[0][1]);  // rows 2 t4 (+1)
+    const uint32_t pa2 = dev::pack_bf16x2(p[1][0], p[1][1]);  // rows 8 + 2 t4 (+1)
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int c16 = 2 * j + vchunk;
+      uint32_t r[4];
+      ldsm_x4_t(vb + (c16 >> 3) * 8192 + vrow * 128 + (((c16 & 7) ^ (vrow & 7)) << 4), r);
+      mma_heads(o[2 * j], pa0, pa2, r[0], r[1]);
+      mma_heads(o[2 * j + 1], pa0, pa2, r[2], r[3]);
+    }
+    __syncwarp();
+    if (lane == 0) dev::mbar_arrive(&empty[s]);
+    if (++s == kAttnStages) { s = 0; ph ^= 1; }
+  }
+
+  // merge the four warps through the (now idle) first ring stage:
+  // mrg[warp][head][2 + 128] = (max, sum, o)
+  asm volatile("bar.sync 1, %0;" ::"n"(kAttnWarps * 32));  // every warp is past its last tile read
+  float* mrg = reinterpret_cast<float*>(smem);
+  if (g8 < R) {
+    float* dst = mrg + (warp * R + g8) * (kHd + 2);
+    if (t4 == 0) {
+      dst[0] = m_run;
+      dst[1] = l_run;
+    }
+#pragma unroll
+    for (int nt = 0; nt < 16; ++nt)
+      *reinterpret_cast<float2*>(dst + 2 + 8 * nt + 2 * t4) = make_float2(o[nt][0], o[nt][1]);
+  }
+  asm volatile("bar.sync 1, %0;" ::"n"(kAttnWarps * 32));
+  // part layout: [bh][split][head][2 + 128] = (max in natural-log units, sum, o[128])
+  const int d = threadIdx.x;  // 0..127
+  for (int h = 0; h < R; ++h) {
+    float mw[kAttnWarps], m_tot = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) {
+      mw[w] = mrg[(w * R + h) * (kHd + 2)];
+      m_tot = fmaxf(m_tot, mw[w]);
+    }
+    float l_tot = 0.f, acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < kAttnWarps; ++w) {
+      const float wgt = (mw[w] == -INFINITY) ? 0.f : exp2f(mw[w] - m_tot);
+      l_tot = fmaf(wgt, mrg[(w * R + h) * (kHd + 2) + 1], l_tot);
+      acc = fmaf(wgt, mrg[(w * R + h) * (kHd + 2) + 2 + d], acc);
+    }
+    float* dst = part + ((static_cast<size_t>(bh) * nsplit + split) * R + h) * (kHd + 2);
+    dst[2 + d] = acc;
+    if (d == 0) {
+      dst[0] = m_tot * 0.6931471805599453f;
+      dst[1] = l_tot;
     }
   }
 }
 
-// one block per (b, q head): merge the chunks and the new key/value row
+// one block per (b, q head): merge the splits and the new key/value row
 __global__ void __launch_bounds__(128)
 attn_combine_kernel(const float* __restrict__ part, const uint16_t* __restrict__ q,
                     const uint16_t* __restrict__ knew, const uint16_t* __restrict__ vnew,
-                    uint16_t* __restrict__ out, int Hq, int Hkv, int R, int nchunks, float scale) {
+                    uint16_t* __restrict__ out, int Hq, int Hkv, int R, int nsplit, float scale, long long q_ld,
+                    long long new_ld) {
   const int b = blockIdx.x / Hq, hq = blockIdx.x % Hq;
   const int kvh = hq / R, h = hq % R;
   const int bh = b * Hkv + kvh;
   const int d = threadIdx.x;
   __shared__ float red[4];
   // score of the new row
-  const float qd = dev::bf16_bits_to_float(q[(static_cast<size_t>(b) * Hq + hq) * kHd + d]) * scale;
-  const float kd = dev::bf16_bits_to_float(knew[static_cast<size_t>(bh) * kHd + d]);
+  const float qd = dev::bf16_bits_to_float(q[static_cast<size_t>(b) * q_ld + static_cast<size_t>(hq) * kHd + d]);
+  const float kd = dev::bf16_bits_to_float(knew[static_cast<size_t>(b) * new_ld + static_cast<size_t>(kvh) * kHd + d]);
   float s = qd * kd;
   for (int off = 16; off >= 1; off >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, off);
   if ((d & 31) == 0) red[d >> 5] = s;
   __syncthreads();
-  const float s_new = red[0] + red[1] + red[2] + red[3];
+  const float s_new = (red[0] + red[1] + red[2] + red[3]) * scale;
   float m = s_new;
-  const float* base = part + (static_cast<size_t>(bh) * nchunks * R + h) * (kHd + 2);
+  const float* base = part + (static_cast<size_t>(bh) * nsplit * R + h) * (kHd + 2);
   const size_t stride = static_cast<size_t>(R) * (kHd + 2);
-  for (int c = 0; c < nchunks; ++c) m = fmaxf(m, base[c * stride]);
+  for (int c = 0; c < nsplit; ++c) m = fmaxf(m, base[c * stride]);
   float denom = __expf(s_new - m);
-  float acc = denom * dev::bf16_bits_to_float(vnew[static_cast<size_t>(bh) * kHd + d]);
-  for (int c = 0; c < nchunks; ++c) {
+  float acc = denom * dev::bf16_bits_to_float(vnew[static_cast<size_t>(b) * new_ld + static_cast<size_t>(kvh) * kHd + d]);
+  for (int c = 0; c < nsplit; ++c) {
     const float* p = base + c * stride;
     const float wgt = __expf(p[0] - m);
     denom = fmaf(wgt, p[1], denom);
@@ -454,13 +539,16 @@ int qmm_add_rmsnorm_bf16(const uint16_t* x, const uint16_t* residual, const uint
 }
 
 int qmm_rope_bf16(uint16_t* q, uint16_t* k, const int32_t* positions, int64_t B, int64_t Hq, int64_t Hkv,
-                  int64_t head_dim, float theta, void* stream) {
+                  int64_t head_dim, float theta, int64_t q_ld, int64_t k_ld, void* stream) {
   using namespace qmm;
   QMM_REQUIRE(q && k && positions, QMM_ERR_INVALID_ARGUMENT, "qmm_rope_bf16: null pointer");
-  QMM_REQUIRE(B >= 0 && Hq > 0 && Hkv > 0 && head_dim > 0 && head_dim % 2 == 0, QMM_ERR_INVALID_ARGUMENT,
-              "qmm_rope_bf16: bad shape");
+  QMM_REQUIRE(B >= 0 && Hq > 0 && Hkv > 0 && head_dim > 0 && head_dim % 2 == 0 && q_ld >= Hq * head_dim &&
+                  k_ld >= Hkv * head_dim && B * (Hq + Hkv) * head_dim < (1ll << 31),
+              QMM_ERR_INVALID_ARGUMENT, "qmm_rope_bf16: bad shape");
   if (B == 0) return QMM_OK;
-  dec::rope_kernel<<<(unsigned)B, 256, 0, (cudaStream_t)stream>>>(q, k, positions, (int)Hq, (int)Hkv, (int)head_dim, theta);
+  const long long threads = B * (Hq + Hkv) * (head_dim / 2);
+  dec::rope_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
+      q, k, positions, (int)B, (int)Hq, (int)Hkv, (int)head_dim, theta, (long long)q_ld, (long long)k_ld);
   QMM_CHECK_LAUNCH("rope_kernel");
   return QMM_OK;
 }
@@ -478,16 +566,29 @@ int qmm_silu_mul_bf16(const uint16_t* gate, const uint16_t* up, uint16_t* out, i
   return QMM_OK;
 }
 
+namespace qmm {
+namespace dec {
+// Splits per (b, kv head): enough CTAs to put two on every SM, at most one per tile.
+static int attn_splits(int64_t B, int64_t Hkv, int64_t L) {
+  const int64_t ntiles = (L + kTileRows - 1) / kTileRows;
+  if (ntiles <= 0) return 0;
+  int64_t want = (2 * static_cast<int64_t>(num_sms())) / (B * Hkv);
+  if (want < 1) want = 1;
+  return static_cast<int>(want < ntiles ? want : ntiles);
+}
+}  // namespace dec
+}  // namespace qmm
+
 size_t qmm_attention_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, int64_t L) {
   if (B <= 0 || Hq <= 0 || Hkv <= 0 || L < 0 || Hq % Hkv) return 0;
-  const int64_t nchunks = (L + qmm::dec::kChunk - 1) / qmm::dec::kChunk;
-  return static_cast<size_t>(B * Hq * (nchunks > 0 ? nchunks : 1)) * (qmm::dec::kHd + 2) * sizeof(float);
+  const int nsplit = qmm::dec::attn_splits(B, Hkv, L);
+  return static_cast<size_t>(B * Hq * (nsplit > 0 ? nsplit : 1)) * (qmm::dec::kHd + 2) * sizeof(float);
 }
 
 int qmm_attention_decode_bf16(const uint16_t* q, const uint16_t* kcache, const uint16_t* vcache,
                               const uint16_t* knew, const uint16_t* vnew, uint16_t* out, int64_t B, int64_t Hq,
-                              int64_t Hkv, int64_t L, int64_t head_dim, float scale, void* workspace,
-                              size_t workspace_bytes, void* stream) {
+                              int64_t Hkv, int64_t L, int64_t head_dim, float scale, int64_t q_ld, int64_t new_ld,
+                              void* workspace, size_t workspace_bytes, void* stream) {
   using namespace qmm;
   using namespace qmm::dec;
   QMM_REQUIRE(q && knew && vnew && out && (L == 0 || (kcache && vcache)), QMM_ERR_INVALID_ARGUMENT,
@@ -495,10 +596,12 @@ int qmm_attention_decode_bf16(const uint16_t* q, const uint16_t* kcache, const u
   QMM_REQUIRE(head_dim == kHd, QMM_ERR_UNSUPPORTED, "qmm_attention_decode_bf16: head_dim must be 128");
   QMM_REQUIRE(B > 0 && Hkv > 0 && Hq % Hkv == 0 && L >= 0 && B * Hkv <= 65535 && B * Hkv * L < (1ll << 31),
               QMM_ERR_INVALID_ARGUMENT, "qmm_attention_decode_bf16: bad shape");
+  QMM_REQUIRE(q_ld >= Hq * kHd && new_ld >= Hkv * kHd && q_ld % 2 == 0 && aligned(q, 4), QMM_ERR_INVALID_ARGUMENT,
+              "qmm_attention_decode_bf16: q_ld / new_ld smaller than a row, or q not 4-byte aligned");
   const int R = static_cast<int>(Hq / Hkv);
-  QMM_REQUIRE(R == 1 || R == 2 || R == 4 || R == 8, QMM_ERR_UNSUPPORTED,
-              "qmm_attention_decode_bf16: %d query heads per kv head (supported: 1, 2, 4, 8)", R);
-  const int nchunks = static_cast<int>((L + kChunk - 1) / kChunk);
+  QMM_REQUIRE(R >= 1 && R <= 8, QMM_ERR_UNSUPPORTED,
+              "qmm_attention_decode_bf16: %d query heads per kv head (supported: 1 to 8)", R);
+  const int nsplit = attn_splits(B, Hkv, L);
   const size_t need = qmm_attention_decode_workspace_bytes(B, Hq, Hkv, L);
   QMM_REQUIRE(workspace && workspace_bytes >= need, QMM_ERR_WORKSPACE,
               "qmm_attention_decode_bf16: %zu bytes of workspace required", need);
@@ -506,34 +609,29 @@ int qmm_attention_decode_bf16(const uint16_t* q, const uint16_t* kcache, const u
     return set_error(QMM_ERR_TIMEOUT, "a previous kernel gave up waiting (status word 0x%x)", st);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   float* part = static_cast<float*>(workspace);
-  if (nchunks > 0) {
+  if (nsplit > 0) {
+    QMM_REQUIRE(aligned(kcache, 16) && aligned(vcache, 16), QMM_ERR_INVALID_ARGUMENT,
+                "qmm_attention_decode_bf16: the cache must be 16-byte aligned");
     CUtensorMap kmap, vmap;
     const uint64_t rows = static_cast<uint64_t>(B * Hkv * L);
-    if (int rc = make_tensor_map_2d(&kmap, kcache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows, kHd, kHd * 2, kChunk, 64,
-                                    CU_TENSOR_MAP_SWIZZLE_128B))
+    if (int rc = make_tensor_map_2d(&kmap, kcache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows, kHd, kHd * 2, kTileRows,
+                                    64, CU_TENSOR_MAP_SWIZZLE_128B))
       return rc;
-    if (int rc = make_tensor_map_2d(&vmap, vcache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows, kHd, kHd * 2, kChunk, 64,
-                                    CU_TENSOR_MAP_SWIZZLE_128B))
+    if (int rc = make_tensor_map_2d(&vmap, vcache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows, kHd, kHd * 2, kTileRows,
+                                    64, CU_TENSOR_MAP_SWIZZLE_128B))
       return rc;
-    const size_t smem = 65536 + (R * kHd + kChunk * R + 4 * R + 64 * R * 2) * sizeof(float) + 64 + 1024;
-    dim3 grid(nchunks, static_cast<unsigned>(B * Hkv));
-#define QMM_ATTN(RR)                                                                                         \
-  {                                                                                                          \
-    static bool configured = false;                                                                          \
-    if (!configured) {                                                                                       \
-      QMM_CUDA_TRY(cudaFuncSetAttribute(attn_partial_kernel<RR>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
-                                        (int)(65536 + (RR * kHd + kChunk * RR + 4 * RR + 64 * RR * 2) * 4 + 64 + 1024))); \
-      configured = true;                                                                                     \
-    }                                                                                                        \
-    attn_partial_kernel<RR><<<grid, 128, smem, s>>>(kmap, vmap, q, part, (int)Hq, (int)Hkv, (int)L, nchunks, scale, \
-                                                    device_status_word());                                   \
-  }
-    if (R == 1) QMM_ATTN(1) else if (R == 2) QMM_ATTN(2) else if (R == 4) QMM_ATTN(4) else QMM_ATTN(8)
-#undef QMM_ATTN
+    static bool configured = false;
+    if (!configured) {
+      QMM_CUDA_TRY(cudaFuncSetAttribute(attn_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));
+      configured = true;
+    }
+    dim3 grid(nsplit, static_cast<unsigned>(B * Hkv));
+    attn_partial_kernel<<<grid, kAttnThreads, kAttnSmem, s>>>(kmap, vmap, q, part, (int)Hq, (int)Hkv, R, (int)L, nsplit,
+                                                             scale, (long long)q_ld, device_status_word());
     QMM_CHECK_LAUNCH("attn_partial_kernel");
   }
-  attn_combine_kernel<<<static_cast<unsigned>(B * Hq), 128, 0, s>>>(part, q, knew, vnew, out, (int)Hq, (int)Hkv, R, nchunks,
-                                                                    scale);
+  attn_combine_kernel<<<static_cast<unsigned>(B * Hq), 128, 0, s>>>(part, q, knew, vnew, out, (int)Hq, (int)Hkv, R, nsplit,
+                                                                    scale, (long long)q_ld, (long long)new_ld);
   QMM_CHECK_LAUNCH("attn_combine_kernel");
   return QMM_OK;
 }

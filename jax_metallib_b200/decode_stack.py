@@ -6,12 +6,16 @@ vocab 128256), random-init, every linear projection quantized to int4 with
 asymmetric group-wise (128 along K) parameters, bf16 activations, an
 unquantized bf16 lm_head; decode of one token per sequence over a KV cache of
 a given context.  All seven projections of a layer go through
-``qmm_w4a16_g128``; the other operators are the small kernels of
-``csrc/decode_ops.cu``.  The KV cache is a read-only input and the step
+``qmm_w4a16_g128``, as four launches: q, k, v share their input, so their
+packed weights, scales and zero points are laid side by side along N at load
+time and run as one matmul, and likewise gate and up (per output column the
+arithmetic is that of the separate projection).  The other operators are the
+small kernels of ``csrc/decode_ops.cu``; rope and attention read the q | k | v
+slices of the fused output in place.  The KV cache is a read-only input and the step
 returns the new K/V rows (the reference has no buffer donation, so a step that
 returned an updated cache would copy it whole, src/pjrt_plugin/api/pjrt_api.cc:310).
 
-``DecodeStep`` pre-allocates every buffer, issues the ~420 launches of a step
+``DecodeStep`` pre-allocates every buffer, issues the ~320 launches of a step
 on the current stream and can capture them in a CUDA graph for replay.
 """
 
@@ -65,6 +69,17 @@ def random_int4_linear(k: int, n: int, group: int, device, gen) -> dict:
     }
 
 
+def fuse_linears(lins: list) -> dict:
+    """Projections that share their input, laid side by side along N (packed weights, scales and
+    packed zero points all have N as their last axis; every N here is even, so zero-point bytes
+    do not straddle a boundary)."""
+    assert all(l["k"] == lins[0]["k"] and l["n"] % 2 == 0 for l in lins)
+    return {"wq": torch.cat([l["wq"] for l in lins], dim=1).contiguous(),
+            "s": torch.cat([l["s"] for l in lins], dim=1).contiguous(),
+            "z": torch.cat([l["z"] for l in lins], dim=1).contiguous(),
+            "k": lins[0]["k"], "n": sum(l["n"] for l in lins)}
+
+
 def random_model(shape: LlamaShape, device, seed: int = 4000) -> dict:
     gen = torch.Generator(device=device)
     gen.manual_seed(seed)
@@ -103,17 +118,21 @@ class DecodeStep:
         self.h = buf(B, s.d_model)        # residual stream
         self.h2 = buf(B, s.d_model)
         self.n = buf(B, s.d_model)        # normed activations
-        self.q = buf(B, s.n_heads * s.head_dim)
-        self.attn = buf(B, s.n_heads * s.head_dim)
+        nq, nkv = s.n_heads * s.head_dim, s.n_kv_heads * s.head_dim
+        # one q | k | v row per layer and sequence: the new K/V rows a step returns are slices of it
+        self.qkv = buf(s.n_layers, B, nq + 2 * nkv)
+        self.new_k = self.qkv[:, :, nq:nq + nkv]
+        self.new_v = self.qkv[:, :, nq + nkv:]
+        self.attn = buf(B, nq)
         self.o = buf(B, s.d_model)
-        self.gate = buf(B, s.ffn)
-        self.up = buf(B, s.ffn)
+        self.gate_up = buf(B, 2 * s.ffn)
         self.act = buf(B, s.ffn)
         self.down = buf(B, s.d_model)
-        self.new_k = buf(s.n_layers, B, s.n_kv_heads * s.head_dim)
-        self.new_v = buf(s.n_layers, B, s.n_kv_heads * s.head_dim)
         self.logits = buf(B, s.vocab)
-        need = max(self.lib.qmm_w4a16_g128_workspace_bytes(B, n, k) for k, n in s.linears().values())
+        self.fused = [{"qkv": fuse_linears([layer["q"], layer["k"], layer["v"]]),
+                       "gate_up": fuse_linears([layer["gate"], layer["up"]])} for layer in model["layers"]]
+        need = max(self.lib.qmm_w4a16_g128_workspace_bytes(B, n, k)
+                   for k, n in [(s.d_model, nq + 2 * nkv), (nq, s.d_model), (s.d_model, 2 * s.ffn), (s.ffn, s.d_model)])
         self.w4_ws = torch.zeros(need, dtype=torch.uint8, device=device)
         self.attn_ws = torch.empty(max(1, self.lib.qmm_attention_decode_workspace_bytes(B, s.n_heads, s.n_kv_heads,
                                                                                         context)),
@@ -152,23 +171,23 @@ class DecodeStep:
             else:
                 # h <- h2 + down of the previous layer, and its norm, in one launch
                 self._norm(self.h2, pending, layer["attn_norm"], self.h, self.n, stream)
-            k_new, v_new = self.new_k[li], self.new_v[li]
-            self._linear(self.n, layer["q"], self.q, stream)
-            self._linear(self.n, layer["k"], k_new, stream)
-            self._linear(self.n, layer["v"], v_new, stream)
-            _lib.check(lib.qmm_rope_bf16(self.q.data_ptr(), k_new.data_ptr(), self.pos.data_ptr(), B, s.n_heads,
-                                         s.n_kv_heads, s.head_dim, ctypes.c_float(s.rope_theta), stream))
+            qkv = self.qkv[li]
+            nq, nkv, ld = s.n_heads * s.head_dim, s.n_kv_heads * s.head_dim, qkv.shape[1]
+            q_ptr = qkv.data_ptr()
+            k_ptr, v_ptr = q_ptr + 2 * nq, q_ptr + 2 * (nq + nkv)
+            self._linear(self.n, self.fused[li]["qkv"], qkv, stream)
+            _lib.check(lib.qmm_rope_bf16(q_ptr, k_ptr, self.pos.data_ptr(), B, s.n_heads, s.n_kv_heads, s.head_dim,
+                                         ctypes.c_float(s.rope_theta), ld, ld, stream))
             _lib.check(lib.qmm_attention_decode_bf16(
-                self.q.data_ptr(), kcache[li].data_ptr(), vcache[li].data_ptr(), k_new.data_ptr(), v_new.data_ptr(),
-                self.attn.data_ptr(), B, s.n_heads, s.n_kv_heads, self.L, s.head_dim,
-                ctypes.c_float(1.0 / (s.head_dim ** 0.5)), self.attn_ws.data_ptr(), self.attn_ws.numel(), stream))
+                q_ptr, kcache[li].data_ptr(), vcache[li].data_ptr(), k_ptr, v_ptr, self.attn.data_ptr(), B, s.n_heads,
+                s.n_kv_heads, self.L, s.head_dim, ctypes.c_float(1.0 / (s.head_dim ** 0.5)), ld, ld,
+                self.attn_ws.data_ptr(), self.attn_ws.numel(), stream))
             self.launches_per_step += 3  # rope + two attention launches
             self._linear(self.attn, layer["o"], self.o, stream)
             self._norm(self.h, self.o, layer["mlp_norm"], self.h2, self.n, stream)
-            self._linear(self.n, layer["gate"], self.gate, stream)
-            self._linear(self.n, layer["up"], self.up, stream)
-            _lib.check(lib.qmm_silu_mul_bf16(self.gate.data_ptr(), self.up.data_ptr(), self.act.data_ptr(), B, s.ffn,
-                                             s.ffn, stream))
+            self._linear(self.n, self.fused[li]["gate_up"], self.gate_up, stream)
+            _lib.check(lib.qmm_silu_mul_bf16(self.gate_up.data_ptr(), self.gate_up.data_ptr() + 2 * s.ffn,
+                                             self.act.data_ptr(), B, s.ffn, 2 * s.ffn, stream))
             self.launches_per_step += 1
             self._linear(self.act, layer["down"], self.down, stream)
             pending = self.down

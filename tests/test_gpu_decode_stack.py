@@ -58,19 +58,32 @@ def test_add_rmsnorm(cuda, with_residual):
     assert O.max_rel_err(f32(n_out), D.rmsnorm(h, w, 1e-5)) <= 1e-2
 
 
-def test_rope(cuda):
+@pytest.mark.parametrize("fused", [False, True])
+def test_rope(cuda, fused):
     lib = _lib.load()
     rng = np.random.default_rng(3)
     B, Hq, Hkv, hd = 4, 8, 2, 128
     q = O.round_to_bf16(rng.standard_normal((B, Hq, hd)).astype(np.float32))
     k = O.round_to_bf16(rng.standard_normal((B, Hkv, hd)).astype(np.float32))
     pos = np.array([0, 1, 2047, 100000], dtype=np.int32)
-    qt, kt, pt = bft(q, cuda), bft(k, cuda), torch.from_numpy(pos).to(cuda)
-    _lib.check(lib.qmm_rope_bf16(qt.data_ptr(), kt.data_ptr(), pt.data_ptr(), B, Hq, Hkv, hd,
-                                 ctypes.c_float(500000.0), stream()))
-    assert O.max_rel_err(f32(qt), D.rope(q, pos, 500000.0)) <= 1e-2
-    assert O.max_rel_err(f32(kt), D.rope(k, pos, 500000.0)) <= 1e-2
-    np.testing.assert_array_equal(f32(qt)[0], q[0])  # position 0 is the identity
+    pt = torch.from_numpy(pos).to(cuda)
+    if fused:
+        # q | k | v side by side in one buffer, as a fused projection writes them
+        buf = torch.zeros((B, (Hq + 2 * Hkv) * hd), dtype=torch.bfloat16, device=cuda)
+        buf[:, :Hq * hd] = bft(q, cuda).reshape(B, -1)
+        buf[:, Hq * hd:(Hq + Hkv) * hd] = bft(k, cuda).reshape(B, -1)
+        qt, kt = buf[:, :Hq * hd], buf[:, Hq * hd:(Hq + Hkv) * hd]
+        ld = buf.shape[1]
+        _lib.check(lib.qmm_rope_bf16(qt.data_ptr(), kt.data_ptr(), pt.data_ptr(), B, Hq, Hkv, hd,
+                                     ctypes.c_float(500000.0), ld, ld, stream()))
+        assert float(buf[:, (Hq + Hkv) * hd:].abs().max()) == 0.0  # the v slice is untouched
+    else:
+        qt, kt = bft(q, cuda), bft(k, cuda)
+        _lib.check(lib.qmm_rope_bf16(qt.data_ptr(), kt.data_ptr(), pt.data_ptr(), B, Hq, Hkv, hd,
+                                     ctypes.c_float(500000.0), Hq * hd, Hkv * hd, stream()))
+    assert O.max_rel_err(f32(qt).reshape(q.shape), D.rope(q, pos, 500000.0)) <= 1e-2
+    assert O.max_rel_err(f32(kt).reshape(k.shape), D.rope(k, pos, 500000.0)) <= 1e-2
+    np.testing.assert_array_equal(f32(qt).reshape(q.shape)[0], q[0])  # position 0 is the identity
 
 
 def test_silu_mul(cuda):
@@ -85,7 +98,8 @@ def test_silu_mul(cuda):
     assert O.max_rel_err(f32(out), D.silu_mul(g, u)) <= 1e-2
 
 
-@pytest.mark.parametrize("B,Hq,Hkv,L", [(8, 32, 8, 2048), (3, 4, 1, 300), (2, 8, 8, 128), (2, 16, 2, 1), (2, 8, 2, 0)])
+@pytest.mark.parametrize("B,Hq,Hkv,L", [(8, 32, 8, 2048), (3, 4, 1, 300), (2, 8, 8, 128), (2, 16, 2, 1), (2, 8, 2, 0),
+                                        (1, 6, 2, 65), (2, 8, 1, 1000), (16, 32, 8, 63), (1, 5, 1, 4099)])
 def test_attention_decode(cuda, B, Hq, Hkv, L):
     lib = _lib.load()
     rng = np.random.default_rng(5)
@@ -102,10 +116,50 @@ def test_attention_decode(cuda, B, Hq, Hkv, L):
     qt, knt, vnt = bft(q, cuda), bft(kn, cuda), bft(vn, cuda)
     _lib.check(lib.qmm_attention_decode_bf16(qt.data_ptr(), kct.data_ptr(), vct.data_ptr(), knt.data_ptr(),
                                              vnt.data_ptr(), out.data_ptr(), B, Hq, Hkv, L, hd,
-                                             ctypes.c_float(1 / np.sqrt(hd)), ws.data_ptr(), ws.numel(), stream()))
+                                             ctypes.c_float(1 / np.sqrt(hd)), Hq * hd, Hkv * hd, ws.data_ptr(),
+                                             ws.numel(), stream()))
     torch.cuda.synchronize()
     assert lib.qmm_device_status() == 0
-    assert O.max_rel_err(f32(out), D.attention_decode(q, kc, vc, kn, vn, 1 / np.sqrt(hd))) <= 1e-2
+    ref = D.attention_decode(q, kc, vc, kn, vn, 1 / np.sqrt(hd))
+    assert O.max_rel_err(f32(out), ref) <= 1e-2
+    # the same through slices of one fused q | k | v buffer
+    fused = torch.zeros((B, (Hq + 2 * Hkv) * hd), dtype=torch.bfloat16, device=cuda)
+    fused[:, :Hq * hd] = qt.reshape(B, -1)
+    fused[:, Hq * hd:(Hq + Hkv) * hd] = knt.reshape(B, -1)
+    fused[:, (Hq + Hkv) * hd:] = vnt.reshape(B, -1)
+    out2 = torch.empty_like(out)
+    ld = fused.shape[1]
+    _lib.check(lib.qmm_attention_decode_bf16(fused.data_ptr(), kct.data_ptr(), vct.data_ptr(),
+                                             fused[:, Hq * hd:].data_ptr(), fused[:, (Hq + Hkv) * hd:].data_ptr(),
+                                             out2.data_ptr(), B, Hq, Hkv, L, hd, ctypes.c_float(1 / np.sqrt(hd)), ld, ld,
+                                             ws.data_ptr(), ws.numel(), stream()))
+    torch.cuda.synchronize()
+    assert torch.equal(out, out2)
+
+
+def test_attention_decode_peaked_softmax(cuda):
+    """One cache row dominates (a score far above the rest) and sits in the ragged last tile."""
+    lib = _lib.load()
+    rng = np.random.default_rng(6)
+    B, Hq, Hkv, L, hd = 1, 4, 1, 200, 128
+    q = O.round_to_bf16(rng.standard_normal((B, Hq, hd)).astype(np.float32))
+    kc = O.round_to_bf16(rng.standard_normal((B, Hkv, L, hd)).astype(np.float32) * 0.1)
+    kc[0, 0, 199] = O.round_to_bf16(q[0, 1] * 8)  # head 1 attends to row 199 almost exclusively
+    vc = O.round_to_bf16(rng.standard_normal((B, Hkv, L, hd)).astype(np.float32))
+    kn = O.round_to_bf16(rng.standard_normal((B, Hkv, hd)).astype(np.float32) * 0.1)
+    vn = O.round_to_bf16(rng.standard_normal((B, Hkv, hd)).astype(np.float32))
+    out = torch.empty((B, Hq, hd), dtype=torch.bfloat16, device=cuda)
+    ws = torch.empty(lib.qmm_attention_decode_workspace_bytes(B, Hq, Hkv, L), dtype=torch.uint8, device=cuda)
+    kct, vct, qt, knt, vnt = bft(kc, cuda), bft(vc, cuda), bft(q, cuda), bft(kn, cuda), bft(vn, cuda)
+    _lib.check(lib.qmm_attention_decode_bf16(qt.data_ptr(), kct.data_ptr(), vct.data_ptr(), knt.data_ptr(),
+                                             vnt.data_ptr(), out.data_ptr(), B, Hq, Hkv, L, hd,
+                                             ctypes.c_float(1 / np.sqrt(hd)), Hq * hd, Hkv * hd, ws.data_ptr(),
+                                             ws.numel(), stream()))
+    torch.cuda.synchronize()
+    assert lib.qmm_device_status() == 0
+    ref = D.attention_decode(q, kc, vc, kn, vn, 1 / np.sqrt(hd))
+    assert O.max_rel_err(f32(out), ref) <= 1e-2
+    assert O.max_rel_err(f32(out)[0, 1], vc[0, 0, 199]) <= 2e-2
 
 
 @pytest.mark.parametrize("M,K,N", [(8, 4096, 128256), (1, 64, 64), (16, 512, 1024), (5, 128, 192)])
