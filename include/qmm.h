@@ -221,9 +221,15 @@ QMM_API int qmm_mx_matmul(const void* x, const uint8_t* w_packed, const uint8_t*
  *   sequence over a read-only cache [B,Hkv,L,128] plus the new key/value row
  *   [B,Hkv,128]; batch rows of q are q_ld elements apart, those of knew / vnew
  *   new_ld; scores and P.V on the tensor cores (bf16 operands, f32 accumulate),
- *   softmax in f32; two launches (per-split partials, merge).
+ *   softmax in f32; two launches (per-split partials, merge).  flags:
+ *   QMM_ATTN_STATIC_CACHE states that no kernel still in flight on the stream
+ *   writes the cache (a step that returns the new rows instead of appending
+ *   them), so that the cache may be fetched before those kernels finish.
  * qmm_bf16_matmul_small_m: y[M,N] = bf16(x[M,K] @ w[K,N]), bf16 operands, f32
- *   accumulate, M <= 16 (the unquantized lm_head of the decode step). */
+ *   accumulate, M <= 16 (the unquantized lm_head of the decode step).
+ * All of these start early behind the previous kernel of the stream
+ * (programmatic stream serialization) and wait for it before touching data. */
+#define QMM_ATTN_STATIC_CACHE 1u
 QMM_API int qmm_take_rows_bf16(const uint16_t* table, const int32_t* ids, uint16_t* out, int64_t V,
                                int64_t D, int64_t B, uint16_t fill_bits, void* stream);
 QMM_API int qmm_add_rmsnorm_bf16(const uint16_t* x, const uint16_t* residual, const uint16_t* weight,
@@ -240,7 +246,7 @@ QMM_API int qmm_attention_decode_bf16(const uint16_t* q, const uint16_t* kcache,
                                       const uint16_t* vnew, uint16_t* out, int64_t B, int64_t Hq,
                                       int64_t Hkv, int64_t L, int64_t head_dim, float scale,
                                       int64_t q_ld, int64_t new_ld, void* workspace,
-                                      size_t workspace_bytes, void* stream);
+                                      size_t workspace_bytes, unsigned flags, void* stream);
 QMM_API int qmm_bf16_matmul_small_m(const uint16_t* x, const uint16_t* w, uint16_t* y, int64_t M,
                                     int64_t N, int64_t K, void* stream);
 

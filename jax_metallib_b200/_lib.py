@@ -16,6 +16,7 @@ LIB_PATH = os.environ.get("QMM_LIBRARY_PATH", os.path.join(HERE, "libqmm.so"))
 QMM_F32, QMM_F16, QMM_BF16, QMM_S8, QMM_U8, QMM_S32, QMM_U4, QMM_U32 = range(8)
 QMM_MXFP4, QMM_MXFP8, QMM_NVFP4 = range(3)
 QMM_W4_STATIC_WEIGHTS = 1
+QMM_ATTN_STATIC_CACHE = 1
 MX_MODE_IDS = {"mxfp4": QMM_MXFP4, "mxfp8": QMM_MXFP8, "nvfp4": QMM_NVFP4}
 
 # name -> (restype, argtypes); mirrors include/qmm.h
@@ -50,7 +51,7 @@ SIGNATURES = {
     "qmm_attention_decode_workspace_bytes": (c_size_t, [c_int64, c_int64, c_int64, c_int64]),
     "qmm_attention_decode_bf16": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_int64,
-                ctypes.c_float, c_int64, c_int64, c_void_p, c_size_t, c_void_p]),
+                ctypes.c_float, c_int64, c_int64, c_void_p, c_size_t, ctypes.c_uint, c_void_p]),
     "qmm_bf16_matmul_small_m": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]),
     "qmm_plan_compile": (c_int, [c_char_p, c_size_t, ctypes.POINTER(c_void_p)]),
     "qmm_plan_destroy": (None, [c_void_p]),

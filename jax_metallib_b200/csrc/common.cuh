@@ -39,6 +39,28 @@ int set_error(int status, const char* fmt, ...) __attribute__((format(printf, 2,
                               cudaGetErrorString(_e));                                  \
   } while (0)
 
+// Launch with programmatic stream serialization: the kernel may start while the
+// kernel before it on the stream is still running, and orders itself behind it
+// with griddepcontrol.wait (dev::pdl_wait) before it touches anything that
+// kernel, or one further back that may still be running, could write.
+// Every kernel launched this way calls dev::pdl_wait.
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+
 // A host-mapped status word that device-side bounded waits write to when they
 // give up (code in the low 16 bits, a site tag above).  Allocated once per
 // process; readable by the host without synchronising.
@@ -79,6 +101,12 @@ __device__ __forceinline__ float bf16_bits_to_float(uint16_t b) {
 // round-to-nearest-even, NaN -> quiet NaN with the sign kept
 __device__ __forceinline__ uint16_t float_to_bf16_bits(float f) {
   return __bfloat16_as_ushort(__float2bfloat16_rn(f));
+}
+// Programmatic dependent launch: wait for the kernels before this one on the
+// stream (complete and visible); allow the kernel after this one to start early.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 __device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
   __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);

@@ -3,7 +3,10 @@
 // gating, grouped-query decode attention over a read-only KV cache, and a
 // bf16 matmul for a few activation rows (the unquantized lm_head).
 // They are small next to the int4 linears; each is one launch, written to be
-// captured in a CUDA graph together with the quantized matmuls.
+// captured in a CUDA graph together with the quantized matmuls.  Every kernel
+// here is launched with programmatic stream serialization: it lets the next
+// kernel start at once (so that a following int4 matmul streams its weights
+// while this one runs) and waits for its predecessors before touching data.
 //
 // Reference semantics kept where the reference pins them: take-rows wraps
 // negative indices and fills out-of-range rows
@@ -27,6 +30,8 @@ __device__ __forceinline__ float2 bf2_to_f2(uint32_t v) {
 // ---------------------------------------------------------------------------
 __global__ void take_rows_kernel(const uint16_t* __restrict__ table, const int32_t* __restrict__ ids,
                                  uint16_t* __restrict__ out, int V, int D, uint16_t fill_bits) {
+  dev::pdl_launch_dependents();
+  dev::pdl_wait();
   const int b = blockIdx.x;
   int id = ids[b];
   if (id < 0) id += V;  // negative indices count from the end
@@ -44,6 +49,8 @@ __global__ void __launch_bounds__(256)
 add_rmsnorm_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ r,
                    const uint16_t* __restrict__ w, uint16_t* __restrict__ sum_out,
                    uint16_t* __restrict__ norm_out, int D, float eps) {
+  dev::pdl_launch_dependents();
+  dev::pdl_wait();
   const int row = blockIdx.x;
   const uint32_t* xp = reinterpret_cast<const uint32_t*>(x + static_cast<size_t>(row) * D);
   const uint32_t* rp = r ? reinterpret_cast<const uint32_t*>(r + static_cast<size_t>(row) * D) : nullptr;
@@ -85,6 +92,8 @@ add_rmsnorm_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ 
 __global__ void __launch_bounds__(256)
 rope_kernel(uint16_t* __restrict__ q, uint16_t* __restrict__ k, const int32_t* __restrict__ pos, int B, int Hq,
             int Hkv, int hd, float theta, long long q_ld, long long k_ld) {
+  dev::pdl_launch_dependents();
+  dev::pdl_wait();
   const int half = hd / 2;
   const int per_row = (Hq + Hkv) * half;
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;
@@ -108,6 +117,8 @@ rope_kernel(uint16_t* __restrict__ q, uint16_t* __restrict__ k, const int32_t* _
 // ---------------------------------------------------------------------------
 __global__ void silu_mul_kernel(const uint16_t* __restrict__ gate, const uint16_t* __restrict__ up,
                                 uint16_t* __restrict__ out, int F, long long ld_in) {
+  dev::pdl_launch_dependents();
+  dev::pdl_wait();
   const int row = blockIdx.y;
   const int i = blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= F / 2) return;
@@ -166,7 +177,8 @@ __host__ __device__ inline int split_begin(int s, int nsplit, int ntiles) {
 __global__ void __launch_bounds__(kAttnThreads)
 attn_partial_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_constant__ CUtensorMap vmap,
                     const uint16_t* __restrict__ q, float* __restrict__ part, int Hq, int Hkv, int R, int L,
-                    int nsplit, float scale, long long q_ld, int* status) {
+                    int nsplit, float scale, long long q_ld, int static_cache, int* status) {
+  dev::pdl_launch_dependents();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -190,6 +202,9 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
 
   if (warp == kAttnWarps) {
     // ------------------------------ producer -------------------------------
+    // A cache that no kernel still in flight writes can be fetched before the
+    // kernels ahead on the stream have finished.
+    if (!static_cache) dev::pdl_wait();
     if (lane == 0) {
       const uint64_t policy = dev::policy_evict_first();
       int s = 0;
@@ -210,6 +225,7 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
   }
 
   // -------------------------------- consumers -------------------------------
+  dev::pdl_wait();  // q comes from the kernels ahead; the partials go to a shared workspace
   const int g8 = lane >> 2, t4 = lane & 3;  // this thread's head (if g8 < R) and column pair
   // Q fragments of the A operand: head g8, d = 16 ks + 2 t4 (+1) and + 8
   uint32_t qa[8][2];
@@ -348,6 +364,8 @@ attn_combine_kernel(const float* __restrict__ part, const uint16_t* __restrict__
                     const uint16_t* __restrict__ knew, const uint16_t* __restrict__ vnew,
                     uint16_t* __restrict__ out, int Hq, int Hkv, int R, int nsplit, float scale, long long q_ld,
                     long long new_ld) {
+  dev::pdl_launch_dependents();
+  dev::pdl_wait();
   const int b = blockIdx.x / Hq, hq = blockIdx.x % Hq;
   const int kvh = hq / R, h = hq % R;
   const int bh = b * Hkv + kvh;
@@ -408,6 +426,8 @@ template <int MT>
 __global__ void __launch_bounds__(160)
 bf16_small_m_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
                     uint16_t* __restrict__ y, int M, int N, int K, int* status) {
+  dev::pdl_launch_dependents();
+  dev::pdl_wait();
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -515,8 +535,8 @@ int qmm_take_rows_bf16(const uint16_t* table, const int32_t* ids, uint16_t* out,
               "qmm_take_rows_bf16: bad shape (D must be a multiple of 8)");
   QMM_REQUIRE(aligned(table, 16) && aligned(out, 16), QMM_ERR_INVALID_ARGUMENT, "qmm_take_rows_bf16: 16-byte alignment");
   if (B == 0) return QMM_OK;
-  dec::take_rows_kernel<<<(unsigned)B, 256, 0, (cudaStream_t)stream>>>(table, ids, out, (int)V, (int)D, fill_bits);
-  QMM_CHECK_LAUNCH("take_rows_kernel");
+  QMM_CUDA_TRY(launch_pdl(dec::take_rows_kernel, dim3((unsigned)B), dim3(256), 0, (cudaStream_t)stream, table, ids, out,
+                          (int)V, (int)D, fill_bits));
   return QMM_OK;
 }
 
@@ -532,9 +552,8 @@ int qmm_add_rmsnorm_bf16(const uint16_t* x, const uint16_t* residual, const uint
     QMM_CUDA_TRY(cudaFuncSetAttribute(dec::add_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536));
     configured = true;
   }
-  dec::add_rmsnorm_kernel<<<(unsigned)B, 256, D * sizeof(float), (cudaStream_t)stream>>>(x, residual, weight, sum_out,
-                                                                                       norm_out, (int)D, eps);
-  QMM_CHECK_LAUNCH("add_rmsnorm_kernel");
+  QMM_CUDA_TRY(launch_pdl(dec::add_rmsnorm_kernel, dim3((unsigned)B), dim3(256), D * sizeof(float), (cudaStream_t)stream,
+                          x, residual, weight, sum_out, norm_out, (int)D, eps));
   return QMM_OK;
 }
 
@@ -547,9 +566,9 @@ int qmm_rope_bf16(uint16_t* q, uint16_t* k, const int32_t* positions, int64_t B,
               QMM_ERR_INVALID_ARGUMENT, "qmm_rope_bf16: bad shape");
   if (B == 0) return QMM_OK;
   const long long threads = B * (Hq + Hkv) * (head_dim / 2);
-  dec::rope_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, (cudaStream_t)stream>>>(
-      q, k, positions, (int)B, (int)Hq, (int)Hkv, (int)head_dim, theta, (long long)q_ld, (long long)k_ld);
-  QMM_CHECK_LAUNCH("rope_kernel");
+  QMM_CUDA_TRY(launch_pdl(dec::rope_kernel, dim3((unsigned)((threads + 255) / 256)), dim3(256), 0, (cudaStream_t)stream,
+                          q, k, positions, (int)B, (int)Hq, (int)Hkv, (int)head_dim, theta, (long long)q_ld,
+                          (long long)k_ld));
   return QMM_OK;
 }
 
@@ -561,8 +580,8 @@ int qmm_silu_mul_bf16(const uint16_t* gate, const uint16_t* up, uint16_t* out, i
               "qmm_silu_mul_bf16: bad shape");
   if (B == 0) return QMM_OK;
   dim3 grid((unsigned)((F / 2 + 255) / 256), (unsigned)B);
-  dec::silu_mul_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(gate, up, out, (int)F, (long long)ld_in);
-  QMM_CHECK_LAUNCH("silu_mul_kernel");
+  QMM_CUDA_TRY(launch_pdl(dec::silu_mul_kernel, grid, dim3(256), 0, (cudaStream_t)stream, gate, up, out, (int)F,
+                          (long long)ld_in));
   return QMM_OK;
 }
 
@@ -588,7 +607,7 @@ size_t qmm_attention_decode_workspace_bytes(int64_t B, int64_t Hq, int64_t Hkv, 
 int qmm_attention_decode_bf16(const uint16_t* q, const uint16_t* kcache, const uint16_t* vcache,
                               const uint16_t* knew, const uint16_t* vnew, uint16_t* out, int64_t B, int64_t Hq,
                               int64_t Hkv, int64_t L, int64_t head_dim, float scale, int64_t q_ld, int64_t new_ld,
-                              void* workspace, size_t workspace_bytes, void* stream) {
+                              void* workspace, size_t workspace_bytes, unsigned flags, void* stream) {
   using namespace qmm;
   using namespace qmm::dec;
   QMM_REQUIRE(q && knew && vnew && out && (L == 0 || (kcache && vcache)), QMM_ERR_INVALID_ARGUMENT,
@@ -626,13 +645,12 @@ int qmm_attention_decode_bf16(const uint16_t* q, const uint16_t* kcache, const u
       configured = true;
     }
     dim3 grid(nsplit, static_cast<unsigned>(B * Hkv));
-    attn_partial_kernel<<<grid, kAttnThreads, kAttnSmem, s>>>(kmap, vmap, q, part, (int)Hq, (int)Hkv, R, (int)L, nsplit,
-                                                             scale, (long long)q_ld, device_status_word());
-    QMM_CHECK_LAUNCH("attn_partial_kernel");
+    QMM_CUDA_TRY(launch_pdl(attn_partial_kernel, grid, dim3(kAttnThreads), kAttnSmem, s, kmap, vmap, q, part, (int)Hq,
+                            (int)Hkv, R, (int)L, nsplit, scale, (long long)q_ld,
+                            (flags & QMM_ATTN_STATIC_CACHE) ? 1 : 0, device_status_word()));
   }
-  attn_combine_kernel<<<static_cast<unsigned>(B * Hq), 128, 0, s>>>(part, q, knew, vnew, out, (int)Hq, (int)Hkv, R, nsplit,
-                                                                    scale, (long long)q_ld, (long long)new_ld);
-  QMM_CHECK_LAUNCH("attn_combine_kernel");
+  QMM_CUDA_TRY(launch_pdl(attn_combine_kernel, dim3(static_cast<unsigned>(B * Hq)), dim3(128), 0, s, part, q, knew, vnew,
+                          out, (int)Hq, (int)Hkv, R, nsplit, scale, (long long)q_ld, (long long)new_ld));
   return QMM_OK;
 }
 
@@ -665,10 +683,11 @@ int qmm_bf16_matmul_small_m(const uint16_t* x, const uint16_t* w, uint16_t* y, i
   const unsigned grid = static_cast<unsigned>((N + BN - 1) / BN);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (MT == 1)
-    bf16_small_m_kernel<1><<<grid, 160, kSmem, s>>>(wmap, xmap, y, (int)M, (int)N, (int)K, device_status_word());
+    QMM_CUDA_TRY(launch_pdl(bf16_small_m_kernel<1>, dim3(grid), dim3(160), kSmem, s, wmap, xmap, y, (int)M, (int)N, (int)K,
+                            device_status_word()));
   else
-    bf16_small_m_kernel<2><<<grid, 160, kSmem, s>>>(wmap, xmap, y, (int)M, (int)N, (int)K, device_status_word());
-  QMM_CHECK_LAUNCH("bf16_small_m_kernel");
+    QMM_CUDA_TRY(launch_pdl(bf16_small_m_kernel<2>, dim3(grid), dim3(160), kSmem, s, wmap, xmap, y, (int)M, (int)N, (int)K,
+                            device_status_word()));
   return QMM_OK;
 }
 

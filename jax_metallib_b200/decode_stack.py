@@ -181,7 +181,7 @@ class DecodeStep:
             _lib.check(lib.qmm_attention_decode_bf16(
                 q_ptr, kcache[li].data_ptr(), vcache[li].data_ptr(), k_ptr, v_ptr, self.attn.data_ptr(), B, s.n_heads,
                 s.n_kv_heads, self.L, s.head_dim, ctypes.c_float(1.0 / (s.head_dim ** 0.5)), ld, ld,
-                self.attn_ws.data_ptr(), self.attn_ws.numel(), stream))
+                self.attn_ws.data_ptr(), self.attn_ws.numel(), _lib.QMM_ATTN_STATIC_CACHE, stream))
             self.launches_per_step += 3  # rope + two attention launches
             self._linear(self.attn, layer["o"], self.o, stream)
             self._norm(self.h, self.o, layer["mlp_norm"], self.h2, self.n, stream)

@@ -117,7 +117,7 @@ def test_attention_decode(cuda, B, Hq, Hkv, L):
     _lib.check(lib.qmm_attention_decode_bf16(qt.data_ptr(), kct.data_ptr(), vct.data_ptr(), knt.data_ptr(),
                                              vnt.data_ptr(), out.data_ptr(), B, Hq, Hkv, L, hd,
                                              ctypes.c_float(1 / np.sqrt(hd)), Hq * hd, Hkv * hd, ws.data_ptr(),
-                                             ws.numel(), stream()))
+                                             ws.numel(), 0, stream()))
     torch.cuda.synchronize()
     assert lib.qmm_device_status() == 0
     ref = D.attention_decode(q, kc, vc, kn, vn, 1 / np.sqrt(hd))
@@ -132,7 +132,7 @@ def test_attention_decode(cuda, B, Hq, Hkv, L):
     _lib.check(lib.qmm_attention_decode_bf16(fused.data_ptr(), kct.data_ptr(), vct.data_ptr(),
                                              fused[:, Hq * hd:].data_ptr(), fused[:, (Hq + Hkv) * hd:].data_ptr(),
                                              out2.data_ptr(), B, Hq, Hkv, L, hd, ctypes.c_float(1 / np.sqrt(hd)), ld, ld,
-                                             ws.data_ptr(), ws.numel(), stream()))
+                                             ws.data_ptr(), ws.numel(), _lib.QMM_ATTN_STATIC_CACHE, stream()))
     torch.cuda.synchronize()
     assert torch.equal(out, out2)
 
@@ -154,7 +154,7 @@ def test_attention_decode_peaked_softmax(cuda):
     _lib.check(lib.qmm_attention_decode_bf16(qt.data_ptr(), kct.data_ptr(), vct.data_ptr(), knt.data_ptr(),
                                              vnt.data_ptr(), out.data_ptr(), B, Hq, Hkv, L, hd,
                                              ctypes.c_float(1 / np.sqrt(hd)), Hq * hd, Hkv * hd, ws.data_ptr(),
-                                             ws.numel(), stream()))
+                                             ws.numel(), 0, stream()))
     torch.cuda.synchronize()
     assert lib.qmm_device_status() == 0
     ref = D.attention_decode(q, kc, vc, kn, vn, 1 / np.sqrt(hd))
