@@ -2,9 +2,10 @@
 //
 // Two kernels share one skeleton: a persistent CTA per SM walks output tiles;
 // warp 0 feeds shared memory with TMA (128-byte swizzle), one thread of warp 1
-// issues tcgen05.mma into a double-buffered TMEM accumulator (2 x 256 columns),
-// warps 2-5 drain the accumulator with tcgen05.ld and apply the fused epilogue
-// while the next tile's MMAs run.  Every wait is bounded.
+// issues tcgen05.mma into TMEM accumulators (2 x 256 columns: double-buffered
+// in the int8 kernel, two channel blocks of one tile in the weight-only one),
+// epilogue warps drain them with tcgen05.ld and apply the fused epilogue.
+// Every wait is bounded.
 //
 //  (1) i8gemm: acc[M,N] = a[M,K] . b[K,N], int8/uint8 operands, int32
 //      accumulate (kind::i8, exact).  a is K-major, b is consumed N-major
@@ -15,12 +16,15 @@
 //  (2) w8a16: y[M,N] = bf16((x[M,K] @ float(w[K,N])) * scale[N]), bf16
 //      activations, int8 weights.  The weight tile is the 128-row MMA operand
 //      (MN-major: its 128 output channels are contiguous in memory), the
-//      activation tile the 256-column operand, so each CTA converts only
-//      128 x 64 weights per k-step: converter warps read the raw int8 tile,
-//      turn it into bf16 (exactly) and write the MMA's swizzled layout.  The
+//      activation tile the 256-column operand; a CTA runs two weight blocks
+//      against one activation tile (256 channels x 256 rows, all 512 TMEM
+//      columns), which cuts the bytes it stages per FLOP.  Converter warps
+//      read the raw int8 tile, turn it into bf16 (exactly) and write the MMA's
+//      swizzled layout in 32-k sub-blocks through a ring of four.  The
 //      accumulator holds the transposed tile (lane = output channel), so the
 //      per-channel scale is one register per thread and stores of a warp are
-//      contiguous along N.  Tile 128 (n) x 256 (m) x 64 (k).
+//      contiguous along N.  Leftover tiles of the last round are cut into
+//      halves or quarters.
 #include "common.cuh"
 
 namespace qmm {
@@ -189,20 +193,46 @@ i8gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ 
 // (2) bf16 activations x int8 weights (per-output-channel scale) -> bf16
 // ============================================================================
 namespace w8 {
-constexpr int BNW = 128;   // output channels per tile (MMA M)
+constexpr int BNW = 128;   // output channels per MMA (its M); a full tile has two such blocks
 constexpr int BMX = 256;   // activation rows per tile (MMA N)
-constexpr int BK = 64;
-constexpr int kStages = 4;     // TMA ring: raw weights + activations
-constexpr int kCvtBufs = 2;    // converted-weight buffers between the converter warps and the MMA
-constexpr int kCvtWarps = 8;
-constexpr int kRawBytes = BK * BNW;        // 8 KB  int8 [k][n]
-constexpr int kCvtBytes = BK * BNW * 2;    // 16 KB bf16, two 64-channel blocks of [k][128 B]
-constexpr int kXBytes = BMX * BK * 2;      // 32 KB bf16 [m][k]
-constexpr int kStageBytes = kRawBytes + kXBytes;  // 40 KB
-constexpr int kCvtBase = kStages * kStageBytes;   // 160 KB
-constexpr int kThreads = (2 + kEpiWarps + kCvtWarps) * 32;
-constexpr int kSmemBytes = kCvtBase + kCvtBufs * kCvtBytes + 1024 + 1024;
+constexpr int BK = 64;     // k per TMA stage
+constexpr int BKS = 32;    // k per converted sub-block
+constexpr int kXStages = 3;    // activation ring, held until the MMAs that read a stage retire
+constexpr int kWStages = 4;    // raw-weight ring, held only until a stage is in the converters' registers
+constexpr int kCvtBufs = 4;    // converted sub-blocks between the converter warps and the MMA
+constexpr int kCvtWarps = 8;    // converter warps per group
+constexpr int kCvtGroups = 2;   // groups take alternate 64-k stages
+constexpr int kEpiWarpsW = 8;
+// Warp roles: 0 TMA (activations), 1 MMA issue for channel block 0, 2-9 epilogue, 10-25 converters,
+// 26 TMA (raw weights), 27 MMA issue for channel block 1.  One thread needs ~85 cycles to issue a
+// tcgen05.mma and ~150 more per sub-block for its waits and commits, about what the MMAs themselves
+// take; two issuing threads (one per accumulator) leave the tensor pipe as the limit.
+constexpr int kFirstCvtWarp = 2 + kEpiWarpsW;
+constexpr int kWProducerWarp = kFirstCvtWarp + kCvtGroups * kCvtWarps;
+constexpr int kSecondMmaWarp = kWProducerWarp + 1;
+constexpr int kWarps = kSecondMmaWarp + 1;
+constexpr int kRawBlock = BK * BNW;               // 8 KB  int8 [k][128 n]
+constexpr int kRawBytes = 2 * kRawBlock;          // 16 KB: both channel blocks
+constexpr int kXBytes = BMX * BK * 2;             // 32 KB bf16 [m][k]
+constexpr int kCvtBlock = BKS * BNW * 2;          // 8 KB bf16: two 64-channel halves of [32 k][128 B]
+constexpr int kCvtBytes = 2 * kCvtBlock;          // 16 KB: both channel blocks
+constexpr int kRawBase = kXStages * kXBytes;                 // 96 KB
+constexpr int kCvtBase = kRawBase + kWStages * kRawBytes;    // 160 KB
+constexpr int kBarBase = kCvtBase + kCvtBufs * kCvtBytes;    // 224 KB
+constexpr int kThreads = kWarps * 32;
+constexpr int kSmemBytes = kBarBase + 256 + 1024;
 constexpr int kPanelTiles = 8;  // activation tiles swept together so that they stay in L2
+
+#ifdef QMM_W8_PROFILE
+// per CTA: [0] MMA thread total, [1] its wait for activations, [2] for converted sub-blocks, [3] for the
+// epilogue; [4] converter warp total, [5] its wait for raw weights, [6] for free buffers, [7] load + convert
+__device__ unsigned long long g_w8_prof[256 * 8];
+#define W8_PROF_T(var) const long long var = clock64()
+#define W8_PROF_ADD(acc, t0) acc += clock64() - (t0)
+#else
+#define W8_PROF_T(var)
+#define W8_PROF_ADD(acc, t0)
+#endif
 
 // Eight int8 (one 8-byte read) -> eight bf16, exactly: the byte, biased to
 // unsigned, becomes the low mantissa bits of 2^23 (an f32 holding 2^23 + 128 + v),
@@ -225,6 +255,21 @@ __device__ __forceinline__ uint4 convert8(const uint2& in) {
   return make_uint4(o[0], o[1], o[2], o[3]);
 }
 
+// The work of one launch.  A full tile is 256 channels x 256 rows: two channel
+// blocks share one activation tile, so a CTA stages 48 KB per 64 k for
+// 2 x 128 x 256 outputs.  CTA c takes tiles c, c + G, ... for `full_waves`
+// rounds; the tiles left over (fewer than G) are cut into `tail_div` parts each
+// (1: whole, 2: one channel block, 4: one channel block x 128 rows) and dealt
+// round-robin, so that the last round costs 1 / tail_div of a tile.
+struct Sched {
+  int tiles_n2, tiles_m, full_waves, tail_tiles, tail_div;
+};
+struct Work {
+  int tn2, tm;   // tile coordinates (256-channel, 256-row units)
+  int h0, nh;    // channel blocks [h0, h0 + nh); nh == 0: nothing to do
+  int m_off, m_cols;  // rows [m_off, m_off + m_cols) of the activation tile
+};
+
 // Tile order: activation tiles are swept in panels of kPanelTiles; inside a
 // panel the weight tile changes slowest, so the CTAs that run together share
 // one panel of activations (it stays in L2) and a handful of weight tiles.
@@ -236,39 +281,64 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   tm = p * kPanelTiles + r % rows;
 }
 
+// Item `i` of this CTA; false when the CTA is done.
+__device__ __forceinline__ bool get_work(const Sched& sc, int i, int M, int N, Work& w) {
+  const int G = gridDim.x;
+  int tile, sub = 0, div = 1;
+  if (i < sc.full_waves) {
+    tile = blockIdx.x + i * G;
+  } else {
+    const int v = blockIdx.x + (i - sc.full_waves) * G;
+    if (v >= sc.tail_tiles * sc.tail_div) return false;
+    div = sc.tail_div;
+    tile = sc.full_waves * G + v / div;
+    sub = v % div;
+  }
+  tile_coords(tile, sc.tiles_m, sc.tiles_n2, w.tm, w.tn2);
+  w.h0 = 0; w.nh = 2; w.m_off = 0; w.m_cols = BMX;
+  if (div == 2) { w.h0 = sub; w.nh = 1; }
+  if (div == 4) { w.h0 = sub >> 1; w.nh = 1; w.m_off = (sub & 1) * (BMX / 2); w.m_cols = BMX / 2; }
+  const int blocks_left = (N - w.tn2 * 2 * BNW + BNW - 1) / BNW - w.h0;  // channel blocks that exist
+  w.nh = max(0, min(w.nh, blocks_left));
+  if (w.tm * BMX + w.m_off >= M) w.nh = 0;
+  return true;
+}
+
 __global__ void __launch_bounds__(kThreads, 1)
 w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
              const float* __restrict__ scale, uint16_t* __restrict__ y, int M, int N, int K,
-             long long ldy, uint32_t idesc, int* status) {
+             long long ldy, uint32_t idesc256, uint32_t idesc128, const Sched sc, int* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + kCvtBase + kCvtBufs * kCvtBytes);  // TMA landed
-  uint64_t* empty = full + kStages;     // MMAs that read the stage's activations retired
-  uint64_t* cfull = empty + kStages;    // weights converted
-  uint64_t* cempty = cfull + kCvtBufs;  // MMAs that read the converted buffer retired
-  uint64_t* tfull = cempty + kCvtBufs;
-  uint64_t* tempty = tfull + 2;
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  uint64_t* xfull = reinterpret_cast<uint64_t*>(smem + kBarBase);  // activations landed
+  uint64_t* xempty = xfull + kXStages;   // MMAs that read the stage retired
+  uint64_t* wfull = xempty + kXStages;   // raw weights landed
+  uint64_t* wempty = wfull + kWStages;   // raw weights are in the converters' registers
+  uint64_t* cfull = wempty + kWStages;   // sub-block converted
+  uint64_t* cempty = cfull + kCvtBufs;   // MMAs that read the converted sub-block retired
+  uint64_t* tfull = cempty + kCvtBufs;   // accumulators complete
+  uint64_t* tempty = tfull + 1;          // accumulators drained
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tiles_n = (N + BNW - 1) / BNW, tiles_m = (M + BMX - 1) / BMX;
-  const int num_tiles = tiles_n * tiles_m;
   const int kblocks = (K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
-      dev::mbar_init(&full[s], 1);
-      dev::mbar_init(&empty[s], 1);
+    for (int s = 0; s < kXStages; ++s) {
+      dev::mbar_init(&xfull[s], 1);
+      dev::mbar_init(&xempty[s], 2);  // one commit per issuing thread
+    }
+    for (int s = 0; s < kWStages; ++s) {
+      dev::mbar_init(&wfull[s], 1);
+      dev::mbar_init(&wempty[s], kCvtWarps);
     }
     for (int i = 0; i < kCvtBufs; ++i) {
       dev::mbar_init(&cfull[i], kCvtWarps);
-      dev::mbar_init(&cempty[i], 1);
+      dev::mbar_init(&cempty[i], 2);
     }
-    for (int i = 0; i < 2; ++i) {
-      dev::mbar_init(&tfull[i], 1);
-      dev::mbar_init(&tempty[i], kEpiWarps);
-    }
+    dev::mbar_init(tfull, 2);
+    dev::mbar_init(tempty, kEpiWarpsW);
     dev::fence_mbar_init();
   }
   if (warp == 1) {
@@ -280,135 +350,239 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
   dev::tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
 
+  // Stage `cnt` (counted over the whole launch) uses activation slot cnt % 3,
+  // raw-weight slot cnt % 4 and converted buffers 2 (cnt % 2) and 2 (cnt % 2) + 1.
   if (warp == 0) {
-    // ------------------------------ TMA producer ---------------------------
+    // ------------------------ TMA producer: activations --------------------
+    if (lane == 0) {
+      dev::tma_prefetch_desc(&xmap);
+      int xs = 0;
+      uint32_t xph = 0;
+      bool ok = true;
+      Work w;
+      for (int i = 0; ok && get_work(sc, i, M, N, w); ++i) {
+        if (w.nh == 0) continue;
+        for (int kb = 0; kb < kblocks; ++kb) {
+          if (!dev::mbar_wait(&xempty[xs], xph ^ 1, status, 21)) { ok = false; break; }
+          dev::mbar_expect_tx(&xfull[xs], kXBytes);
+          dev::tma_load_2d(smem + xs * kXBytes, &xmap, &xfull[xs], kb * BK, w.tm * BMX);
+          if (++xs == kXStages) { xs = 0; xph ^= 1; }
+        }
+      }
+    }
+  } else if (warp == kWProducerWarp) {
+    // ------------------------ TMA producer: raw weights --------------------
     if (lane == 0) {
       dev::tma_prefetch_desc(&wmap);
-      dev::tma_prefetch_desc(&xmap);
-      int s = 0;
-      uint32_t ph = 0;
+      unsigned cnt = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        int tm, tn;
-        tile_coords(tile, tiles_m, tiles_n, tm, tn);
-        for (int kb = 0; kb < kblocks; ++kb) {
-          if (!dev::mbar_wait(&empty[s], ph ^ 1, status, 21)) { ok = false; break; }
-          uint8_t* st = smem + s * kStageBytes;
-          dev::mbar_expect_tx(&full[s], kRawBytes + kXBytes);
-          dev::tma_load_2d(st, &wmap, &full[s], tn * BNW, kb * BK);
-          dev::tma_load_2d(st + kRawBytes, &xmap, &full[s], kb * BK, tm * BMX);
-          if (++s == kStages) { s = 0; ph ^= 1; }
+      Work w;
+      for (int i = 0; ok && get_work(sc, i, M, N, w); ++i) {
+        if (w.nh == 0) continue;
+        for (int kb = 0; kb < kblocks; ++kb, ++cnt) {
+          const int ws = cnt & (kWStages - 1);
+          if (!dev::mbar_wait(&wempty[ws], ((cnt / kWStages) & 1) ^ 1, status, 20)) { ok = false; break; }
+          uint8_t* raw = smem + kRawBase + ws * kRawBytes;
+          dev::mbar_expect_tx(&wfull[ws], w.nh * kRawBlock);
+          for (int h = w.h0; h < w.h0 + w.nh; ++h)
+            dev::tma_load_2d(raw + h * kRawBlock, &wmap, &wfull[ws], (w.tn2 * 2 + h) * BNW, kb * BK);
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------ MMA issuer -----------------------------
+  } else if (warp == 1 || warp == kSecondMmaWarp) {
+    // ------------------------------ MMA issuers ----------------------------
+    // Issuer j multiplies channel block j of every item that has it into accumulator j; both
+    // follow the same barriers and both commit, whether or not they issued anything.
     if (lane == 0) {
-      int s = 0, c = 0, tcount = 0;
-      uint32_t ph = 0, cph = 0;
+      const int me = (warp == 1) ? 0 : 1;
+      // descriptor halves: the high half is constant, the low half carries the start address
+      constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (kSwizzle128 << 29);  // SBO, version, swizzle
+      constexpr uint32_t kAStepK = (16 * 128) >> 4, kAStepH = kCvtBlock >> 4, kAStepBuf = kCvtBytes >> 4;
+      constexpr uint32_t kBStepK = 32 >> 4, kBStepStage = kXBytes >> 4;
+      const uint32_t a_lo0 = (((dev::smem_u32(smem + kCvtBase) >> 4) & 0x3FFF) | (((BKS * 128u) >> 4) << 16)) +
+                             me * kAStepH;
+      const uint32_t b_lo0 = ((dev::smem_u32(smem) >> 4) & 0x3FFF) | ((16u >> 4) << 16);
+      const uint32_t d = tmem_base + me * BMX;
+      unsigned cnt = 0;
+      int items = 0, xs = 0;
+      uint32_t xph = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
-        const int as = tcount & 1;
-        if (!dev::mbar_wait(&tempty[as], ((tcount >> 1) & 1) ^ 1, status, 22)) { ok = false; break; }
+      Work w;
+#ifdef QMM_W8_PROFILE
+      long long pw_full = 0, pw_cfull = 0, pw_tempty = 0;
+      const long long p_start = clock64();
+#endif
+      for (int i = 0; ok && get_work(sc, i, M, N, w); ++i) {
+        if (w.nh == 0) continue;
+        W8_PROF_T(t_t);
+        if (!dev::mbar_wait(tempty, (items & 1) ^ 1, status, 22)) break;
+        W8_PROF_ADD(pw_tempty, t_t);
         dev::tc_fence_after();
-        const uint32_t d_tmem = tmem_base + as * BMX;
-        for (int kb = 0; kb < kblocks; ++kb) {
-          if (!dev::mbar_wait(&full[s], ph, status, 23) ||
-              !dev::mbar_wait(&cfull[c], cph, status, 24)) { ok = false; break; }
-          dev::tc_fence_after();
-          const uint32_t w_addr = dev::smem_u32(smem + kCvtBase + c * kCvtBytes);
-          const uint32_t x_addr = dev::smem_u32(smem + s * kStageBytes + kRawBytes);
+        const uint32_t idesc = (w.m_cols == BMX) ? idesc256 : idesc128;
+        const uint32_t b_item = b_lo0 + ((w.m_off * 128) >> 4);
+        const bool mine = (me >= w.h0) && (me < w.h0 + w.nh);
+        for (int kb = 0; kb < kblocks && ok; ++kb, ++cnt) {
+          W8_PROF_T(t_f);
+          if (!dev::mbar_wait(&xfull[xs], xph, status, 23)) { ok = false; break; }
+          W8_PROF_ADD(pw_full, t_f);
+          const uint32_t b_s = b_item + xs * kBStepStage;
+          const uint32_t cpar = (cnt >> 1) & 1;
 #pragma unroll
-          for (int k = 0; k < BK / 16; ++k) {
-            // weights: MN-major, 16 k-rows (2 KB) per instruction, 64-channel blocks 8 KB apart
-            const uint64_t adesc =
-                dev::make_smem_desc(w_addr + k * 16 * 128, BK * 128, 1024, kSwizzle128);
-            // activations: K-major, 32 bytes of k per instruction
-            const uint64_t bdesc = dev::make_smem_desc(x_addr + k * 32, 16, 1024, kSwizzle128);
-            dev::umma_f16(d_tmem, adesc, bdesc, idesc, (kb | k) != 0);
+          for (int sb = 0; sb < BK / BKS; ++sb) {
+            const int c = 2 * (cnt & 1) + sb;
+            W8_PROF_T(t_c);
+            if (!dev::mbar_wait(&cfull[c], cpar, status, 24)) { ok = false; break; }
+            W8_PROF_ADD(pw_cfull, t_c);
+            dev::tc_fence_after();
+            if (mine) {
+              const uint32_t a_c = a_lo0 + c * kAStepBuf;
+              const uint32_t b_c = b_s + sb * (BKS / 16) * kBStepK;
+              dev::umma_f16_lh(d, a_c, kDescHi, b_c, kDescHi, idesc, (kb | sb) != 0);
+              dev::umma_f16_lh(d, a_c + kAStepK, kDescHi, b_c + kBStepK, kDescHi, idesc, 1);
+            }
+            dev::tc_commit(&cempty[c]);  // frees the converted sub-block (second arrival: the other issuer)
           }
-          dev::tc_commit(&empty[s]);    // frees the TMA stage (raw weights were consumed earlier)
-          dev::tc_commit(&cempty[c]);   // frees the converted buffer
-          if (++s == kStages) { s = 0; ph ^= 1; }
-          if (++c == kCvtBufs) { c = 0; cph ^= 1; }
+          dev::tc_commit(&xempty[xs]);  // frees the activation stage
+          if (++xs == kXStages) { xs = 0; xph ^= 1; }
         }
-        if (ok) dev::tc_commit(&tfull[as]);
+        if (ok) dev::tc_commit(tfull);
+        ++items;
       }
+#ifdef QMM_W8_PROFILE
+      if (me == 0) {
+        g_w8_prof[blockIdx.x * 8 + 0] = clock64() - p_start;
+        g_w8_prof[blockIdx.x * 8 + 1] = pw_full;
+        g_w8_prof[blockIdx.x * 8 + 2] = pw_cfull;
+        g_w8_prof[blockIdx.x * 8 + 3] = pw_tempty;
+      }
+#endif
     }
-  } else if (warp < 2 + kEpiWarps) {
+  } else if (warp < 2 + kEpiWarpsW) {
     // ------------------------------ epilogue -------------------------------
-    const int q = warp & 3;
-    int tcount = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcount) {
-      int tm, tn;
-      tile_coords(tile, tiles_m, tiles_n, tm, tn);
-      const int as = tcount & 1;
-      if (!dev::mbar_wait(&tfull[as], (tcount >> 1) & 1, status, 25)) break;
+    // warp & 3 selects the 32 TMEM lanes (channels) a warp may read; the two
+    // warps of a lane quarter take alternate 32-row chunks.
+    const int q = warp & 3, half = (warp - 2) >> 2;
+    int items = 0;
+    Work w;
+    for (int i = 0; get_work(sc, i, M, N, w); ++i) {
+      if (w.nh == 0) continue;
+      if (!dev::mbar_wait(tfull, items & 1, status, 25)) break;
       dev::tc_fence_after();
-      const int n = tn * BNW + q * 32 + lane;  // this thread's output channel
-      const float sc = (n < N) ? __ldg(scale + n) : 0.f;
+      for (int h = w.h0; h < w.h0 + w.nh; ++h) {
+        const int n = (w.tn2 * 2 + h) * BNW + q * 32 + lane;  // this thread's output channel
+        const float scl = (n < N) ? __ldg(scale + n) : 0.f;
 #pragma unroll 1
-      for (int ch = 0; ch < BMX / 32; ++ch) {
-        uint32_t r[32];
-        dev::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * BMX + ch * 32, r);
-        dev::tc_wait_ld();
-        const int m0 = tm * BMX + ch * 32;
-        // pair neighbouring channels so that every lane stores 4 bytes: even
-        // lanes write rows m0+2j, odd lanes rows m0+2j+1
+        for (int ch = half; ch < w.m_cols / 32; ch += 2) {
+          uint32_t r[32];
+          dev::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + h * BMX + ch * 32, r);
+          dev::tc_wait_ld();
+          const int m0 = w.tm * BMX + w.m_off + ch * 32;
+          // pair neighbouring channels so that every lane stores 4 bytes: even
+          // lanes write rows m0+2j, odd lanes rows m0+2j+1
 #pragma unroll
-        for (int j = 0; j < 16; ++j) {
-          const float a = __uint_as_float(r[2 * j]) * sc;
-          const float b = __uint_as_float(r[2 * j + 1]) * sc;
-          const float send = (lane & 1) ? a : b;
-          const float got = __shfl_xor_sync(0xFFFFFFFFu, send, 1);
-          const int m = m0 + 2 * j + (lane & 1);
-          const uint32_t packed = (lane & 1) ? dev::pack_bf16x2(got, b) : dev::pack_bf16x2(a, got);
-          const int n_even = n & ~1;
-          if (m < M && n_even < N)
-            *reinterpret_cast<uint32_t*>(y + static_cast<size_t>(m) * ldy + n_even) = packed;
+          for (int j = 0; j < 16; ++j) {
+            const float a = __uint_as_float(r[2 * j]) * scl;
+            const float b = __uint_as_float(r[2 * j + 1]) * scl;
+            const float send = (lane & 1) ? a : b;
+            const float got = __shfl_xor_sync(0xFFFFFFFFu, send, 1);
+            const int m = m0 + 2 * j + (lane & 1);
+            const uint32_t packed = (lane & 1) ? dev::pack_bf16x2(got, b) : dev::pack_bf16x2(a, got);
+            const int n_even = n & ~1;
+            if (m < M && n_even < N)
+              *reinterpret_cast<uint32_t*>(y + static_cast<size_t>(m) * ldy + n_even) = packed;
+          }
         }
       }
       dev::tc_fence_before();
       __syncwarp();
-      if (lane == 0) dev::mbar_arrive(&tempty[as]);
+      if (lane == 0) dev::mbar_arrive(tempty);
+      ++items;
     }
   } else {
     // ------------------------------ converters -----------------------------
     // A half-warp reads one 128-byte raw row, 8 bytes per lane (conflict-free
     // in any permutation); each lane writes the 16-byte bf16 chunk it made, so
     // a quarter-warp store covers the eight chunks of one 128-byte row of one
-    // 64-channel block: conflict-free as well, with no divergence.
-    const int cw = warp - (2 + kEpiWarps);  // 0..7
-    const int piece = lane & 15;            // 8 channels: [8*piece, 8*piece+8)
-    const int rsub = lane >> 4;             // row within a pair
-    int s = 0, c = 0;
-    uint32_t ph = 0, cph = 0;
+    // 64-channel half: conflict-free as well, with no divergence.  One warp
+    // needs several hundred cycles for its share of a sub-block (dependent ALU
+    // chains), more than the MMAs of the sub-block take, so two groups of
+    // eight warps take alternate stages.  The raw slot is handed back as soon
+    // as its bytes are in registers.
+    const int o = warp - kFirstCvtWarp;
+    const int grp = o / kCvtWarps, cw = o % kCvtWarps;
+    const int piece = lane & 15;         // 8 channels: [8*piece, 8*piece+8)
+    const int rsub = lane >> 4;          // row within a pair
+    const int c0 = 2 * grp;              // this group's two converted buffers
+    unsigned cnt = 0;  // stages since the start of the launch
     bool ok = true;
-    for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-      for (int kb = 0; kb < kblocks; ++kb) {
-        if (!dev::mbar_wait(&full[s], ph, status, 26) ||
-            !dev::mbar_wait(&cempty[c], cph ^ 1, status, 27)) { ok = false; break; }
-        const uint8_t* raw = smem + s * kStageBytes;
-        uint8_t* dst = smem + kCvtBase + c * kCvtBytes + (piece >> 3) * (BK * 128);
-        uint2 in[BK / (2 * kCvtWarps)];
+    Work w;
+#ifdef QMM_W8_PROFILE
+    long long pc_full = 0, pc_cempty = 0, pc_conv = 0;
+    const long long pc_start = clock64();
+#endif
+    for (int i = 0; ok && get_work(sc, i, M, N, w); ++i) {
+      if (w.nh == 0) continue;
+      for (int kb = 0; kb < kblocks; ++kb, ++cnt) {
+        if ((cnt & 1) != static_cast<unsigned>(grp)) continue;
+        const uint32_t par = (cnt >> 1) & 1;
+        const int ws = cnt & (kWStages - 1);
+        const uint8_t* raw = smem + kRawBase + ws * kRawBytes;
+        W8_PROF_T(t_f);
+        if (!dev::mbar_wait(&wfull[ws], (cnt / kWStages) & 1, status, 26)) { ok = false; break; }
+        W8_PROF_ADD(pc_full, t_f);
+        W8_PROF_T(t_a);
+        // tasks of this warp: per sub-block and channel block 16 row pairs, two per warp
+        uint2 in[8];
 #pragma unroll
-        for (int p = 0; p < BK / (2 * kCvtWarps); ++p) {
-          const int r = (p * kCvtWarps + cw) * 2 + rsub;  // k-row 0..63
-          in[p] = *reinterpret_cast<const uint2*>(raw + r * 128 + (((piece >> 1) ^ (r & 7)) << 4) +
-                                                  ((piece & 1) << 3));
+        for (int p = 0; p < 8; ++p) {
+          const int sb = p >> 2, hh = (p >> 1) & 1;  // sub-block; 0: first block of the item, 1: second
+          const int r = ((p & 1) * kCvtWarps + cw) * 2 + rsub;  // row 0..31 of the sub-block
+          const int krow = sb * BKS + r;
+          if (hh < w.nh)
+            in[p] = *reinterpret_cast<const uint2*>(raw + (w.h0 + hh) * kRawBlock + krow * 128 +
+                                                    (((piece >> 1) ^ (krow & 7)) << 4) + ((piece & 1) << 3));
         }
 #pragma unroll
-        for (int p = 0; p < BK / (2 * kCvtWarps); ++p) {
-          const int r = (p * kCvtWarps + cw) * 2 + rsub;
-          *reinterpret_cast<uint4*>(dst + r * 128 + (((piece & 7) ^ (r & 7)) << 4)) = convert8(in[p]);
+        for (int sb = 0; sb < 2; ++sb) {
+          uint4 out[4];
+#pragma unroll
+          for (int p = 0; p < 4; ++p)
+            if ((p >> 1) < w.nh) out[p] = convert8(in[sb * 4 + p]);
+          if (sb == 1) {
+            // every raw byte of the stage is in registers: hand the slot back
+            __syncwarp();
+            if (lane == 0) dev::mbar_arrive(&wempty[ws]);
+          }
+#ifdef QMM_W8_PROFILE
+          if (out[0].x == 0x12345678u) pc_full += 1;  // keep the conversion ahead of the clock read
+          if (sb == 1) pc_conv += clock64() - t_a;
+#endif
+          W8_PROF_T(t_c);
+          if (!dev::mbar_wait(&cempty[c0 + sb], par ^ 1, status, 27)) { ok = false; break; }
+          W8_PROF_ADD(pc_cempty, t_c);
+          uint8_t* cvt = smem + kCvtBase + (c0 + sb) * kCvtBytes;
+#pragma unroll
+          for (int p = 0; p < 4; ++p) {
+            const int hh = p >> 1;
+            const int r = ((p & 1) * kCvtWarps + cw) * 2 + rsub;
+            if (hh < w.nh)
+              *reinterpret_cast<uint4*>(cvt + (w.h0 + hh) * kCvtBlock + (piece >> 3) * (BKS * 128) + r * 128 +
+                                        (((piece & 7) ^ (r & 7)) << 4)) = out[p];
+          }
+          dev::fence_proxy_async();
+          __syncwarp();
+          if (lane == 0) dev::mbar_arrive(&cfull[c0 + sb]);
         }
-        dev::fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) dev::mbar_arrive(&cfull[c]);
-        if (++s == kStages) { s = 0; ph ^= 1; }
-        if (++c == kCvtBufs) { c = 0; cph ^= 1; }
       }
     }
+#ifdef QMM_W8_PROFILE
+    if (o == 0 && lane == 0) {
+      g_w8_prof[blockIdx.x * 8 + 4] = clock64() - pc_start;
+      g_w8_prof[blockIdx.x * 8 + 5] = pc_full;
+      g_w8_prof[blockIdx.x * 8 + 6] = pc_cempty;
+      g_w8_prof[blockIdx.x * 8 + 7] = pc_conv;
+    }
+#endif
   }
   dev::tc_fence_before();
   __syncthreads();
@@ -469,12 +643,31 @@ int w8a16_tcgen05(const uint16_t* x, const int8_t* w, const float* scale, uint16
     configured = true;
   }
   // operand "a" of the MMA = weights (bf16, MN-major), "b" = activations (bf16, K-major)
-  const uint32_t idesc = dev::make_idesc(/*c=f32*/ 1, /*bf16*/ 1, /*bf16*/ 1,
-                                         /*a MN-major*/ 1, /*b K-major*/ 0, BNW, BMX);
-  const int tiles = static_cast<int>(((N + BNW - 1) / BNW) * ((M + BMX - 1) / BMX));
-  const int grid = tiles < num_sms() ? tiles : num_sms();
+  const uint32_t idesc256 = dev::make_idesc(/*c=f32*/ 1, /*bf16*/ 1, /*bf16*/ 1,
+                                            /*a MN-major*/ 1, /*b K-major*/ 0, BNW, BMX);
+  const uint32_t idesc128 = dev::make_idesc(1, 1, 1, 1, 0, BNW, BMX / 2);
+  Sched sc;
+  sc.tiles_n2 = static_cast<int>((N + 2 * BNW - 1) / (2 * BNW));
+  sc.tiles_m = static_cast<int>((M + BMX - 1) / BMX);
+  const int tiles = sc.tiles_n2 * sc.tiles_m;
+  const int sms = num_sms();
+  sc.full_waves = tiles / sms;
+  sc.tail_tiles = tiles - sc.full_waves * sms;
+  // cut the leftover tiles as finely as shortens the last round
+  sc.tail_div = 1;
+  int best_num = 1, best_den = 1;  // cost of the last round = rounds / parts, in tiles
+  for (int d = 2; d <= 4 && sc.tail_tiles > 0; d *= 2) {
+    const int rounds = (sc.tail_tiles * d + sms - 1) / sms;
+    if (rounds * best_den < best_num * d) {
+      best_num = rounds;
+      best_den = d;
+      sc.tail_div = d;
+    }
+  }
+  const int grid = sc.full_waves > 0 ? sms : (sc.tail_tiles * sc.tail_div < sms ? sc.tail_tiles * sc.tail_div : sms);
   w8a16_kernel<<<grid, kThreads, kSmemBytes, stream>>>(wmap, xmap, scale, y, (int)M, (int)N, (int)K,
-                                                       (long long)ldy, idesc, device_status_word());
+                                                       (long long)ldy, idesc256, idesc128, sc,
+                                                       device_status_word());
   QMM_CHECK_LAUNCH("w8a16_kernel");
   return QMM_OK;
 }
