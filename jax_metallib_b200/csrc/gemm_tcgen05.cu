@@ -234,25 +234,25 @@ __device__ unsigned long long g_w8_prof[256 * 8];
 #define W8_PROF_ADD(acc, t0)
 #endif
 
-// Eight int8 (one 8-byte read) -> eight bf16, exactly: the byte, biased to
-// unsigned, becomes the low mantissa bits of 2^23 (an f32 holding 2^23 + 128 + v),
-// the constant is subtracted and pairs are packed with round-to-nearest (exact,
-// |v| <= 128 fits bf16's 8 significant bits).  The MMA needs both operands in
-// one 16-bit format (an f16 weight operand against bf16 activations raises an
-// illegal-instruction error on sm_100a), so the weights follow the activations.
+// Eight int8 (one 8-byte read) -> eight bf16, exactly, in 16 instructions.
+// For a byte b (two's complement v): A = 0x4300 | (b & 0x7F) is the bf16
+// 128 + (b & 0x7F); C = 0xC300 | (b & 0x80) is -128 for v >= 0 and -256 for
+// v < 0; A + C = v, exact in bf16 (|v| <= 128 has 8 significant bits).  One
+// byte-permute spreads two bytes over the two halves of a register, two
+// logic ops build A and C for both, one packed add finishes the pair.  The MMA
+// needs both operands in one 16-bit format (an f16 weight operand against bf16
+// activations raises an illegal-instruction error on sm_100a), so the weights
+// follow the activations.
+__device__ __forceinline__ uint32_t convert2(uint32_t word, uint32_t selector) {
+  const uint32_t t = __byte_perm(word, 0u, selector);  // 0x00bb00aa
+  uint32_t a, c, r;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(a) : "r"(t), "r"(0x007F007Fu), "r"(0x43004300u));  // (t & m) | k
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(c) : "r"(t), "r"(0x00800080u), "r"(0xC300C300u));
+  asm("add.rn.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(c));
+  return r;
+}
 __device__ __forceinline__ uint4 convert8(const uint2& in) {
-  const uint32_t w[2] = {in.x ^ 0x80808080u, in.y ^ 0x80808080u};
-  uint32_t o[4];
-#pragma unroll
-  for (int i = 0; i < 2; ++i) {
-    const float f0 = __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7440)) - 8388736.f;
-    const float f1 = __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7441)) - 8388736.f;
-    const float f2 = __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7442)) - 8388736.f;
-    const float f3 = __uint_as_float(__byte_perm(w[i], 0x4B000000u, 0x7443)) - 8388736.f;
-    o[2 * i] = dev::pack_bf16x2(f0, f1);
-    o[2 * i + 1] = dev::pack_bf16x2(f2, f3);
-  }
-  return make_uint4(o[0], o[1], o[2], o[3]);
+  return make_uint4(convert2(in.x, 0x4140), convert2(in.x, 0x4342), convert2(in.y, 0x4140), convert2(in.y, 0x4342));
 }
 
 // The work of one launch.  A full tile is 256 channels x 256 rows: two channel
