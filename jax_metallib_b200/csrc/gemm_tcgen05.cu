@@ -222,6 +222,10 @@ constexpr int kBarBase = kCvtBase + kCvtBufs * kCvtBytes;    // 224 KB
 constexpr int kThreads = kWarps * 32;
 constexpr int kSmemBytes = kBarBase + 256 + 1024;
 constexpr int kPanelTiles = 8;  // activation tiles swept together so that they stay in L2
+// One "consumed" barrier per stage in a ring of 6 (a multiple of both the activation ring and the
+// two converted stage slots): the activation producer waits for stage cnt - 3, the converters for
+// stage cnt - 2, and the issuing threads commit once per stage.
+constexpr int kConsumed = 6;
 
 #ifdef QMM_W8_PROFILE
 // per CTA: [0] MMA thread total, [1] its wait for activations, [2] for converted sub-blocks, [3] for the
@@ -312,31 +316,25 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint64_t* xfull = reinterpret_cast<uint64_t*>(smem + kBarBase);  // activations landed
-  uint64_t* xempty = xfull + kXStages;   // MMAs that read the stage retired
-  uint64_t* wfull = xempty + kXStages;   // raw weights landed
+  uint64_t* wfull = xfull + kXStages;    // raw weights landed
   uint64_t* wempty = wfull + kWStages;   // raw weights are in the converters' registers
-  uint64_t* cfull = wempty + kWStages;   // sub-block converted
-  uint64_t* cempty = cfull + kCvtBufs;   // MMAs that read the converted sub-block retired
-  uint64_t* tfull = cempty + kCvtBufs;   // accumulators complete
-  uint64_t* tempty = tfull + 1;          // accumulators drained
+  uint64_t* sfull = wempty + kWStages;   // stage ready for the MMAs: converted, and its activations landed
+  uint64_t* consumed = sfull + kCvtGroups;  // the MMAs of a stage retired (ring of kConsumed stages)
+  uint64_t* tfull = consumed + kConsumed;   // accumulators complete
+  uint64_t* tempty = tfull + 1;             // accumulators drained
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int kblocks = (K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kXStages; ++s) {
-      dev::mbar_init(&xfull[s], 1);
-      dev::mbar_init(&xempty[s], 2);  // one commit per issuing thread
-    }
+    for (int s = 0; s < kXStages; ++s) dev::mbar_init(&xfull[s], 1);
     for (int s = 0; s < kWStages; ++s) {
       dev::mbar_init(&wfull[s], 1);
       dev::mbar_init(&wempty[s], kCvtWarps);
     }
-    for (int i = 0; i < kCvtBufs; ++i) {
-      dev::mbar_init(&cfull[i], kCvtWarps);
-      dev::mbar_init(&cempty[i], 2);
-    }
+    for (int g = 0; g < kCvtGroups; ++g) dev::mbar_init(&sfull[g], kCvtWarps);
+    for (int i = 0; i < kConsumed; ++i) dev::mbar_init(&consumed[i], 2);  // one commit per issuing thread
     dev::mbar_init(tfull, 2);
     dev::mbar_init(tempty, kEpiWarpsW);
     dev::fence_mbar_init();
@@ -356,17 +354,19 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
     // ------------------------ TMA producer: activations --------------------
     if (lane == 0) {
       dev::tma_prefetch_desc(&xmap);
-      int xs = 0;
-      uint32_t xph = 0;
+      unsigned cnt = 0;
       bool ok = true;
       Work w;
       for (int i = 0; ok && get_work(sc, i, M, N, w); ++i) {
         if (w.nh == 0) continue;
-        for (int kb = 0; kb < kblocks; ++kb) {
-          if (!dev::mbar_wait(&xempty[xs], xph ^ 1, status, 21)) { ok = false; break; }
+        for (int kb = 0; kb < kblocks; ++kb, ++cnt) {
+          const int xs = cnt % kXStages;
+          if (cnt >= kXStages) {  // the slot's previous stage must have been multiplied
+            const unsigned prev = cnt - kXStages;
+            if (!dev::mbar_wait(&consumed[prev % kConsumed], (prev / kConsumed) & 1, status, 21)) { ok = false; break; }
+          }
           dev::mbar_expect_tx(&xfull[xs], kXBytes);
           dev::tma_load_2d(smem + xs * kXBytes, &xmap, &xfull[xs], kb * BK, w.tm * BMX);
-          if (++xs == kXStages) { xs = 0; xph ^= 1; }
         }
       }
     }
@@ -392,7 +392,10 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
   } else if (warp == 1 || warp == kSecondMmaWarp) {
     // ------------------------------ MMA issuers ----------------------------
     // Issuer j multiplies channel block j of every item that has it into accumulator j; both
-    // follow the same barriers and both commit, whether or not they issued anything.
+    // follow the same barriers and both commit, whether or not they issued anything.  The
+    // issuing thread is a slow scalar processor (a branch or a shared-memory poll costs it
+    // tens of cycles, a commit ~90), so a stage costs it one wait, one fence, four predicated
+    // MMAs with descriptors advanced by adds, and one commit.
     if (lane == 0) {
       const int me = (warp == 1) ? 0 : 1;
       // descriptor halves: the high half is constant, the low half carries the start address
@@ -403,13 +406,14 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
                              me * kAStepH;
       const uint32_t b_lo0 = ((dev::smem_u32(smem) >> 4) & 0x3FFF) | ((16u >> 4) << 16);
       const uint32_t d = tmem_base + me * BMX;
-      unsigned cnt = 0;
-      int items = 0, xs = 0;
-      uint32_t xph = 0;
+      uint32_t g = 0, gpar = 0;   // converter group of the stage and the parity of its use
+      uint32_t xs = 0;            // activation slot
+      uint32_t c6 = 0;            // consumed-ring index
+      int items = 0;
       bool ok = true;
       Work w;
 #ifdef QMM_W8_PROFILE
-      long long pw_full = 0, pw_cfull = 0, pw_tempty = 0;
+      long long pw_full = 0, pw_tempty = 0;
       const long long p_start = clock64();
 #endif
       for (int i = 0; ok && get_work(sc, i, M, N, w); ++i) {
@@ -420,30 +424,23 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
         dev::tc_fence_after();
         const uint32_t idesc = (w.m_cols == BMX) ? idesc256 : idesc128;
         const uint32_t b_item = b_lo0 + ((w.m_off * 128) >> 4);
-        const bool mine = (me >= w.h0) && (me < w.h0 + w.nh);
-        for (int kb = 0; kb < kblocks && ok; ++kb, ++cnt) {
+        const uint32_t mine = (me >= w.h0) && (me < w.h0 + w.nh);
+        for (int kb = 0; kb < kblocks; ++kb) {
           W8_PROF_T(t_f);
-          if (!dev::mbar_wait(&xfull[xs], xph, status, 23)) { ok = false; break; }
+          if (!dev::mbar_wait(&sfull[g], gpar, status, 23)) { ok = false; break; }
           W8_PROF_ADD(pw_full, t_f);
+          dev::tc_fence_after();
+          const uint32_t a_c = a_lo0 + g * (2 * kAStepBuf);
           const uint32_t b_s = b_item + xs * kBStepStage;
-          const uint32_t cpar = (cnt >> 1) & 1;
-#pragma unroll
-          for (int sb = 0; sb < BK / BKS; ++sb) {
-            const int c = 2 * (cnt & 1) + sb;
-            W8_PROF_T(t_c);
-            if (!dev::mbar_wait(&cfull[c], cpar, status, 24)) { ok = false; break; }
-            W8_PROF_ADD(pw_cfull, t_c);
-            dev::tc_fence_after();
-            if (mine) {
-              const uint32_t a_c = a_lo0 + c * kAStepBuf;
-              const uint32_t b_c = b_s + sb * (BKS / 16) * kBStepK;
-              dev::umma_f16_lh(d, a_c, kDescHi, b_c, kDescHi, idesc, (kb | sb) != 0);
-              dev::umma_f16_lh(d, a_c + kAStepK, kDescHi, b_c + kBStepK, kDescHi, idesc, 1);
-            }
-            dev::tc_commit(&cempty[c]);  // frees the converted sub-block (second arrival: the other issuer)
-          }
-          dev::tc_commit(&xempty[xs]);  // frees the activation stage
-          if (++xs == kXStages) { xs = 0; xph ^= 1; }
+          dev::umma_f16_lh_if(mine, d, a_c, kDescHi, b_s, kDescHi, idesc, kb != 0);
+          dev::umma_f16_lh_if(mine, d, a_c + kAStepK, kDescHi, b_s + kBStepK, kDescHi, idesc, 1);
+          dev::umma_f16_lh_if(mine, d, a_c + kAStepBuf, kDescHi, b_s + 2 * kBStepK, kDescHi, idesc, 1);
+          dev::umma_f16_lh_if(mine, d, a_c + kAStepBuf + kAStepK, kDescHi, b_s + 3 * kBStepK, kDescHi, idesc, 1);
+          dev::tc_commit(&consumed[c6]);  // second arrival: the other issuer
+          gpar ^= g;  // the parity flips after group 1's stage
+          g ^= 1;
+          xs = (xs == kXStages - 1) ? 0 : xs + 1;
+          c6 = (c6 == kConsumed - 1) ? 0 : c6 + 1;
         }
         if (ok) dev::tc_commit(tfull);
         ++items;
@@ -452,7 +449,7 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
       if (me == 0) {
         g_w8_prof[blockIdx.x * 8 + 0] = clock64() - p_start;
         g_w8_prof[blockIdx.x * 8 + 1] = pw_full;
-        g_w8_prof[blockIdx.x * 8 + 2] = pw_cfull;
+        g_w8_prof[blockIdx.x * 8 + 2] = 0;
         g_w8_prof[blockIdx.x * 8 + 3] = pw_tempty;
       }
 #endif
@@ -524,7 +521,6 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
       if (w.nh == 0) continue;
       for (int kb = 0; kb < kblocks; ++kb, ++cnt) {
         if ((cnt & 1) != static_cast<unsigned>(grp)) continue;
-        const uint32_t par = (cnt >> 1) & 1;
         const int ws = cnt & (kWStages - 1);
         const uint8_t* raw = smem + kRawBase + ws * kRawBytes;
         W8_PROF_T(t_f);
@@ -542,24 +538,19 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
             in[p] = *reinterpret_cast<const uint2*>(raw + (w.h0 + hh) * kRawBlock + krow * 128 +
                                                     (((piece >> 1) ^ (krow & 7)) << 4) + ((piece & 1) << 3));
         }
+        // sub-block 0 is converted before the wait for its buffers, sub-block 1 after its stores
+        uint4 out[4];
+#pragma unroll
+        for (int p = 0; p < 4; ++p)
+          if ((p >> 1) < w.nh) out[p] = convert8(in[p]);
+        W8_PROF_T(t_c);
+        if (cnt >= 2) {  // the MMAs of the stage that used these buffers before must have retired
+          const unsigned prev = cnt - 2;
+          if (!dev::mbar_wait(&consumed[prev % kConsumed], (prev / kConsumed) & 1, status, 27)) { ok = false; break; }
+        }
+        W8_PROF_ADD(pc_cempty, t_c);
 #pragma unroll
         for (int sb = 0; sb < 2; ++sb) {
-          uint4 out[4];
-#pragma unroll
-          for (int p = 0; p < 4; ++p)
-            if ((p >> 1) < w.nh) out[p] = convert8(in[sb * 4 + p]);
-          if (sb == 1) {
-            // every raw byte of the stage is in registers: hand the slot back
-            __syncwarp();
-            if (lane == 0) dev::mbar_arrive(&wempty[ws]);
-          }
-#ifdef QMM_W8_PROFILE
-          if (out[0].x == 0x12345678u) pc_full += 1;  // keep the conversion ahead of the clock read
-          if (sb == 1) pc_conv += clock64() - t_a;
-#endif
-          W8_PROF_T(t_c);
-          if (!dev::mbar_wait(&cempty[c0 + sb], par ^ 1, status, 27)) { ok = false; break; }
-          W8_PROF_ADD(pc_cempty, t_c);
           uint8_t* cvt = smem + kCvtBase + (c0 + sb) * kCvtBytes;
 #pragma unroll
           for (int p = 0; p < 4; ++p) {
@@ -569,10 +560,23 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
               *reinterpret_cast<uint4*>(cvt + (w.h0 + hh) * kCvtBlock + (piece >> 3) * (BKS * 128) + r * 128 +
                                         (((piece & 7) ^ (r & 7)) << 4)) = out[p];
           }
-          dev::fence_proxy_async();
-          __syncwarp();
-          if (lane == 0) dev::mbar_arrive(&cfull[c0 + sb]);
+          if (sb == 0) {
+#pragma unroll
+            for (int p = 0; p < 4; ++p)
+              if ((p >> 1) < w.nh) out[p] = convert8(in[4 + p]);
+            // every raw byte of the stage is in registers: hand the slot back
+            __syncwarp();
+            if (lane == 0) dev::mbar_arrive(&wempty[ws]);
+          }
         }
+#ifdef QMM_W8_PROFILE
+        pc_conv += clock64() - t_a;
+#endif
+        dev::fence_proxy_async();
+        // the issuing threads wait only for this barrier: make sure the activations are there too
+        if (!dev::mbar_wait(&xfull[cnt % kXStages], (cnt / kXStages) & 1, status, 28)) { ok = false; break; }
+        __syncwarp();
+        if (lane == 0) dev::mbar_arrive(&sfull[grp]);
       }
     }
 #ifdef QMM_W8_PROFILE
