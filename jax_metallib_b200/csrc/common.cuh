@@ -284,6 +284,16 @@ __device__ __forceinline__ void umma_i8_lh(uint32_t d_tmem, uint32_t a_lo, uint3
       : "memory");
 }
 
+__device__ __forceinline__ void umma_i8_lh_if(uint32_t enable, uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi,
+                                              uint32_t b_lo, uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %6, 0;\n\tsetp.ne.b32 q, %7, 0;\n\t"
+      "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %5, p;\n\t}" ::"r"(d_tmem),
+      "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate), "r"(enable)
+      : "memory");
+}
+
 // Shared-memory matrix descriptor (sm_100 format): start address, leading and
 // stride byte offsets in 16-byte units, descriptor version 1, swizzle mode in
 // bits 61..63 (0 none, 2 = 128B, 4 = 64B, 6 = 32B).

@@ -10,7 +10,8 @@
 //  (1) i8gemm: acc[M,N] = a[M,K] . b[K,N], int8/uint8 operands, int32
 //      accumulate (kind::i8, exact).  a is K-major, b is consumed N-major
 //      straight from its row-major [K,N] layout (MN-major descriptor), so no
-//      transposed copy of b is ever made.  Tile 128 (m) x 256 (n) x 128 (k).
+//      transposed copy of b is ever made.  Tile 256 (m, two accumulators) x
+//      256 (n) x 128 (k), one issuing thread per accumulator.
 //      Epilogue: optional int32 store and/or float(acc) * row[m] * col[n].
 //
 //  (2) w8a16: y[M,N] = bf16((x[M,K] @ float(w[K,N])) * scale[N]), bf16
@@ -30,49 +31,73 @@
 namespace qmm {
 namespace tc {
 
-constexpr int kEpiWarps = 4;
 constexpr uint32_t kSwizzle128 = 2;  // UMMA layout type of the 128-byte swizzle
 
 // ============================================================================
 // (1) int8 x int8 -> int32
 // ============================================================================
 namespace i8 {
-constexpr int BM = 128, BN = 256, BK = 128;
-constexpr int kStages = 4;
-constexpr int kABytes = BM * BK;       // 16 KB
-constexpr int kBBytes = BK * BN;       // 32 KB: two [BK x 128] column blocks
-constexpr int kStageBytes = kABytes + kBBytes;
-constexpr int kThreads = (2 + kEpiWarps) * 32;
+constexpr int BMB = 128;            // rows per MMA (its M); a full tile has two such blocks
+constexpr int BN = 256, BK = 128;
+constexpr int kStages = 3;
+constexpr int kABlock = BMB * BK;      // 16 KB: [128 rows][128 k]
+constexpr int kABytes = 2 * kABlock;   // 32 KB: both row blocks
+constexpr int kBBytes = BK * BN;       // 32 KB: two [128 k][128 n] column blocks
+constexpr int kStageBytes = kABytes + kBBytes;  // 64 KB
+constexpr int kEpiWarpsI = 8;
+// Warp roles: 0 TMA, 1 MMA issue for row block 0, 2-9 epilogue, 10 MMA issue for row block 1.
+constexpr int kSecondMmaWarp = 2 + kEpiWarpsI;
+constexpr int kThreads = (kSecondMmaWarp + 1) * 32;
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*barriers*/ + 1024 /*alignment*/;
+static_assert(BK == 128, "the issue loop is written out for four 32-byte k-steps");
+
+// Item i of this CTA.  A tile is 256 rows x 256 columns: two row blocks against
+// one column tile (a 128 x 256 tile needs 94 bytes per clock and SM from L2 at
+// the int8 MMA rate, more than L2 delivers to all SMs at once; sharing the
+// column tile between two accumulators needs 63).  When whole tiles would leave
+// half of the SMs idle, row blocks are dealt out singly.
+struct Work {
+  int tm2, tn, h0, nh;
+};
+__device__ __forceinline__ bool get_work(int i, int tiles_m2, int tiles_n, int halves, int M, Work& w) {
+  const int v = blockIdx.x + i * gridDim.x;
+  const int total = tiles_m2 * tiles_n * (halves ? 2 : 1);
+  if (v >= total) return false;
+  const int tile = halves ? (v >> 1) : v;
+  w.tm2 = tile % tiles_m2;
+  w.tn = tile / tiles_m2;
+  w.h0 = halves ? (v & 1) : 0;
+  w.nh = halves ? 1 : 2;
+  const int blocks_left = (M - w.tm2 * 2 * BMB + BMB - 1) / BMB - w.h0;
+  w.nh = max(0, min(w.nh, blocks_left));
+  return true;
+}
 
 __global__ void __launch_bounds__(kThreads, 1)
 i8gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap,
               int32_t* __restrict__ acc_out, float* __restrict__ f_out,
               const float* __restrict__ row_scale, const float* __restrict__ col_scale, int M, int N,
-              int K, uint32_t idesc, int* status) {
+              int K, uint32_t idesc, int halves, int* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes);
-  uint64_t* empty = full + kStages;
-  uint64_t* tfull = empty + kStages;   // accumulator ready for the epilogue
-  uint64_t* tempty = tfull + 2;        // accumulator drained
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  uint64_t* empty = full + kStages;    // count 2: one commit per issuing thread
+  uint64_t* tfull = empty + kStages;   // accumulators ready for the epilogue (count 2)
+  uint64_t* tempty = tfull + 1;        // accumulators drained
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
-  const int num_tiles = tiles_m * tiles_n;
+  const int tiles_m2 = (M + 2 * BMB - 1) / (2 * BMB), tiles_n = (N + BN - 1) / BN;
   const int kblocks = (K + BK - 1) / BK;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) {
       dev::mbar_init(&full[s], 1);
-      dev::mbar_init(&empty[s], 1);
+      dev::mbar_init(&empty[s], 2);
     }
-    for (int i = 0; i < 2; ++i) {
-      dev::mbar_init(&tfull[i], 1);
-      dev::mbar_init(&tempty[i], kEpiWarps);
-    }
+    dev::mbar_init(tfull, 2);
+    dev::mbar_init(tempty, kEpiWarpsI);
     dev::fence_mbar_init();
   }
   if (warp == 1) {
@@ -89,98 +114,114 @@ i8gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ 
     if (lane == 0) {
       dev::tma_prefetch_desc(&amap);
       dev::tma_prefetch_desc(&bmap);
-      int it = 0;
+      uint32_t s = 0, ph = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
-        const int tm = tile % tiles_m, tn = tile / tiles_m;
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          const int s = it % kStages;
-          const uint32_t ph = (it / kStages) & 1;
+      Work w;
+      for (int i = 0; ok && get_work(i, tiles_m2, tiles_n, halves, M, w); ++i) {
+        if (w.nh == 0) continue;
+        for (int kb = 0; kb < kblocks; ++kb) {
           if (!dev::mbar_wait(&empty[s], ph ^ 1, status, 11)) { ok = false; break; }
           uint8_t* st = smem + s * kStageBytes;
-          dev::mbar_expect_tx(&full[s], kStageBytes);
-          dev::tma_load_2d(st, &amap, &full[s], kb * BK, tm * BM);
-          dev::tma_load_2d(st + kABytes, &bmap, &full[s], tn * BN, kb * BK);
-          dev::tma_load_2d(st + kABytes + BK * 128, &bmap, &full[s], tn * BN + 128, kb * BK);
+          dev::mbar_expect_tx(&full[s], w.nh * kABlock + kBBytes);
+          for (int h = w.h0; h < w.h0 + w.nh; ++h)
+            dev::tma_load_2d(st + h * kABlock, &amap, &full[s], kb * BK, (w.tm2 * 2 + h) * BMB);
+          dev::tma_load_2d(st + kABytes, &bmap, &full[s], w.tn * BN, kb * BK);
+          dev::tma_load_2d(st + kABytes + BK * 128, &bmap, &full[s], w.tn * BN + 128, kb * BK);
+          ph ^= (s == kStages - 1);
+          s = (s == kStages - 1) ? 0 : s + 1;
         }
       }
     }
-  } else if (warp == 1) {
-    // ------------------------------ MMA issuer -----------------------------
+  } else if (warp == 1 || warp == kSecondMmaWarp) {
+    // ------------------------------ MMA issuers ----------------------------
+    // Issuer j multiplies row block j of every item that has it into accumulator j.  The issuing
+    // thread is the serial resource (a tcgen05.mma costs it ~85 cycles, a poll or a commit about
+    // as much), so descriptors are advanced by adds on their low halves, the ring index by a
+    // select, and an absent block is a predicated-off instruction, not a branch.
     if (lane == 0) {
-      int it = 0, tcount = 0;
+      const int me = (warp == 1) ? 0 : 1;
+      constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (kSwizzle128 << 29);  // SBO, version, swizzle
+      // a: K-major, 32 bytes of k per instruction inside the 128-byte swizzle span
+      const uint32_t a_lo0 = (((dev::smem_u32(smem) >> 4) & 0x3FFF) | ((16u >> 4) << 16)) + me * (kABlock >> 4);
+      // b: MN-major, 32 k-rows (4 KB) per instruction; column blocks 16 KB apart
+      const uint32_t b_lo0 = ((dev::smem_u32(smem + kABytes) >> 4) & 0x3FFF) | (((BK * 128u) >> 4) << 16);
+      constexpr uint32_t kStageStep = kStageBytes >> 4, kAStepK = 32 >> 4, kBStepK = (32 * 128) >> 4;
+      const uint32_t d_tmem = tmem_base + me * BN;
+      uint32_t s = 0, ph = 0;
+      int items = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
-        const int as = tcount & 1;
-        if (!dev::mbar_wait(&tempty[as], ((tcount >> 1) & 1) ^ 1, status, 12)) { ok = false; break; }
+      Work w;
+      for (int i = 0; ok && get_work(i, tiles_m2, tiles_n, halves, M, w); ++i) {
+        if (w.nh == 0) continue;
+        if (!dev::mbar_wait(tempty, (items & 1) ^ 1, status, 12)) break;
         dev::tc_fence_after();
-        const uint32_t d_tmem = tmem_base + as * BN;
-        for (int kb = 0; kb < kblocks; ++kb, ++it) {
-          const int s = it % kStages;
-          const uint32_t ph = (it / kStages) & 1;
+        const uint32_t mine = (me >= w.h0) && (me < w.h0 + w.nh);
+        for (int kb = 0; kb < kblocks; ++kb) {
           if (!dev::mbar_wait(&full[s], ph, status, 13)) { ok = false; break; }
           dev::tc_fence_after();
-          const uint32_t a_addr = dev::smem_u32(smem + s * kStageBytes);
-          const uint32_t b_addr = a_addr + kABytes;
-#pragma unroll
-          for (int k = 0; k < BK / 32; ++k) {
-            // a: K-major, 32 bytes of k per instruction inside the 128-byte swizzle span
-            const uint64_t adesc = dev::make_smem_desc(a_addr + k * 32, 16, 1024, kSwizzle128);
-            // b: MN-major, 32 k-rows (4 KB) per instruction; column blocks 16 KB apart
-            const uint64_t bdesc =
-                dev::make_smem_desc(b_addr + k * 32 * 128, BK * 128, 1024, kSwizzle128);
-            dev::umma_i8(d_tmem, adesc, bdesc, idesc, (kb | k) != 0);
-          }
-          dev::tc_commit(&empty[s]);
+          const uint32_t a_s = a_lo0 + s * kStageStep, b_s = b_lo0 + s * kStageStep;
+          dev::umma_i8_lh_if(mine, d_tmem, a_s, kDescHi, b_s, kDescHi, idesc, kb != 0);
+          dev::umma_i8_lh_if(mine, d_tmem, a_s + kAStepK, kDescHi, b_s + kBStepK, kDescHi, idesc, 1);
+          dev::umma_i8_lh_if(mine, d_tmem, a_s + 2 * kAStepK, kDescHi, b_s + 2 * kBStepK, kDescHi, idesc, 1);
+          dev::umma_i8_lh_if(mine, d_tmem, a_s + 3 * kAStepK, kDescHi, b_s + 3 * kBStepK, kDescHi, idesc, 1);
+          dev::tc_commit(&empty[s]);  // second arrival: the other issuer
+          ph ^= (s == kStages - 1);
+          s = (s == kStages - 1) ? 0 : s + 1;
         }
-        if (ok) dev::tc_commit(&tfull[as]);
+        if (ok) dev::tc_commit(tfull);
+        ++items;
       }
     }
   } else {
     // ------------------------------ epilogue -------------------------------
-    const int q = warp & 3;  // TMEM lane quarter this warp may access
-    int tcount = 0;
-    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++tcount) {
-      const int tm = tile % tiles_m, tn = tile / tiles_m;
-      const int as = tcount & 1;
-      if (!dev::mbar_wait(&tfull[as], (tcount >> 1) & 1, status, 14)) break;
+    const int q = warp & 3;         // TMEM lane quarter this warp may access
+    const int j = (warp - 2) >> 2;  // accumulator (row block) of this warp
+    int items = 0;
+    Work w;
+    for (int i = 0; get_work(i, tiles_m2, tiles_n, halves, M, w); ++i) {
+      if (w.nh == 0) continue;
+      if (!dev::mbar_wait(tfull, items & 1, status, 14)) break;
       dev::tc_fence_after();
-      const int row = tm * BM + q * 32 + lane;
-      const float rs = (f_out && row < M) ? __ldg(row_scale + row) : 0.f;
+      const int row = (w.tm2 * 2 + j) * BMB + q * 32 + lane;
+      const bool mine = (j >= w.h0) && (j < w.h0 + w.nh) && row < M;
+      const float rs = (f_out && mine) ? __ldg(row_scale + row) : 0.f;
+      if (j >= w.h0 && j < w.h0 + w.nh) {
 #pragma unroll 1
-      for (int ch = 0; ch < BN / 32; ++ch) {
-        uint32_t r[32];
-        dev::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + as * BN + ch * 32, r);
-        dev::tc_wait_ld();
-        const int col0 = tn * BN + ch * 32;
-        if (row < M) {
-          if (acc_out) {
-            int32_t* dst = acc_out + static_cast<size_t>(row) * N + col0;
+        for (int ch = 0; ch < BN / 32; ++ch) {
+          uint32_t r[32];
+          dev::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + j * BN + ch * 32, r);
+          dev::tc_wait_ld();
+          const int col0 = w.tn * BN + ch * 32;
+          if (mine) {
+            if (acc_out) {
+              int32_t* dst = acc_out + static_cast<size_t>(row) * N + col0;
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
-              if (col0 + 4 * i < N)
-                *reinterpret_cast<uint4*>(dst + 4 * i) =
-                    make_uint4(r[4 * i], r[4 * i + 1], r[4 * i + 2], r[4 * i + 3]);
-          }
-          if (f_out) {
-            float* dst = f_out + static_cast<size_t>(row) * N + col0;
+              for (int i4 = 0; i4 < 8; ++i4)
+                if (col0 + 4 * i4 < N)
+                  *reinterpret_cast<uint4*>(dst + 4 * i4) =
+                      make_uint4(r[4 * i4], r[4 * i4 + 1], r[4 * i4 + 2], r[4 * i4 + 3]);
+            }
+            if (f_out) {
+              float* dst = f_out + static_cast<size_t>(row) * N + col0;
 #pragma unroll
-            for (int i = 0; i < 8; ++i)
-              if (col0 + 4 * i < N) {
-                const float4 cs = __ldg(reinterpret_cast<const float4*>(col_scale + col0 + 4 * i));
-                float4 o;
-                o.x = static_cast<float>(static_cast<int32_t>(r[4 * i])) * rs * cs.x;
-                o.y = static_cast<float>(static_cast<int32_t>(r[4 * i + 1])) * rs * cs.y;
-                o.z = static_cast<float>(static_cast<int32_t>(r[4 * i + 2])) * rs * cs.z;
-                o.w = static_cast<float>(static_cast<int32_t>(r[4 * i + 3])) * rs * cs.w;
-                *reinterpret_cast<float4*>(dst + 4 * i) = o;
-              }
+              for (int i4 = 0; i4 < 8; ++i4)
+                if (col0 + 4 * i4 < N) {
+                  const float4 cs = __ldg(reinterpret_cast<const float4*>(col_scale + col0 + 4 * i4));
+                  float4 o;
+                  o.x = static_cast<float>(static_cast<int32_t>(r[4 * i4])) * rs * cs.x;
+                  o.y = static_cast<float>(static_cast<int32_t>(r[4 * i4 + 1])) * rs * cs.y;
+                  o.z = static_cast<float>(static_cast<int32_t>(r[4 * i4 + 2])) * rs * cs.z;
+                  o.w = static_cast<float>(static_cast<int32_t>(r[4 * i4 + 3])) * rs * cs.w;
+                  *reinterpret_cast<float4*>(dst + 4 * i4) = o;
+                }
+            }
           }
         }
       }
       dev::tc_fence_before();
       __syncwarp();
-      if (lane == 0) dev::mbar_arrive(&tempty[as]);
+      if (lane == 0) dev::mbar_arrive(tempty);
+      ++items;
     }
   }
   dev::tc_fence_before();
@@ -608,7 +649,7 @@ int i8gemm_tcgen05(const void* a, const void* b, int32_t* acc, const float* row_
   using namespace tc::i8;
   CUtensorMap amap, bmap;
   if (int rc = make_tensor_map_2d(&amap, a, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)M,
-                                  (uint64_t)K, (uint64_t)K, BM, 128, CU_TENSOR_MAP_SWIZZLE_128B))
+                                  (uint64_t)K, (uint64_t)K, BMB, 128, CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
   if (int rc = make_tensor_map_2d(&bmap, b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)K,
                                   (uint64_t)N, (uint64_t)N, BK, 128, CU_TENSOR_MAP_SWIZZLE_128B))
@@ -620,11 +661,13 @@ int i8gemm_tcgen05(const void* a, const void* b, int32_t* acc, const float* row_
     configured = true;
   }
   const uint32_t idesc = dev::make_idesc(/*c=s32*/ 2, a_unsigned ? 0 : 1, b_unsigned ? 0 : 1,
-                                         /*a K-major*/ 0, /*b MN-major*/ 1, BM, BN);
-  const int tiles = static_cast<int>(((M + BM - 1) / BM) * ((N + BN - 1) / BN));
-  const int grid = tiles < num_sms() ? tiles : num_sms();
+                                         /*a K-major*/ 0, /*b MN-major*/ 1, BMB, BN);
+  const int tiles = static_cast<int>(((M + 2 * BMB - 1) / (2 * BMB)) * ((N + BN - 1) / BN));
+  const int halves = (tiles * 2 <= num_sms()) ? 1 : 0;  // few tiles: one row block per CTA
+  const int items = tiles * (halves ? 2 : 1);
+  const int grid = items < num_sms() ? items : num_sms();
   i8gemm_kernel<<<grid, kThreads, kSmemBytes, stream>>>(amap, bmap, acc, out, row_scale, col_scale,
-                                                        (int)M, (int)N, (int)K, idesc,
+                                                        (int)M, (int)N, (int)K, idesc, halves,
                                                         device_status_word());
   QMM_CHECK_LAUNCH("i8gemm_kernel");
   return QMM_OK;
