@@ -385,15 +385,17 @@ def run_gpu(args):
             "roofline": {"bound": "tensor", "kernel": "w8a16_kernel (tcgen05 kind::f16, in-kernel int8->bf16)",
                          "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                          "peak_source": f"{peaks['source']} bf16_tflops_sustained (burst {peaks['bf16_tflops']})",
-                         # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture (qkv and o launches,
-                         # 1.09 bytes per kFLOP), scaled by FLOPs to this run's mean launch
-                         "traffic": 1.09e-3 * kern_flops / max(1, len(kernel_events)),
+                         # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture (qkv launch
+                         # 411 MB for 687 GFLOP, o launch 336 MB for 550 GFLOP: 0.60 bytes per kFLOP),
+                         # scaled by FLOPs to this run's mean launch
+                         "traffic": 0.60e-3 * kern_flops / max(1, len(kernel_events)),
                          "traffic_unit": "bytes per launch (mean)"},
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": timed_launches,
             "clocks": clocks,
         }
     if world == 1 and rank == 0 and not args.no_detail:
+        time.sleep(2.0)  # let the power-capped clocks of the timed region recover before the small kernels
         line["detail"] = run_detail(torch, ops, synthetic, lib, device, peaks)
         base, _ = cpu_linears_tflops(budget_s=12.0)
         line["cpu_baseline"] = base
@@ -495,6 +497,23 @@ def _detail_int8_dot(torch, synthetic, lib, device, peaks, graph_time, detail):
         "note": "fused float(acc)*row*col epilogue, f32 output only; 10 rotating B operands; the int8 peak is "
                 "not in MEASURED_PEAKS.json, 2 x the measured bf16 burst stands in for it"}
     del bs
+    # the same M and N at four times the K: separates the per-launch fixed cost from the main-loop rate
+    Kl = 16384
+    al = synthetic.device_int8((Mi, Kl), device, gen)
+    bl = [synthetic.device_int8((Kl, Ni), device, gen) for _ in range(3)]  # 192 MB of B operands
+
+    def run_long(i):
+        st = lib.qmm_i8i8_i32(al.data_ptr(), bl[i % 3].data_ptr(), None, row.data_ptr(), col.data_ptr(),
+                              out.data_ptr(), Mi, Ni, Kl, 0, 0, torch.cuda.current_stream().cuda_stream)
+        assert st == 0
+
+    us_l = graph_time(run_long, 6, replays=10)
+    tops_l = 2.0 * Mi * Ni * Kl / (us_l * 1e-6) / 1e12
+    detail["int8_dot_2048x16384x4096_f32_rescale"] = {
+        "us": us_l, "TOP/s": tops_l, "frac_of_2x_measured_bf16_burst": tops_l / (2 * peaks["bf16_tflops"]),
+        "main_loop_us_per_4096_k": (us_l - us) / 3.0, "fixed_us_per_launch": us - (us_l - us) / 3.0,
+        "note": "context for the line above: same M and N, K x 4"}
+    del bl
 
 
 def _detail_llama_decode(torch, synthetic, device, hbm, stream, detail):
