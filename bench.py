@@ -39,6 +39,11 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
+# SMs left to the all-gather kernel at N > 1.  Measured at N = 2 (40 layers): NCCL's own choice with no SMs
+# reserved 1786 TFLOP/s (its CTAs queue behind the resident GEMM CTAs and delay the next launch), 8 reserved
+# 1660 (the gather becomes the bottleneck), 16: 1967, 32: 1996 (under the power cap the GEMM loses less than
+# its share of SMs).
+NCCL_CTAS = int(os.environ.get("QMM_BENCH_NCCL_CTAS", "32"))
 M_TOKENS = 4096
 D_MODEL, FFN, QKV = 8192, 28672, 10240
 N_LAYERS = 80
@@ -229,9 +234,14 @@ def run_gpu(args):
             raise SystemExit("launch with torch.distributed.run for --gpus > 1")
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=device)
     lib = _lib.load()
+    if world > 1:
+        # The GEMM keeps one CTA per SM resident for a whole launch; leave the all-gather its own SMs.
+        os.environ.setdefault("NCCL_MAX_CTAS", str(NCCL_CTAS))
+        os.environ.setdefault("NCCL_MIN_CTAS", str(NCCL_CTAS))
+        dist.init_process_group("nccl", device_id=device)
+        sms = torch.cuda.get_device_properties(device).multi_processor_count
+        _lib.check(lib.qmm_set_cta_limit(sms - NCCL_CTAS))
     peaks = measured_peaks()
     layers = args.layers
 

@@ -78,6 +78,15 @@ QMM_API size_t qmm_last_error(char* buf, size_t cap);
 QMM_API int qmm_device_status(void);
 QMM_API void qmm_clear_device_status(void);
 
+/* Upper bound on the CTAs of the persistent tcgen05 GEMMs (qmm_w8a16_perchannel,
+ * qmm_i8i8_i32); 0 = one per SM (the default).  Those kernels keep one CTA per
+ * SM resident for the whole launch, so a communication kernel that should run
+ * next to them (an NCCL all-gather of the previous output on a second stream)
+ * finds no SM unless some are left free; a tensor-parallel caller sets the
+ * limit to the SM count minus the CTAs its collective uses.  Process-wide.
+ * No reference counterpart (the reference runs one device). */
+QMM_API int qmm_set_cta_limit(int max_ctas);
+
 /* ---------------------------------------------------------------------------
  * Weight-only int8, per-output-channel scale, f32 activations.
  *   y[M,N] = x[M,K] @ (float(w[K,N]) * scale[N])

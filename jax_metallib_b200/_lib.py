@@ -42,6 +42,7 @@ SIGNATURES = {
     "qmm_affine_matmul": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int64, c_int,
                 c_void_p]),
+    "qmm_set_cta_limit": (c_int, [c_int]),
     "qmm_take_rows_bf16": (c_int, [c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, ctypes.c_uint16, c_void_p]),
     "qmm_add_rmsnorm_bf16": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, ctypes.c_float, c_void_p]),

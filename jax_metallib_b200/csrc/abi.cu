@@ -5,6 +5,8 @@
 
 #include <mutex>
 
+#include <atomic>
+
 #include "common.cuh"
 
 namespace qmm {
@@ -53,6 +55,14 @@ int read_device_status() {
 void clear_device_status() {
   std::call_once(g_status_once, init_status_word);
   if (g_status_host) *reinterpret_cast<volatile int*>(g_status_host) = 0;
+}
+
+static std::atomic<int> g_cta_limit{0};
+
+int gemm_ctas() {
+  const int sms = num_sms();
+  const int lim = g_cta_limit.load(std::memory_order_relaxed);
+  return (lim > 0 && lim < sms) ? lim : sms;
 }
 
 int num_sms() {
@@ -117,6 +127,13 @@ int make_tensor_map_2d(CUtensorMap* out, const void* base, CUtensorMapDataType d
 }  // namespace qmm
 
 extern "C" {
+
+int qmm_set_cta_limit(int max_ctas) {
+  if (max_ctas < 0) return qmm::set_error(QMM_ERR_INVALID_ARGUMENT, "qmm_set_cta_limit: negative limit");
+  qmm::g_cta_limit.store(max_ctas, std::memory_order_relaxed);
+  return QMM_OK;
+}
+
 
 const char* qmm_version(void) { return "qmm-b200 0.1 (sm_100a)"; }
 

@@ -69,6 +69,7 @@ int* device_status_word_if_ready();  // same, but never creates it (null until s
 int read_device_status();    // current value (0 = healthy)
 void clear_device_status();
 int num_sms();               // of the current device (cached)
+int gemm_ctas();             // CTAs a persistent GEMM may launch: num_sms() unless qmm_set_cta_limit lowered it
 
 // 2-D tiled tensor map (TMA descriptor).  rows x cols elements of elem_bytes,
 // row pitch in bytes, box = box_rows x box_cols, swizzle = CU_TENSOR_MAP_SWIZZLE_*.

@@ -663,9 +663,10 @@ int i8gemm_tcgen05(const void* a, const void* b, int32_t* acc, const float* row_
   const uint32_t idesc = dev::make_idesc(/*c=s32*/ 2, a_unsigned ? 0 : 1, b_unsigned ? 0 : 1,
                                          /*a K-major*/ 0, /*b MN-major*/ 1, BMB, BN);
   const int tiles = static_cast<int>(((M + 2 * BMB - 1) / (2 * BMB)) * ((N + BN - 1) / BN));
-  const int halves = (tiles * 2 <= num_sms()) ? 1 : 0;  // few tiles: one row block per CTA
+  const int ctas = gemm_ctas();
+  const int halves = (tiles * 2 <= ctas) ? 1 : 0;  // few tiles: one row block per CTA
   const int items = tiles * (halves ? 2 : 1);
-  const int grid = items < num_sms() ? items : num_sms();
+  const int grid = items < ctas ? items : ctas;
   i8gemm_kernel<<<grid, kThreads, kSmemBytes, stream>>>(amap, bmap, acc, out, row_scale, col_scale,
                                                         (int)M, (int)N, (int)K, idesc, halves,
                                                         device_status_word());
@@ -697,7 +698,7 @@ int w8a16_tcgen05(const uint16_t* x, const int8_t* w, const float* scale, uint16
   sc.tiles_n2 = static_cast<int>((N + 2 * BNW - 1) / (2 * BNW));
   sc.tiles_m = static_cast<int>((M + BMX - 1) / BMX);
   const int tiles = sc.tiles_n2 * sc.tiles_m;
-  const int sms = num_sms();
+  const int sms = gemm_ctas();  // persistent CTAs of this launch
   sc.full_waves = tiles / sms;
   sc.tail_tiles = tiles - sc.full_waves * sms;
   // cut the leftover tiles as finely as shortens the last round

@@ -186,6 +186,31 @@ def test_w8a16_writes_a_column_shard_in_place(cuda):
     assert float(out[:, :256].abs().sum()) == 0 and float(out[:, 384:].abs().sum()) == 0
 
 
+@pytest.mark.parametrize("limit", [140, 37, 1])
+def test_w8a16_and_int8_dot_under_a_cta_limit(cuda, limit):
+    """Fewer persistent CTAs than SMs (SMs left to a collective): same results, bit for bit."""
+    lib = _lib.load()
+    c = synthetic.config5_small(1024, 512, 1280)
+    x = dev(c["x_bits"].view(np.int16), cuda, torch.bfloat16)
+    w, sc = dev(c["w"], cuda), dev(c["scale"], cuda)
+    rng = np.random.default_rng(77)
+    a = torch.from_numpy(rng.integers(-128, 128, (512, 256), dtype=np.int8)).to(cuda)
+    b = torch.from_numpy(rng.integers(-128, 128, (256, 768), dtype=np.int8)).to(cuda)
+    full = ops.w8a16_perchannel(x, w, sc)
+    acc_full, _ = ops.i8_dot(a, b)
+    try:
+        _lib.check(lib.qmm_set_cta_limit(limit))
+        limited = ops.w8a16_perchannel(x, w, sc)
+        acc_limited, _ = ops.i8_dot(a, b)
+        torch.cuda.synchronize()
+    finally:
+        _lib.check(lib.qmm_set_cta_limit(0))
+    assert lib.qmm_device_status() == 0
+    assert torch.equal(full, limited)
+    assert torch.equal(acc_full, acc_limited)
+    assert lib.qmm_set_cta_limit(-1) != 0
+
+
 def test_w8a16_small_shape_route(cuda):
     c = synthetic.config5_small(7, 50, 30)
     y = ops.w8a16_perchannel(dev(c["x_bits"].view(np.int16), cuda, torch.bfloat16), dev(c["w"], cuda),
