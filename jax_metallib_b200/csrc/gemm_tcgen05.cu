@@ -242,14 +242,16 @@ constexpr int kXStages = 3;    // activation ring, held until the MMAs that read
 constexpr int kWStages = 4;    // raw-weight ring, held only until a stage is in the converters' registers
 constexpr int kCvtBufs = 4;    // converted sub-blocks between the converter warps and the MMA
 constexpr int kCvtWarps = 8;    // converter warps per group
-constexpr int kCvtGroups = 2;   // groups take alternate 64-k stages
-constexpr int kEpiWarpsW = 8;
-// Warp roles: 0 TMA (activations), 1 MMA issue for channel block 0, 2-9 epilogue, 10-25 converters,
-// 26 TMA (raw weights), 27 MMA issue for channel block 1.  One thread needs ~85 cycles to issue a
-// tcgen05.mma and ~150 more per sub-block for its waits and commits, about what the MMAs themselves
-// take; two issuing threads (one per accumulator) leave the tensor pipe as the limit.
-constexpr int kFirstCvtWarp = 2 + kEpiWarpsW;
-constexpr int kWProducerWarp = kFirstCvtWarp + kCvtGroups * kCvtWarps;
+constexpr int kCvtGroups = 3;   // group g converts the stages with cnt % 3 == g
+constexpr int kCvtSlots = 2;    // converted stages in flight (two sub-block buffers each)
+// Warp roles: 0 TMA (activations), 1 MMA issue for channel block 0, 2-25 workers (convert the
+// stages of a tile, then drain its accumulators), 26 TMA (raw weights), 27 MMA issue for channel
+// block 1.  One thread needs ~85 cycles to issue a tcgen05.mma and about as much per wait and per
+// commit, about what the MMAs themselves take; two issuing threads (one per accumulator) leave the
+// tensor pipe as the limit.
+constexpr int kFirstCvtWarp = 2;
+constexpr int kWorkerWarps = kCvtGroups * kCvtWarps;
+constexpr int kWProducerWarp = kFirstCvtWarp + kWorkerWarps;
 constexpr int kSecondMmaWarp = kWProducerWarp + 1;
 constexpr int kWarps = kSecondMmaWarp + 1;
 constexpr int kRawBlock = BK * BNW;               // 8 KB  int8 [k][128 n]
@@ -360,7 +362,7 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
   uint64_t* wfull = xfull + kXStages;    // raw weights landed
   uint64_t* wempty = wfull + kWStages;   // raw weights are in the converters' registers
   uint64_t* sfull = wempty + kWStages;   // stage ready for the MMAs: converted, and its activations landed
-  uint64_t* consumed = sfull + kCvtGroups;  // the MMAs of a stage retired (ring of kConsumed stages)
+  uint64_t* consumed = sfull + kCvtSlots;   // the MMAs of a stage retired (ring of kConsumed stages)
   uint64_t* tfull = consumed + kConsumed;   // accumulators complete
   uint64_t* tempty = tfull + 1;             // accumulators drained
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 1);
@@ -374,10 +376,10 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
       dev::mbar_init(&wfull[s], 1);
       dev::mbar_init(&wempty[s], kCvtWarps);
     }
-    for (int g = 0; g < kCvtGroups; ++g) dev::mbar_init(&sfull[g], kCvtWarps);
+    for (int g = 0; g < kCvtSlots; ++g) dev::mbar_init(&sfull[g], kCvtWarps);
     for (int i = 0; i < kConsumed; ++i) dev::mbar_init(&consumed[i], 2);  // one commit per issuing thread
     dev::mbar_init(tfull, 2);
-    dev::mbar_init(tempty, kEpiWarpsW);
+    dev::mbar_init(tempty, kWorkerWarps);
     dev::fence_mbar_init();
   }
   if (warp == 1) {
@@ -447,7 +449,7 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
                              me * kAStepH;
       const uint32_t b_lo0 = ((dev::smem_u32(smem) >> 4) & 0x3FFF) | ((16u >> 4) << 16);
       const uint32_t d = tmem_base + me * BMX;
-      uint32_t g = 0, gpar = 0;   // converter group of the stage and the parity of its use
+      uint32_t g = 0, gpar = 0;   // converted-stage slot and the parity of its use
       uint32_t xs = 0;            // activation slot
       uint32_t c6 = 0;            // consumed-ring index
       int items = 0;
@@ -478,7 +480,7 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
           dev::umma_f16_lh_if(mine, d, a_c + kAStepBuf, kDescHi, b_s + 2 * kBStepK, kDescHi, idesc, 1);
           dev::umma_f16_lh_if(mine, d, a_c + kAStepBuf + kAStepK, kDescHi, b_s + 3 * kBStepK, kDescHi, idesc, 1);
           dev::tc_commit(&consumed[c6]);  // second arrival: the other issuer
-          gpar ^= g;  // the parity flips after group 1's stage
+          gpar ^= g;  // the parity flips after slot 1's stage
           g ^= 1;
           xs = (xs == kXStages - 1) ? 0 : xs + 1;
           c6 = (c6 == kConsumed - 1) ? 0 : c6 + 1;
@@ -495,63 +497,25 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
       }
 #endif
     }
-  } else if (warp < 2 + kEpiWarpsW) {
-    // ------------------------------ epilogue -------------------------------
-    // warp & 3 selects the 32 TMEM lanes (channels) a warp may read; the two
-    // warps of a lane quarter take alternate 32-row chunks.
-    const int q = warp & 3, half = (warp - 2) >> 2;
-    int items = 0;
-    Work w;
-    for (int i = 0; get_work(sc, i, M, N, w); ++i) {
-      if (w.nh == 0) continue;
-      if (!dev::mbar_wait(tfull, items & 1, status, 25)) break;
-      dev::tc_fence_after();
-      for (int h = w.h0; h < w.h0 + w.nh; ++h) {
-        const int n = (w.tn2 * 2 + h) * BNW + q * 32 + lane;  // this thread's output channel
-        const float scl = (n < N) ? __ldg(scale + n) : 0.f;
-#pragma unroll 1
-        for (int ch = half; ch < w.m_cols / 32; ch += 2) {
-          uint32_t r[32];
-          dev::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + h * BMX + ch * 32, r);
-          dev::tc_wait_ld();
-          const int m0 = w.tm * BMX + w.m_off + ch * 32;
-          // pair neighbouring channels so that every lane stores 4 bytes: even
-          // lanes write rows m0+2j, odd lanes rows m0+2j+1
-#pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const float a = __uint_as_float(r[2 * j]) * scl;
-            const float b = __uint_as_float(r[2 * j + 1]) * scl;
-            const float send = (lane & 1) ? a : b;
-            const float got = __shfl_xor_sync(0xFFFFFFFFu, send, 1);
-            const int m = m0 + 2 * j + (lane & 1);
-            const uint32_t packed = (lane & 1) ? dev::pack_bf16x2(got, b) : dev::pack_bf16x2(a, got);
-            const int n_even = n & ~1;
-            if (m < M && n_even < N)
-              *reinterpret_cast<uint32_t*>(y + static_cast<size_t>(m) * ldy + n_even) = packed;
-          }
-        }
-      }
-      dev::tc_fence_before();
-      __syncwarp();
-      if (lane == 0) dev::mbar_arrive(tempty);
-      ++items;
-    }
   } else {
-    // ------------------------------ converters -----------------------------
-    // A half-warp reads one 128-byte raw row, 8 bytes per lane (conflict-free
-    // in any permutation); each lane writes the 16-byte bf16 chunk it made, so
-    // a quarter-warp store covers the eight chunks of one 128-byte row of one
-    // 64-channel half: conflict-free as well, with no divergence.  One warp
-    // needs several hundred cycles for its share of a sub-block (dependent ALU
-    // chains), more than the MMAs of the sub-block take, so two groups of
-    // eight warps take alternate stages.  The raw slot is handed back as soon
-    // as its bytes are in registers.
+    // ------------------------------ workers --------------------------------
+    // Conversion: a half-warp reads one 128-byte raw row, 8 bytes per lane (conflict-free in any
+    // permutation); each lane writes the 16-byte bf16 chunk it made, so a quarter-warp store
+    // covers the eight chunks of one 128-byte row of one 64-channel half: conflict-free as well,
+    // with no divergence.  One warp needs ~1000 cycles for its share of a stage (dependent ALU
+    // chains), as long as the MMAs of the stage take, so three groups of eight warps take every
+    // third stage.  The raw slot is handed back as soon as its bytes are in registers.
+    // Epilogue: when the tile's stages are converted the same 24 warps drain its accumulators
+    // (warp & 3 selects the 32 TMEM lanes = channels a warp may read; the six warps of a lane
+    // quarter share the 32-row chunks).
     const int o = warp - kFirstCvtWarp;
     const int grp = o / kCvtWarps, cw = o % kCvtWarps;
+    const int q = warp & 3, esub = o >> 2;
     const int piece = lane & 15;         // 8 channels: [8*piece, 8*piece+8)
     const int rsub = lane >> 4;          // row within a pair
-    const int c0 = 2 * grp;              // this group's two converted buffers
     unsigned cnt = 0;  // stages since the start of the launch
+    int r3 = 0;        // cnt % 3
+    int items = 0;
     bool ok = true;
     Work w;
 #ifdef QMM_W8_PROFILE
@@ -560,9 +524,10 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
 #endif
     for (int i = 0; ok && get_work(sc, i, M, N, w); ++i) {
       if (w.nh == 0) continue;
-      for (int kb = 0; kb < kblocks; ++kb, ++cnt) {
-        if ((cnt & 1) != static_cast<unsigned>(grp)) continue;
+      for (int kb = 0; kb < kblocks; ++kb, ++cnt, r3 = (r3 == 2) ? 0 : r3 + 1) {
+        if (r3 != grp) continue;
         const int ws = cnt & (kWStages - 1);
+        const int slot = cnt & 1, c0 = 2 * slot;  // the stage's two converted buffers
         const uint8_t* raw = smem + kRawBase + ws * kRawBytes;
         W8_PROF_T(t_f);
         if (!dev::mbar_wait(&wfull[ws], (cnt / kWStages) & 1, status, 26)) { ok = false; break; }
@@ -617,8 +582,41 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
         // the issuing threads wait only for this barrier: make sure the activations are there too
         if (!dev::mbar_wait(&xfull[cnt % kXStages], (cnt / kXStages) & 1, status, 28)) { ok = false; break; }
         __syncwarp();
-        if (lane == 0) dev::mbar_arrive(&sfull[grp]);
+        if (lane == 0) dev::mbar_arrive(&sfull[slot]);
       }
+      if (!ok) break;
+      // ---- epilogue of this item
+      if (!dev::mbar_wait(tfull, items & 1, status, 25)) break;
+      dev::tc_fence_after();
+      const int chunks = w.m_cols / 32;
+#pragma unroll 1
+      for (int idx = esub; idx < w.nh * chunks; idx += kWorkerWarps / 4) {
+        const int h = w.h0 + idx / chunks, ch = idx % chunks;
+        const int n = (w.tn2 * 2 + h) * BNW + q * 32 + lane;  // this thread's output channel
+        const float scl = (n < N) ? __ldg(scale + n) : 0.f;
+        uint32_t r[32];
+        dev::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + h * BMX + ch * 32, r);
+        dev::tc_wait_ld();
+        const int m0 = w.tm * BMX + w.m_off + ch * 32;
+        // pair neighbouring channels so that every lane stores 4 bytes: even
+        // lanes write rows m0+2j, odd lanes rows m0+2j+1
+#pragma unroll
+        for (int j = 0; j < 16; ++j) {
+          const float a = __uint_as_float(r[2 * j]) * scl;
+          const float b = __uint_as_float(r[2 * j + 1]) * scl;
+          const float send = (lane & 1) ? a : b;
+          const float got = __shfl_xor_sync(0xFFFFFFFFu, send, 1);
+          const int m = m0 + 2 * j + (lane & 1);
+          const uint32_t packed = (lane & 1) ? dev::pack_bf16x2(got, b) : dev::pack_bf16x2(a, got);
+          const int n_even = n & ~1;
+          if (m < M && n_even < N)
+            *reinterpret_cast<uint32_t*>(y + static_cast<size_t>(m) * ldy + n_even) = packed;
+        }
+      }
+      dev::tc_fence_before();
+      __syncwarp();
+      if (lane == 0) dev::mbar_arrive(tempty);
+      ++items;
     }
 #ifdef QMM_W8_PROFILE
     if (o == 0 && lane == 0) {
