@@ -235,13 +235,13 @@ def run_gpu(args):
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     lib = _lib.load()
+    gather = os.environ.get("QMM_BENCH_GATHER", "p2p") if world > 1 else "none"
     if world > 1:
-        # The GEMM keeps one CTA per SM resident for a whole launch; leave the all-gather its own SMs.
-        os.environ.setdefault("NCCL_MAX_CTAS", str(NCCL_CTAS))
-        os.environ.setdefault("NCCL_MIN_CTAS", str(NCCL_CTAS))
+        if gather == "nccl":
+            # The GEMM keeps one CTA per SM resident for a whole launch; leave the all-gather its own SMs.
+            os.environ.setdefault("NCCL_MAX_CTAS", str(NCCL_CTAS))
+            os.environ.setdefault("NCCL_MIN_CTAS", str(NCCL_CTAS))
         dist.init_process_group("nccl", device_id=device)
-        sms = torch.cuda.get_device_properties(device).multi_processor_count
-        _lib.check(lib.qmm_set_cta_limit(sms - NCCL_CTAS))
     peaks = measured_peaks()
     layers = args.layers
 
@@ -250,21 +250,49 @@ def run_gpu(args):
     x_host = torch.randn((M_TOKENS, D_MODEL), dtype=torch.float32).to(torch.bfloat16).pin_memory()
     h_host = torch.randn((M_TOKENS, FFN), dtype=torch.float32).to(torch.bfloat16).pin_memory()
     acts = {"x": x_host.to(device), "h": h_host.to(device)}
-    # gathered outputs, one buffer per linear kind (reused by every layer)
-    outs = {}
+    # gathered outputs, one buffer per linear kind (reused by every layer); at N > 1 each is [P, M, N/P]
+    # (what all_gather_into_tensor builds); a consumer addresses it as (rank, row, column-in-shard)
+    outs, peer_outs = {}, {}
+    if gather == "p2p":
+        # Symmetric (peer-mapped) output buffers: a rank's GEMM writes its [M, N/P] block in place and
+        # copy-engine peer copies put the same block into every other rank's buffer.  No SM is spent on
+        # the exchange, so the GEMM keeps all of them.
+        ok = 1
+        try:
+            import torch.distributed._symmetric_memory as symm_mem
+            total = sum(M_TOKENS * n for _, _, n, _ in layer_shapes())
+            sym = symm_mem.empty((total,), dtype=torch.bfloat16, device=device)
+            hdl = symm_mem.rendezvous(sym, dist.group.WORLD)
+        except Exception as exc:  # noqa: BLE001 - any failure means "not available here"
+            ok = 0
+            print(f"[rank {rank}] symmetric memory unavailable ({exc!r}); using the NCCL all-gather", file=sys.stderr)
+        flag = torch.tensor([ok], dtype=torch.int32, device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            gather = "nccl"
+        else:
+            off = 0
+            for name, k, n, act in layer_shapes():
+                shape = (world, M_TOKENS, n // world)
+                outs[name] = sym[off:off + M_TOKENS * n].view(shape)
+                peer_outs[name] = {p: hdl.get_buffer(p, shape, torch.bfloat16, off) for p in range(world) if p != rank}
+                off += M_TOKENS * n
+    if gather == "nccl":
+        sms = torch.cuda.get_device_properties(device).multi_processor_count
+        _lib.check(lib.qmm_set_cta_limit(sms - NCCL_CTAS))
     for name, k, n, act in layer_shapes():
         if world == 1:
             outs[name] = torch.empty((M_TOKENS, n), dtype=torch.bfloat16, device=device)
-        else:
-            # all_gather_into_tensor concatenates rank buffers: [P, M, N/P]; a consumer
-            # addresses it as a 3-D tensor (rank, row, column-in-shard)
+        elif gather == "nccl":
             outs[name] = torch.empty((world, M_TOKENS, n // world), dtype=torch.bfloat16, device=device)
     shard_out = {name: torch.empty((M_TOKENS, n // world), dtype=torch.bfloat16, device=device)
-                 for name, k, n, act in layer_shapes()} if world > 1 else None
+                 for name, k, n, act in layer_shapes()} if gather == "nccl" else None
     result_host = torch.empty((M_TOKENS, D_MODEL), dtype=torch.bfloat16).pin_memory()
 
     compute = torch.cuda.current_stream()
     comm = torch.cuda.Stream() if world > 1 else None
+    peer_streams = {p: torch.cuda.Stream() for p in range(world) if p != rank} if gather == "p2p" else {}
+    sync_word = torch.zeros(1, dtype=torch.int32, device=device) if world > 1 else None
     launches = [0]
     kernel_events = []
 
@@ -290,22 +318,38 @@ def run_gpu(args):
                         e0 = torch.cuda.Event(enable_timing=True)
                         e1 = torch.cuda.Event(enable_timing=True)
                         e0.record()
-                    ops.w8a16_perchannel(xin, w, s, out=shard_out[name])
+                    mine = outs[name][rank] if gather == "p2p" else shard_out[name]
+                    ops.w8a16_perchannel(xin, w, s, out=mine)
                     if record_kernels:
                         e1.record()
                         kernel_events.append((e0, e1, 2.0 * M_TOKENS * k * ns))
                     ready = torch.cuda.Event()
                     ready.record(compute)
                     comm.wait_event(ready)
-                    with torch.cuda.stream(comm):
-                        dist.all_gather_into_tensor(outs[name].view(-1), shard_out[name].view(-1))
-                        done = torch.cuda.Event()
-                        done.record(comm)
+                    if gather == "p2p":
+                        # one contiguous [M, N/P] block per peer, each on its own stream (copy engines)
+                        for p, st in peer_streams.items():
+                            st.wait_event(ready)
+                            with torch.cuda.stream(st):
+                                peer_outs[name][p][rank].copy_(mine, non_blocking=True)
+                            comm.wait_stream(st)
+                        with torch.cuda.stream(comm):
+                            done = torch.cuda.Event()
+                            done.record(comm)
+                    else:
+                        with torch.cuda.stream(comm):
+                            dist.all_gather_into_tensor(outs[name].view(-1), shard_out[name].view(-1))
+                            done = torch.cuda.Event()
+                            done.record(comm)
                     prev_done = prev_done or {}
                     prev_done[name] = done
                 launches[0] += 1
         if world > 1:
             compute.wait_stream(comm)
+            if gather == "p2p":
+                # a rank's buffers are complete when every peer's copies are: one 4-byte all-reduce,
+                # ordered behind each rank's own copies, is the step's rendezvous
+                dist.all_reduce(sync_word)
 
     def barrier():
         if world > 1:
@@ -388,8 +432,11 @@ def run_gpu(args):
             "config": {"workload": f"int8 per-channel weight-only linears, Llama-3-70B shapes, {layers} layers x "
                                    "(qkv 8192->10240, o 8192->8192, gate_up 8192->57344, down 28672->8192), "
                                    "bf16 activations [4096,8192]",
-                       "parallelism": f"tp{world} (weights column-sharded along N, NCCL all-gather of outputs "
-                                      "into [P, M, N/P], overlapped on a second stream)" if world > 1 else "tp1",
+                       "parallelism": (f"tp{world} (weights column-sharded along N; outputs gathered into [P, M, N/P] "
+                                       + ("by copy-engine peer copies of each finished [M, N/P] block into every peer's "
+                                          "symmetric buffer over NVLink, overlapped on side streams, one 4-byte NCCL "
+                                          "all-reduce per step as the rendezvous)" if gather == "p2p" else
+                                          "by NCCL all-gather overlapped on a second stream)")) if world > 1 else "tp1",
                        "l2": "every launch reads a different weight matrix (>= 67 MB each), inputs exceed L2",
                        "layers": layers},
             "roofline": {"bound": "tensor", "kernel": "w8a16_kernel (tcgen05 kind::f16, in-kernel int8->bf16)",
