@@ -34,6 +34,7 @@
 // drains.  Everything that can depend on earlier work (activations, output,
 // workspace) is touched only after griddepcontrol.wait; when the caller states
 // that the weights are static, their first loads are issued before that wait.
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -580,11 +581,22 @@ static int launch(const CUtensorMap& wmap, const CUtensorMap& xmap, const uint16
 }
 
 static int blocks_per_sm(int M) { return M <= 16 ? 2 : 1; }
+static int min_units_per_cta() {
+  // QMM_W4_MIN_UNITS overrides it for experiments.  On the decode-step bench (4096x6144, 4096x4096,
+  // 4096x28672, 14336x4096 at M = 8): 2 and 3 units 3.35 ms per step, 4 units 3.26 ms, 6 units 3.50 ms.
+  static const int v = [] {
+    const char* e = getenv("QMM_W4_MIN_UNITS");
+    const int n = e ? atoi(e) : 4;
+    return n >= 1 && n <= 64 ? n : 4;
+  }();
+  return v;
+}
 static int grid_size(int U, int M) {
-  // every CTA resident at once; small problems get at least two units per CTA
+  // every CTA resident at once; small problems get at least four units per CTA
   // so that few CTAs share a column block
   const int p = blocks_per_sm(M) * num_sms();
-  const int q = (U + 1) / 2;
+  const int mu = min_units_per_cta();
+  const int q = (U + mu - 1) / mu;
   return q < p ? q : p;
 }
 static int slots_for(int G, int U, int P) {
