@@ -144,9 +144,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// The same with a suspend-time hint: the thread may sleep in hardware for up to `ns` nanoseconds
+// waiting for the phase instead of returning at once, so a waiting warp issues a few instructions
+// per millisecond instead of a few per 30 cycles (polling warps otherwise take issue slots from
+// the warps that share their scheduler).
+__device__ __forceinline__ bool mbar_try_wait_sleep(uint64_t* bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
 // Bounded wait.  Returns false (and records `tag` in the status word) when the
 // phase did not complete within kWaitLimitNs; callers then stop issuing work
-// and fall through to their teardown (free TMEM, return).
+// and fall through to their teardown (free TMEM, return).  This form polls: the
+// wake-up is immediate, at the price of issue slots; it is for waits on the
+// critical path of a tensor-core pipeline.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* status, int tag) {
   for (int i = 0; i < 128; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
@@ -157,6 +174,19 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, int* s
     for (int i = 0; i < 32; ++i) {
       if (mbar_try_wait(bar, parity)) return true;
     }
+    if (globaltimer_ns() - t0 > kWaitLimitNs) break;
+  }
+  if (status) atomicExch(status, (tag << 16) | QMM_ERR_TIMEOUT);
+  return false;
+}
+// The same bound, sleeping in hardware between tries: for warps that wait long
+// (an epilogue warp during a main loop) or whose wake-up latency does not matter
+// (the bandwidth-bound decode kernels, where polling neighbours cost more).
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, int* status, int tag) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint64_t t0 = globaltimer_ns();
+  while (true) {
+    if (mbar_try_wait_sleep(bar, parity, 1000000u)) return true;  // sleeps up to 1 ms per try
     if (globaltimer_ns() - t0 > kWaitLimitNs) break;
   }
   if (status) atomicExch(status, (tag << 16) | QMM_ERR_TIMEOUT);

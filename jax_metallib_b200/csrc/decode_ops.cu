@@ -210,7 +210,7 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
       int s = 0;
       uint32_t ph = 0;
       for (int t = t_begin; t < t_end; ++t) {
-        if (!dev::mbar_wait(&empty[s], ph ^ 1, status, 31)) break;
+        if (!dev::mbar_wait_relaxed(&empty[s], ph ^ 1, status, 31)) break;
         uint8_t* st = smem + s * kAttnStageBytes;
         const int grow = bh * L + t * kTileRows;  // row in the [B*Hkv*L, 128] view
         dev::mbar_expect_tx(&full[s], kAttnStageBytes);
@@ -255,7 +255,7 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
   int s = 0;
   uint32_t ph = 0;
   for (int t = t_begin; t < t_end; ++t) {
-    if (!dev::mbar_wait(&full[s], ph, status, 32)) return;
+    if (!dev::mbar_wait_relaxed(&full[s], ph, status, 32)) return;
     const uint32_t kb = dev::smem_u32(smem + s * kAttnStageBytes);
     const uint32_t vb = kb + 16384;
     float sacc[2][4];
@@ -450,7 +450,7 @@ bf16_small_m_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
       int s = 0;
       uint32_t ph = 0;
       for (int kb = 0; kb < kblocks; ++kb) {
-        if (!dev::mbar_wait(&empty[s], ph ^ 1, status, 41)) break;
+        if (!dev::mbar_wait_relaxed(&empty[s], ph ^ 1, status, 41)) break;
         uint8_t* st = smem + s * kStage;
         dev::mbar_expect_tx(&full[s], kWBytes + MT * 8 * BK * 2);
         dev::tma_load_2d_hint(st, &wmap, &full[s], n0, kb * BK, policy);
@@ -477,7 +477,7 @@ bf16_small_m_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
   int s = 0;
   uint32_t ph = 0;
   for (int kb = 0; kb < kblocks; ++kb) {
-    if (!dev::mbar_wait(&full[s], ph, status, 42)) return;
+    if (!dev::mbar_wait_relaxed(&full[s], ph, status, 42)) return;
     const uint32_t st = dev::smem_u32(smem + s * kStage);
     const uint32_t wbase = st + (warp >> 1) * (kWBytes / 2);
     const uint32_t xbase = st + kWBytes;

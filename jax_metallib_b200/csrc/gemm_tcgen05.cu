@@ -180,7 +180,7 @@ i8gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ 
     Work w;
     for (int i = 0; get_work(i, tiles_m2, tiles_n, halves, M, w); ++i) {
       if (w.nh == 0) continue;
-      if (!dev::mbar_wait(tfull, items & 1, status, 14)) break;
+      if (!dev::mbar_wait_relaxed(tfull, items & 1, status, 14)) break;
       dev::tc_fence_after();
       const int row = (w.tm2 * 2 + j) * BMB + q * 32 + lane;
       const bool mine = (j >= w.h0) && (j < w.h0 + w.nh) && row < M;
@@ -586,7 +586,7 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
       }
       if (!ok) break;
       // ---- epilogue of this item
-      if (!dev::mbar_wait(tfull, items & 1, status, 25)) break;
+      if (!dev::mbar_wait_relaxed(tfull, items & 1, status, 25)) break;
       dev::tc_fence_after();
       const int chunks = w.m_cols / 32;
 #pragma unroll 1

@@ -238,7 +238,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
     for (int it = 0; it < n_units + kXLag; ++it) {
       if (it < n_units) {
         if (it >= prefetched) {
-          if (!dev::mbar_wait(&empty[s_issue], ph_issue ^ 1, status, 1)) break;
+          if (!dev::mbar_wait_relaxed(&empty[s_issue], ph_issue ^ 1, status, 1)) break;
           if (lane == 0) issue_weights(s_issue, c, g, it);
         }
         if (lane == 0) issue_x(s_issue, g);
@@ -246,7 +246,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
         if (++s_issue == S) { s_issue = 0; ph_issue ^= 1; }
       }
       if (it >= kXLag) {
-        if (!dev::mbar_wait(&xraw[s_conv], ph_conv, status, 4)) break;
+        if (!dev::mbar_wait_relaxed(&xraw[s_conv], ph_conv, status, 4)) break;
         uint8_t* st = smem + s_conv * L::kStage;
         float* fac = reinterpret_cast<float*>(st + L::kOffF);
         uint4 v[kPasses];
@@ -411,7 +411,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
 #ifdef QMM_W4_PROFILE
       long long c0 = clock64();
 #endif
-      if (!dev::mbar_wait(&full[s], ph, status, 2)) {
+      if (!dev::mbar_wait_relaxed(&full[s], ph, status, 2)) {
         ok = false;
         break;
       }
