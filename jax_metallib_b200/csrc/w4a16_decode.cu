@@ -16,15 +16,15 @@
 // permuted to fragment order, written back in place.
 // Eight consumer warps each own 32 columns.  A consumer reads the tile with
 // ldmatrix.trans, which turns the k-pair-per-byte layout into registers that
-// hold (same column, two k) in their 16-bit halves; one logic op per register
-// makes the f16 pair 1024+q (low nibbles) or 1024+16q (high nibbles, no shift
-// needed: the factor 16 is what the activations of odd k were divided by), one
-// packed subtract removes 1024+z resp. 1024+16z, and mma.sync.m16n8k16 (f16,
-// f32 accumulate) takes the weights as its 16-row operand and the activations
-// as its 8-column operand: one MMA per 256 weights for M <= 8.  The integer
-// ALU pipe, the narrow one on this SM, sees five instructions per eight
-// weights; the subtracts go to the FMA pipe.  Per group:
-//   y += s[g,n] * 2^e[m,g] * acc.
+// hold (same column, two k) in their 16-bit halves; one AND per register
+// leaves the f16 subnormal q * 2^-24 (low nibbles) or 16 q * 2^-24 (high
+// nibbles, no shift needed: the factor 16 is what the activations of odd k
+// were divided by), and mma.sync.m16n8k16 (f16, f32 accumulate) takes the
+// weights as its 16-row operand and the activations as its 8-column operand:
+// one MMA per 256 weights for M <= 8, plus one MMA per slab with an all-ones
+// weight operand that yields sum_k x, the factor of the zero point.  Five
+// integer instructions per eight weights and nothing else.  Per group:
+//   y += s[g,n] * 2^e[m,g] * 2^24 * (acc - z[g,n] * sum_k x).
 // Partial sums of CTAs sharing a column block meet in the caller's workspace;
 // the last CTA to arrive adds them in a fixed order (deterministic result) and
 // writes bf16.  The workspace counters are left at zero.
@@ -96,16 +96,6 @@ __device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32
       : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t mask, uint32_t orv) {
-  uint32_t r;
-  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(r) : "r"(a), "r"(mask), "r"(orv));  // (a & b) | c
-  return r;
-}
-__device__ __forceinline__ uint32_t hsub2_u32(uint32_t a, uint32_t b) {
-  uint32_t r;
-  asm("sub.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
-  return r;
-}
 __device__ __forceinline__ uint32_t pack_f16x2(float lo, float hi) {
   uint32_t r;
   asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
@@ -129,15 +119,16 @@ __device__ __forceinline__ int cta_of_unit(long long u, int P, int U) {
 }
 
 // Eight packed weights of one register -> four f16x2 MMA operand registers
-// (columns c and c+1, k pairs (4t, 4t+2) and (4t+1, 4t+3) of the slab), zero
-// point removed.
-__device__ __forceinline__ void dequant8(uint32_t w, uint32_t zlo0, uint32_t zhi0, uint32_t zlo1,
-                                         uint32_t zhi1, uint32_t (&r)[4]) {
+// (columns c and c+1, k pairs (4t, 4t+2) and (4t+1, 4t+3) of the slab).  A
+// nibble left in place is the f16 subnormal q * 2^-24 (low nibble) or
+// 16 q * 2^-24 (high nibble; the factor 16 is what the activations of odd k
+// were divided by): no offset to remove, exact products.
+__device__ __forceinline__ void dequant8(uint32_t w, uint32_t (&r)[4]) {
   const uint32_t t = w >> 8;
-  r[0] = hsub2_u32(lop3_and_or(w, 0x000F000Fu, 0x64006400u), zlo0);  // bytes 0/2, low nibbles
-  r[1] = hsub2_u32(lop3_and_or(w, 0x00F000F0u, 0x64006400u), zhi0);  // bytes 0/2, high nibbles (x16)
-  r[2] = hsub2_u32(lop3_and_or(t, 0x000F000Fu, 0x64006400u), zlo1);  // bytes 1/3
-  r[3] = hsub2_u32(lop3_and_or(t, 0x00F000F0u, 0x64006400u), zhi1);
+  r[0] = w & 0x000F000Fu;  // bytes 0/2, low nibbles
+  r[1] = w & 0x00F000F0u;  // bytes 0/2, high nibbles (x16)
+  r[2] = t & 0x000F000Fu;  // bytes 1/3
+  r[3] = t & 0x00F000F0u;
 }
 
 template <int MT, bool ZP_PACKED>
@@ -425,7 +416,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
 
       // per-group constants of this thread's four columns (pairs lc, lc+16)
       float sc[2][2];
-      uint32_t zc[2][4];  // per pair: 1024+z and 1024+16z as f16x2, for both columns
+      float zf[2][2];  // zero points
 #pragma unroll
       for (int j = 0; j < 2; ++j) {
         const int col = lc + 16 * j;
@@ -442,19 +433,20 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
           z0 = zb & 0xFFu;
           z1 = zb >> 8;
         }
-        zc[j][0] = (0x6400u | z0) * 0x00010001u;
-        zc[j][1] = (0x6400u | (z0 << 4)) * 0x00010001u;
-        zc[j][2] = (0x6400u | z1) * 0x00010001u;
-        zc[j][3] = (0x6400u | (z1 << 4)) * 0x00010001u;
+        zf[j][0] = __uint_as_float(0x4B000000u | z0) - 8388608.f;
+        zf[j][1] = __uint_as_float(0x4B000000u | z1) - 8388608.f;
       }
 
       float acc[2][MT][4];
+      float xsum[MT][4];  // [0], [1]: sum over the group of this thread's two activation rows (x 2^-24)
 #pragma unroll
-      for (int j = 0; j < 2; ++j)
+      for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt)
-#pragma unroll
-          for (int i = 0; i < 4; ++i) acc[j][mt][i] = 0.f;
+        for (int i = 0; i < 4; ++i) {
+          acc[0][mt][i] = 0.f;
+          acc[1][mt][i] = 0.f;
+          xsum[mt][i] = 0.f;
+        }
       const uint32_t xb = st_addr + x_off;
 
       const int hl = half_lo(it), hh = half_hi(it);
@@ -474,14 +466,19 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
                          : "=r"(xf[mt][0]), "=r"(xf[mt][1])
                          : "r"((xb ^ (slab << 5)) + mt * 8 * kXRowBytes));
           uint32_t r[4];
-          dequant8(wa[q], zc[0][0], zc[0][1], zc[0][2], zc[0][3], r);
+          dequant8(wa[q], r);
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt)
             mma_f16_16816(acc[0][mt], r[0], r[2], r[1], r[3], xf[mt][0], xf[mt][1]);
-          dequant8(wb[q], zc[1][0], zc[1][1], zc[1][2], zc[1][3], r);
+          dequant8(wb[q], r);
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt)
             mma_f16_16816(acc[1][mt], r[0], r[2], r[1], r[3], xf[mt][0], xf[mt][1]);
+          // a weight operand of all ones gives the sum of the slab's activations, which is what
+          // the zero point multiplies
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt)
+            mma_f16_16816(xsum[mt], 0x00010001u, 0x00010001u, 0x00100010u, 0x00100010u, xf[mt][0], xf[mt][1]);
         }
       }
       // group epilogue: per pair this thread holds columns (c, c+1) for rows
@@ -492,10 +489,15 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
         const float2 f = *reinterpret_cast<const float2*>(fac + mt * 8 + 2 * t4);
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
-          yacc[j][mt][0] = fmaf(sc[j][0] * f.x, acc[j][mt][0], yacc[j][mt][0]);
-          yacc[j][mt][1] = fmaf(sc[j][0] * f.y, acc[j][mt][1], yacc[j][mt][1]);
-          yacc[j][mt][2] = fmaf(sc[j][1] * f.x, acc[j][mt][2], yacc[j][mt][2]);
-          yacc[j][mt][3] = fmaf(sc[j][1] * f.y, acc[j][mt][3], yacc[j][mt][3]);
+          // sum_k (q - z) x = acc - z * sum_k x, both in units of 2^-24
+          const float v0 = fmaf(-zf[j][0], xsum[mt][0], acc[j][mt][0]) * 16777216.f;
+          const float v1 = fmaf(-zf[j][0], xsum[mt][1], acc[j][mt][1]) * 16777216.f;
+          const float v2 = fmaf(-zf[j][1], xsum[mt][0], acc[j][mt][2]) * 16777216.f;
+          const float v3 = fmaf(-zf[j][1], xsum[mt][1], acc[j][mt][3]) * 16777216.f;
+          yacc[j][mt][0] = fmaf(sc[j][0] * f.x, v0, yacc[j][mt][0]);
+          yacc[j][mt][1] = fmaf(sc[j][0] * f.y, v1, yacc[j][mt][1]);
+          yacc[j][mt][2] = fmaf(sc[j][1] * f.x, v2, yacc[j][mt][2]);
+          yacc[j][mt][3] = fmaf(sc[j][1] * f.y, v3, yacc[j][mt][3]);
         }
       }
       __syncwarp();
