@@ -498,6 +498,8 @@ def run_detail(torch, ops, synthetic, lib, device, peaks, items=None):
         _detail_int4_decode(torch, ops, synthetic, lib, device, hbm, graph_time, detail)
     if want("int8_dot"):
         _detail_int8_dot(torch, synthetic, lib, device, peaks, graph_time, detail)
+    if items is not None and "int4_decode_sweep" in items:  # not part of the default run
+        _detail_int4_sweep(torch, ops, synthetic, lib, device, graph_time, detail)
     if want("llama_decode"):
         _detail_llama_decode(torch, synthetic, device, hbm, stream, detail)
     if want("small_f32"):
@@ -530,6 +532,27 @@ def _detail_int4_decode(torch, ops, synthetic, lib, device, hbm, graph_time, det
             "us_warm_l2_single_copy": us_warm,
             "note": f"{copies} rotating weight copies (cold L2), zero points packed 4-bit, CUDA-graph replay"}
     del wqs
+
+
+def _detail_int4_sweep(torch, ops, synthetic, lib, device, graph_time, detail):
+    # M = 1 int4 g128 matmul over a range of sizes: time = fixed cost + bytes / streaming rate
+    gen = synthetic.torch_generator(device, 3, 7)
+    ws = torch.zeros(lib.qmm_w4a16_g128_workspace_bytes(8, 28672, 16384), dtype=torch.uint8, device=device)
+    rows = []
+    for K, N in [(128, 256), (2048, 14336), (4096, 14336), (8192, 14336), (16384, 14336), (4096, 4096), (4096, 28672)]:
+        G = K // 128
+        copies = max(2, min(12, (300 << 20) // max(1, K * N // 2)))
+        wqs = [torch.randint(0, 256, (K // 2, N), dtype=torch.uint8, device=device, generator=gen) for _ in range(copies)]
+        sc = synthetic.device_uniform((G, N), 0.002, 0.01, device, gen, torch.bfloat16)
+        zp = torch.randint(0, 256, (G, N // 2), dtype=torch.uint8, device=device, generator=gen)
+        x = synthetic.device_normal((1, K), device, gen, torch.bfloat16)
+        y = torch.empty((1, N), dtype=torch.bfloat16, device=device)
+        us = graph_time(lambda i: ops.w4a16_g128(x, wqs[i % copies], sc, zp, zeros_packed=True, out=y, workspace=ws,
+                                                   static_weights=True), copies * 2)
+        nbytes = K * N // 2 + G * N * 2 + G * N // 2
+        rows.append({"K": K, "N": N, "MB": nbytes / 1e6, "us": us, "TB/s": nbytes / us / 1e6})
+        del wqs
+    detail["int4_g128_decode_M1_size_sweep"] = rows
 
 
 def _detail_int8_dot(torch, synthetic, lib, device, peaks, graph_time, detail):
@@ -645,7 +668,8 @@ def main():
     ap.add_argument("--detail-only", action="store_true",
                     help="run only the per-workload detail (small case for profiling) and print it as JSON")
     ap.add_argument("--detail-items", default="",
-                    help="comma-separated subset of int4_decode,int8_dot,llama_decode,small_f32")
+                    help="comma-separated subset of int4_decode,int8_dot,llama_decode,small_f32 (and int4_decode_sweep, "
+                         "which is not part of the default run)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
