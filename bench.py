@@ -502,6 +502,8 @@ def run_detail(torch, ops, synthetic, lib, device, peaks, items=None):
         _detail_int4_sweep(torch, ops, synthetic, lib, device, graph_time, detail)
     if want("llama_decode"):
         _detail_llama_decode(torch, synthetic, device, hbm, stream, detail)
+    if want("operator_api"):
+        _detail_operator_api(torch, synthetic, lib, device, hbm, graph_time, detail)
     if want("small_f32"):
         _detail_small_f32(torch, synthetic, lib, device, hbm, graph_time, detail)
     return detail
@@ -553,6 +555,47 @@ def _detail_int4_sweep(torch, ops, synthetic, lib, device, graph_time, detail):
         rows.append({"K": K, "N": N, "MB": nbytes / 1e6, "us": us, "TB/s": nbytes / us / 1e6})
         del wqs
     detail["int4_g128_decode_M1_size_sweep"] = rows
+
+
+def _detail_operator_api(torch, synthetic, lib, device, hbm, graph_time, detail):
+    # the operator-API formats at a decode-sized shape: f16 activations [M, 4096] x packed weights [14336, 4096]
+    M, K, N = 4, 4096, 14336
+    gen = synthetic.torch_generator(device, 6, 0)
+    x = synthetic.device_normal((M, K), device, gen, torch.float16)
+    y = torch.empty((M, N), dtype=torch.float16, device=device)
+    st = lambda: torch.cuda.current_stream().cuda_stream  # noqa: E731
+    QMM_F16 = 1
+    cases = []
+    for bits, gs in ((4, 64), (8, 64)):
+        wbytes = N * K * bits // 8
+        copies = max(2, (300 << 20) // wbytes)
+        ws = [torch.randint(0, 256, (wbytes,), dtype=torch.uint8, device=device, generator=gen) for _ in range(copies)]
+        sc = synthetic.device_uniform((N, K // gs), 0.002, 0.01, device, gen)
+        bi = synthetic.device_uniform((N, K // gs), -0.05, 0.05, device, gen)
+
+        def run(i, ws=ws, sc=sc, bi=bi, bits=bits, gs=gs, copies=copies):
+            assert lib.qmm_affine_matmul(x.data_ptr(), ws[i % copies].data_ptr(), sc.data_ptr(), bi.data_ptr(),
+                                         y.data_ptr(), M, N, K, bits, gs, QMM_F16, st()) == 0
+
+        cases.append((f"affine_{bits}bit_g{gs}", run, copies, wbytes + 2 * N * (K // gs) * 4))
+    for mode, name, gs, wb in ((0, "mxfp4", 32, 4), (1, "mxfp8", 32, 8), (2, "nvfp4", 16, 4)):
+        wbytes = N * K * wb // 8
+        copies = max(2, (300 << 20) // wbytes)
+        # element codes and scale codes below the NaN patterns
+        ws = [torch.randint(0, 0x70, (wbytes,), dtype=torch.uint8, device=device, generator=gen) for _ in range(copies)]
+        sc = torch.randint(0x70, 0x7C, (N, K // gs), dtype=torch.uint8, device=device, generator=gen)
+
+        def run(i, ws=ws, sc=sc, mode=mode, copies=copies):
+            assert lib.qmm_mx_matmul(x.data_ptr(), ws[i % copies].data_ptr(), sc.data_ptr(), y.data_ptr(), M, N, K,
+                                     mode, QMM_F16, st()) == 0
+
+        cases.append((name, run, copies, wbytes + N * (K // gs)))
+    for name, run, copies, nbytes in cases:
+        us = graph_time(run, copies * 2)
+        detail[f"operator_api_{name}_M{M}_{N}x{K}"] = {
+            "us": us, "bytes": nbytes, "GB/s": nbytes / (us * 1e-6) / 1e9,
+            "frac_of_measured_hbm": nbytes / (us * 1e-6) / 1e9 / hbm,
+            "note": "qgemm_kernel (one warp per output column); rotating weight copies (cold L2)"}
 
 
 def _detail_int8_dot(torch, synthetic, lib, device, peaks, graph_time, detail):
@@ -668,7 +711,7 @@ def main():
     ap.add_argument("--detail-only", action="store_true",
                     help="run only the per-workload detail (small case for profiling) and print it as JSON")
     ap.add_argument("--detail-items", default="",
-                    help="comma-separated subset of int4_decode,int8_dot,llama_decode,small_f32 (and int4_decode_sweep, "
+                    help="comma-separated subset of int4_decode,int8_dot,llama_decode,operator_api,small_f32 (and int4_decode_sweep, "
                          "which is not part of the default run)")
     args = ap.parse_args()
     if args.impl == "reference":
