@@ -83,7 +83,7 @@ def max_rel_err(out: np.ndarray, ref: np.ndarray) -> float:
 
 
 # --------------------------------------------------------------------------
-# StableHLO-level configs (BASELINE configs 1, 2, 3, 5)
+# StableHLO-level configurations (int8 per-channel, int8 dot, int4 g128, sharded int8 per-channel)
 # --------------------------------------------------------------------------
 
 
