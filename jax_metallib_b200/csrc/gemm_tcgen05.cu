@@ -328,23 +328,43 @@ __device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, 
   tm = p * kPanelTiles + r % rows;
 }
 
-// Item `i` of this CTA; false when the CTA is done.
+// Item `i` of this CTA; false when the CTA is done.  After its full-wave tiles a CTA takes a
+// contiguous run of the tail's parts (tile-major: part 2h + mh of a tile cut in four is channel
+// block h, row half mh) and works it off in the largest aligned pieces: a whole tile, a channel
+// block with all its rows, or a single part, so that neighbouring parts cost one pipeline fill
+// and use the full-width MMA.
 __device__ __forceinline__ bool get_work(const Sched& sc, int i, int M, int N, Work& w) {
   const int G = gridDim.x;
-  int tile, sub = 0, div = 1;
+  int tile, sub = 0, len = 0;  // len: parts covered, in units of 1 / tail_div tile; 0 = whole tile
+  const int div = sc.tail_div;
   if (i < sc.full_waves) {
     tile = blockIdx.x + i * G;
   } else {
-    const int v = blockIdx.x + (i - sc.full_waves) * G;
-    if (v >= sc.tail_tiles * sc.tail_div) return false;
-    div = sc.tail_div;
-    tile = sc.full_waves * G + v / div;
-    sub = v % div;
+    const long long total = static_cast<long long>(sc.tail_tiles) * div;
+    int pos = static_cast<int>(blockIdx.x * total / G);
+    const int end = static_cast<int>((blockIdx.x + 1) * total / G);
+    for (int skip = i - sc.full_waves;; --skip) {
+      if (pos >= end) return false;
+      const int r = pos % div;
+      if (r == 0 && pos + div <= end) len = div;                       // whole tile
+      else if (div == 4 && (r & 1) == 0 && pos + 2 <= end) len = 2;    // one channel block, all rows
+      else len = 1;
+      if (skip == 0) break;
+      pos += len;
+    }
+    tile = sc.full_waves * G + pos / div;
+    sub = pos % div;
+    if (len == div) len = 0;
   }
   tile_coords(tile, sc.tiles_m, sc.tiles_n2, w.tm, w.tn2);
   w.h0 = 0; w.nh = 2; w.m_off = 0; w.m_cols = BMX;
-  if (div == 2) { w.h0 = sub; w.nh = 1; }
-  if (div == 4) { w.h0 = sub >> 1; w.nh = 1; w.m_off = (sub & 1) * (BMX / 2); w.m_cols = BMX / 2; }
+  if (len != 0) {
+    if (div == 2) { w.h0 = sub; w.nh = 1; }
+    if (div == 4) {
+      w.h0 = sub >> 1; w.nh = 1;
+      if (len == 1) { w.m_off = (sub & 1) * (BMX / 2); w.m_cols = BMX / 2; }
+    }
+  }
   const int blocks_left = (N - w.tn2 * 2 * BNW + BNW - 1) / BNW - w.h0;  // channel blocks that exist
   w.nh = max(0, min(w.nh, blocks_left));
   if (w.tm * BMX + w.m_off >= M) w.nh = 0;
