@@ -26,6 +26,8 @@
 //      per-channel scale is one register per thread and stores of a warp are
 //      contiguous along N.  Leftover tiles of the last round are cut into
 //      halves or quarters.
+#include <cstdlib>
+
 #include "common.cuh"
 
 namespace qmm {
@@ -264,7 +266,7 @@ constexpr int kCvtBase = kRawBase + kWStages * kRawBytes;    // 160 KB
 constexpr int kBarBase = kCvtBase + kCvtBufs * kCvtBytes;    // 224 KB
 constexpr int kThreads = kWarps * 32;
 constexpr int kSmemBytes = kBarBase + 256 + 1024;
-constexpr int kPanelTiles = 8;  // activation tiles swept together so that they stay in L2
+constexpr int kPanelTiles = 8;  // most activation tiles swept together (fewer when K is long: a panel should stay in L2)
 // One "consumed" barrier per stage in a ring of 6 (a multiple of both the activation ring and the
 // two converted stage slots): the activation producer waits for stage cnt - 3, the converters for
 // stage cnt - 2, and the issuing threads commit once per stage.
@@ -310,6 +312,7 @@ __device__ __forceinline__ uint4 convert8(const uint2& in) {
 // round-robin, so that the last round costs 1 / tail_div of a tile.
 struct Sched {
   int tiles_n2, tiles_m, full_waves, tail_tiles, tail_div;
+  int panel;  // activation tiles per panel
 };
 struct Work {
   int tn2, tm;   // tile coordinates (256-channel, 256-row units)
@@ -317,15 +320,15 @@ struct Work {
   int m_off, m_cols;  // rows [m_off, m_off + m_cols) of the activation tile
 };
 
-// Tile order: activation tiles are swept in panels of kPanelTiles; inside a
+// Tile order: activation tiles are swept in panels of `panel` tiles; inside a
 // panel the weight tile changes slowest, so the CTAs that run together share
 // one panel of activations (it stays in L2) and a handful of weight tiles.
-__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int& tm, int& tn) {
-  const int per_panel = kPanelTiles * tiles_n;
+__device__ __forceinline__ void tile_coords(int tile, int tiles_m, int tiles_n, int panel, int& tm, int& tn) {
+  const int per_panel = panel * tiles_n;
   const int p = tile / per_panel, r = tile - p * per_panel;
-  const int rows = min(kPanelTiles, tiles_m - p * kPanelTiles);  // the last panel may be short
+  const int rows = min(panel, tiles_m - p * panel);  // the last panel may be short
   tn = r / rows;
-  tm = p * kPanelTiles + r % rows;
+  tm = p * panel + r % rows;
 }
 
 // Item `i` of this CTA; false when the CTA is done.  After its full-wave tiles a CTA takes a
@@ -356,7 +359,7 @@ __device__ __forceinline__ bool get_work(const Sched& sc, int i, int M, int N, W
     sub = pos % div;
     if (len == div) len = 0;
   }
-  tile_coords(tile, sc.tiles_m, sc.tiles_n2, w.tm, w.tn2);
+  tile_coords(tile, sc.tiles_m, sc.tiles_n2, sc.panel, w.tm, w.tn2);
   w.h0 = 0; w.nh = 2; w.m_off = 0; w.m_cols = BMX;
   if (len != 0) {
     if (div == 2) { w.h0 = sub; w.nh = 1; }
@@ -716,6 +719,14 @@ int w8a16_tcgen05(const uint16_t* x, const int8_t* w, const float* scale, uint16
   sc.tiles_n2 = static_cast<int>((N + 2 * BNW - 1) / (2 * BNW));
   sc.tiles_m = static_cast<int>((M + BMX - 1) / BMX);
   const int tiles = sc.tiles_n2 * sc.tiles_m;
+  {
+    // a panel of activation tiles (256 rows x K bf16 each) should fit in half of L2 (measured at
+    // K = 28672, N = 8192: panels of 8 / 4 / 3 / 2 tiles give 1180 / 1218 / 1149 / 1134 TFLOP/s)
+    const long long tile_bytes = 2ll * BMX * K;
+    long long pt = (64ll << 20) / (tile_bytes > 0 ? tile_bytes : 1);
+    sc.panel = static_cast<int>(pt < 2 ? 2 : (pt > kPanelTiles ? kPanelTiles : pt));
+    if (const char* e = getenv("QMM_W8_PANEL")) sc.panel = atoi(e) > 0 ? atoi(e) : sc.panel;
+  }
   const int sms = gemm_ctas();  // persistent CTAs of this launch
   sc.full_waves = tiles / sms;
   sc.tail_tiles = tiles - sc.full_waves * sms;
