@@ -45,7 +45,9 @@ __global__ void take_rows_kernel(const uint16_t* __restrict__ table, const int32
 // ---------------------------------------------------------------------------
 // h = x (+ r);  y = bf16( float(bf16(h * rsqrt(mean(h^2) + eps))) * w )
 // ---------------------------------------------------------------------------
-__global__ void __launch_bounds__(256)
+constexpr int kNormThreads = 1024, kNormPairs = 8;  // a row of up to 16384 values lives in registers
+
+__global__ void __launch_bounds__(kNormThreads)
 add_rmsnorm_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ r,
                    const uint16_t* __restrict__ w, uint16_t* __restrict__ sum_out,
                    uint16_t* __restrict__ norm_out, int D, float eps) {
@@ -55,32 +57,40 @@ add_rmsnorm_kernel(const uint16_t* __restrict__ x, const uint16_t* __restrict__ 
   const uint32_t* xp = reinterpret_cast<const uint32_t*>(x + static_cast<size_t>(row) * D);
   const uint32_t* rp = r ? reinterpret_cast<const uint32_t*>(r + static_cast<size_t>(row) * D) : nullptr;
   const uint32_t* wp = reinterpret_cast<const uint32_t*>(w);
-  extern __shared__ float hbuf[];  // D floats: the (rounded) sum row
-  __shared__ float red[8];
+  __shared__ float red[kNormThreads / 32];
+  float2 h[kNormPairs];  // the (rounded) sum row, this thread's pairs
   float ss = 0.f;
-  for (int i = threadIdx.x; i < D / 2; i += blockDim.x) {
-    float2 a = bf2_to_f2(xp[i]);
-    if (rp) {
-      const float2 b = bf2_to_f2(rp[i]);
-      // the residual stream is kept in bf16: round the sum once
-      const uint32_t s = dev::pack_bf16x2(a.x + b.x, a.y + b.y);
-      if (sum_out) reinterpret_cast<uint32_t*>(sum_out + static_cast<size_t>(row) * D)[i] = s;
-      a = bf2_to_f2(s);
+#pragma unroll
+  for (int it = 0; it < kNormPairs; ++it) {
+    const int i = threadIdx.x + it * kNormThreads;
+    h[it] = make_float2(0.f, 0.f);
+    if (i < D / 2) {
+      float2 a = bf2_to_f2(__ldg(xp + i));
+      if (rp) {
+        const float2 b = bf2_to_f2(__ldg(rp + i));
+        // the residual stream is kept in bf16: round the sum once
+        const uint32_t s = dev::pack_bf16x2(a.x + b.x, a.y + b.y);
+        if (sum_out) reinterpret_cast<uint32_t*>(sum_out + static_cast<size_t>(row) * D)[i] = s;
+        a = bf2_to_f2(s);
+      }
+      h[it] = a;
+      ss += a.x * a.x + a.y * a.y;
     }
-    hbuf[2 * i] = a.x;
-    hbuf[2 * i + 1] = a.y;
-    ss += a.x * a.x + a.y * a.y;
   }
   for (int off = 16; off >= 1; off >>= 1) ss += __shfl_xor_sync(0xFFFFFFFFu, ss, off);
   if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = ss;
   __syncthreads();
-  float tot = 0.f;
-  for (int i = 0; i < (blockDim.x >> 5); ++i) tot += red[i];
+  float tot = (threadIdx.x & 31) < kNormThreads / 32 ? red[threadIdx.x & 31] : 0.f;
+  for (int off = 16; off >= 1; off >>= 1) tot += __shfl_xor_sync(0xFFFFFFFFu, tot, off);
   const float inv = rsqrtf(tot / static_cast<float>(D) + eps);
-  for (int i = threadIdx.x; i < D / 2; i += blockDim.x) {
-    const float2 g = bf2_to_f2(wp[i]);
-    const float2 n = bf2_to_f2(dev::pack_bf16x2(hbuf[2 * i] * inv, hbuf[2 * i + 1] * inv));
-    reinterpret_cast<uint32_t*>(norm_out + static_cast<size_t>(row) * D)[i] = dev::pack_bf16x2(n.x * g.x, n.y * g.y);
+#pragma unroll
+  for (int it = 0; it < kNormPairs; ++it) {
+    const int i = threadIdx.x + it * kNormThreads;
+    if (i < D / 2) {
+      const float2 g = bf2_to_f2(__ldg(wp + i));
+      const float2 n = bf2_to_f2(dev::pack_bf16x2(h[it].x * inv, h[it].y * inv));
+      reinterpret_cast<uint32_t*>(norm_out + static_cast<size_t>(row) * D)[i] = dev::pack_bf16x2(n.x * g.x, n.y * g.y);
+    }
   }
 }
 
@@ -547,13 +557,8 @@ int qmm_add_rmsnorm_bf16(const uint16_t* x, const uint16_t* residual, const uint
   QMM_REQUIRE(B >= 0 && D > 0 && D % 2 == 0 && D <= 16384, QMM_ERR_UNSUPPORTED,
               "qmm_add_rmsnorm_bf16: D must be even and <= 16384");
   if (B == 0) return QMM_OK;
-  static bool configured = false;
-  if (!configured) {
-    QMM_CUDA_TRY(cudaFuncSetAttribute(dec::add_rmsnorm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 65536));
-    configured = true;
-  }
-  QMM_CUDA_TRY(launch_pdl(dec::add_rmsnorm_kernel, dim3((unsigned)B), dim3(256), D * sizeof(float), (cudaStream_t)stream,
-                          x, residual, weight, sum_out, norm_out, (int)D, eps));
+  QMM_CUDA_TRY(launch_pdl(dec::add_rmsnorm_kernel, dim3((unsigned)B), dim3(dec::kNormThreads), 0, (cudaStream_t)stream, x,
+                          residual, weight, sum_out, norm_out, (int)D, eps));
   return QMM_OK;
 }
 
