@@ -5,9 +5,12 @@
  * erfanzar/jax-metallib.  Every entry point takes plain device pointers, sizes
  * and a CUDA stream (passed as void*, i.e. a cudaStream_t); nothing in the
  * signatures depends on PyTorch, JAX or C++ types.  All tensors are dense and
- * row-major unless a leading dimension is given.  Calls are asynchronous on
- * the given stream and allocate nothing: scratch memory, where a kernel needs
- * it, is passed in by the caller (see the *_workspace_bytes queries).
+ * row-major unless a leading dimension is given.  Kernel entry points are
+ * asynchronous on the given stream and allocate no device memory: scratch,
+ * where a kernel needs it, is passed in by the caller (see the
+ * *_workspace_bytes queries) or, for qmm_w4a16_g128_static_scratch, is a fixed
+ * array inside the library.  The runtime objects of qmm_rt.h (buffers, events,
+ * executables) do allocate; they are a separate layer on top of these calls.
  *
  * Each function names the interface of the reference it stands in for
  * (paths relative to the reference project root).
@@ -76,6 +79,10 @@ QMM_API size_t qmm_last_error(char* buf, size_t cap);
  * DEADLINE_EXCEEDED (src/pjrt_plugin/core/completion_event.h:62-83,
  * src/pjrt_plugin/api/pjrt_event.cc:46-59). */
 QMM_API int qmm_device_status(void);
+/* Host-only self-check of the library's internal bookkeeping (per-device
+ * "configured once" masks, cached environment switches).  Needs no GPU.
+ * Returns 0 when every check passes.  No reference counterpart. */
+QMM_API int qmm_selftest_host(void);
 QMM_API void qmm_clear_device_status(void);
 
 /* Upper bound on the CTAs of the persistent tcgen05 GEMMs (qmm_w8a16_perchannel,
@@ -181,7 +188,12 @@ QMM_API int qmm_w4a16_g128(const uint16_t* x_bf16, const uint8_t* wq, const uint
  *  - the array is shared by every call on the device and keeps what the last
  *    call wrote; the part that must start at zero is cleared on the stream by
  *    each call, but two calls that may run at the same time on one GPU race
- *    on it — keep them on one stream or order them yourself. */
+ *    on it — keep them on one stream or order them yourself;
+ *  - a device-side wait that gives up is recorded in the status word of
+ *    qmm_device_status() only if that word exists when the kernel is launched;
+ *    creating it allocates pinned host memory, which this call will not do, so
+ *    call qmm_device_status() once during start-up if you want such timeouts
+ *    reported (and later launches refused) here as well. */
 #define QMM_STATIC_SCRATCH_BYTES (8u << 20)
 QMM_API int qmm_w4a16_g128_static_scratch(const uint16_t* x_bf16, const uint8_t* wq,
                                           const uint16_t* scales_bf16, const uint8_t* zeros,

@@ -25,6 +25,7 @@ SIGNATURES = {
     "qmm_status_name": (c_char_p, [c_int]),
     "qmm_last_error": (c_size_t, [c_char_p, c_size_t]),
     "qmm_device_status": (c_int, []),
+    "qmm_selftest_host": (c_int, []),
     "qmm_clear_device_status": (None, []),
     "qmm_w8a32_perchannel": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]),
     "qmm_w8a16_perchannel": (

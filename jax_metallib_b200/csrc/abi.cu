@@ -1,6 +1,7 @@
 // Host-side plumbing shared by every entry point: error strings, the device
 // status word, SM count cache and the TMA descriptor encoder.
 #include <stdarg.h>
+#include <stdlib.h>
 #include <string.h>
 
 #include <mutex>
@@ -48,6 +49,10 @@ int* device_status_word() {
 }
 // The status word if it has been created already, else null.  Never allocates.
 int* device_status_word_if_ready() { return g_status_dev; }
+// Current value if the word exists already, else 0.  Never allocates.
+int read_device_status_if_ready() {
+  return g_status_host ? *reinterpret_cast<volatile int*>(g_status_host) : 0;
+}
 int read_device_status() {
   std::call_once(g_status_once, init_status_word);
   return g_status_host ? *reinterpret_cast<volatile int*>(g_status_host) : 0;
@@ -78,6 +83,28 @@ int num_sms() {
     cached_dev = dev;
   }
   return cached;
+}
+
+int ensure_dynamic_smem(const void* func, int bytes, std::atomic<uint64_t>& done) {
+  int dev = -1;
+  QMM_CUDA_TRY(cudaGetDevice(&dev));
+  if (device_marked(done, dev)) return QMM_OK;
+  // Setting the attribute twice is harmless, so two threads racing here both set it; the mark is
+  // made only after the attribute is in place, so nobody launches without it.
+  QMM_CUDA_TRY(cudaFuncSetAttribute(func, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes));
+  mark_device_once(done, dev);
+  return QMM_OK;
+}
+
+int env_int_once(const char* name, int dflt, std::atomic<int>& cache) {
+  // cache: INT_MIN = not read yet
+  int v = cache.load(std::memory_order_relaxed);
+  if (v != INT32_MIN) return v;
+  const char* e = getenv(name);
+  v = (e && *e) ? atoi(e) : dflt;
+  if (v == INT32_MIN) v = dflt;
+  cache.store(v, std::memory_order_relaxed);
+  return v;
 }
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -158,6 +185,23 @@ size_t qmm_last_error(char* buf, size_t cap) {
     buf[c] = 0;
   }
   return n;
+}
+
+int qmm_selftest_host(void) {
+  // per-device once bookkeeping: every ordinal fires exactly once, independently of the others
+  std::atomic<uint64_t> mask{0};
+  for (int round = 0; round < 2; ++round)
+    for (int d = 0; d < qmm::kMaxDevices; ++d) {
+      const bool first = qmm::mark_device_once(mask, d);
+      if (first != (round == 0)) return 1;
+      if (!qmm::device_marked(mask, d)) return 2;
+    }
+  std::atomic<uint64_t> other{0};
+  if (qmm::device_marked(other, 3) || !qmm::mark_device_once(other, 3) || qmm::device_marked(other, 4)) return 3;
+  if (!qmm::mark_device_once(other, -1) || !qmm::mark_device_once(other, qmm::kMaxDevices)) return 4;
+  std::atomic<int> cache{INT32_MIN};
+  if (qmm::env_int_once("QMM_SELFTEST_UNSET_VARIABLE", 7, cache) != 7 || cache.load() != 7) return 5;
+  return 0;
 }
 
 int qmm_device_status(void) { return qmm::read_device_status(); }

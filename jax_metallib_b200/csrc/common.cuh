@@ -8,6 +8,8 @@
 #include <stdint.h>
 #include <stdio.h>
 
+#include <atomic>
+
 #include "../../include/qmm.h"
 
 // ---------------------------------------------------------------------------
@@ -67,8 +69,29 @@ inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
 int* device_status_word();   // device-visible pointer (may be null on failure)
 int* device_status_word_if_ready();  // same, but never creates it (null until someone has)
 int read_device_status();    // current value (0 = healthy)
+int read_device_status_if_ready();  // same, but never creates the word (0 until someone has)
 void clear_device_status();
 int num_sms();               // of the current device (cached)
+
+// Per-device "done once" bookkeeping.  Function attributes such as the dynamic
+// shared-memory opt-in belong to a device's context, so a process that drives
+// several GPUs has to set them once on each; `done` is a bit mask of device
+// ordinals kept by the call site.  mark_device_once returns true for exactly
+// one caller per (mask, ordinal) and is safe to call from any thread.
+constexpr int kMaxDevices = 64;
+inline bool device_marked(const std::atomic<uint64_t>& done, int ordinal) {
+  return ordinal >= 0 && ordinal < kMaxDevices && ((done.load(std::memory_order_acquire) >> ordinal) & 1ull);
+}
+inline bool mark_device_once(std::atomic<uint64_t>& done, int ordinal) {
+  if (ordinal < 0 || ordinal >= kMaxDevices) return true;  // untracked ordinals repeat the (idempotent) set-up
+  const uint64_t bit = 1ull << ordinal;
+  return (done.fetch_or(bit, std::memory_order_acq_rel) & bit) == 0;
+}
+// Opt a kernel in to `bytes` of dynamic shared memory on the current device,
+// once per device.  `func` is the kernel's host symbol.
+int ensure_dynamic_smem(const void* func, int bytes, std::atomic<uint64_t>& done);
+// Environment switches are read once, when first asked for.
+int env_int_once(const char* name, int dflt, std::atomic<int>& cache);
 int gemm_ctas();             // CTAs a persistent GEMM may launch: num_sms() unless qmm_set_cta_limit lowered it
 
 // 2-D tiled tensor map (TMA descriptor).  rows x cols elements of elem_bytes,
@@ -191,6 +214,18 @@ __device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity
   }
   if (status) atomicExch(status, (tag << 16) | QMM_ERR_TIMEOUT);
   return false;
+}
+
+// Warp-wide forms for waits that all 32 lanes make together: each lane waits
+// (so each observes the phase itself), then the lanes agree on one outcome.
+// Without the vote, right at the time limit one lane could see the phase
+// complete while its neighbour gives up, and the lanes that went on would
+// synchronise with lanes that have left.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, int* status, int tag) {
+  return __all_sync(0xFFFFFFFFu, mbar_wait(bar, parity, status, tag));
+}
+__device__ __forceinline__ bool mbar_wait_relaxed_warp(uint64_t* bar, uint32_t parity, int* status, int tag) {
+  return __all_sync(0xFFFFFFFFu, mbar_wait_relaxed(bar, parity, status, tag));
 }
 
 // ---- TMA --------------------------------------------------------------------

@@ -265,7 +265,7 @@ attn_partial_kernel(const __grid_constant__ CUtensorMap kmap, const __grid_const
   int s = 0;
   uint32_t ph = 0;
   for (int t = t_begin; t < t_end; ++t) {
-    if (!dev::mbar_wait_relaxed(&full[s], ph, status, 32)) return;
+    if (!dev::mbar_wait_relaxed_warp(&full[s], ph, status, 32)) return;
     const uint32_t kb = dev::smem_u32(smem + s * kAttnStageBytes);
     const uint32_t vb = kb + 16384;
     float sacc[2][4];
@@ -487,7 +487,7 @@ bf16_small_m_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
   int s = 0;
   uint32_t ph = 0;
   for (int kb = 0; kb < kblocks; ++kb) {
-    if (!dev::mbar_wait_relaxed(&full[s], ph, status, 42)) return;
+    if (!dev::mbar_wait_relaxed_warp(&full[s], ph, status, 42)) return;
     const uint32_t st = dev::smem_u32(smem + s * kStage);
     const uint32_t wbase = st + (warp >> 1) * (kWBytes / 2);
     const uint32_t xbase = st + kWBytes;
@@ -644,11 +644,8 @@ int qmm_attention_decode_bf16(const uint16_t* q, const uint16_t* kcache, const u
     if (int rc = make_tensor_map_2d(&vmap, vcache, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, rows, kHd, kHd * 2, kTileRows,
                                     64, CU_TENSOR_MAP_SWIZZLE_128B))
       return rc;
-    static bool configured = false;
-    if (!configured) {
-      QMM_CUDA_TRY(cudaFuncSetAttribute(attn_partial_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem));
-      configured = true;
-    }
+    static std::atomic<uint64_t> configured{0};  // per device
+    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(attn_partial_kernel), kAttnSmem, configured)) return rc;
     dim3 grid(nsplit, static_cast<unsigned>(B * Hkv));
     QMM_CUDA_TRY(launch_pdl(attn_partial_kernel, grid, dim3(kAttnThreads), kAttnSmem, s, kmap, vmap, q, part, (int)Hq,
                             (int)Hkv, R, (int)L, nsplit, scale, (long long)q_ld,
@@ -679,12 +676,9 @@ int qmm_bf16_matmul_small_m(const uint16_t* x, const uint16_t* w, uint16_t* y, i
   if (int rc = make_tensor_map_2d(&xmap, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M, (uint64_t)K, (uint64_t)K * 2,
                                   MT * 8, BK, CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
-  static bool configured = false;
-  if (!configured) {
-    QMM_CUDA_TRY(cudaFuncSetAttribute(bf16_small_m_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
-    QMM_CUDA_TRY(cudaFuncSetAttribute(bf16_small_m_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
-    configured = true;
-  }
+  static std::atomic<uint64_t> configured1{0}, configured2{0};  // per device
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(bf16_small_m_kernel<1>), kSmem, configured1)) return rc;
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(bf16_small_m_kernel<2>), kSmem, configured2)) return rc;
   const unsigned grid = static_cast<unsigned>((N + BN - 1) / BN);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (MT == 1)

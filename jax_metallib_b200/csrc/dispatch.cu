@@ -53,10 +53,11 @@ __global__ void w8a16_kernel(const uint16_t* __restrict__ x, const int8_t* __res
 
 }  // namespace simple
 
-static int env_flag(const char* name, int dflt) {
-  const char* v = getenv(name);
-  if (!v || !*v) return dflt;
-  return atoi(v);
+// QMM_FORCE_SIMPLE=1 routes every shape to the CUDA-core kernels (a cross-check of the tensor-core
+// route on a GPU box); read once per process.
+static int force_simple() {
+  static std::atomic<int> cache{INT32_MIN};
+  return env_int_once("QMM_FORCE_SIMPLE", 0, cache);
 }
 
 }  // namespace qmm
@@ -79,7 +80,7 @@ int qmm_i8i8_i32(const void* a, const void* b, int32_t* acc, const float* row_sc
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool tma_ok = K > 0 && K % 16 == 0 && N % 16 == 0 && aligned(a, 16) && aligned(b, 16) &&
                       (!acc || aligned(acc, 16)) && (!out || (aligned(out, 16) && aligned(col_scale, 16)));
-  if (tma_ok && M * N >= 128 * 128 && !env_flag("QMM_FORCE_SIMPLE", 0))
+  if (tma_ok && M * N >= 128 * 128 && !force_simple())
     return i8gemm_tcgen05(a, b, acc, row_scale, col_scale, out, M, N, K, a_unsigned, b_unsigned, s);
   QMM_REQUIRE(M <= 65535, QMM_ERR_UNSUPPORTED, "qmm_i8i8_i32: unaligned shape with M > 65535");
   dim3 grid(static_cast<unsigned>((N + 127) / 128), static_cast<unsigned>(M));
@@ -111,7 +112,7 @@ int qmm_w8a16_perchannel(const uint16_t* x, const int8_t* w, const float* scale,
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool tma_ok = K > 0 && K % 8 == 0 && N % 16 == 0 && ldy % 2 == 0 && aligned(x, 16) &&
                       aligned(w, 16) && aligned(y, 4);
-  if (tma_ok && M * N >= 128 * 128 && !env_flag("QMM_FORCE_SIMPLE", 0))
+  if (tma_ok && M * N >= 128 * 128 && !force_simple())
     return w8a16_tcgen05(x, w, scale, y, M, N, K, ldy, s);
   QMM_REQUIRE(M <= 65535, QMM_ERR_UNSUPPORTED, "qmm_w8a16_perchannel: unaligned shape with M > 65535");
   dim3 grid(static_cast<unsigned>((N + 127) / 128), static_cast<unsigned>(M));

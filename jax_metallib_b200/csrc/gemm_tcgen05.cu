@@ -182,7 +182,7 @@ i8gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ 
     Work w;
     for (int i = 0; get_work(i, tiles_m2, tiles_n, halves, M, w); ++i) {
       if (w.nh == 0) continue;
-      if (!dev::mbar_wait_relaxed(tfull, items & 1, status, 14)) break;
+      if (!dev::mbar_wait_relaxed_warp(tfull, items & 1, status, 14)) break;
       dev::tc_fence_after();
       const int row = (w.tm2 * 2 + j) * BMB + q * 32 + lane;
       const bool mine = (j >= w.h0) && (j < w.h0 + w.nh) && row < M;
@@ -272,16 +272,6 @@ constexpr int kPanelTiles = 8;  // most activation tiles swept together (fewer w
 // stage cnt - 2, and the issuing threads commit once per stage.
 constexpr int kConsumed = 6;
 
-#ifdef QMM_W8_PROFILE
-// per CTA: [0] MMA thread total, [1] its wait for activations, [2] for converted sub-blocks, [3] for the
-// epilogue; [4] converter warp total, [5] its wait for raw weights, [6] for free buffers, [7] load + convert
-__device__ unsigned long long g_w8_prof[256 * 8];
-#define W8_PROF_T(var) const long long var = clock64()
-#define W8_PROF_ADD(acc, t0) acc += clock64() - (t0)
-#else
-#define W8_PROF_T(var)
-#define W8_PROF_ADD(acc, t0)
-#endif
 
 // Eight int8 (one 8-byte read) -> eight bf16, exactly, in 16 instructions.
 // For a byte b (two's complement v): A = 0x4300 | (b & 0x7F) is the bf16
@@ -478,23 +468,15 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
       int items = 0;
       bool ok = true;
       Work w;
-#ifdef QMM_W8_PROFILE
-      long long pw_full = 0, pw_tempty = 0;
-      const long long p_start = clock64();
-#endif
       for (int i = 0; ok && get_work(sc, i, M, N, w); ++i) {
         if (w.nh == 0) continue;
-        W8_PROF_T(t_t);
         if (!dev::mbar_wait(tempty, (items & 1) ^ 1, status, 22)) break;
-        W8_PROF_ADD(pw_tempty, t_t);
         dev::tc_fence_after();
         const uint32_t idesc = (w.m_cols == BMX) ? idesc256 : idesc128;
         const uint32_t b_item = b_lo0 + ((w.m_off * 128) >> 4);
         const uint32_t mine = (me >= w.h0) && (me < w.h0 + w.nh);
         for (int kb = 0; kb < kblocks; ++kb) {
-          W8_PROF_T(t_f);
           if (!dev::mbar_wait(&sfull[g], gpar, status, 23)) { ok = false; break; }
-          W8_PROF_ADD(pw_full, t_f);
           dev::tc_fence_after();
           const uint32_t a_c = a_lo0 + g * (2 * kAStepBuf);
           const uint32_t b_s = b_item + xs * kBStepStage;
@@ -511,14 +493,6 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
         if (ok) dev::tc_commit(tfull);
         ++items;
       }
-#ifdef QMM_W8_PROFILE
-      if (me == 0) {
-        g_w8_prof[blockIdx.x * 8 + 0] = clock64() - p_start;
-        g_w8_prof[blockIdx.x * 8 + 1] = pw_full;
-        g_w8_prof[blockIdx.x * 8 + 2] = 0;
-        g_w8_prof[blockIdx.x * 8 + 3] = pw_tempty;
-      }
-#endif
     }
   } else {
     // ------------------------------ workers --------------------------------
@@ -541,10 +515,6 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
     int items = 0;
     bool ok = true;
     Work w;
-#ifdef QMM_W8_PROFILE
-    long long pc_full = 0, pc_cempty = 0, pc_conv = 0;
-    const long long pc_start = clock64();
-#endif
     for (int i = 0; ok && get_work(sc, i, M, N, w); ++i) {
       if (w.nh == 0) continue;
       for (int kb = 0; kb < kblocks; ++kb, ++cnt, r3 = (r3 == 2) ? 0 : r3 + 1) {
@@ -552,10 +522,7 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
         const int ws = cnt & (kWStages - 1);
         const int slot = cnt & 1, c0 = 2 * slot;  // the stage's two converted buffers
         const uint8_t* raw = smem + kRawBase + ws * kRawBytes;
-        W8_PROF_T(t_f);
-        if (!dev::mbar_wait(&wfull[ws], (cnt / kWStages) & 1, status, 26)) { ok = false; break; }
-        W8_PROF_ADD(pc_full, t_f);
-        W8_PROF_T(t_a);
+        if (!dev::mbar_wait_warp(&wfull[ws], (cnt / kWStages) & 1, status, 26)) { ok = false; break; }
         // tasks of this warp: per sub-block and channel block 16 row pairs, two per warp
         uint2 in[8];
 #pragma unroll
@@ -572,12 +539,10 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
 #pragma unroll
         for (int p = 0; p < 4; ++p)
           if ((p >> 1) < w.nh) out[p] = convert8(in[p]);
-        W8_PROF_T(t_c);
         if (cnt >= 2) {  // the MMAs of the stage that used these buffers before must have retired
           const unsigned prev = cnt - 2;
-          if (!dev::mbar_wait(&consumed[prev % kConsumed], (prev / kConsumed) & 1, status, 27)) { ok = false; break; }
+          if (!dev::mbar_wait_warp(&consumed[prev % kConsumed], (prev / kConsumed) & 1, status, 27)) { ok = false; break; }
         }
-        W8_PROF_ADD(pc_cempty, t_c);
 #pragma unroll
         for (int sb = 0; sb < 2; ++sb) {
           uint8_t* cvt = smem + kCvtBase + (c0 + sb) * kCvtBytes;
@@ -598,18 +563,15 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
             if (lane == 0) dev::mbar_arrive(&wempty[ws]);
           }
         }
-#ifdef QMM_W8_PROFILE
-        pc_conv += clock64() - t_a;
-#endif
         dev::fence_proxy_async();
         // the issuing threads wait only for this barrier: make sure the activations are there too
-        if (!dev::mbar_wait(&xfull[cnt % kXStages], (cnt / kXStages) & 1, status, 28)) { ok = false; break; }
+        if (!dev::mbar_wait_warp(&xfull[cnt % kXStages], (cnt / kXStages) & 1, status, 28)) { ok = false; break; }
         __syncwarp();
         if (lane == 0) dev::mbar_arrive(&sfull[slot]);
       }
       if (!ok) break;
       // ---- epilogue of this item
-      if (!dev::mbar_wait_relaxed(tfull, items & 1, status, 25)) break;
+      if (!dev::mbar_wait_relaxed_warp(tfull, items & 1, status, 25)) break;
       dev::tc_fence_after();
       const int chunks = w.m_cols / 32;
 #pragma unroll 1
@@ -641,14 +603,6 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
       if (lane == 0) dev::mbar_arrive(tempty);
       ++items;
     }
-#ifdef QMM_W8_PROFILE
-    if (o == 0 && lane == 0) {
-      g_w8_prof[blockIdx.x * 8 + 4] = clock64() - pc_start;
-      g_w8_prof[blockIdx.x * 8 + 5] = pc_full;
-      g_w8_prof[blockIdx.x * 8 + 6] = pc_cempty;
-      g_w8_prof[blockIdx.x * 8 + 7] = pc_conv;
-    }
-#endif
   }
   dev::tc_fence_before();
   __syncthreads();
@@ -675,12 +629,8 @@ int i8gemm_tcgen05(const void* a, const void* b, int32_t* acc, const float* row_
   if (int rc = make_tensor_map_2d(&bmap, b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)K,
                                   (uint64_t)N, (uint64_t)N, BK, 128, CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
-  static bool configured = false;
-  if (!configured) {
-    QMM_CUDA_TRY(cudaFuncSetAttribute(i8gemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      kSmemBytes));
-    configured = true;
-  }
+  static std::atomic<uint64_t> configured{0};  // per device
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(i8gemm_kernel), kSmemBytes, configured)) return rc;
   const uint32_t idesc = dev::make_idesc(/*c=s32*/ 2, a_unsigned ? 0 : 1, b_unsigned ? 0 : 1,
                                          /*a K-major*/ 0, /*b MN-major*/ 1, BMB, BN);
   const int tiles = static_cast<int>(((M + 2 * BMB - 1) / (2 * BMB)) * ((N + BN - 1) / BN));
@@ -705,12 +655,8 @@ int w8a16_tcgen05(const uint16_t* x, const int8_t* w, const float* scale, uint16
   if (int rc = make_tensor_map_2d(&xmap, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M,
                                   (uint64_t)K, (uint64_t)K * 2, BMX, BK, CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
-  static bool configured = false;
-  if (!configured) {
-    QMM_CUDA_TRY(cudaFuncSetAttribute(w8a16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                      kSmemBytes));
-    configured = true;
-  }
+  static std::atomic<uint64_t> configured{0};  // per device
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(w8a16_kernel), kSmemBytes, configured)) return rc;
   // operand "a" of the MMA = weights (bf16, MN-major), "b" = activations (bf16, K-major)
   const uint32_t idesc256 = dev::make_idesc(/*c=f32*/ 1, /*bf16*/ 1, /*bf16*/ 1,
                                             /*a MN-major*/ 1, /*b K-major*/ 0, BNW, BMX);
@@ -725,7 +671,6 @@ int w8a16_tcgen05(const uint16_t* x, const int8_t* w, const float* scale, uint16
     const long long tile_bytes = 2ll * BMX * K;
     long long pt = (64ll << 20) / (tile_bytes > 0 ? tile_bytes : 1);
     sc.panel = static_cast<int>(pt < 2 ? 2 : (pt > kPanelTiles ? kPanelTiles : pt));
-    if (const char* e = getenv("QMM_W8_PANEL")) sc.panel = atoi(e) > 0 ? atoi(e) : sc.panel;
   }
   const int sms = gemm_ctas();  // persistent CTAs of this launch
   sc.full_waves = tiles / sms;

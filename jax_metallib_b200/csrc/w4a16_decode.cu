@@ -108,10 +108,6 @@ __device__ __forceinline__ void grid_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
-#ifdef QMM_W4_PROFILE
-__device__ unsigned long long g_w4_prof[2048 * 8];
-__device__ unsigned long long g_w4_span[64 * 4];  // per launch: min start, max first-data, max loop end, max exit
-#endif
 
 // CTA that owns unit u when U units are dealt to P CTAs as [i*U/P, (i+1)*U/P).
 __device__ __forceinline__ int cta_of_unit(long long u, int P, int U) {
@@ -138,9 +134,6 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
                     uint16_t* __restrict__ y, float* __restrict__ ws_partial,
                     int* __restrict__ ws_counter, int M, int N, int K, int G, int U, int max_slots,
                     int static_weights, int* status
-#ifdef QMM_W4_PROFILE
-                    , int launch_id
-#endif
                     ) {
   using L = Smem<MT>;
   constexpr int S = L::kStages;
@@ -229,7 +222,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
     for (int it = 0; it < n_units + kXLag; ++it) {
       if (it < n_units) {
         if (it >= prefetched) {
-          if (!dev::mbar_wait_relaxed(&empty[s_issue], ph_issue ^ 1, status, 1)) break;
+          if (!dev::mbar_wait_relaxed_warp(&empty[s_issue], ph_issue ^ 1, status, 1)) break;
           if (lane == 0) issue_weights(s_issue, c, g, it);
         }
         if (lane == 0) issue_x(s_issue, g);
@@ -237,7 +230,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
         if (++s_issue == S) { s_issue = 0; ph_issue ^= 1; }
       }
       if (it >= kXLag) {
-        if (!dev::mbar_wait_relaxed(&xraw[s_conv], ph_conv, status, 4)) break;
+        if (!dev::mbar_wait_relaxed_warp(&xraw[s_conv], ph_conv, status, 4)) break;
         uint8_t* st = smem + s_conv * L::kStage;
         float* fac = reinterpret_cast<float*>(st + L::kOffF);
         uint4 v[kPasses];
@@ -395,22 +388,11 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
     int s = 0;
     uint32_t ph = 0;
     bool ok = true;
-#ifdef QMM_W4_PROFILE
-    unsigned long long p_start = dev::globaltimer_ns(), p_first = 0, p_wait = 0, p_comp = 0, p_flush = 0;
-#endif
     for (int it = 0; it < n_units; ++it) {
-#ifdef QMM_W4_PROFILE
-      long long c0 = clock64();
-#endif
-      if (!dev::mbar_wait_relaxed(&full[s], ph, status, 2)) {
+      if (!dev::mbar_wait_relaxed_warp(&full[s], ph, status, 2)) {
         ok = false;
         break;
       }
-#ifdef QMM_W4_PROFILE
-      long long c1 = clock64();
-      p_wait += c1 - c0;
-      if (it == 0) p_first = dev::globaltimer_ns();
-#endif
       const uint8_t* st = smem + s * L::kStage;
       const uint32_t st_addr = dev::smem_u32(st);
 
@@ -502,21 +484,11 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
       }
       __syncwarp();
       if (lane == 0) dev::mbar_arrive(&empty[s]);
-#ifdef QMM_W4_PROFILE
-      long long c2 = clock64();
-      p_comp += c2 - c1;
-#endif
       if (++s == S) { s = 0; ph ^= 1; }
       if (++g == G) {
         // the column block is complete as far as this CTA is concerned
         g = 0;
-#ifdef QMM_W4_PROFILE
-        long long f0 = clock64();
         flush(c);
-        p_flush += clock64() - f0;
-#else
-        flush(c);
-#endif
         ++c;
 #pragma unroll
         for (int j = 0; j < 2; ++j)
@@ -526,24 +498,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
             for (int i = 0; i < 4; ++i) yacc[j][mt][i] = 0.f;
       }
     }
-#ifdef QMM_W4_PROFILE
-    unsigned long long p_loop_end = dev::globaltimer_ns();
-    long long f0 = clock64();
-#endif
     if (ok && n_units > 0 && g != 0) flush(c);
-#ifdef QMM_W4_PROFILE
-    p_flush += clock64() - f0;
-    if (warp == 0 && lane == 0 && blockIdx.x < 2048) {
-      unsigned long long* o = g_w4_prof + blockIdx.x * 8;
-      o[0] = p_start; o[1] = p_first; o[2] = p_loop_end; o[3] = dev::globaltimer_ns();
-      o[4] = p_wait; o[5] = p_comp; o[6] = p_flush; { unsigned smid; asm("mov.u32 %0, %%smid;" : "=r"(smid)); o[7] = n_units | ((unsigned long long)smid << 32); }
-      unsigned long long* sp = g_w4_span + (launch_id & 63) * 4;
-      atomicMin(sp + 0, p_start);
-      atomicMax(sp + 1, p_first);
-      atomicMax(sp + 2, p_loop_end);
-      atomicMax(sp + 3, dev::globaltimer_ns());
-    }
-#endif
   }
 }
 
@@ -555,12 +510,9 @@ static int launch(const CUtensorMap& wmap, const CUtensorMap& xmap, const uint16
                   int K, int G, int U, int P, int max_slots, int static_weights, int* status,
                   cudaStream_t stream) {
   using L = Smem<MT>;
-  static bool configured = false;
+  static std::atomic<uint64_t> configured{0};  // per device (one mask per template instance)
   auto kern = w4a16_decode_kernel<MT, ZP>;
-  if (!configured) {
-    QMM_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kTotal));
-    configured = true;
-  }
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), L::kTotal, configured)) return rc;
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(P);
   cfg.blockDim = dim3(kThreads);
@@ -571,33 +523,21 @@ static int launch(const CUtensorMap& wmap, const CUtensorMap& xmap, const uint16
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-#ifdef QMM_W4_PROFILE
-  static int launch_id = 0;
-  QMM_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, wmap, xmap, scales, zeros, y, ws_partial, ws_counter, M,
-                                  N, K, G, U, max_slots, static_weights, status, launch_id++));
-#else
   QMM_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, wmap, xmap, scales, zeros, y, ws_partial, ws_counter, M,
                                   N, K, G, U, max_slots, static_weights, status));
-#endif
   return QMM_OK;
 }
 
 static int blocks_per_sm(int M) { return M <= 16 ? 2 : 1; }
-static int min_units_per_cta() {
-  // QMM_W4_MIN_UNITS overrides it for experiments.  On the decode-step bench (4096x6144, 4096x4096,
-  // 4096x28672, 14336x4096 at M = 8): 2 and 3 units 3.35 ms per step, 4 units 3.26 ms, 6 units 3.50 ms.
-  static const int v = [] {
-    const char* e = getenv("QMM_W4_MIN_UNITS");
-    const int n = e ? atoi(e) : 4;
-    return n >= 1 && n <= 64 ? n : 4;
-  }();
-  return v;
-}
+// Small problems get at least this many units per CTA so that few CTAs share a column block.
+// Measured on the decode step (4096x6144, 4096x4096, 4096x28672, 14336x4096 at M = 8):
+// 2 and 3 units 3.35 ms per step, 4 units 3.26 ms, 6 units 3.50 ms.
+constexpr int kMinUnitsPerCta = 4;
 static int grid_size(int U, int M) {
   // every CTA resident at once; small problems get at least four units per CTA
   // so that few CTAs share a column block
   const int p = blocks_per_sm(M) * num_sms();
-  const int mu = min_units_per_cta();
+  const int mu = kMinUnitsPerCta;
   const int q = (U + mu - 1) / mu;
   return q < p ? q : p;
 }
@@ -684,7 +624,6 @@ static int check_args(const char* name, const void* x, const void* wq, const voi
 constexpr size_t kStaticScratchBytes = QMM_STATIC_SCRATCH_BYTES;
 static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
 
-constexpr int kMaxDevices = 64;
 static void* g_static_scratch_addr[kMaxDevices] = {nullptr};
 static std::mutex g_static_scratch_mutex;
 
@@ -709,19 +648,6 @@ static int static_scratch_address(void** out) {
 }  // namespace w4
 }  // namespace qmm
 
-#ifdef QMM_W4_PROFILE
-extern "C" __attribute__((visibility("default"))) int qmm_w4_profile_read(unsigned long long* dst, int n) {
-  return (int)cudaMemcpyFromSymbol(dst, qmm::w4::g_w4_prof, sizeof(unsigned long long) * n);
-}
-extern "C" __attribute__((visibility("default"))) int qmm_w4_span_read(unsigned long long* dst) {
-  return (int)cudaMemcpyFromSymbol(dst, qmm::w4::g_w4_span, sizeof(unsigned long long) * 256);
-}
-extern "C" __attribute__((visibility("default"))) int qmm_w4_span_reset() {
-  unsigned long long h[256];
-  for (int i = 0; i < 64; ++i) { h[i * 4] = ~0ull; h[i * 4 + 1] = h[i * 4 + 2] = h[i * 4 + 3] = 0; }
-  return (int)cudaMemcpyToSymbol(qmm::w4::g_w4_span, h, sizeof(h));
-}
-#endif
 
 extern "C" {
 
@@ -780,13 +706,16 @@ int qmm_w4a16_g128_static_scratch(const uint16_t* x, const uint8_t* wq, const ui
               "qmm_w4a16_g128_static_scratch: this shape needs %zu bytes of scratch but the built-in "
               "array holds %zu; use qmm_w4a16_g128 with a caller-provided workspace",
               need, kStaticScratchBytes);
+  // The library's status word (where a device-side wait that gives up is
+  // recorded) is pinned host memory created on first use by any other entry
+  // point or by qmm_device_status().  This call will not create it, because
+  // that allocates; when it exists it is honoured as everywhere else.
+  if (int st = read_device_status_if_ready())
+    return set_error(QMM_ERR_TIMEOUT, "a previous kernel gave up waiting (status word 0x%x)", st);
   void* scratch = nullptr;
   if (int rc = static_scratch_address(&scratch)) return rc;
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   QMM_CUDA_TRY(cudaMemsetAsync(scratch, 0, counter_bytes(col_blocks(N)), st));
-  // A wait that gives up is reported through the library's status word when
-  // that word exists already (any other entry point, or qmm_device_status(),
-  // creates it); this call will not create it, because that allocates.
   return run("qmm_w4a16_g128_static_scratch", x, wq, scales, zeros, zeros_packed, y, M, N, K, scratch,
              0u, device_status_word_if_ready(), st);
 }

@@ -186,9 +186,46 @@ def test_w8a16_writes_a_column_shard_in_place(cuda):
     assert float(out[:, :256].abs().sum()) == 0 and float(out[:, 384:].abs().sum()) == 0
 
 
-@pytest.mark.parametrize("limit", [140, 37, 1])
+def _w8a16_rows_check(cuda, M, K, N, seed):
+    """Run the kernel on device-generated operands of a bench-sized launch and check four rows of
+    every 256-row tile (both row halves of a tile, so every kind of cut tail part is hit) over all
+    columns against the oracle."""
+    gen = synthetic.torch_generator(cuda, 5, seed)
+    x = synthetic.device_normal((M, K), cuda, gen, torch.bfloat16)
+    w = synthetic.device_int8((K, N), cuda, gen)
+    sc = synthetic.device_uniform((N,), 0.005, 0.02, cuda, gen)
+    y = ops.w8a16_perchannel(x, w, sc)
+    torch.cuda.synchronize()
+    assert _lib.load().qmm_device_status() == 0
+    rows = np.array(sorted({min(M - 1, t * 256 + o) for t in range((M + 255) // 256) for o in (3, 100, 131, 250)}))
+    rows_t = torch.from_numpy(rows).to(cuda)
+    got = bf16_to_np(y[rows_t].contiguous())
+    xs = bf16_to_np(x[rows_t].contiguous())
+    w_h, sc_h = w.cpu().numpy(), sc.cpu().numpy()
+    ref = np.empty((len(rows), N), np.float32)
+    for c0 in range(0, N, 4096):  # column chunks bound the oracle's float64 copy of the weights
+        ref[:, c0:c0 + 4096] = O.w8_perchannel_matmul(xs, w_h[:, c0:c0 + 4096], sc_h[c0:c0 + 4096])
+    err = O.max_rel_err(got, ref)
+    assert err <= TOL_BF16, err
+    assert np.all(np.abs(got - ref) <= np.abs(ref) * 2.0**-7 + 1e-3 * np.max(np.abs(ref)))
+
+
+# The four launches of a Llama-3-70B-shaped layer (the benchmark's headline workload) at full width
+# and at the column-shard widths of 2, 4 and 8 ranks: every launch has more tiles than SMs or a tail
+# that is cut into parts, which the reduced shapes above do not reach.
+@pytest.mark.parametrize("name,K,N", [(f"{n}/{p}", k, w // p) for n, k, w in synthetic.config5_layer_shapes()
+                                      for p in (1, 2, 4, 8)])
+def test_w8a16_bench_launch_shapes(cuda, name, K, N):
+    _w8a16_rows_check(cuda, 4096, K, N, seed=K // 64 + N)
+
+
+@pytest.mark.parametrize("limit", [140, 37, 1, 7, 9, 6, 3])
 def test_w8a16_and_int8_dot_under_a_cta_limit(cuda, limit):
-    """Fewer persistent CTAs than SMs (SMs left to a collective): same results, bit for bit."""
+    """Fewer persistent CTAs than SMs (SMs left to a collective): same results, bit for bit.
+
+    The w8a16 shape has 20 tiles: limit 7 gives two full rounds and then six whole tail tiles,
+    9 a tail cut in quarters, 6 a tail cut in halves, 3 a quarter-cut tail of which a CTA takes a
+    run of several parts."""
     lib = _lib.load()
     c = synthetic.config5_small(1024, 512, 1280)
     x = dev(c["x_bits"].view(np.int16), cuda, torch.bfloat16)

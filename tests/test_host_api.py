@@ -24,6 +24,11 @@ def test_library_loads_and_exports_every_declared_symbol():
     assert b"sm_100a" in _lib.load().qmm_version()
 
 
+def test_per_device_bookkeeping_selftest():
+    # function attributes (dynamic shared-memory opt-in) are set once per device ordinal, not once per process
+    assert _lib.load().qmm_selftest_host() == 0
+
+
 def test_error_reporting_without_a_gpu():
     lib = _lib.load()
     # argument validation happens before any CUDA call

@@ -83,3 +83,31 @@ def test_static_scratch_refuses_shapes_beyond_its_limit(cuda):
     assert lib.qmm_status_name(st) == b"QMM_ERR_WORKSPACE"
     msg = _lib.last_error()
     assert "built-in" in msg and str(SCRATCH_LIMIT) in msg
+
+
+def test_static_scratch_calls_leave_free_device_memory_unchanged(cuda):
+    """What the name of the entry point promises: once the library's device image is loaded (the
+    first call on a device does that), further calls neither take nor give back device memory."""
+    lib = _lib.load()
+    M, K, N = 4, 1024, 512
+    c = synthetic.config3(M, K, N, index=21)
+    x = _dev(c["x_bits"].view(np.int16), cuda, torch.bfloat16)
+    wq, s, z = _dev(c["wq"], cuda), _dev(c["s_bits"].view(np.int16), cuda, torch.bfloat16), _dev(c["z_packed"], cuda)
+    y = torch.empty((M, N), dtype=torch.bfloat16, device=cuda)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def call():
+        _lib.check(lib.qmm_w4a16_g128_static_scratch(x.data_ptr(), wq.data_ptr(), s.data_ptr(), z.data_ptr(), 1,
+                                                     y.data_ptr(), M, N, K, 128, stream))
+
+    call()  # resolves the array's address and loads the kernel
+    torch.cuda.synchronize()
+    for _attempt in range(3):  # another process on the device may move the figure; it must hold at least once
+        free_before, _ = torch.cuda.mem_get_info(cuda)
+        for _ in range(3):
+            call()
+        torch.cuda.synchronize()
+        free_after, _ = torch.cuda.mem_get_info(cuda)
+        if free_after == free_before:
+            break
+    assert free_after == free_before
