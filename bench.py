@@ -39,11 +39,11 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-# SMs left to the all-gather kernel at N > 1.  Measured at N = 2 (40 layers): NCCL's own choice with no SMs
-# reserved 1786 TFLOP/s (its CTAs queue behind the resident GEMM CTAs and delay the next launch), 8 reserved
-# 1660 (the gather becomes the bottleneck), 16: 1967, 32: 1996 (under the power cap the GEMM loses less than
-# its share of SMs).
-NCCL_CTAS = int(os.environ.get("QMM_BENCH_NCCL_CTAS", "32"))
+# SMs left to the all-gather kernel when the exchange is an NCCL collective (--exchange collective).
+# Measured at N = 2 (40 layers): NCCL's own choice with no SMs reserved 1786 TFLOP/s (its CTAs queue
+# behind the resident GEMM CTAs and delay the next launch), 8 reserved 1660 (the gather becomes the
+# bottleneck), 16: 1967, 32: 1996.
+NCCL_CTAS = 32
 M_TOKENS = 4096
 D_MODEL, FFN, QKV = 8192, 28672, 10240
 N_LAYERS = 80
@@ -136,61 +136,112 @@ class ClockSampler:
 # ----------------------------------------------------------------------------
 # CPU baseline (oracle port) — also the --impl reference arm
 # ----------------------------------------------------------------------------
-def cpu_linears_tflops(budget_s: float, m_rows: int = 256):
-    """Time the NumPy oracle of the weight-only int8 linears on the host cores.
+def workload_config(world, layers, extra=None):
+    """The ``config`` object both arms print (the reference arm runs a bounded sample of it)."""
+    cfg = {"workload": f"int8 per-channel weight-only linears, Llama-3-70B shapes, {layers} layers x "
+                       "(qkv 8192->10240, o 8192->8192, gate_up 8192->57344, down 28672->8192), "
+                       "bf16 activations [4096,8192]",
+           "layers": layers, "parallelism": f"tp{world}",
+           "l2": "every launch reads a different weight matrix (>= 67 MB each at N = 1), inputs exceed L2"}
+    if extra:
+        cfg.update(extra)
+    return cfg
 
-    Sample: the four linears of one layer at m_rows activation rows (full K and
-    N), repeated until budget_s seconds of CPU work have been spent."""
-    import numpy as np
 
-    from jax_metallib_b200 import synthetic
-    from oracle import qmm_oracle as O
+def host_cores():
+    try:
+        return len(os.sched_getaffinity(0))
+    except Exception:  # noqa: BLE001
+        return os.cpu_count() or 1
 
-    rng = np.random.default_rng(5000)
-    problems = []
-    for _name, k, n, _act in layer_shapes():
-        x = synthetic.bf16_bits_to_f32(synthetic.to_bf16_bits(rng.standard_normal((m_rows, k)).astype(np.float32)))
-        w = rng.integers(-127, 128, size=(k, n), dtype=np.int64).astype(np.int8)
-        s = rng.uniform(0.005, 0.02, size=(n,)).astype(np.float32)
-        problems.append((x, w, s))
-    flops = sum(2.0 * m_rows * w.shape[0] * w.shape[1] for _, w, _ in problems)
 
-    def one_pass():
-        for x, w, s in problems:
+def pin_host_threads():
+    """Use every host core for the CPU arm whatever the launcher exported (torch.distributed.run
+    sets OMP_NUM_THREADS=1 for its children).  Must run before NumPy is imported."""
+    n = str(host_cores())
+    for var in ("OMP_NUM_THREADS", "OPENBLAS_NUM_THREADS", "MKL_NUM_THREADS"):
+        os.environ[var] = n
+
+
+class CpuLinears:
+    """The NumPy oracle of one layer's four weight-only int8 linears on the host cores.
+
+    A pass keeps the workload's M = 4096 rows and full K and takes one column slice (N / col_div
+    columns) of each of the four weights, so dequantisation and GEMM work stay in the workload's
+    own proportion; the slice is what bounds the time of a step."""
+
+    def __init__(self, col_div: int):
+        import numpy as np
+
+        from jax_metallib_b200 import synthetic
+
+        self.col_div = col_div
+        rng = np.random.default_rng(5000)
+        self.problems = []
+        for _name, k, n, _act in layer_shapes():
+            nc = max(16, n // col_div)
+            x = synthetic.bf16_bits_to_f32(synthetic.to_bf16_bits(rng.standard_normal((M_TOKENS, k)).astype(np.float32)))
+            w = rng.integers(-127, 128, size=(k, nc), dtype=np.int64).astype(np.int8)
+            s = rng.uniform(0.005, 0.02, size=(nc,)).astype(np.float32)
+            self.problems.append((x, w, s))
+        self.flops = sum(2.0 * M_TOKENS * w.shape[0] * w.shape[1] for _, w, _ in self.problems)
+
+    def one_pass(self):
+        from oracle import qmm_oracle as O
+
+        for x, w, s in self.problems:
             wf = O.w8_perchannel_dequant(w, s)  # fp32 dequantise
             y = x @ wf                            # f32 dot (BLAS, all host threads)
             O.f32_to_bf16_bits(y)                 # round to the declared result type
 
-    one_pass()  # warm-up
-    t0 = time.perf_counter()
-    reps = 0
-    while True:
-        one_pass()
-        reps += 1
-        if time.perf_counter() - t0 >= budget_s:
-            break
-    dt = (time.perf_counter() - t0) / reps
-    cores = os.cpu_count() or 1
-    return dict(value=flops / dt / 1e12, unit="TFLOP/s", cores=cores, kind="port",
-                sample=f"one layer's four linears at M={m_rows} rows (full K, N), fp32 dequantise + NumPy "
-                       f"matmul + bf16 rounding, {reps} passes, {dt:.3f} s each"), dt
+    def sample_text(self, passes, dt):
+        return (f"M=4096 rows, full K, 1/{self.col_div} of the columns of each of one layer's four weights per step "
+                f"({self.flops / 1e12:.3f} TFLOP), fp32 dequantise + NumPy matmul + bf16 rounding, "
+                f"{passes} timed steps, {dt:.3f} s each")
+
+
+def cpu_linears_tflops(steps: int, warmup: int, col_div: int = 16):
+    """Time `steps` passes after `warmup` untimed ones; returns (cpu_baseline dict, seconds per step)."""
+    try:
+        from threadpoolctl import threadpool_limits
+    except Exception:  # noqa: BLE001
+        threadpool_limits = None
+    prob = CpuLinears(col_div)
+    cores = host_cores()
+
+    def run():
+        for _ in range(warmup):
+            prob.one_pass()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            prob.one_pass()
+        return (time.perf_counter() - t0) / steps
+
+    if threadpool_limits is not None:
+        with threadpool_limits(limits=cores):
+            dt = run()
+    else:
+        dt = run()
+    return dict(value=prob.flops / dt / 1e12, unit="TFLOP/s", cores=cores, kind="port",
+                sample=prob.sample_text(steps, dt)), dt
 
 
 def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
-    budget = 20.0
-    # --steps/--warmup are honoured as repetitions of the bounded sample
-    base, dt = cpu_linears_tflops(budget_s=max(5.0, min(60.0, budget)))
+    pin_host_threads()
+    # --steps and --warmup are the passes really run; the column slice keeps the whole run within minutes
+    # (a pass over 1/16 of the columns is about 1.8 s on 16 cores)
+    base, dt = cpu_linears_tflops(steps=max(1, args.steps), warmup=max(0, args.warmup), col_div=16)
     line = {
         "impl": "reference", "metric": METRIC, "value": base["value"], "unit": "TFLOP/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": dt * 1e3, "higher_is_better": True,
+        "steps": max(1, args.steps), "warmup": max(0, args.warmup), "ms_per_step": dt * 1e3, "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "int8 per-channel weight-only linears, Llama-3-70B shapes (80 layers), "
-                               "bf16 activations [4096,8192]; CPU arm runs a bounded sample of one layer",
-                   "parallelism": f"tp{args.gpus}", "note": "reference CPU route = NumPy oracle port "
-                   "(jaxlib CPU backend and the Metal plugin are not installable offline)"},
+        "config": workload_config(args.gpus, args.layers),
+        "note": "reference CPU route = NumPy oracle port on the host cores (jaxlib's CPU backend and the Metal "
+                "plugin are not installable offline); each step is a bounded sample of the workload, see "
+                "cpu_baseline.sample; the CPU rate does not depend on n_gpus",
         "cpu_baseline": base,
         "e2e": {"value": base["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -220,11 +271,70 @@ def build_weights(torch, synthetic, device, rank, world, layers):
     return weights
 
 
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) of one w8a16_kernel launch at M = 4096, by
+# (K, N), from the ncu captures summarised in profiles/w8a16_kernel_dram_traffic.md.  Shapes that
+# were not captured are scaled by FLOPs from the nearest captured shape of the same K and said so.
+MEASURED_TRAFFIC = {
+}
+
+
+def launch_traffic(k, ns):
+    """(bytes, how) for one launch of [4096, k] x [k, ns]."""
+    if (k, ns) in MEASURED_TRAFFIC:
+        return MEASURED_TRAFFIC[(k, ns)], "ncu"
+    same_k = [(n2, b) for (k2, n2), b in MEASURED_TRAFFIC.items() if k2 == k]
+    if same_k:
+        n2, b = min(same_k, key=lambda t: abs(t[0] - ns))
+        return b * ns / n2, "scaled"
+    return None, "none"
+
+
+def check_last_layer(torch, dist, ex, layer, slot, acts, rank, world, device):
+    """Outside the timed region: four rows of every 256-row tile of the last layer's four gathered
+    outputs against the CPU oracle of the unsharded linear.  Each rank computes the reference of its
+    own columns, the references are all-gathered, and every rank compares all P blocks of its own
+    copy of the gathered buffer (so the exchange is checked on every rank)."""
+    import numpy as np
+
+    from jax_metallib_b200 import synthetic, tp
+    from oracle import qmm_oracle as O
+
+    rows = np.array(sorted({t * 256 + o for t in range(M_TOKENS // 256) for o in (3, 100, 131, 250)}))
+    rows_t = torch.from_numpy(rows).to(device)
+    worst = 0.0
+    ok = True
+    for name, k, n, ns, act, w, s in layer:
+        xs = synthetic.bf16_bits_to_f32(acts[act][rows_t].contiguous().view(torch.int16).cpu().numpy().view(np.uint16))
+        w_h, s_h = w.cpu().numpy(), s.cpu().numpy()
+        ref = np.empty((len(rows), ns), np.float32)
+        for c0 in range(0, ns, 4096):
+            ref[:, c0:c0 + 4096] = O.w8_perchannel_matmul(xs, w_h[:, c0:c0 + 4096], s_h[c0:c0 + 4096])
+        ref_t = torch.from_numpy(ref).to(device)
+        if world > 1:
+            allref = torch.empty((world,) + tuple(ref_t.shape), dtype=torch.float32, device=device)
+            dist.all_gather_into_tensor(allref.view(-1), ref_t.view(-1))
+        else:
+            allref = ref_t.unsqueeze(0)
+        logical_ref = tp.gathered_to_logical(allref).cpu().numpy()  # [rows, N] of the unsharded linear
+        got = tp.gathered_to_logical(ex.out(name, slot)[:, rows_t, :].contiguous())  # [rows, N]
+        got = synthetic.bf16_bits_to_f32(got.contiguous().view(torch.int16).cpu().numpy().view(np.uint16))
+        err = O.max_rel_err(got, logical_ref)
+        worst = max(worst, err)
+        ok = ok and err <= 1e-2 and bool(np.all(np.abs(got - logical_ref) <= np.abs(logical_ref) * 2.0**-7
+                                                + 1e-3 * np.max(np.abs(logical_ref))))
+    flag = torch.tensor([1 if ok else 0], dtype=torch.int32, device=device)
+    worst_t = torch.tensor([worst], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        dist.all_reduce(worst_t, op=dist.ReduceOp.MAX)
+    return bool(int(flag.item())), float(worst_t.item()), len(rows)
+
+
 def run_gpu(args):
     import torch
     import torch.distributed as dist
 
-    from jax_metallib_b200 import _lib, ops, synthetic
+    from jax_metallib_b200 import _lib, ops, synthetic, tp
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -235,121 +345,38 @@ def run_gpu(args):
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
     lib = _lib.load()
-    gather = os.environ.get("QMM_BENCH_GATHER", "p2p") if world > 1 else "none"
     if world > 1:
-        if gather == "nccl":
+        if args.exchange == "collective":
             # The GEMM keeps one CTA per SM resident for a whole launch; leave the all-gather its own SMs.
             os.environ.setdefault("NCCL_MAX_CTAS", str(NCCL_CTAS))
             os.environ.setdefault("NCCL_MIN_CTAS", str(NCCL_CTAS))
         dist.init_process_group("nccl", device_id=device)
     peaks = measured_peaks()
     layers = args.layers
+    # --shard-of P (single GPU): rank 0's share of a P-way sharded run, without the exchange
+    shard_world = args.shard_of if world == 1 else world
+    shard_rank = 0 if world == 1 else rank
 
-    weights = build_weights(torch, synthetic, device, rank, world, layers)
-    gen = synthetic.torch_generator(device, 5, 1000)
+    weights = build_weights(torch, synthetic, device, shard_rank, shard_world, layers)
     x_host = torch.randn((M_TOKENS, D_MODEL), dtype=torch.float32).to(torch.bfloat16).pin_memory()
     h_host = torch.randn((M_TOKENS, FFN), dtype=torch.float32).to(torch.bfloat16).pin_memory()
     acts = {"x": x_host.to(device), "h": h_host.to(device)}
-    # gathered outputs, one buffer per linear kind (reused by every layer); at N > 1 each is [P, M, N/P]
-    # (what all_gather_into_tensor builds); a consumer addresses it as (rank, row, column-in-shard)
-    outs, peer_outs = {}, {}
-    if gather == "p2p":
-        # Symmetric (peer-mapped) output buffers: a rank's GEMM writes its [M, N/P] block in place and
-        # copy-engine peer copies put the same block into every other rank's buffer.  No SM is spent on
-        # the exchange, so the GEMM keeps all of them.
-        ok = 1
-        try:
-            import torch.distributed._symmetric_memory as symm_mem
-            total = sum(M_TOKENS * n for _, _, n, _ in layer_shapes())
-            sym = symm_mem.empty((total,), dtype=torch.bfloat16, device=device)
-            hdl = symm_mem.rendezvous(sym, dist.group.WORLD)
-        except Exception as exc:  # noqa: BLE001 - any failure means "not available here"
-            ok = 0
-            print(f"[rank {rank}] symmetric memory unavailable ({exc!r}); using the NCCL all-gather", file=sys.stderr)
-        flag = torch.tensor([ok], dtype=torch.int32, device=device)
-        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
-        if int(flag.item()) == 0:
-            gather = "nccl"
-        else:
-            off = 0
-            for name, k, n, act in layer_shapes():
-                shape = (world, M_TOKENS, n // world)
-                outs[name] = sym[off:off + M_TOKENS * n].view(shape)
-                peer_outs[name] = {p: hdl.get_buffer(p, shape, torch.bfloat16, off) for p in range(world) if p != rank}
-                off += M_TOKENS * n
-    if gather == "nccl":
-        sms = torch.cuda.get_device_properties(device).multi_processor_count
-        _lib.check(lib.qmm_set_cta_limit(sms - NCCL_CTAS))
-    for name, k, n, act in layer_shapes():
-        if world == 1:
-            outs[name] = torch.empty((M_TOKENS, n), dtype=torch.bfloat16, device=device)
-        elif gather == "nccl":
-            outs[name] = torch.empty((world, M_TOKENS, n // world), dtype=torch.bfloat16, device=device)
-    shard_out = {name: torch.empty((M_TOKENS, n // world), dtype=torch.bfloat16, device=device)
-                 for name, k, n, act in layer_shapes()} if gather == "nccl" else None
-    result_host = torch.empty((M_TOKENS, D_MODEL), dtype=torch.bfloat16).pin_memory()
-
-    compute = torch.cuda.current_stream()
-    comm = torch.cuda.Stream() if world > 1 else None
-    peer_streams = {p: torch.cuda.Stream() for p in range(world) if p != rank} if gather == "p2p" else {}
-    sync_word = torch.zeros(1, dtype=torch.int32, device=device) if world > 1 else None
+    # gathered outputs [P, M, N/P] per linear kind, two slots each (layer parity): the exchange of a
+    # layer may run under the whole of the next layer
+    shapes = {name: (M_TOKENS, n // (shard_world if world == 1 else 1)) for name, k, n, act in layer_shapes()}
+    ex = tp.GatherExchange(shapes, device, depth=2, mode=args.exchange, reserve_ctas=NCCL_CTAS)
+    result_host = torch.empty((world, M_TOKENS, shapes["down"][1] // world), dtype=torch.bfloat16).pin_memory()
     launches = [0]
-    kernel_events = []
 
-    def step(record_kernels=False):
-        prev_done = None
-        for layer in weights:
+    def step():
+        # Every launch reads activations and weights that nothing on the stream writes, and writes a
+        # slot whose previous use lies eight launches back: the launches are independent of their
+        # predecessors, so each may fill the SMs that the last round of the one before leaves idle.
+        for li, layer in enumerate(weights):
             for name, k, n, ns, act, w, s in layer:
-                xin = acts[act]
-                if world == 1:
-                    if record_kernels:
-                        e0 = torch.cuda.Event(enable_timing=True)
-                        e1 = torch.cuda.Event(enable_timing=True)
-                        e0.record()
-                    ops.w8a16_perchannel(xin, w, s, out=outs[name])
-                    if record_kernels:
-                        e1.record()
-                        kernel_events.append((e0, e1, 2.0 * M_TOKENS * k * ns))
-                else:
-                    # the gather of the previous use of this buffer must be finished
-                    if prev_done is not None and name in prev_done:
-                        compute.wait_event(prev_done[name])
-                    if record_kernels:
-                        e0 = torch.cuda.Event(enable_timing=True)
-                        e1 = torch.cuda.Event(enable_timing=True)
-                        e0.record()
-                    mine = outs[name][rank] if gather == "p2p" else shard_out[name]
-                    ops.w8a16_perchannel(xin, w, s, out=mine)
-                    if record_kernels:
-                        e1.record()
-                        kernel_events.append((e0, e1, 2.0 * M_TOKENS * k * ns))
-                    ready = torch.cuda.Event()
-                    ready.record(compute)
-                    comm.wait_event(ready)
-                    if gather == "p2p":
-                        # one contiguous [M, N/P] block per peer, each on its own stream (copy engines)
-                        for p, st in peer_streams.items():
-                            st.wait_event(ready)
-                            with torch.cuda.stream(st):
-                                peer_outs[name][p][rank].copy_(mine, non_blocking=True)
-                            comm.wait_stream(st)
-                        with torch.cuda.stream(comm):
-                            done = torch.cuda.Event()
-                            done.record(comm)
-                    else:
-                        with torch.cuda.stream(comm):
-                            dist.all_gather_into_tensor(outs[name].view(-1), shard_out[name].view(-1))
-                            done = torch.cuda.Event()
-                            done.record(comm)
-                    prev_done = prev_done or {}
-                    prev_done[name] = done
+                ex.linear(name, li & 1, acts[act], w, s, independent=True)
                 launches[0] += 1
-        if world > 1:
-            compute.wait_stream(comm)
-            if gather == "p2p":
-                # a rank's buffers are complete when every peer's copies are: one 4-byte all-reduce,
-                # ordered behind each rank's own copies, is the step's rendezvous
-                dist.all_reduce(sync_word)
+        ex.finish()  # every block of every rank has arrived in this rank's buffers
 
     def barrier():
         if world > 1:
@@ -371,33 +398,30 @@ def run_gpu(args):
     ev1 = torch.cuda.Event(enable_timing=True)
     ev0.record()
     for _ in range(args.steps):
-        step(record_kernels=True)
+        step()
     ev1.record()
     barrier()
     t_wall1 = time.time()
     clocks = sampler.stop(t_wall0, t_wall1) if rank == 0 else None
     ms = ev0.elapsed_time(ev1)
     timed_launches = launches[0]
-    kern_ms = sum(a.elapsed_time(b) for a, b, _ in kernel_events)
-    kern_flops = sum(f for _, _, f in kernel_events)
     if world > 1:
         t = torch.tensor([ms], dtype=torch.float64, device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
     ms_per_step = ms / args.steps
-    total_flops = flops_per_layer() * layers
+    rank_flops = sum(2.0 * M_TOKENS * k * ns for layer in weights for _, k, _, ns, _, _, _ in layer)
+    total_flops = rank_flops * world  # = flops_per_layer() * layers unless --shard-of cut it
     value = total_flops / (ms_per_step * 1e-3) / 1e12
 
     # ---- end-to-end timing (host activations in, last result out) ---------------
+    last_slot = (layers - 1) & 1
+
     def e2e_step():
         acts["x"].copy_(x_host, non_blocking=True)
         acts["h"].copy_(h_host, non_blocking=True)
         step()
-        last = outs["down"]
-        if world == 1:
-            result_host.copy_(last, non_blocking=True)
-        else:
-            result_host.view(world, M_TOKENS, D_MODEL // world).copy_(last, non_blocking=True)
+        result_host.copy_(ex.out("down", last_slot), non_blocking=True)
 
     e2e_step()
     barrier()
@@ -421,46 +445,71 @@ def run_gpu(args):
     if status != 0:
         raise SystemExit(f"device status word is 0x{status:x}: a kernel gave up waiting")
 
+    # ---- parity of what was just timed (outside the timed region) -----------------
+    checked, worst_err, n_rows = check_last_layer(torch, dist, ex, weights[-1], last_slot, acts, rank, world, device)
+    if not checked:
+        print(f"[rank {rank}] PARITY CHECK FAILED: max relative error {worst_err:.3e}", file=sys.stderr)
+
     line = None
     if rank == 0:
         peak = peaks["bf16_tflops_sustained"]
-        achieved = kern_flops / (kern_ms * 1e-3) / 1e12 if kern_ms > 0 else 0.0
+        # average launch duration over the timed region (CUDA events on the launching stream; the
+        # launches overlap each other's tails, so they are not timed one by one)
+        launch_ms = ms_per_step * args.steps / max(1, timed_launches)
+        achieved = rank_flops * args.steps / max(1, timed_launches) / (launch_ms * 1e-3) / 1e12
+        traffic, how = 0.0, set()
+        for _, k, _, ns, _, _, _ in weights[0]:
+            b, h = launch_traffic(k, ns)
+            how.add(h)
+            traffic = None if (b is None or traffic is None) else traffic + b / len(weights[0])
+        if ex.mode == "fused":
+            par = ("weights column-sharded along N; the GEMM epilogue stores each output element once with "
+                   "multimem.st to an NVSwitch multicast address, which places it in block r of every rank's "
+                   "[P, M, N/P] buffer (no separate all-gather); per-launch completion signals, bounded wait "
+                   "for all of them at the end of a step")
+        elif ex.mode == "copy":
+            par = ("weights column-sharded along N; outputs gathered into [P, M, N/P] by copy-engine peer copies "
+                   "of each finished [M, N/P] block into every peer's symmetric buffer, overlapped on side "
+                   "streams, one 4-byte NCCL all-reduce per step as the rendezvous")
+        elif ex.mode == "collective":
+            par = "weights column-sharded along N; outputs gathered by NCCL all-gather overlapped on a second stream"
+        else:
+            par = "single GPU" + (f", rank 0's share of a {shard_world}-way sharded run (no exchange)" if shard_world > 1 else "")
         line = {
             "metric": METRIC, "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": f"int8 per-channel weight-only linears, Llama-3-70B shapes, {layers} layers x "
-                                   "(qkv 8192->10240, o 8192->8192, gate_up 8192->57344, down 28672->8192), "
-                                   "bf16 activations [4096,8192]",
-                       "parallelism": (f"tp{world} (weights column-sharded along N; outputs gathered into [P, M, N/P] "
-                                       + ("by copy-engine peer copies of each finished [M, N/P] block into every peer's "
-                                          "symmetric buffer over NVLink, overlapped on side streams, one 4-byte NCCL "
-                                          "all-reduce per step as the rendezvous)" if gather == "p2p" else
-                                          "by NCCL all-gather overlapped on a second stream)")) if world > 1 else "tp1",
-                       "l2": "every launch reads a different weight matrix (>= 67 MB each), inputs exceed L2",
-                       "layers": layers},
+            "config": workload_config(world, layers),
+            "exchange": {"mode": ex.mode, "detail": par},
+            "checked": checked,
+            "check": {"rows": n_rows, "linears": 4, "max_rel_err": worst_err, "tolerance": 1e-2,
+                      "what": "last layer's four gathered outputs, four rows of every 256-row tile, all columns, "
+                              "against the CPU oracle of the unsharded linear, on every rank"},
             "roofline": {"bound": "tensor", "kernel": "w8a16_kernel (tcgen05 kind::f16, in-kernel int8->bf16)",
                          "achieved": achieved, "peak": peak, "unit": "TFLOP/s", "frac": achieved / peak,
                          "peak_source": f"{peaks['source']} bf16_tflops_sustained (burst {peaks['bf16_tflops']})",
-                         # dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture (qkv launch
-                         # 411 MB for 687 GFLOP, o launch 336 MB for 550 GFLOP: 0.60 bytes per kFLOP),
-                         # scaled by FLOPs to this run's mean launch
-                         "traffic": 0.60e-3 * kern_flops / max(1, len(kernel_events)),
-                         "traffic_unit": "bytes per launch (mean)"},
+                         "launch_ms_mean": launch_ms,
+                         "traffic": traffic, "traffic_unit": "DRAM bytes per launch (mean of a layer's four)",
+                         "traffic_source": "+".join(sorted(how))},
             "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": timed_launches,
             "clocks": clocks,
         }
+        if ex.why_not_fused:
+            line["exchange"]["note"] = ex.why_not_fused
     if world == 1 and rank == 0 and not args.no_detail:
         time.sleep(2.0)  # let the power-capped clocks of the timed region recover before the small kernels
+        del weights, ex
+        torch.cuda.empty_cache()
         line["detail"] = run_detail(torch, ops, synthetic, lib, device, peaks)
-        base, _ = cpu_linears_tflops(budget_s=12.0)
+        base, _ = cpu_linears_tflops(steps=6, warmup=1)
         line["cpu_baseline"] = base
     if rank == 0:
         print(json.dumps(line))
     if world > 1:
+        dist.barrier()
         dist.destroy_process_group()
-    return 0
+    return 0 if checked else 1
 
 
 def run_detail(torch, ops, synthetic, lib, device, peaks, items=None):
@@ -615,10 +664,13 @@ def _detail_int8_dot(torch, synthetic, lib, device, peaks, graph_time, detail):
 
     us = graph_time(run_i8, 20, replays=10)
     tops = 2.0 * Mi * Ni * Ki / (us * 1e-6) / 1e12
+    lib_peak = _int8_library_peak(torch, device)
+    detail["int8_library_peak"] = lib_peak
     detail["int8_dot_2048x4096x4096_f32_rescale"] = {
-        "us": us, "TOP/s": tops, "frac_of_2x_measured_bf16_burst": tops / (2 * peaks["bf16_tflops"]),
-        "note": "fused float(acc)*row*col epilogue, f32 output only; 10 rotating B operands; the int8 peak is "
-                "not in MEASURED_PEAKS.json, 2 x the measured bf16 burst stands in for it"}
+        "us": us, "TOP/s": tops, "frac_of_measured_int8": tops / lib_peak["burst_TOPs"] if lib_peak.get("burst_TOPs") else None,
+        "frac_of_2x_measured_bf16_burst": tops / (2 * peaks["bf16_tflops"]),
+        "note": "fused float(acc)*row*col epilogue, f32 output only; 10 rotating B operands; measured int8 peak = "
+                "the library int8 GEMM of int8_library_peak (burst, as this kernel is timed in isolation)"}
     del bs
     # the same M and N at four times the K: separates the per-launch fixed cost from the main-loop rate
     Kl = 16384
@@ -633,10 +685,49 @@ def _detail_int8_dot(torch, synthetic, lib, device, peaks, graph_time, detail):
     us_l = graph_time(run_long, 6, replays=10)
     tops_l = 2.0 * Mi * Ni * Kl / (us_l * 1e-6) / 1e12
     detail["int8_dot_2048x16384x4096_f32_rescale"] = {
-        "us": us_l, "TOP/s": tops_l, "frac_of_2x_measured_bf16_burst": tops_l / (2 * peaks["bf16_tflops"]),
+        "us": us_l, "TOP/s": tops_l,
+        "frac_of_measured_int8": tops_l / lib_peak["burst_TOPs"] if lib_peak.get("burst_TOPs") else None,
+        "frac_of_2x_measured_bf16_burst": tops_l / (2 * peaks["bf16_tflops"]),
         "main_loop_us_per_4096_k": (us_l - us) / 3.0, "fixed_us_per_launch": us - (us_l - us) / 3.0,
         "note": "context for the line above: same M and N, K x 4"}
     del bl
+
+
+def _int8_library_peak(torch, device):
+    """A library int8 GEMM (torch._int_mm, 8192^3, int32 result) as the int8 tensor-core denominator:
+    best of 10 (burst) and back to back for 4 s (sustained), the recipe the bf16 peaks of
+    MEASURED_PEAKS.json were taken with.  Timing only: nothing of it is on the product path."""
+    n = 8192
+    try:
+        a = torch.randint(-127, 128, (n, n), dtype=torch.int8, device=device)
+        b = torch.randint(-127, 128, (n, n), dtype=torch.int8, device=device)
+        for _ in range(3):
+            torch._int_mm(a, b)
+        torch.cuda.synchronize()
+        best = float("inf")
+        for _ in range(10):
+            e0 = torch.cuda.Event(enable_timing=True)
+            e1 = torch.cuda.Event(enable_timing=True)
+            e0.record()
+            torch._int_mm(a, b)
+            e1.record()
+            e1.synchronize()
+            best = min(best, e0.elapsed_time(e1))
+        ops_per = 2.0 * n * n * n
+        reps = max(10, int(4000.0 / best))
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            torch._int_mm(a, b)
+        e1.record()
+        e1.synchronize()
+        sustained = e0.elapsed_time(e1) / reps
+        del a, b
+        return {"burst_TOPs": ops_per / (best * 1e-3) / 1e12, "sustained_TOPs": ops_per / (sustained * 1e-3) / 1e12,
+                "how": "torch._int_mm int8 8192^3 -> int32: best of 10 (burst), back to back for 4 s (sustained)"}
+    except Exception as exc:  # noqa: BLE001
+        return {"burst_TOPs": None, "sustained_TOPs": None, "how": f"torch._int_mm unavailable: {exc!r}"}
 
 
 def _detail_llama_decode(torch, synthetic, device, hbm, stream, detail):
@@ -707,6 +798,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--layers", type=int, default=N_LAYERS, help="layers in the pass (the workload names 80)")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "fused", "copy", "collective"],
+                    help="how the outputs are gathered at N > 1 (auto: fused multimem stores when the symmetric "
+                         "allocation has a multicast address, else peer copies, else the NCCL all-gather)")
+    ap.add_argument("--shard-of", type=int, default=1, choices=[1, 2, 4, 8],
+                    help="single GPU only: run rank 0's share of a P-way sharded pass (no exchange)")
     ap.add_argument("--no-detail", action="store_true", help="skip the per-workload detail and the CPU baseline")
     ap.add_argument("--detail-only", action="store_true",
                     help="run only the per-workload detail (small case for profiling) and print it as JSON")
@@ -716,6 +812,7 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference(args)
+    pin_host_threads()  # the CPU baseline leg uses every host core whatever the launcher exported
     if args.detail_only:
         import torch
 

@@ -119,6 +119,50 @@ QMM_API int qmm_w8a32_perchannel(const float* x, const int8_t* w, const float* s
 QMM_API int qmm_w8a16_perchannel(const uint16_t* x_bf16, const int8_t* w, const float* scale,
                                  uint16_t* y_bf16, int64_t M, int64_t N, int64_t K, int64_t ldy,
                                  void* stream);
+/* The same matmul with launch options (a struct led by its own size, so that
+ * fields can be added; only the fields inside struct_size are read).
+ *
+ * QMM_GEMM_INDEPENDENT: the caller states that nothing queued earlier on the
+ *   stream and possibly still running writes x, w or scale or touches y.  The
+ *   launch then does not order itself behind its predecessor, and its first
+ *   tiles run on the SMs that the predecessor's last, partly filled round
+ *   leaves idle.  Without the flag the kernel starts early but waits for the
+ *   work ahead of it before it touches memory.
+ * QMM_GEMM_STORE_MULTIMEM: y is a multicast (NVSwitch multimem) address: every
+ *   store of the epilogue lands at the same offset of the buffer of every GPU
+ *   bound to the multicast object, this one included.  This is the all-gather
+ *   of a column-sharded linear (stablehlo.all_gather over one replica group;
+ *   the reference's handler is src/pjrt_plugin/ops/collective_ops.mm:88-229,
+ *   an identity on its single device) done by the GEMM's own stores: rank r
+ *   passes the multicast address of block r of the gathered [P, M, N/P] buffer.
+ * done_signal / arrive_counter (both or neither): when the launch's stores are
+ *   complete, done_signal (a multicast address under QMM_GEMM_STORE_MULTIMEM)
+ *   is incremented by 1 with release semantics at system scope; a reader that
+ *   observes the count with an acquire load (qmm_wait_signals) may read the
+ *   output.  arrive_counter is a local uint32, zero before its first use and
+ *   left zero, on which the launch's CTAs count themselves. */
+#define QMM_GEMM_INDEPENDENT 1u
+#define QMM_GEMM_STORE_MULTIMEM 2u
+typedef struct qmm_gemm_ext {
+  size_t struct_size; /* sizeof(qmm_gemm_ext) as the caller knows it */
+  uint32_t flags;
+  uint32_t* done_signal;
+  uint32_t* arrive_counter;
+} qmm_gemm_ext;
+QMM_API int qmm_w8a16_perchannel_ex(const uint16_t* x_bf16, const int8_t* w, const float* scale,
+                                    uint16_t* y_bf16, int64_t M, int64_t N, int64_t K, int64_t ldy,
+                                    const qmm_gemm_ext* ext, void* stream);
+/* Queues a kernel that waits until words[i] >= expected for all i < count
+ * (the done_signal words of the ranks of a sharded linear), for at most
+ * timeout_ns (0 = the library's 2 s default).  A wait that runs out records
+ * QMM_ERR_TIMEOUT in the device status word and the kernel returns, so the
+ * context stays usable; the reference's counterpart is the bounded event wait
+ * (src/pjrt_plugin/core/completion_event.h:62-83).  The words must be written
+ * by other GPUs (or be set already), never by a kernel queued on this GPU after
+ * the wait. */
+QMM_API int qmm_wait_signals(const uint32_t* words, int count, uint32_t expected, uint64_t timeout_ns,
+                             void* stream);
+
 /* ---------------------------------------------------------------------------
  * int8 x int8 -> int32 dot with optional fused f32 rescale.
  *   acc[M,N]  = a[M,K] . b[K,N]            (exact, int32)          if acc != NULL

@@ -30,6 +30,9 @@ SIGNATURES = {
     "qmm_w8a32_perchannel": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_void_p]),
     "qmm_w8a16_perchannel": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p]),
+    "qmm_w8a16_perchannel_ex": (
+        c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
+    "qmm_wait_signals": (c_int, [c_void_p, c_int, ctypes.c_uint32, ctypes.c_uint64, c_void_p]),
     "qmm_i8i8_i32": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int,
                 c_void_p]),
@@ -68,6 +71,20 @@ SIGNATURES = {
     "qmm_mx_matmul": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_void_p]),
 }
+
+
+QMM_GEMM_INDEPENDENT = 1
+QMM_GEMM_STORE_MULTIMEM = 2
+
+
+class GemmExt(ctypes.Structure):
+    """``qmm_gemm_ext`` of include/qmm.h."""
+
+    _fields_ = [("struct_size", c_size_t), ("flags", ctypes.c_uint32), ("done_signal", c_void_p),
+                ("arrive_counter", c_void_p)]
+
+    def __init__(self, flags=0, done_signal=None, arrive_counter=None):
+        super().__init__(ctypes.sizeof(GemmExt), flags, done_signal, arrive_counter)
 
 
 class QmmError(RuntimeError):

@@ -3,6 +3,7 @@
 // describe (16-byte row pitches); anything else (the few-element shapes of the
 // reference's integer-dot tests, odd strides) runs on the simple kernels below.
 // Both routes are GPU code; there is no host fallback.
+#include <stddef.h>
 #include <stdlib.h>
 #include <string.h>
 
@@ -14,7 +15,8 @@ int i8gemm_tcgen05(const void* a, const void* b, int32_t* acc, const float* row_
                    const float* col_scale, float* out, int64_t M, int64_t N, int64_t K,
                    int a_unsigned, int b_unsigned, cudaStream_t stream);
 int w8a16_tcgen05(const uint16_t* x, const int8_t* w, const float* scale, uint16_t* y, int64_t M,
-                  int64_t N, int64_t K, int64_t ldy, cudaStream_t stream);
+                  int64_t N, int64_t K, int64_t ldy, uint32_t flags, uint32_t* signal, uint32_t* arrive,
+                  cudaStream_t stream);
 
 namespace simple {
 
@@ -49,6 +51,22 @@ __global__ void w8a16_kernel(const uint16_t* __restrict__ x, const int8_t* __res
     s = fmaf(dev::bf16_bits_to_float(x[static_cast<size_t>(m) * K + k]),
              static_cast<float>(w[static_cast<size_t>(k) * N + n]), s);
   y[static_cast<size_t>(m) * ldy + n] = dev::float_to_bf16_bits(s * scale[n]);
+}
+
+// One thread per word: wait (bounded) until words[i] >= expected.  The words are written by other
+// GPUs (the completion signals of a sharded linear), never by a kernel sharing this GPU.
+__global__ void wait_words_kernel(const uint32_t* words, int count, uint32_t expected, unsigned long long limit_ns,
+                                  int* status) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= count) return;
+  const uint64_t t0 = dev::globaltimer_ns();
+  while (true) {
+    // counts wrap: "reached" means no more than 2^31 behind
+    if (static_cast<int32_t>(dev::ld_acquire_sys_u32(words + i) - expected) >= 0) return;
+    if (dev::globaltimer_ns() - t0 > limit_ns) break;
+    __nanosleep(200);
+  }
+  if (status) atomicExch(status, (60 << 16) | QMM_ERR_TIMEOUT);
 }
 
 }  // namespace simple
@@ -99,25 +117,73 @@ int qmm_i8i8_i32(const void* a, const void* b, int32_t* acc, const float* row_sc
   return QMM_OK;
 }
 
-int qmm_w8a16_perchannel(const uint16_t* x, const int8_t* w, const float* scale, uint16_t* y,
-                         int64_t M, int64_t N, int64_t K, int64_t ldy, void* stream) {
+static int w8a16_entry(const char* name, const uint16_t* x, const int8_t* w, const float* scale, uint16_t* y,
+                       int64_t M, int64_t N, int64_t K, int64_t ldy, const qmm_gemm_ext* ext, void* stream) {
   using namespace qmm;
   QMM_REQUIRE(M >= 0 && N >= 0 && K >= 0 && M < (1ll << 30) && N < (1ll << 30) && K < (1ll << 30) &&
                   ldy >= N,
-              QMM_ERR_INVALID_ARGUMENT, "qmm_w8a16_perchannel: bad shape (ldy must be >= N)");
-  if (M == 0 || N == 0) return QMM_OK;  // empty result
-  QMM_REQUIRE(x && w && scale && y, QMM_ERR_INVALID_ARGUMENT, "qmm_w8a16_perchannel: null pointer");
+              QMM_ERR_INVALID_ARGUMENT, "%s: bad shape (ldy must be >= N)", name);
+  uint32_t flags = 0;
+  uint32_t* signal = nullptr;
+  uint32_t* arrive = nullptr;
+  if (ext) {
+    // fields are read only as far as the caller's struct reaches
+    QMM_REQUIRE(ext->struct_size >= offsetof(qmm_gemm_ext, flags) + sizeof(ext->flags), QMM_ERR_INVALID_ARGUMENT,
+                "%s: qmm_gemm_ext.struct_size (%zu) is too small", name, ext->struct_size);
+    flags = ext->flags;
+    if (ext->struct_size >= offsetof(qmm_gemm_ext, arrive_counter) + sizeof(ext->arrive_counter)) {
+      signal = ext->done_signal;
+      arrive = ext->arrive_counter;
+    }
+    QMM_REQUIRE((flags & ~(QMM_GEMM_INDEPENDENT | QMM_GEMM_STORE_MULTIMEM)) == 0, QMM_ERR_INVALID_ARGUMENT,
+                "%s: unknown flag bits 0x%x", name, flags);
+    QMM_REQUIRE((signal == nullptr) == (arrive == nullptr), QMM_ERR_INVALID_ARGUMENT,
+                "%s: done_signal and arrive_counter go together", name);
+    QMM_REQUIRE(aligned(signal, 4) && aligned(arrive, 4), QMM_ERR_INVALID_ARGUMENT, "%s: misaligned signal word", name);
+  }
+  if (M == 0 || N == 0) {
+    QMM_REQUIRE(signal == nullptr, QMM_ERR_UNSUPPORTED, "%s: an empty result cannot signal", name);
+    return QMM_OK;  // empty result
+  }
+  QMM_REQUIRE(x && w && scale && y, QMM_ERR_INVALID_ARGUMENT, "%s: null pointer", name);
   if (int st = read_device_status())
     return set_error(QMM_ERR_TIMEOUT, "a previous kernel gave up waiting (status word 0x%x)", st);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const bool tma_ok = K > 0 && K % 8 == 0 && N % 16 == 0 && ldy % 2 == 0 && aligned(x, 16) &&
                       aligned(w, 16) && aligned(y, 4);
   if (tma_ok && M * N >= 128 * 128 && !force_simple())
-    return w8a16_tcgen05(x, w, scale, y, M, N, K, ldy, s);
-  QMM_REQUIRE(M <= 65535, QMM_ERR_UNSUPPORTED, "qmm_w8a16_perchannel: unaligned shape with M > 65535");
+    return w8a16_tcgen05(x, w, scale, y, M, N, K, ldy, flags, signal, arrive, s);
+  QMM_REQUIRE(!(flags & QMM_GEMM_STORE_MULTIMEM) && signal == nullptr, QMM_ERR_UNSUPPORTED,
+              "%s: multicast stores and completion signals need the tensor-core route "
+              "(K %% 8 == 0, N %% 16 == 0, even ldy, 16-byte aligned x and w, M*N >= 16384)", name);
+  QMM_REQUIRE(M <= 65535, QMM_ERR_UNSUPPORTED, "%s: unaligned shape with M > 65535", name);
   dim3 grid(static_cast<unsigned>((N + 127) / 128), static_cast<unsigned>(M));
   simple::w8a16_kernel<<<grid, 128, 0, s>>>(x, w, scale, y, (int)M, (int)N, (int)K, (long long)ldy);
   QMM_CHECK_LAUNCH("w8a16_kernel(simple)");
+  return QMM_OK;
+}
+
+int qmm_w8a16_perchannel(const uint16_t* x, const int8_t* w, const float* scale, uint16_t* y,
+                         int64_t M, int64_t N, int64_t K, int64_t ldy, void* stream) {
+  return w8a16_entry("qmm_w8a16_perchannel", x, w, scale, y, M, N, K, ldy, nullptr, stream);
+}
+
+int qmm_w8a16_perchannel_ex(const uint16_t* x, const int8_t* w, const float* scale, uint16_t* y,
+                            int64_t M, int64_t N, int64_t K, int64_t ldy, const qmm_gemm_ext* ext,
+                            void* stream) {
+  return w8a16_entry("qmm_w8a16_perchannel_ex", x, w, scale, y, M, N, K, ldy, ext, stream);
+}
+
+int qmm_wait_signals(const uint32_t* words, int count, uint32_t expected, uint64_t timeout_ns, void* stream) {
+  using namespace qmm;
+  QMM_REQUIRE(words != nullptr && count >= 1 && count <= 4096 && aligned(words, 4), QMM_ERR_INVALID_ARGUMENT,
+              "qmm_wait_signals: bad arguments");
+  if (int st = read_device_status())
+    return set_error(QMM_ERR_TIMEOUT, "a previous kernel gave up waiting (status word 0x%x)", st);
+  if (timeout_ns == 0 || timeout_ns > 10000000000ull) timeout_ns = dev::kWaitLimitNs;
+  simple::wait_words_kernel<<<(count + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+      words, count, expected, timeout_ns, device_status_word());
+  QMM_CHECK_LAUNCH("wait_words_kernel");
   return QMM_OK;
 }
 

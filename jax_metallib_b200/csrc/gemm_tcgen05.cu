@@ -1,31 +1,34 @@
 // tcgen05 / TMEM GEMMs for the prefill-sized quantized matmuls (sm_100a).
 //
-// Two kernels share one skeleton: a persistent CTA per SM walks output tiles;
-// warp 0 feeds shared memory with TMA (128-byte swizzle), one thread of warp 1
-// issues tcgen05.mma into TMEM accumulators (2 x 256 columns: double-buffered
-// in the int8 kernel, two channel blocks of one tile in the weight-only one),
-// epilogue warps drain them with tcgen05.ld and apply the fused epilogue.
-// Every wait is bounded.
+// Both kernels keep one persistent CTA per SM that walks output tiles, feed
+// shared memory with TMA (128-byte swizzle), accumulate in all 512 TMEM columns
+// (two 256-column accumulators, one MMA-issuing thread each: a single thread
+// cannot issue tcgen05.mma fast enough to keep the tensor pipe busy) and drain
+// the accumulators with tcgen05.ld into a fused epilogue.  Every wait is bounded.
 //
 //  (1) i8gemm: acc[M,N] = a[M,K] . b[K,N], int8/uint8 operands, int32
 //      accumulate (kind::i8, exact).  a is K-major, b is consumed N-major
 //      straight from its row-major [K,N] layout (MN-major descriptor), so no
 //      transposed copy of b is ever made.  Tile 256 (m, two accumulators) x
-//      256 (n) x 128 (k), one issuing thread per accumulator.
-//      Epilogue: optional int32 store and/or float(acc) * row[m] * col[n].
+//      256 (n) x 128 (k).  Warps: one TMA producer, two MMA issuers, eight
+//      epilogue warps (optional int32 store and/or float(acc) * row[m] * col[n]).
 //
 //  (2) w8a16: y[M,N] = bf16((x[M,K] @ float(w[K,N])) * scale[N]), bf16
 //      activations, int8 weights.  The weight tile is the 128-row MMA operand
 //      (MN-major: its 128 output channels are contiguous in memory), the
 //      activation tile the 256-column operand; a CTA runs two weight blocks
-//      against one activation tile (256 channels x 256 rows, all 512 TMEM
-//      columns), which cuts the bytes it stages per FLOP.  Converter warps
-//      read the raw int8 tile, turn it into bf16 (exactly) and write the MMA's
-//      swizzled layout in 32-k sub-blocks through a ring of four.  The
-//      accumulator holds the transposed tile (lane = output channel), so the
-//      per-channel scale is one register per thread and stores of a warp are
-//      contiguous along N.  Leftover tiles of the last round are cut into
-//      halves or quarters.
+//      against one activation tile (256 channels x 256 rows).  Warps: a TMA
+//      producer for activations, one for raw int8 weights, two MMA issuers and
+//      24 worker warps in three groups that take every third 64-k stage: a
+//      group reads the raw tile, converts it to bf16 (exactly) and writes the
+//      MMA's swizzled layout; when a tile's stages are done the same 24 warps
+//      drain its accumulators.  The accumulator holds the transposed tile
+//      (lane = output channel), so the per-channel scale is one register per
+//      thread.  Leftover tiles of the last round are cut into halves or
+//      quarters.  The output may be stored with multimem.st to a multicast
+//      address (one store reaches the same offset of every rank's buffer:
+//      the all-gather of a column-sharded linear happens in the epilogue), and
+//      the launch can signal its completion to every rank.
 #include <cstdlib>
 
 #include "common.cuh"
@@ -367,8 +370,10 @@ __device__ __forceinline__ bool get_work(const Sched& sc, int i, int M, int N, W
 __global__ void __launch_bounds__(kThreads, 1)
 w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
              const float* __restrict__ scale, uint16_t* __restrict__ y, int M, int N, int K,
-             long long ldy, uint32_t idesc256, uint32_t idesc128, const Sched sc, int* status) {
+             long long ldy, uint32_t idesc256, uint32_t idesc128, const Sched sc, uint32_t flags,
+             uint32_t* signal, uint32_t* arrive, int* status) {
   extern __shared__ uint8_t smem_raw[];
+  dev::pdl_launch_dependents();  // the next kernel on the stream may start its prologue
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint64_t* xfull = reinterpret_cast<uint64_t*>(smem + kBarBase);  // activations landed
@@ -403,6 +408,10 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
   __syncthreads();
   dev::tc_fence_after();
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
+  // Ordered behind the kernels ahead on the stream before global memory is touched, unless the
+  // caller stated that none of them writes this launch's operands or touches its output.
+  if (!(flags & QMM_GEMM_INDEPENDENT)) dev::pdl_wait();
+  const bool mc_store = (flags & QMM_GEMM_STORE_MULTIMEM) != 0;
 
   // Stage `cnt` (counted over the whole launch) uses activation slot cnt % 3,
   // raw-weight slot cnt % 4 and converted buffers 2 (cnt % 2) and 2 (cnt % 2) + 1.
@@ -594,8 +603,11 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
           const int m = m0 + 2 * j + (lane & 1);
           const uint32_t packed = (lane & 1) ? dev::pack_bf16x2(got, b) : dev::pack_bf16x2(a, got);
           const int n_even = n & ~1;
-          if (m < M && n_even < N)
-            *reinterpret_cast<uint32_t*>(y + static_cast<size_t>(m) * ldy + n_even) = packed;
+          if (m < M && n_even < N) {
+            uint16_t* dst = y + static_cast<size_t>(m) * ldy + n_even;
+            if (mc_store) dev::multimem_st_b32(dst, packed);  // the same offset of every rank's buffer
+            else *reinterpret_cast<uint32_t*>(dst) = packed;
+          }
         }
       }
       dev::tc_fence_before();
@@ -604,9 +616,22 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
       ++items;
     }
   }
+  // Completion signal: every thread that stored makes its stores visible system-wide, the CTAs
+  // count themselves on a local counter (which wraps back to zero), and the last one adds 1 to
+  // the signal word with release semantics: on every rank at once when the word is a multicast
+  // address.  A reader that sees the new count with an acquire load sees the whole output block.
+  if (signal != nullptr) dev::fence_sys();
   dev::tc_fence_before();
   __syncthreads();
   if (warp == 1) dev::tmem_dealloc(tmem_base, 512);
+  if (signal != nullptr && threadIdx.x == 0) {
+    const unsigned prev = atomicInc(arrive, gridDim.x - 1);
+    if (prev == gridDim.x - 1) {
+      dev::fence_sys();
+      if (mc_store) dev::multimem_red_release_add_u32(signal, 1u);
+      else dev::red_release_sys_add_u32(signal, 1u);
+    }
+  }
 }
 }  // namespace w8
 
@@ -646,7 +671,8 @@ int i8gemm_tcgen05(const void* a, const void* b, int32_t* acc, const float* row_
 }
 
 int w8a16_tcgen05(const uint16_t* x, const int8_t* w, const float* scale, uint16_t* y, int64_t M,
-                  int64_t N, int64_t K, int64_t ldy, cudaStream_t stream) {
+                  int64_t N, int64_t K, int64_t ldy, uint32_t flags, uint32_t* signal, uint32_t* arrive,
+                  cudaStream_t stream) {
   using namespace tc::w8;
   CUtensorMap wmap, xmap;
   if (int rc = make_tensor_map_2d(&wmap, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)K,
@@ -687,10 +713,13 @@ int w8a16_tcgen05(const uint16_t* x, const int8_t* w, const float* scale, uint16
     }
   }
   const int grid = sc.full_waves > 0 ? sms : (sc.tail_tiles * sc.tail_div < sms ? sc.tail_tiles * sc.tail_div : sms);
-  w8a16_kernel<<<grid, kThreads, kSmemBytes, stream>>>(wmap, xmap, scale, y, (int)M, (int)N, (int)K,
-                                                       (long long)ldy, idesc256, idesc128, sc,
-                                                       device_status_word());
-  QMM_CHECK_LAUNCH("w8a16_kernel");
+  // Programmatic stream serialization: the CTAs of this launch may become resident while the
+  // kernel ahead of it drains; they order themselves behind it inside the kernel (or not at all
+  // when the caller states independence, which fills the last, partly idle round of one launch
+  // with the first tiles of the next).
+  QMM_CUDA_TRY(launch_pdl(w8a16_kernel, dim3(grid), dim3(kThreads), kSmemBytes, stream, wmap, xmap, scale, y, (int)M,
+                          (int)N, (int)K, (long long)ldy, idesc256, idesc128, sc, flags, signal, arrive,
+                          device_status_word()));
   return QMM_OK;
 }
 

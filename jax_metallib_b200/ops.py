@@ -51,12 +51,15 @@ def w8a32_perchannel(x: torch.Tensor, w: torch.Tensor, scale: torch.Tensor) -> t
 
 
 def w8a16_perchannel(x: torch.Tensor, w: torch.Tensor, scale: torch.Tensor, out: torch.Tensor | None = None,
-                     out_col_offset: int = 0) -> torch.Tensor:
+                     out_col_offset: int = 0, independent: bool = False) -> torch.Tensor:
     """bf16 ``x[M,K]`` times int8 ``w[K,N]`` with per-channel f32 ``scale[N]`` -> bf16.
 
     ``out`` may be a wider ``[M, N_total]`` buffer; the result is written to
     columns ``[out_col_offset, out_col_offset + N)`` (how a rank that holds a
-    column shard writes into the gathered output).
+    column shard writes into the gathered output).  ``independent=True`` states
+    that nothing still running on the stream writes the operands or touches
+    the output (``QMM_GEMM_INDEPENDENT``): the launch is not ordered behind
+    its predecessor.
     """
     _need_cuda(x, w, scale, out)
     if x.dtype != torch.bfloat16 or w.dtype != torch.int8 or scale.dtype != torch.float32:
@@ -72,6 +75,13 @@ def w8a16_perchannel(x: torch.Tensor, w: torch.Tensor, scale: torch.Tensor, out:
         raise ValueError("bad output buffer")
     ldy = out.shape[1]
     yptr = out.data_ptr() + 2 * out_col_offset
+    if independent:
+        import ctypes
+
+        ext = _lib.GemmExt(_lib.QMM_GEMM_INDEPENDENT)
+        _lib.check(_lib.load().qmm_w8a16_perchannel_ex(x.data_ptr(), w.data_ptr(), scale.data_ptr(), yptr, M, N, K, ldy,
+                                                       ctypes.byref(ext), _stream_ptr()))
+        return out
     _lib.check(_lib.load().qmm_w8a16_perchannel(x.data_ptr(), w.data_ptr(), scale.data_ptr(), yptr, M, N, K, ldy,
                                                 _stream_ptr()))
     return out

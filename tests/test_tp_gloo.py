@@ -61,6 +61,55 @@ def test_two_rank_column_sharding_and_gather(tmp_path):
     assert torch.equal(a, b)
 
 
+def _exchange_worker(rank, world, port, result_dir):
+    # GatherExchange over gloo ranks: the slot/linear bookkeeping and the [P, M, N/P] buffers, with the
+    # oracle in place of the CUDA kernel
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=30))
+    try:
+        M, K = 16, 64
+        shapes = {"a": (M, 96), "b": (M, 32)}
+        rng = np.random.default_rng(6)
+        x = torch.from_numpy(rng.standard_normal((M, K)).astype(np.float32)).to(torch.bfloat16)
+        ex = tp.GatherExchange(shapes, "cpu", depth=2)
+        assert ex.mode == "collective" and ex.world == world
+        for use in range(3):  # slots alternate; the third use overwrites slot 0
+            slot = use & 1
+            for name, (_, n) in shapes.items():
+                w = torch.from_numpy(rng.integers(-127, 128, size=(K, n), dtype=np.int64).astype(np.int8))
+                scale = torch.from_numpy(rng.uniform(0.005, 0.02, size=(n,)).astype(np.float32))
+                a, b = tp.shard_bounds(n, world, rank)
+                out = ex.linear(name, slot, x, w[:, a:b].contiguous(), scale[a:b].contiguous(), matmul=_oracle_matmul)
+                assert out.shape == (world, M, n // world)
+                assert torch.equal(ex.logical(name, slot), _oracle_matmul(x, w, scale))
+                assert torch.equal(tp.gathered_view(out)[:, rank, :], _oracle_matmul(x, w[:, a:b], scale[a:b]))
+        ex.finish()
+        with open(os.path.join(result_dir, f"ok{rank}"), "w") as f:
+            f.write("ok")
+    finally:
+        dist.destroy_process_group()
+
+
+def test_two_rank_gather_exchange_bookkeeping(tmp_path):
+    port = _free_port()
+    mp.spawn(_exchange_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+    assert (tmp_path / "ok0").exists() and (tmp_path / "ok1").exists()
+
+
+def test_exchange_layout_plan():
+    blocks, sig, total = tp.plan_layout({"qkv": (4096, 10240), "o": (4096, 8192)}, world=8, depth=2)
+    assert blocks[(0, "qkv")].offset == 0 and blocks[(0, "qkv")].block_bytes == 4096 * 1280 * 2
+    assert blocks[(0, "o")].offset == 4096 * 10240 * 2
+    assert blocks[(1, "qkv")].offset == 4096 * (10240 + 8192) * 2
+    assert sig == 2 * 4096 * (10240 + 8192) * 2 and total >= sig + 2 * 2 * 8 * 4 and total % 256 == 0
+    assert all(b.offset % 256 == 0 for b in blocks.values())
+    with pytest.raises(ValueError):
+        tp.plan_layout({"x": (4, 10)}, world=4, depth=1)
+    with pytest.raises(ValueError):
+        tp.plan_layout({"x": (4, 8)}, world=4, depth=0)
+
+
 def test_shard_bounds_and_errors():
     assert tp.shard_bounds(10240, 8, 3) == (3840, 5120)
     assert [tp.shard_bounds(8, 2, r) for r in range(2)] == [(0, 4), (4, 8)]
@@ -72,6 +121,9 @@ def test_shard_bounds_and_errors():
     logical = tp.gathered_to_logical(g)
     assert logical.shape == (3, 8)
     assert torch.equal(logical[1], torch.cat([g[0, 1], g[1, 1]]))
+    view = tp.gathered_view(g)  # [M, P, N/P] without a copy
+    assert view.shape == (3, 2, 4) and view.data_ptr() == g.data_ptr()
+    assert torch.equal(view[1, 1], g[1, 1])
 
 
 def _absent_peer_worker(rank, world, port, result_dir):
