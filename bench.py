@@ -416,30 +416,83 @@ def run_gpu(args):
 
     # ---- end-to-end timing (host activations in, last result out) ---------------
     last_slot = (layers - 1) & 1
+    h2d = x_host.numel() * 2 + h_host.numel() * 2
+    d2h = result_host.numel() * 2
+    if world == 1:
+        # Through the runtime layer's C ABI (what a PJRT plugin's callbacks call): host buffers are
+        # uploaded with BufferFromHostBuffer, every layer is one Execute of a compiled StableHLO module
+        # with its four linears, the last layer's `down` output comes back with ToHostBuffer, and the
+        # step ends when that transfer's event is ready.  Weights are device-resident views.
+        import numpy as np
 
-    def e2e_step():
-        acts["x"].copy_(x_host, non_blocking=True)
-        acts["h"].copy_(h_host, non_blocking=True)
-        step()
-        result_host.copy_(ex.out("down", last_slot), non_blocking=True)
+        from jax_metallib_b200 import runtime
+        from jax_metallib_b200.stablehlo import weight_only_linears_module
 
-    e2e_step()
-    barrier()
-    ee0 = torch.cuda.Event(enable_timing=True)
-    ee1 = torch.cuda.Event(enable_timing=True)
-    ee0.record()
-    for _ in range(args.steps):
+        rt = runtime.Client()
+        exe = rt.compile(weight_only_linears_module(
+            [(M_TOKENS, k, ns, 0 if act == "x" else 1) for _, k, _, ns, act, _, _ in weights[0]]))
+        layer_bufs = []
+        for layer in weights:
+            bufs = []
+            for _, k, _, ns, _, w, s in layer:
+                bufs.append(rt.view_of_device_memory(w.data_ptr(), _lib.QMM_S8, (k, ns), local_rank, keepalive=w))
+                bufs.append(rt.view_of_device_memory(s.data_ptr(), _lib.QMM_F32, (ns,), local_rank, keepalive=s))
+            layer_bufs.append(bufs)
+        x_np = x_host.view(torch.int16).numpy().view(np.uint16)
+        h_np = h_host.view(torch.int16).numpy().view(np.uint16)
+        res_np = result_host.view(torch.int16).numpy().view(np.uint16).reshape(M_TOKENS, -1)
+
+        def e2e_step():
+            xb = rt.buffer_from_host(x_np, local_rank, dtype=_lib.QMM_BF16)
+            hb = rt.buffer_from_host(h_np, local_rank, dtype=_lib.QMM_BF16)
+            outs = None
+            for bufs in layer_bufs:
+                if outs is not None:
+                    for o in outs:
+                        o.destroy()  # stream-ordered free behind the launch that produced it
+                outs, _ = exe.execute([xb, hb] + bufs, want_event=False)
+            ev = outs[3].to_host(res_np)
+            ev.await_(60000)
+            for o in outs:
+                o.destroy()
+            xb.destroy()
+            hb.destroy()
+
+        torch.cuda.synchronize()
         e2e_step()
-    ee1.record()
-    barrier()
-    e2e_ms = ee0.elapsed_time(ee1)
-    if world > 1:
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            e2e_step()
+        e2e_ms = (time.perf_counter() - t0) * 1e3  # every step ends with a host-visible completion
+        e2e_launches = args.steps * layers * 4
+        e2e_api = ("qmm_rt_buffer_from_host -> qmm_rt_executable_execute (one compiled four-linear StableHLO module per "
+                   "layer) -> qmm_rt_buffer_to_host, host wall clock around steps that each end with an awaited event")
+        # what the runtime path computed is checked as well (the last layer's `down` output, rows sampled)
+        rt_down = torch.from_numpy(res_np.view(np.int16).copy()).view(torch.bfloat16)
+    else:
+        def e2e_step():
+            acts["x"].copy_(x_host, non_blocking=True)
+            acts["h"].copy_(h_host, non_blocking=True)
+            step()
+            result_host.copy_(ex.out("down", last_slot), non_blocking=True)
+
+        e2e_step()
+        barrier()
+        ee0 = torch.cuda.Event(enable_timing=True)
+        ee1 = torch.cuda.Event(enable_timing=True)
+        ee0.record()
+        for _ in range(args.steps):
+            e2e_step()
+        ee1.record()
+        barrier()
+        e2e_ms = ee0.elapsed_time(ee1)
         t = torch.tensor([e2e_ms], dtype=torch.float64, device=device)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t.item())
+        e2e_api = ("tp.GatherExchange.linear per linear (qmm_w8a16_perchannel_ex) with pinned-host activations copied in "
+                   "and the gathered `down` output copied out every step; CUDA events, max over ranks")
+        rt_down = None
     e2e_value = total_flops / (e2e_ms / args.steps * 1e-3) / 1e12
-    h2d = x_host.numel() * 2 + h_host.numel() * 2
-    d2h = result_host.numel() * 2
 
     status = lib.qmm_device_status()
     if status != 0:
@@ -447,6 +500,12 @@ def run_gpu(args):
 
     # ---- parity of what was just timed (outside the timed region) -----------------
     checked, worst_err, n_rows = check_last_layer(torch, dist, ex, weights[-1], last_slot, acts, rank, world, device)
+    if rt_down is not None:
+        # the runtime path ran the same last layer on the same inputs: bit-identical to the direct path
+        same = bool(torch.equal(rt_down.to(device), ex.out("down", last_slot)[0]))
+        checked = checked and same
+        if not same:
+            print("[rank 0] the runtime path's output differs from the direct path's", file=sys.stderr)
     if not checked:
         print(f"[rank {rank}] PARITY CHECK FAILED: max relative error {worst_err:.3e}", file=sys.stderr)
 
@@ -491,7 +550,8 @@ def run_gpu(args):
                          "launch_ms_mean": launch_ms,
                          "traffic": traffic, "traffic_unit": "DRAM bytes per launch (mean of a layer's four)",
                          "traffic_source": "+".join(sorted(how))},
-            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "e2e": {"value": e2e_value, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "api": e2e_api},
             "gpu_launches": timed_launches,
             "clocks": clocks,
         }
@@ -500,6 +560,12 @@ def run_gpu(args):
     if world == 1 and rank == 0 and not args.no_detail:
         time.sleep(2.0)  # let the power-capped clocks of the timed region recover before the small kernels
         del weights, ex
+        if rt_down is not None:
+            for bufs in layer_bufs:
+                for b in bufs:
+                    b.destroy()
+            del layer_bufs, bufs, exe
+            rt.destroy()
         torch.cuda.empty_cache()
         line["detail"] = run_detail(torch, ops, synthetic, lib, device, peaks)
         base, _ = cpu_linears_tflops(steps=6, warmup=1)

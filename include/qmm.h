@@ -122,12 +122,17 @@ QMM_API int qmm_w8a16_perchannel(const uint16_t* x_bf16, const int8_t* w, const 
 /* The same matmul with launch options (a struct led by its own size, so that
  * fields can be added; only the fields inside struct_size are read).
  *
- * QMM_GEMM_INDEPENDENT: the caller states that nothing queued earlier on the
- *   stream and possibly still running writes x, w or scale or touches y.  The
- *   launch then does not order itself behind its predecessor, and its first
- *   tiles run on the SMs that the predecessor's last, partly filled round
- *   leaves idle.  Without the flag the kernel starts early but waits for the
- *   work ahead of it before it touches memory.
+ * QMM_GEMM_INDEPENDENT: the caller states that no launch of this entry point
+ *   queued earlier on the stream, back to and including the last one made
+ *   without this flag, writes x, w or scale or touches y.  The launch then does
+ *   not order itself behind those launches, and its first tiles run on the SMs
+ *   that its predecessor's last, partly filled round leaves idle.  A launch
+ *   without the flag waits for everything ahead of it on the stream before it
+ *   touches memory, and holds back its successors until it has done so; so a
+ *   flagged launch never overlaps anything older than the last unflagged one.
+ *   (Kernels of other entry points between two launches order them fully,
+ *   except the decode operators, which start early behind their predecessor:
+ *   do not put a flagged launch directly behind those.)
  * QMM_GEMM_STORE_MULTIMEM: y is a multicast (NVSwitch multimem) address: every
  *   store of the epilogue lands at the same offset of the buffer of every GPU
  *   bound to the multicast object, this one included.  This is the all-gather
@@ -340,6 +345,17 @@ QMM_API int qmm_plan_num_steps(const qmm_plan* plan);
 QMM_API int qmm_plan_num_args(const qmm_plan* plan);
 QMM_API int qmm_plan_num_results(const qmm_plan* plan);
 QMM_API size_t qmm_plan_workspace_bytes(const qmm_plan* plan);
+/* Element type (a qmm_dtype, or -1 for a type the library has no tag for), rank
+ * and dimensions of @main's arguments and results.  *rank carries the capacity
+ * of dims on entry and the rank on return; dims may be NULL. */
+QMM_API int qmm_plan_arg_info(const qmm_plan* plan, int index, int* dtype, int64_t* dims, int* rank);
+QMM_API int qmm_plan_result_info(const qmm_plan* plan, int index, int* dtype, int64_t* dims, int* rank);
+/* Module symbol, mhlo.num_replicas / mhlo.num_partitions, and the operation
+ * count (2 M N K summed over the fused matmuls) of the plan. */
+QMM_API const char* qmm_plan_name(const qmm_plan* plan);
+QMM_API int qmm_plan_num_replicas(const qmm_plan* plan);
+QMM_API int qmm_plan_num_partitions(const qmm_plan* plan);
+QMM_API double qmm_plan_flops(const qmm_plan* plan);
 QMM_API size_t qmm_plan_trace(const qmm_plan* plan, char* buf, size_t cap);
 QMM_API int qmm_plan_execute(const qmm_plan* plan, const void* const* args, int num_args,
                              void* const* results, int num_results, void* workspace,

@@ -64,6 +64,13 @@ SIGNATURES = {
     "qmm_plan_num_args": (c_int, [c_void_p]),
     "qmm_plan_num_results": (c_int, [c_void_p]),
     "qmm_plan_workspace_bytes": (c_size_t, [c_void_p]),
+    "qmm_plan_arg_info": (c_int, [c_void_p, c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int64), ctypes.POINTER(c_int)]),
+    "qmm_plan_result_info": (c_int, [c_void_p, c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int64),
+                                     ctypes.POINTER(c_int)]),
+    "qmm_plan_name": (c_char_p, [c_void_p]),
+    "qmm_plan_num_replicas": (c_int, [c_void_p]),
+    "qmm_plan_num_partitions": (c_int, [c_void_p]),
+    "qmm_plan_flops": (ctypes.c_double, [c_void_p]),
     "qmm_plan_trace": (c_size_t, [c_void_p, c_char_p, c_size_t]),
     "qmm_plan_execute": (
         c_int, [c_void_p, ctypes.POINTER(c_void_p), c_int, ctypes.POINTER(c_void_p), c_int, c_void_p, c_size_t,
@@ -72,6 +79,95 @@ SIGNATURES = {
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int, c_void_p]),
 }
 
+
+# name -> (restype, argtypes); mirrors include/qmm_rt.h
+RT_SIGNATURES = {
+    "qmm_rt_status_to_pjrt_code": (c_int, [c_int]),
+    "qmm_rt_client_create": (c_int, [c_void_p]),
+    "qmm_rt_client_destroy": (c_int, [c_void_p]),
+    "qmm_rt_default_client": (c_void_p, []),
+    "qmm_rt_client_platform_name": (c_char_p, [c_void_p]),
+    "qmm_rt_client_platform_version": (c_char_p, [c_void_p]),
+    "qmm_rt_client_process_index": (c_int, [c_void_p]),
+    "qmm_rt_client_num_devices": (c_int, [c_void_p]),
+    "qmm_rt_client_device": (c_void_p, [c_void_p, c_int]),
+    "qmm_rt_client_lookup_device": (c_int, [c_void_p, c_int, c_void_p]),
+    "qmm_rt_client_num_memories": (c_int, [c_void_p]),
+    "qmm_rt_client_memory": (c_void_p, [c_void_p, c_int]),
+    "qmm_rt_client_default_device_assignment": (c_int, [c_void_p, c_int, c_int, c_void_p, c_size_t]),
+    "qmm_rt_device_id": (c_int, [c_void_p]),
+    "qmm_rt_device_process_index": (c_int, [c_void_p]),
+    "qmm_rt_device_local_hardware_id": (c_int, [c_void_p]),
+    "qmm_rt_device_is_addressable": (c_int, [c_void_p]),
+    "qmm_rt_device_kind": (c_char_p, [c_void_p]),
+    "qmm_rt_device_debug_string": (c_char_p, [c_void_p]),
+    "qmm_rt_device_to_string": (c_char_p, [c_void_p]),
+    "qmm_rt_device_default_memory": (c_void_p, [c_void_p]),
+    "qmm_rt_device_memory_stats": (c_int, [c_void_p, c_void_p, c_void_p]),
+    "qmm_rt_memory_id": (c_int, [c_void_p]),
+    "qmm_rt_memory_kind": (c_char_p, [c_void_p]),
+    "qmm_rt_memory_kind_id": (c_int, [c_void_p]),
+    "qmm_rt_memory_debug_string": (c_char_p, [c_void_p]),
+    "qmm_rt_memory_to_string": (c_char_p, [c_void_p]),
+    "qmm_rt_memory_device": (c_void_p, [c_void_p]),
+    "qmm_rt_memory_set_user_data": (c_int, [c_void_p, ctypes.c_uint64, c_void_p, c_void_p]),
+    "qmm_rt_memory_get_user_data": (c_void_p, [c_void_p, ctypes.c_uint64]),
+    "qmm_rt_event_create": (c_int, [c_void_p]),
+    "qmm_rt_event_set": (c_int, [c_void_p, c_int, c_char_p]),
+    "qmm_rt_event_destroy": (c_int, [c_void_p]),
+    "qmm_rt_event_is_ready": (c_int, [c_void_p]),
+    "qmm_rt_event_error": (c_int, [c_void_p]),
+    "qmm_rt_event_await": (c_int, [c_void_p, c_int]),
+    "qmm_rt_event_on_ready": (c_int, [c_void_p, c_void_p, c_void_p]),
+    "qmm_rt_buffer_from_host": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "qmm_rt_buffer_create_uninitialized": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p]),
+    "qmm_rt_buffer_view_of_device_memory": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "qmm_rt_buffer_create_error": (c_int, [c_void_p, c_int, c_char_p, c_int, c_void_p, c_int, c_void_p, c_void_p]),
+    "qmm_rt_buffer_dtype": (c_int, [c_void_p]),
+    "qmm_rt_buffer_rank": (c_int, [c_void_p]),
+    "qmm_rt_buffer_dims": (c_void_p, [c_void_p]),
+    "qmm_rt_buffer_size_bytes": (c_size_t, [c_void_p]),
+    "qmm_rt_buffer_device": (c_void_p, [c_void_p]),
+    "qmm_rt_buffer_memory": (c_void_p, [c_void_p]),
+    "qmm_rt_buffer_is_on_cpu": (c_int, [c_void_p]),
+    "qmm_rt_buffer_delete": (c_int, [c_void_p]),
+    "qmm_rt_buffer_is_deleted": (c_int, [c_void_p]),
+    "qmm_rt_buffer_destroy": (c_int, [c_void_p]),
+    "qmm_rt_buffer_ready_event": (c_int, [c_void_p, c_void_p]),
+    "qmm_rt_buffer_to_host": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p, c_void_p]),
+    "qmm_rt_buffer_copy_raw_to_host": (c_int, [c_void_p, c_void_p, c_int64, c_int64, c_void_p]),
+    "qmm_rt_buffer_copy_to_device": (c_int, [c_void_p, c_void_p, c_void_p]),
+    "qmm_rt_buffer_device_pointer": (c_void_p, [c_void_p]),
+    "qmm_rt_buffer_increase_external_refs": (c_int, [c_void_p]),
+    "qmm_rt_buffer_decrease_external_refs": (c_int, [c_void_p]),
+    "qmm_rt_client_compile": (c_int, [c_void_p, c_void_p, c_size_t, c_char_p, c_void_p]),
+    "qmm_rt_executable_destroy": (c_int, [c_void_p]),
+    "qmm_rt_executable_delete": (c_int, [c_void_p]),
+    "qmm_rt_executable_is_deleted": (c_int, [c_void_p]),
+    "qmm_rt_executable_name": (c_char_p, [c_void_p]),
+    "qmm_rt_executable_num_replicas": (c_int, [c_void_p]),
+    "qmm_rt_executable_num_partitions": (c_int, [c_void_p]),
+    "qmm_rt_executable_num_outputs": (c_int, [c_void_p]),
+    "qmm_rt_executable_num_args": (c_int, [c_void_p]),
+    "qmm_rt_executable_code_size": (c_int64, [c_void_p]),
+    "qmm_rt_executable_fingerprint": (c_char_p, [c_void_p]),
+    "qmm_rt_executable_program": (c_char_p, [c_void_p, c_void_p]),
+    "qmm_rt_executable_output_dtype": (c_int, [c_void_p, c_int]),
+    "qmm_rt_executable_output_rank": (c_int, [c_void_p, c_int]),
+    "qmm_rt_executable_output_dims": (c_void_p, [c_void_p, c_int]),
+    "qmm_rt_executable_output_memory_kind": (c_char_p, [c_void_p, c_int]),
+    "qmm_rt_executable_arg_dtype": (c_int, [c_void_p, c_int]),
+    "qmm_rt_executable_arg_rank": (c_int, [c_void_p, c_int]),
+    "qmm_rt_executable_arg_dims": (c_void_p, [c_void_p, c_int]),
+    "qmm_rt_executable_flops": (ctypes.c_double, [c_void_p]),
+    "qmm_rt_executable_trace": (c_size_t, [c_void_p, c_void_p, c_size_t]),
+    "qmm_rt_executable_serialize": (c_int, [c_void_p, c_void_p, c_void_p]),
+    "qmm_rt_serialized_free": (None, [c_void_p]),
+    "qmm_rt_executable_deserialize_and_load": (c_int, [c_void_p, c_void_p, c_size_t, c_void_p]),
+    "qmm_rt_executable_client": (c_void_p, [c_void_p]),
+    "qmm_rt_executable_execute": (c_int, [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]),
+}
+SIGNATURES.update(RT_SIGNATURES)
 
 QMM_GEMM_INDEPENDENT = 1
 QMM_GEMM_STORE_MULTIMEM = 2

@@ -373,7 +373,10 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
              long long ldy, uint32_t idesc256, uint32_t idesc128, const Sched sc, uint32_t flags,
              uint32_t* signal, uint32_t* arrive, int* status) {
   extern __shared__ uint8_t smem_raw[];
-  dev::pdl_launch_dependents();  // the next kernel on the stream may start its prologue
+  // An independent launch lets its successor start at once.  A dependent one does so only after
+  // its own wait below: a successor that is itself flagged independent can then overlap this
+  // launch, but never anything older than it.
+  if (flags & QMM_GEMM_INDEPENDENT) dev::pdl_launch_dependents();
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
   uint64_t* xfull = reinterpret_cast<uint64_t*>(smem + kBarBase);  // activations landed
@@ -410,7 +413,10 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
   const uint32_t tmem_base = *reinterpret_cast<volatile uint32_t*>(tmem_slot);
   // Ordered behind the kernels ahead on the stream before global memory is touched, unless the
   // caller stated that none of them writes this launch's operands or touches its output.
-  if (!(flags & QMM_GEMM_INDEPENDENT)) dev::pdl_wait();
+  if (!(flags & QMM_GEMM_INDEPENDENT)) {
+    dev::pdl_wait();
+    dev::pdl_launch_dependents();
+  }
   const bool mc_store = (flags & QMM_GEMM_STORE_MULTIMEM) != 0;
 
   // Stage `cnt` (counted over the whole launch) uses activation slot cnt % 3,

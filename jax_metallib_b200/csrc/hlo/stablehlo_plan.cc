@@ -56,6 +56,8 @@ struct Module {
   std::vector<std::string> returns;
   std::map<std::string, int> def;   // SSA name -> op index
   std::map<std::string, int> argi;  // SSA name -> argument index
+  std::string name = "main";        // module symbol (jit_<function> in what jax prints)
+  int num_replicas = 1, num_partitions = 1;  // mhlo.num_replicas / mhlo.num_partitions of the module
   std::string error;
 };
 
@@ -164,7 +166,24 @@ static bool parse_module(const char* text, size_t len, Module& m) {
     std::string l = trim(raw);
     size_t loc = l.find(" loc(");
     if (loc != std::string::npos) l = trim(l.substr(0, loc));
-    if (l.empty() || l.compare(0, 2, "//") == 0 || l[0] == '#' || l.compare(0, 6, "module") == 0) continue;
+    if (l.compare(0, 6, "module") == 0) {
+      size_t at = l.find('@');
+      if (at != std::string::npos) {
+        size_t e = at + 1;
+        while (e < l.size() && (isalnum((unsigned char)l[e]) || l[e] == '_' || l[e] == '.' || l[e] == '$')) ++e;
+        if (e > at + 1) m.name = l.substr(at + 1, e - at - 1);
+      }
+      for (const char* key : {"mhlo.num_replicas", "mhlo.num_partitions"}) {
+        size_t k = l.find(key);
+        if (k == std::string::npos) continue;
+        size_t eqs = l.find('=', k);
+        if (eqs == std::string::npos) continue;
+        const int v = atoi(l.c_str() + eqs + 1);
+        if (v >= 1) (key[9] == 'r' ? m.num_replicas : m.num_partitions) = v;
+      }
+      continue;
+    }
+    if (l.empty() || l.compare(0, 2, "//") == 0 || l[0] == '#') continue;
     if (l.compare(0, 9, "func.func") == 0) {
       bool is_main = l.find("@main(") != std::string::npos;
       if (!is_main) {
@@ -792,6 +811,61 @@ int qmm_plan_num_args(const qmm_plan* plan) { return plan ? (int)plan->p.mod.arg
 int qmm_plan_num_results(const qmm_plan* plan) { return plan ? (int)plan->p.mod.returns.size() : 0; }
 size_t qmm_plan_workspace_bytes(const qmm_plan* plan) { return plan ? plan->p.workspace : 0; }
 
+static int dtype_of_elem(const std::string& e) {
+  if (e == "f32") return QMM_F32;
+  if (e == "f16") return QMM_F16;
+  if (e == "bf16") return QMM_BF16;
+  if (e == "i8" || e == "si8") return QMM_S8;
+  if (e == "ui8") return QMM_U8;
+  if (e == "i32" || e == "si32") return QMM_S32;
+  if (e == "ui4") return QMM_U4;
+  if (e == "ui32") return QMM_U32;
+  return -1;
+}
+
+static int type_info(const qmm::hlo::TType& t, int* dtype, int64_t* dims, int* rank) {
+  using namespace qmm;
+  const int cap = rank ? *rank : 0;
+  QMM_REQUIRE(static_cast<int>(t.dims.size()) <= cap || dims == nullptr, QMM_ERR_INVALID_ARGUMENT,
+              "tensor of rank %zu does not fit the caller's %d dimensions", t.dims.size(), cap);
+  if (dtype) *dtype = dtype_of_elem(t.elem);
+  if (rank) *rank = static_cast<int>(t.dims.size());
+  if (dims)
+    for (size_t i = 0; i < t.dims.size(); ++i) dims[i] = t.dims[i];
+  return QMM_OK;
+}
+
+int qmm_plan_arg_info(const qmm_plan* plan, int index, int* dtype, int64_t* dims, int* rank) {
+  using namespace qmm;
+  QMM_REQUIRE(plan && index >= 0 && index < (int)plan->p.mod.arg_types.size(), QMM_ERR_INVALID_ARGUMENT,
+              "qmm_plan_arg_info: bad plan or index %d", index);
+  return type_info(plan->p.mod.arg_types[index], dtype, dims, rank);
+}
+
+int qmm_plan_result_info(const qmm_plan* plan, int index, int* dtype, int64_t* dims, int* rank) {
+  using namespace qmm;
+  QMM_REQUIRE(plan && index >= 0 && index < (int)plan->p.mod.returns.size(), QMM_ERR_INVALID_ARGUMENT,
+              "qmm_plan_result_info: bad plan or index %d", index);
+  const hlo::Module& m = plan->p.mod;
+  const std::string& v = m.returns[index];
+  auto d = m.def.find(v);
+  if (d != m.def.end()) return type_info(m.ops[d->second].out_type, dtype, dims, rank);
+  auto a = m.argi.find(v);
+  QMM_REQUIRE(a != m.argi.end(), QMM_ERR_PARSE, "result %d (%s) has no definition", index, v.c_str());
+  return type_info(m.arg_types[a->second], dtype, dims, rank);
+}
+
+const char* qmm_plan_name(const qmm_plan* plan) { return plan ? plan->p.mod.name.c_str() : ""; }
+int qmm_plan_num_replicas(const qmm_plan* plan) { return plan ? plan->p.mod.num_replicas : 0; }
+int qmm_plan_num_partitions(const qmm_plan* plan) { return plan ? plan->p.mod.num_partitions : 0; }
+
+double qmm_plan_flops(const qmm_plan* plan) {
+  double f = 0;
+  if (plan)
+    for (const auto& s : plan->p.steps) f += 2.0 * (double)s.M * (double)s.N * (double)s.K;
+  return f;
+}
+
 size_t qmm_plan_trace(const qmm_plan* plan, char* buf, size_t cap) {
   if (!plan) return 0;
   const std::string& t = plan->p.trace;
@@ -812,18 +886,32 @@ int qmm_plan_execute(const qmm_plan* plan, const void* const* args, int num_args
               (int)plan->p.mod.arg_names.size(), (int)plan->p.mod.returns.size(), num_args, num_results);
   QMM_REQUIRE(plan->p.workspace == 0 || (workspace && workspace_bytes >= plan->p.workspace), QMM_ERR_WORKSPACE,
               "qmm_plan_execute: %zu bytes of workspace required", plan->p.workspace);
+  // Steps read only arguments of @main and write distinct results, so they do not depend on one
+  // another: a weight-only GEMM step that follows only GEMM steps of this call is launched as
+  // independent of them (it fills the SMs their last round leaves idle).  The first step is always
+  // ordered behind everything queued before the call.
+  bool only_gemms_so_far = true;
+  bool first = true;
   for (const hlo::Step& s : plan->p.steps) {
     int rc = QMM_OK;
     void* out = s.out >= 0 ? results[s.out] : nullptr;
+    const bool independent = !first && only_gemms_so_far;
+    first = false;
+    if (s.kind != hlo::kW8A16 && s.kind != hlo::kI8Dot) only_gemms_so_far = false;
     switch (s.kind) {
       case hlo::kW8A32:
         rc = qmm_w8a32_perchannel((const float*)args[s.x], (const int8_t*)args[s.w], (const float*)args[s.scale],
                                   (float*)out, s.M, s.N, s.K, stream);
         break;
       case hlo::kW8A16:
-        rc = qmm_w8a16_perchannel((const uint16_t*)args[s.x], (const int8_t*)args[s.w], (const float*)args[s.scale],
-                                  (uint16_t*)out, s.M, s.N, s.K, s.N, stream);
+      {
+        qmm_gemm_ext ext = {};
+        ext.struct_size = sizeof(ext);
+        ext.flags = independent ? QMM_GEMM_INDEPENDENT : 0u;
+        rc = qmm_w8a16_perchannel_ex((const uint16_t*)args[s.x], (const int8_t*)args[s.w], (const float*)args[s.scale],
+                                     (uint16_t*)out, s.M, s.N, s.K, s.N, &ext, stream);
         break;
+      }
       case hlo::kI8Dot:
         rc = qmm_i8i8_i32(args[s.x], args[s.w], s.acc_out >= 0 ? (int32_t*)results[s.acc_out] : nullptr,
                           s.row >= 0 ? (const float*)args[s.row] : nullptr,

@@ -19,6 +19,46 @@ import json
 from . import _lib
 
 
+def weight_only_linears_module(linears, name: str = "jit_layer") -> str:
+    """Text of a StableHLO module that applies several int8 per-channel weight-only linears.
+
+    ``linears`` is a list of ``(M, K, N, activation)`` with ``activation`` an integer naming which
+    activation argument the linear reads (activations with the same number are one argument).
+    ``@main`` takes the distinct activations (bf16 ``[M, K]``) first, then for every linear its
+    weight (i8 ``[K, N]``) and scale (f32 ``[N]``), and returns one bf16 ``[M, N]`` per linear:
+    ``x @ (convert(w) * broadcast(convert(scale)))``, the form of ``tests/fixtures/cfg5_w8a16.mlir``.
+    """
+    acts = {}
+    for m, k, _n, a in linears:
+        if acts.setdefault(a, (m, k)) != (m, k):
+            raise ValueError(f"activation {a} is used with two different shapes")
+    order = sorted(acts)
+    args, body, rets, types = [], [], [], []
+    for i, a in enumerate(order):
+        m, k = acts[a]
+        args.append(f"%arg{i}: tensor<{m}x{k}xbf16>")
+    nxt = len(order)
+    v = 0
+    for m, k, n, a in linears:
+        xi, wi, si = order.index(a), nxt, nxt + 1
+        nxt += 2
+        args += [f"%arg{wi}: tensor<{k}x{n}xi8>", f"%arg{si}: tensor<{n}xf32>"]
+        body += [
+            f"    %{v} = stablehlo.convert %arg{wi} : (tensor<{k}x{n}xi8>) -> tensor<{k}x{n}xbf16>",
+            f"    %{v + 1} = stablehlo.convert %arg{si} : (tensor<{n}xf32>) -> tensor<{n}xbf16>",
+            f"    %{v + 2} = stablehlo.broadcast_in_dim %{v + 1}, dims = [1] : (tensor<{n}xbf16>) -> tensor<{k}x{n}xbf16>",
+            f"    %{v + 3} = stablehlo.multiply %{v}, %{v + 2} : tensor<{k}x{n}xbf16>",
+            f"    %{v + 4} = stablehlo.dot_general %arg{xi}, %{v + 3}, contracting_dims = [1] x [0] : "
+            f"(tensor<{m}x{k}xbf16>, tensor<{k}x{n}xbf16>) -> tensor<{m}x{n}xbf16>",
+        ]
+        rets.append(f"%{v + 4}")
+        types.append(f"tensor<{m}x{n}xbf16>")
+        v += 5
+    head = (f"module @{name} attributes {{mhlo.num_partitions = 1 : i32, mhlo.num_replicas = 1 : i32}} {{\n"
+            f"  func.func public @main({', '.join(args)}) -> ({', '.join(types)}) {{\n")
+    return head + "\n".join(body) + f"\n    return {', '.join(rets)} : {', '.join(types)}\n  }}\n}}\n"
+
+
 class Executable:
     def __init__(self, text: str):
         lib = _lib.load()

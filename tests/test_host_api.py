@@ -14,9 +14,10 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
 def test_library_loads_and_exports_every_declared_symbol():
-    header = open(os.path.join(ROOT, "include", "qmm.h")).read()
+    inc = os.path.join(ROOT, "include")
+    header = "".join(open(os.path.join(inc, f)).read() for f in sorted(os.listdir(inc)) if f.endswith(".h"))
     declared = set(re.findall(r"QMM_API\s+[\w\s\*]+?\b(qmm_\w+)\s*\(", header))
-    assert len(declared) >= 12
+    assert len(declared) >= 100
     lib = ctypes.CDLL(_lib.LIB_PATH)
     for name in sorted(declared):
         assert hasattr(lib, name), f"{name} is declared in include/qmm.h but not exported"
@@ -125,3 +126,50 @@ def test_matmul_refuses_to_run_without_cuda():
     p, s, b = Q.affine_quantize(w, bits=4, group_size=64)
     with pytest.raises(RuntimeError, match="no CPU fallback"):
         Q.affine_quantized_matmul(np.ones((1, 64), np.float32), p, s, b, bits=4, group_size=64, K=64)
+
+
+# ---- runtime events: host-side objects, no GPU involved -------------------------------------------
+def test_event_bounded_await_set_and_callbacks():
+    """A caller-facing wait gives up after its timeout with a DEADLINE_EXCEEDED-class status and leaves
+    the event pending (src/pjrt_plugin/core/completion_event.h:62-83, api/pjrt_event.cc:46-59)."""
+    import time
+
+    from jax_metallib_b200 import runtime
+
+    lib = _lib.load()
+    ev = runtime.Event()
+    assert not ev.is_ready()
+    t0 = time.time()
+    with pytest.raises(_lib.QmmError) as e:
+        ev.await_(60)  # nothing sets it: the wait runs out on the host
+    assert e.value.status_name == "QMM_ERR_TIMEOUT" and 0.05 <= time.time() - t0 < 5.0
+    assert lib.qmm_rt_status_to_pjrt_code(e.value.status) == 4  # DEADLINE_EXCEEDED
+    assert not ev.is_ready()  # still pending
+    seen = []
+    ev.on_ready(lambda status, msg: seen.append((status, msg)))
+    assert seen == []
+    ev.set()
+    assert ev.is_ready() and seen == [(0, "")]
+    ev.await_(10)
+    ev.on_ready(lambda status, msg: seen.append("late"))  # ready already: runs at once
+    assert seen[-1] == "late"
+    ev.set(3, "second completion is ignored")
+    assert ev.error() == 0
+    bad = runtime.Event()
+    bad.set(3, "upload failed")
+    with pytest.raises(_lib.QmmError) as e:
+        bad.await_(10)
+    assert "upload failed" in str(e.value) and e.value.status == 3
+
+
+def test_runtime_timeout_env_is_read_per_wait(monkeypatch):
+    import time
+
+    from jax_metallib_b200 import runtime
+
+    ev = runtime.Event()
+    monkeypatch.setenv("QMM_RT_COMPLETION_TIMEOUT_MS", "40")
+    t0 = time.time()
+    with pytest.raises(_lib.QmmError):
+        ev.await_()
+    assert time.time() - t0 < 5.0

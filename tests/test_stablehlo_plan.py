@@ -9,7 +9,7 @@ import os
 import pytest
 
 from jax_metallib_b200 import _lib
-from jax_metallib_b200.stablehlo import Executable
+from jax_metallib_b200.stablehlo import Executable, weight_only_linears_module
 
 FIX = os.path.join(os.path.dirname(os.path.abspath(__file__)), "fixtures")
 
@@ -101,3 +101,27 @@ def test_malformed_and_foreign_programs():
     with pytest.raises(_lib.QmmError) as e:
         Executable(load("cfg3_w4a16.mlir").replace("32x128x14336", "64x64x14336").replace("32x14336", "64x14336"))
     assert "group 128" in str(e.value)
+
+
+def test_a_layer_of_four_linears_is_four_fused_steps_with_introspection():
+    text = weight_only_linears_module([(256, 512, 640, 0), (256, 512, 512, 0), (256, 512, 3584, 0), (256, 1792, 512, 1)])
+    exe = Executable(text)
+    assert (exe.num_args, exe.num_results, exe.num_steps) == (10, 4, 4)
+    assert [(f["M"], f["N"], f["K"]) for f in fused(exe)] == [(256, 640, 512), (256, 512, 512), (256, 3584, 512),
+                                                             (256, 512, 1792)]
+    assert all(f["kernel"] == "qmm_w8a16_perchannel" for f in fused(exe))
+    lib = _lib.load()
+    import ctypes
+
+    dt, rank = ctypes.c_int(), ctypes.c_int(8)
+    dims = (ctypes.c_int64 * 8)()
+    assert lib.qmm_plan_arg_info(exe._h, 1, ctypes.byref(dt), dims, ctypes.byref(rank)) == 0
+    assert (dt.value, rank.value, dims[0], dims[1]) == (_lib.QMM_BF16, 2, 256, 1792)
+    rank.value = 8
+    assert lib.qmm_plan_result_info(exe._h, 2, ctypes.byref(dt), dims, ctypes.byref(rank)) == 0
+    assert (dt.value, dims[0], dims[1]) == (_lib.QMM_BF16, 256, 3584)
+    rank.value = 1  # too small for a rank-2 tensor
+    assert lib.qmm_plan_result_info(exe._h, 2, ctypes.byref(dt), dims, ctypes.byref(rank)) != 0
+    assert lib.qmm_plan_name(exe._h) == b"jit_layer"
+    assert lib.qmm_plan_num_replicas(exe._h) == 1 and lib.qmm_plan_num_partitions(exe._h) == 1
+    assert lib.qmm_plan_flops(exe._h) == 2.0 * 256 * (512 * (640 + 512 + 3584) + 1792 * 512)
