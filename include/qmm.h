@@ -183,7 +183,7 @@ QMM_API int qmm_i8i8_i32(const void* a, const void* b, int32_t* acc, const float
                          int a_unsigned, int b_unsigned, void* stream);
 
 /* ---------------------------------------------------------------------------
- * int4 asymmetric group-wise weight-only matmul at decode sizes (M <= 32).
+ * int4 asymmetric group-wise weight-only matmul, decode and prefill sizes.
  *   w[k,n] = (q[k,n] - z[k/group, n]) * s[k/group, n]
  *   y[M,N] = bf16( x[M,K] @ w[K,N] )
  * wq is uint8 [K/2, N]: byte [kk, n] holds q[2kk, n] in its low nibble and
@@ -196,10 +196,16 @@ QMM_API int qmm_i8i8_i32(const void* a, const void* b, int32_t* acc, const float
  * (src/pjrt_plugin/ops/bitwise_ops.mm:33-51,169-305; ops/shape_ops.mm:793-829;
  *  ops/binary_ops.mm:66-193, :644-1245).
  * Zero points are 4-bit values (0..15) in either form.
- * Requires group == 128, K % 128 == 0, N % 128 == 0, 1 <= M <= 32.
- * workspace: qmm_w4a16_g128_workspace_bytes(M, N, K) bytes, 256-byte aligned,
- * zero-filled before its first use; the kernel leaves it zero-filled, so
- * back-to-back calls on one stream may share it.
+ * Requires group == 128, K % 128 == 0, N % 128 == 0, M >= 1.
+ * M <= 32 runs the HBM-bound decode kernel (weights read once, split-K over
+ * all SMs); larger M runs a tcgen05 GEMM whose converter warps dequantise the
+ * nibbles in shared memory: bf16((q - z) * s) per weight, which is what the
+ * StableHLO chain computes in bf16, f32 accumulation, one rounding of the
+ * result.  That route needs no workspace (qmm_w4a16_g128_workspace_bytes
+ * returns 0 for M > 32 and workspace may be NULL) and ignores flags.
+ * workspace (M <= 32): qmm_w4a16_g128_workspace_bytes(M, N, K) bytes, 256-byte
+ * aligned, zero-filled before its first use; the kernel leaves it zero-filled,
+ * so back-to-back calls on one stream may share it.
  * flags: 0, or QMM_W4_STATIC_WEIGHTS when wq, scales and zeros are not written
  * by any work queued earlier on the stream (the usual case for model weights).
  * The kernel is launched with programmatic stream serialization: its blocks

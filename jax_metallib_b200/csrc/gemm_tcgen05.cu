@@ -367,11 +367,39 @@ __device__ __forceinline__ bool get_work(const Sched& sc, int i, int M, int N, W
   return true;
 }
 
+// Per-group constants of the int4 variant (null / unused for int8 weights).
+struct GroupQuant {
+  const uint16_t* scales;  // bf16 [K/128, N]
+  const uint8_t* zeros;    // u8 [K/128, N], or two per byte [K/128, N/2]
+  int packed;
+};
+
+// Four packed weights (the two k of two neighbouring channels, one byte per channel, low nibble =
+// even k) -> the bf16 pairs (q - z) * s of the even and of the odd k.  0x4300 | q is the bf16
+// 128 + q exactly, zz holds 128 + z, so the subtraction is exact and the product is rounded to
+// bf16 once: bit for bit what the StableHLO chain convert -> subtract -> multiply computes in bf16.
+__device__ __forceinline__ void dequant4(uint32_t t, uint32_t zz, uint32_t ss, uint32_t& even_k, uint32_t& odd_k) {
+  uint32_t lo, hi;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(lo) : "r"(t), "r"(0x000F000Fu), "r"(0x43004300u));
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(hi) : "r"(t >> 4), "r"(0x000F000Fu), "r"(0x43004300u));
+  asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(lo) : "r"(lo), "r"(zz));
+  asm("sub.rn.bf16x2 %0, %1, %2;" : "=r"(hi) : "r"(hi), "r"(zz));
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(even_k) : "r"(lo), "r"(ss));
+  asm("mul.rn.bf16x2 %0, %1, %2;" : "=r"(odd_k) : "r"(hi), "r"(ss));
+}
+
+// WBITS = 8: int8 weights [K, N], per-channel f32 scale applied in the epilogue.
+// WBITS = 4: packed int4 weights [K/2, N] (byte = two k of one channel), per-(128-k group, channel)
+//            bf16 scale and zero point applied by the converter warps; K % 128 == 0.
+template <int WBITS>
 __global__ void __launch_bounds__(kThreads, 1)
 w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
-             const float* __restrict__ scale, uint16_t* __restrict__ y, int M, int N, int K,
+             const float* __restrict__ scale, const GroupQuant gq, uint16_t* __restrict__ y, int M, int N, int K,
              long long ldy, uint32_t idesc256, uint32_t idesc128, const Sched sc, uint32_t flags,
              uint32_t* signal, uint32_t* arrive, int* status) {
+  // a raw stage holds 64 k of both channel blocks: 64 byte-rows of int8, 32 of packed int4
+  constexpr int kRawRows = (WBITS == 8) ? BK : BK / 2;
+  constexpr int kRawBlockW = kRawRows * BNW;
   extern __shared__ uint8_t smem_raw[];
   // An independent launch lets its successor start at once.  A dependent one does so only after
   // its own wait below: a successor that is itself flagged independent can then overlap this
@@ -454,9 +482,9 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
           const int ws = cnt & (kWStages - 1);
           if (!dev::mbar_wait(&wempty[ws], ((cnt / kWStages) & 1) ^ 1, status, 20)) { ok = false; break; }
           uint8_t* raw = smem + kRawBase + ws * kRawBytes;
-          dev::mbar_expect_tx(&wfull[ws], w.nh * kRawBlock);
+          dev::mbar_expect_tx(&wfull[ws], w.nh * kRawBlockW);
           for (int h = w.h0; h < w.h0 + w.nh; ++h)
-            dev::tma_load_2d(raw + h * kRawBlock, &wmap, &wfull[ws], (w.tn2 * 2 + h) * BNW, kb * BK);
+            dev::tma_load_2d(raw + h * kRawBlockW, &wmap, &wfull[ws], (w.tn2 * 2 + h) * BNW, kb * kRawRows);
         }
       }
     }
@@ -537,6 +565,81 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
         const int ws = cnt & (kWStages - 1);
         const int slot = cnt & 1, c0 = 2 * slot;  // the stage's two converted buffers
         const uint8_t* raw = smem + kRawBase + ws * kRawBytes;
+        if constexpr (WBITS == 4) {
+          // ---- packed int4: a lane owns 8 channels of each channel block; a byte-row of the raw
+          // tile (two k per byte) becomes two k-rows of the converted tile.  Scales and zero points
+          // of the stage's 128-k group are fetched before the wait for the weights.
+          const int grp_q = kb >> 1;
+          uint4 sv[2];
+          uint2 zv[2];
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            sv[hh] = make_uint4(0, 0, 0, 0);
+            zv[hh] = make_uint2(0, 0);
+            if (hh < w.nh) {
+              const long long n0 = static_cast<long long>(w.tn2 * 2 + w.h0 + hh) * BNW + piece * 8;
+              sv[hh] = __ldg(reinterpret_cast<const uint4*>(gq.scales + static_cast<long long>(grp_q) * N + n0));
+              if (gq.packed) zv[hh].x = __ldg(reinterpret_cast<const uint32_t*>(gq.zeros + (static_cast<long long>(grp_q) * N + n0) / 2));
+              else zv[hh] = __ldg(reinterpret_cast<const uint2*>(gq.zeros + static_cast<long long>(grp_q) * N + n0));
+            }
+          }
+          if (!dev::mbar_wait_warp(&wfull[ws], (cnt / kWStages) & 1, status, 26)) { ok = false; break; }
+          uint2 in[4];  // [sub-block][channel block]
+#pragma unroll
+          for (int p = 0; p < 4; ++p) {
+            const int sb = p >> 1, hh = p & 1;
+            const int brow = sb * (BKS / 2) + cw * 2 + rsub;  // byte-row 0..31 of the stage
+            in[p] = make_uint2(0, 0);
+            if (hh < w.nh)
+              in[p] = *reinterpret_cast<const uint2*>(raw + (w.h0 + hh) * kRawBlockW + brow * 128 +
+                                                      (((piece >> 1) ^ (brow & 7)) << 4) + ((piece & 1) << 3));
+          }
+          __syncwarp();
+          if (lane == 0) dev::mbar_arrive(&wempty[ws]);  // every raw byte of the stage is in registers
+          bool waited = false;
+#pragma unroll
+          for (int hh = 0; hh < 2; ++hh) {
+            if (hh >= w.nh) continue;
+            // 128 + z and s of the lane's four channel pairs
+            uint32_t zz[4], ss[4] = {sv[hh].x, sv[hh].y, sv[hh].z, sv[hh].w};
+            if (gq.packed) {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const uint32_t b = (zv[hh].x >> (8 * j)) & 0xFFu;  // channels 2j (low nibble), 2j+1 (high)
+                zz[j] = 0x43004300u | (b & 0xFu) | ((b >> 4) << 16);
+              }
+            } else {
+              zz[0] = __byte_perm(zv[hh].x, 0x43004300u, 0x7150);
+              zz[1] = __byte_perm(zv[hh].x, 0x43004300u, 0x7352);
+              zz[2] = __byte_perm(zv[hh].y, 0x43004300u, 0x7150);
+              zz[3] = __byte_perm(zv[hh].y, 0x43004300u, 0x7352);
+            }
+#pragma unroll
+            for (int sb = 0; sb < 2; ++sb) {
+              const uint2 v = in[sb * 2 + hh];
+              uint4 ev, od;
+              dequant4(__byte_perm(v.x, 0u, 0x4140), zz[0], ss[0], ev.x, od.x);
+              dequant4(__byte_perm(v.x, 0u, 0x4342), zz[1], ss[1], ev.y, od.y);
+              dequant4(__byte_perm(v.y, 0u, 0x4140), zz[2], ss[2], ev.z, od.z);
+              dequant4(__byte_perm(v.y, 0u, 0x4342), zz[3], ss[3], ev.w, od.w);
+              if (!waited) {
+                waited = true;
+                if (cnt >= 2) {  // the MMAs of the stage that used these buffers before must have retired
+                  const unsigned prev = cnt - 2;
+                  if (!dev::mbar_wait_warp(&consumed[prev % kConsumed], (prev / kConsumed) & 1, status, 27)) ok = false;
+                }
+              }
+              if (ok) {
+                uint8_t* cvt = smem + kCvtBase + (c0 + sb) * kCvtBytes + (w.h0 + hh) * kCvtBlock +
+                               (piece >> 3) * (BKS * 128);
+                const int r = 2 * (cw * 2 + rsub);  // k-row of the even k inside the 32-k sub-block
+                *reinterpret_cast<uint4*>(cvt + r * 128 + (((piece & 7) ^ (r & 7)) << 4)) = ev;
+                *reinterpret_cast<uint4*>(cvt + (r + 1) * 128 + (((piece & 7) ^ ((r + 1) & 7)) << 4)) = od;
+              }
+            }
+          }
+          if (!ok) break;
+        } else {
         if (!dev::mbar_wait_warp(&wfull[ws], (cnt / kWStages) & 1, status, 26)) { ok = false; break; }
         // tasks of this warp: per sub-block and channel block 16 row pairs, two per warp
         uint2 in[8];
@@ -546,7 +649,7 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
           const int r = ((p & 1) * kCvtWarps + cw) * 2 + rsub;  // row 0..31 of the sub-block
           const int krow = sb * BKS + r;
           if (hh < w.nh)
-            in[p] = *reinterpret_cast<const uint2*>(raw + (w.h0 + hh) * kRawBlock + krow * 128 +
+            in[p] = *reinterpret_cast<const uint2*>(raw + (w.h0 + hh) * kRawBlockW + krow * 128 +
                                                     (((piece >> 1) ^ (krow & 7)) << 4) + ((piece & 1) << 3));
         }
         // sub-block 0 is converted before the wait for its buffers, sub-block 1 after its stores
@@ -578,6 +681,7 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
             if (lane == 0) dev::mbar_arrive(&wempty[ws]);
           }
         }
+        }
         dev::fence_proxy_async();
         // the issuing threads wait only for this barrier: make sure the activations are there too
         if (!dev::mbar_wait_warp(&xfull[cnt % kXStages], (cnt / kXStages) & 1, status, 28)) { ok = false; break; }
@@ -593,7 +697,7 @@ w8a16_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ C
       for (int idx = esub; idx < w.nh * chunks; idx += kWorkerWarps / 4) {
         const int h = w.h0 + idx / chunks, ch = idx % chunks;
         const int n = (w.tn2 * 2 + h) * BNW + q * 32 + lane;  // this thread's output channel
-        const float scl = (n < N) ? __ldg(scale + n) : 0.f;
+        const float scl = (WBITS == 4) ? 1.f : ((n < N) ? __ldg(scale + n) : 0.f);
         uint32_t r[32];
         dev::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + h * BMX + ch * 32, r);
         dev::tc_wait_ld();
@@ -676,19 +780,23 @@ int i8gemm_tcgen05(const void* a, const void* b, int32_t* acc, const float* row_
   return QMM_OK;
 }
 
-int w8a16_tcgen05(const uint16_t* x, const int8_t* w, const float* scale, uint16_t* y, int64_t M,
-                  int64_t N, int64_t K, int64_t ldy, uint32_t flags, uint32_t* signal, uint32_t* arrive,
-                  cudaStream_t stream) {
+// Shared launch path of the weight-only GEMMs (int8 per-channel, int4 group-wise).
+template <int WBITS>
+static int launch_weight_only(const uint16_t* x, const void* w, const float* scale, const tc::w8::GroupQuant& gq,
+                              uint16_t* y, int64_t M, int64_t N, int64_t K, int64_t ldy, uint32_t flags,
+                              uint32_t* signal, uint32_t* arrive, cudaStream_t stream) {
   using namespace tc::w8;
   CUtensorMap wmap, xmap;
-  if (int rc = make_tensor_map_2d(&wmap, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)K,
-                                  (uint64_t)N, (uint64_t)N, BK, BNW, CU_TENSOR_MAP_SWIZZLE_128B))
+  constexpr int kRawRows = (WBITS == 8) ? BK : BK / 2;
+  if (int rc = make_tensor_map_2d(&wmap, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)(WBITS == 8 ? K : K / 2),
+                                  (uint64_t)N, (uint64_t)N, kRawRows, BNW, CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
   if (int rc = make_tensor_map_2d(&xmap, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (uint64_t)M,
                                   (uint64_t)K, (uint64_t)K * 2, BMX, BK, CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
-  static std::atomic<uint64_t> configured{0};  // per device
-  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(w8a16_kernel), kSmemBytes, configured)) return rc;
+  static std::atomic<uint64_t> configured{0};  // per device (one mask per template instance)
+  auto kern = w8a16_kernel<WBITS>;
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kern), kSmemBytes, configured)) return rc;
   // operand "a" of the MMA = weights (bf16, MN-major), "b" = activations (bf16, K-major)
   const uint32_t idesc256 = dev::make_idesc(/*c=f32*/ 1, /*bf16*/ 1, /*bf16*/ 1,
                                             /*a MN-major*/ 1, /*b K-major*/ 0, BNW, BMX);
@@ -723,10 +831,26 @@ int w8a16_tcgen05(const uint16_t* x, const int8_t* w, const float* scale, uint16
   // kernel ahead of it drains; they order themselves behind it inside the kernel (or not at all
   // when the caller states independence, which fills the last, partly idle round of one launch
   // with the first tiles of the next).
-  QMM_CUDA_TRY(launch_pdl(w8a16_kernel, dim3(grid), dim3(kThreads), kSmemBytes, stream, wmap, xmap, scale, y, (int)M,
+  QMM_CUDA_TRY(launch_pdl(kern, dim3(grid), dim3(kThreads), kSmemBytes, stream, wmap, xmap, scale, gq, y, (int)M,
                           (int)N, (int)K, (long long)ldy, idesc256, idesc128, sc, flags, signal, arrive,
                           device_status_word()));
   return QMM_OK;
+}
+
+int w8a16_tcgen05(const uint16_t* x, const int8_t* w, const float* scale, uint16_t* y, int64_t M,
+                  int64_t N, int64_t K, int64_t ldy, uint32_t flags, uint32_t* signal, uint32_t* arrive,
+                  cudaStream_t stream) {
+  const tc::w8::GroupQuant none = {nullptr, nullptr, 0};
+  return launch_weight_only<8>(x, w, scale, none, y, M, N, K, ldy, flags, signal, arrive, stream);
+}
+
+// int4 g128 weight-only GEMM for prefill-sized M: same pipeline, nibbles dequantised by the
+// converter warps.  Requires K % 128 == 0 and N % 128 == 0 (checked by the caller).
+int w4a16_tcgen05(const uint16_t* x, const uint8_t* wq, const uint16_t* scales, const uint8_t* zeros,
+                  int zeros_packed, uint16_t* y, int64_t M, int64_t N, int64_t K, uint32_t flags,
+                  cudaStream_t stream) {
+  const tc::w8::GroupQuant gq = {scales, zeros, zeros_packed};
+  return launch_weight_only<4>(x, wq, nullptr, gq, y, M, N, K, N, flags, nullptr, nullptr, stream);
 }
 
 }  // namespace qmm

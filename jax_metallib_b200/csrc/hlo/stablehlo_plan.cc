@@ -764,9 +764,11 @@ static int build_plan(Plan& plan) {
   for (auto& s : plan.steps)
     if (s.kind == kW4A16) {
       size_t w = qmm_w4a16_g128_workspace_bytes(s.M, s.N, s.K);
-      if (w == 0)
+      const bool prefill = s.M > 32 && s.N >= 128 && s.N % 128 == 0 && s.K >= 128 && s.K % 128 == 0;  // no scratch
+      if (w == 0 && !prefill)
         return set_error(QMM_ERR_UNSUPPORTED,
-                         "line %d: int4 matmul with M=%lld N=%lld K=%lld is outside the decode kernel's range",
+                         "line %d: int4 matmul with M=%lld N=%lld K=%lld is outside the kernels' range (N and K "
+                         "must be multiples of 128)",
                          s.anchor_line, (long long)s.M, (long long)s.N, (long long)s.K);
       if (w > plan.workspace) plan.workspace = w;
     }

@@ -40,8 +40,14 @@
 #include "common.cuh"
 
 namespace qmm {
+
+int w4a16_tcgen05(const uint16_t* x, const uint8_t* wq, const uint16_t* scales, const uint8_t* zeros,
+                  int zeros_packed, uint16_t* y, int64_t M, int64_t N, int64_t K, uint32_t flags,
+                  cudaStream_t stream);
+
 namespace w4 {
 
+constexpr int kDecodeMaxM = 32;      // rows the decode kernel covers; larger M goes to the tcgen05 GEMM
 constexpr int kColsPerBlock = 256;   // columns per unit: two 128-byte TMA boxes
 constexpr int kGroup = 128;          // k per unit
 constexpr int kRowsPerUnit = 64;     // packed byte-rows per unit
@@ -595,12 +601,12 @@ static int run(const char* name, const uint16_t* x, const uint8_t* wq, const uin
 
 static int check_args(const char* name, const void* x, const void* wq, const void* scales,
                       const void* zeros, const void* y, int64_t M, int64_t N, int64_t K,
-                      int64_t group) {
+                      int64_t group, int64_t max_m) {
   QMM_REQUIRE(x && wq && scales && zeros && y, QMM_ERR_INVALID_ARGUMENT, "%s: null tensor pointer", name);
   QMM_REQUIRE(group == kGroup, QMM_ERR_UNSUPPORTED, "%s: group must be 128, got %lld", name,
               (long long)group);
-  QMM_REQUIRE(M >= 1 && M <= 32, QMM_ERR_UNSUPPORTED, "%s: decode kernel covers 1 <= M <= 32, got %lld",
-              name, (long long)M);
+  QMM_REQUIRE(M >= 1 && M <= max_m, QMM_ERR_UNSUPPORTED, "%s: covers 1 <= M <= %lld, got %lld", name,
+              (long long)max_m, (long long)M);
   QMM_REQUIRE(N >= 128 && N % 128 == 0 && K >= kGroup && K % kGroup == 0, QMM_ERR_UNSUPPORTED,
               "%s: N (%lld) and K (%lld) must be positive multiples of 128", name, (long long)N,
               (long long)K);
@@ -653,7 +659,8 @@ extern "C" {
 
 size_t qmm_w4a16_g128_workspace_bytes(int64_t M, int64_t N, int64_t K) {
   using namespace qmm::w4;
-  if (M < 1 || M > 32 || N < 128 || K < kGroup || N % 128 || K % kGroup) return 0;
+  if (M < 1 || N < 128 || K < kGroup || N % 128 || K % kGroup) return 0;
+  if (M > kDecodeMaxM) return 0;  // the prefill GEMM needs no scratch
   const int G = static_cast<int>(K / kGroup);
   const int C = col_blocks(N);
   const int U = G * C;
@@ -670,7 +677,13 @@ int qmm_w4a16_g128(const uint16_t* x, const uint8_t* wq, const uint16_t* scales,
                    unsigned flags, void* stream) {
   using namespace qmm;
   using namespace qmm::w4;
-  if (int rc = check_args("qmm_w4a16_g128", x, wq, scales, zeros, y, M, N, K, group)) return rc;
+  if (int rc = check_args("qmm_w4a16_g128", x, wq, scales, zeros, y, M, N, K, group, (1ll << 30) - 1)) return rc;
+  if (M > kDecodeMaxM) {
+    // prefill-sized M: the tcgen05 GEMM with the nibbles dequantised in shared memory (no scratch)
+    if (int st = read_device_status())
+      return set_error(QMM_ERR_TIMEOUT, "a previous kernel gave up waiting (status word 0x%x)", st);
+    return w4a16_tcgen05(x, wq, scales, zeros, zeros_packed, y, M, N, K, 0u, static_cast<cudaStream_t>(stream));
+  }
   const size_t need = qmm_w4a16_g128_workspace_bytes(M, N, K);
   QMM_REQUIRE(workspace != nullptr && workspace_bytes >= need && aligned(workspace, 256),
               QMM_ERR_WORKSPACE, "qmm_w4a16_g128: workspace of %zu bytes (256-byte aligned) required",
@@ -699,7 +712,7 @@ int qmm_w4a16_g128_static_scratch(const uint16_t* x, const uint8_t* wq, const ui
                                   int64_t N, int64_t K, int64_t group, void* stream) {
   using namespace qmm;
   using namespace qmm::w4;
-  if (int rc = check_args("qmm_w4a16_g128_static_scratch", x, wq, scales, zeros, y, M, N, K, group))
+  if (int rc = check_args("qmm_w4a16_g128_static_scratch", x, wq, scales, zeros, y, M, N, K, group, kDecodeMaxM))
     return rc;
   const size_t need = qmm_w4a16_g128_workspace_bytes(M, N, K);
   QMM_REQUIRE(need > 0 && need <= kStaticScratchBytes, QMM_ERR_WORKSPACE,

@@ -141,9 +141,9 @@ _w4_workspaces: dict = {}
 def w4a16_g128(x: torch.Tensor, wq: torch.Tensor, scales: torch.Tensor, zeros: torch.Tensor, *,
                zeros_packed: bool = False, group: int = 128, out: torch.Tensor | None = None,
                workspace: torch.Tensor | None = None, static_weights: bool = False) -> torch.Tensor:
-    """int4 group-wise asymmetric weight-only matmul at decode sizes.
+    """int4 group-wise asymmetric weight-only matmul (decode kernel for M <= 32, tcgen05 GEMM above).
 
-    x bf16 ``[M,K]`` (M <= 32); wq uint8 ``[K/2,N]`` (low nibble = even k);
+    x bf16 ``[M,K]``; wq uint8 ``[K/2,N]`` (low nibble = even k);
     scales bf16 ``[K/group,N]``; zeros uint8 ``[K/group,N]`` or packed
     ``[K/group,N/2]``; returns bf16 ``[M,N]``.  ``static_weights=True`` tells
     the kernel that nothing queued earlier on the stream writes the weights,
@@ -162,15 +162,17 @@ def w4a16_g128(x: torch.Tensor, wq: torch.Tensor, scales: torch.Tensor, zeros: t
     if scales.shape != (G, N) or zeros.shape != ((G, N // 2) if zeros_packed else (G, N)):
         raise ValueError(f"scales/zeros shapes do not match: {tuple(scales.shape)}, {tuple(zeros.shape)}")
     lib = _lib.load()
-    need = lib.qmm_w4a16_g128_workspace_bytes(M, N, K)
-    if workspace is None:
+    need = lib.qmm_w4a16_g128_workspace_bytes(M, N, K)  # 0 for M > 32: the prefill GEMM needs no scratch
+    if workspace is None and need > 0:
         key = (x.device.index,)
         ws = _w4_workspaces.setdefault(key, W4Workspace(x.device))
         workspace = ws.get(need)
     if out is None:
         out = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
     _lib.check(lib.qmm_w4a16_g128(x.data_ptr(), wq.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
-                                  1 if zeros_packed else 0, out.data_ptr(), M, N, K, group, workspace.data_ptr(),
-                                  workspace.numel(), _lib.QMM_W4_STATIC_WEIGHTS if static_weights else 0,
+                                  1 if zeros_packed else 0, out.data_ptr(), M, N, K, group,
+                                  workspace.data_ptr() if workspace is not None else None,
+                                  workspace.numel() if workspace is not None else 0,
+                                  _lib.QMM_W4_STATIC_WEIGHTS if static_weights else 0,
                                   _stream_ptr()))
     return out

@@ -151,11 +151,62 @@ def test_w4a16_rejects_what_it_does_not_cover(cuda):
     x = dev(c["x_bits"].view(np.int16), cuda, torch.bfloat16)
     wq, s, z = dev(c["wq"], cuda), dev(c["s_bits"].view(np.int16), cuda, torch.bfloat16), dev(c["z"], cuda)
     with pytest.raises(_lib.QmmError) as e:
-        ops.w4a16_g128(x.repeat(40, 1), wq, s, z)
+        ops.w4a16_g128(x, wq, s, z, group=64)
     assert e.value.status_name == "QMM_ERR_UNSUPPORTED"
     with pytest.raises(_lib.QmmError) as e:
         ops.w4a16_g128(x, wq, s, z, workspace=torch.zeros(256, dtype=torch.uint8, device=cuda)[:16])
     assert e.value.status_name == "QMM_ERR_WORKSPACE"
+
+
+# ---------------------------------------------------------------- int4 g128 at prefill sizes (tcgen05)
+def _w4_prefill_check(cuda, M, K, N, packed, seed):
+    """Device-generated operands; sampled rows (four per 256-row tile) over all columns against the oracle."""
+    gen = synthetic.torch_generator(cuda, 3, seed)
+    G = K // 128
+    x = synthetic.device_normal((M, K), cuda, gen, torch.bfloat16)
+    wq = torch.randint(0, 256, (K // 2, N), dtype=torch.uint8, device=cuda, generator=gen)
+    sc = synthetic.device_uniform((G, N), 0.002, 0.01, cuda, gen, torch.bfloat16)
+    z = torch.randint(0, 16, (G, N), dtype=torch.uint8, device=cuda, generator=gen)
+    zarg = (z[:, 0::2] | (z[:, 1::2] << 4)).contiguous() if packed else z
+    y = ops.w4a16_g128(x, wq, sc, zarg, zeros_packed=packed)
+    torch.cuda.synchronize()
+    assert _lib.load().qmm_device_status() == 0
+    rows = np.array(sorted({min(M - 1, t * 256 + o) for t in range((M + 255) // 256) for o in (3, 100, 131, 250)}))
+    rows_t = torch.from_numpy(rows).to(cuda)
+    got = bf16_to_np(y[rows_t].contiguous())
+    xs = bf16_to_np(x[rows_t].contiguous())
+    wq_h, z_h = wq.cpu().numpy(), z.cpu().numpy()
+    s_h = bf16_to_np(sc)
+    ref = np.empty((len(rows), N), np.float32)
+    for c0 in range(0, N, 2048):
+        ref[:, c0:c0 + 2048] = O.w4a16_matmul(xs, wq_h[:, c0:c0 + 2048], s_h[:, c0:c0 + 2048], z_h[:, c0:c0 + 2048])
+    err = O.max_rel_err(got, ref)
+    assert err <= TOL_BF16, err
+    return err
+
+
+@pytest.mark.parametrize("M", [64, 512, 4096])
+def test_w4a16_prefill_full_shape(cuda, M):
+    _w4_prefill_check(cuda, M, 4096, 14336, packed=(M != 512), seed=M)
+
+
+@pytest.mark.parametrize("shape", [(33, 128, 128), (100, 256, 384), (257, 1024, 640), (300, 14336, 4096)])
+def test_w4a16_prefill_other_shapes(cuda, shape):
+    M, K, N = shape
+    _w4_prefill_check(cuda, M, K, N, packed=(M % 2 == 0), seed=M + K)
+
+
+def test_w4a16_prefill_agrees_with_the_decode_kernel_at_the_boundary(cuda):
+    # M = 32 runs the decode kernel, M = 33 the GEMM: the rows they share agree within the contract
+    gen = synthetic.torch_generator(cuda, 3, 99)
+    K, N = 1024, 512
+    x = synthetic.device_normal((33, K), cuda, gen, torch.bfloat16)
+    wq = torch.randint(0, 256, (K // 2, N), dtype=torch.uint8, device=cuda, generator=gen)
+    sc = synthetic.device_uniform((K // 128, N), 0.002, 0.01, cuda, gen, torch.bfloat16)
+    z = torch.randint(0, 16, (K // 128, N), dtype=torch.uint8, device=cuda, generator=gen)
+    a = ops.w4a16_g128(x[:32].contiguous(), wq, sc, z)
+    b = ops.w4a16_g128(x, wq, sc, z)
+    assert O.max_rel_err(bf16_to_np(b[:32].contiguous()), bf16_to_np(a)) <= TOL_BF16
 
 
 # ---------------------------------------------------------------- config 5 (one rank)

@@ -212,9 +212,15 @@ def test_execute_config2_and_config3_fixtures(client):
     ref = O.i8_dot_i32(c["a"], c["b"])
     np.testing.assert_array_equal(acc.to_numpy(), ref)
     assert O.max_rel_err(out.to_numpy(), O.i8_dot_rescale(ref, c["row"], c["col"])) <= 2e-3
-    only = client.compile(load("cfg2_i8dot_only.mlir"))
-    (acc2,), _ = only.execute(args[:2])
-    np.testing.assert_array_equal(acc2.to_numpy(), ref)
+    only = client.compile(load("cfg2_i8dot_only.mlir"))  # ui8 [256,512] x i8 [512,128]
+    assert only.arg_info(0) == (_lib.QMM_U8, (256, 512))
+    rng = np.random.default_rng(2)
+    a_u = rng.integers(0, 256, size=(256, 512)).astype(np.uint8)
+    b_s = rng.integers(-128, 128, size=(512, 128)).astype(np.int8)
+    (acc2,), _ = only.execute([client.buffer_from_host(a_u), client.buffer_from_host(b_s)])
+    np.testing.assert_array_equal(acc2.to_numpy(), O.i8_dot_i32(a_u, b_s))
+    with pytest.raises(_lib.QmmError):  # an argument of the wrong element type is refused
+        only.execute([client.buffer_from_host(a_u.view(np.int8)), client.buffer_from_host(b_s)])
 
     exe3 = client.compile(load("cfg3_w4a16.mlir"))
     c = synthetic.config3(4, 4096, 14336)
