@@ -335,19 +335,30 @@ QMM_API int qmm_bf16_matmul_small_m(const uint16_t* x, const uint16_t* w, uint16
  * it stands where the reference parses and plans a program
  * (src/pjrt_plugin/core/stablehlo_parser.mm:521-586,
  *  src/pjrt_plugin/core/mps_executable.mm:7627-9008; pattern fusions
- *  :1214-1326).  An op that is not part of a supported pattern makes
- * compilation fail with QMM_ERR_UNSUPPORTED and a message naming the op and
- * its line, as the reference reports unsupported ops
- * (src/pjrt_plugin/api/pjrt_client.cc:211-220); nothing is executed on the CPU.
- * qmm_plan_trace returns one JSON line per decision ("QMM_PLAN_JSON:{...}",
- * also written to stderr when QMM_TRACE_PLAN is set), the counterpart of the
- * reference's JAX_METALLIB_TRACE_PLAN output (mps_executable.mm:7925-7961).
+ *  :1214-1326).  Ops that no match absorbs run as standalone GPU kernels when
+ * they belong to the supported set (convert, multiply, subtract, add, and,
+ * shift_right_logical, broadcast_in_dim, reshape, transpose, slice,
+ * concatenate, constant, dot / dot_general without batch dimensions); any
+ * other op makes compilation fail with QMM_ERR_UNSUPPORTED and a message
+ * naming the op and its line, as the reference reports unsupported ops
+ * (src/pjrt_plugin/api/pjrt_client.cc:211-220).  Nothing is executed on the
+ * CPU.  Dense constants become extra arguments owned by the plan (device
+ * copies are made on the first execution on a device, which therefore
+ * allocates; do it outside a stream capture).
+ * qmm_plan_trace returns one JSON line per decision ("QMM_PLAN_JSON:{...}":
+ * "fused" with the kernel, "not_fused" with the op — and the reason for a dot
+ * that no pattern took —, "plan" with the step counts; also written to stderr
+ * when QMM_TRACE_PLAN is set), the counterpart of the reference's
+ * JAX_METALLIB_TRACE_PLAN output (mps_executable.mm:7925-7961).
  * qmm_plan_execute takes the device pointers of @main's arguments and results
- * in declaration order. */
+ * in declaration order and a 256-byte aligned workspace of
+ * qmm_plan_workspace_bytes (kernel scratch and the temporaries of unfused
+ * ops; its first use must find it zero-filled). */
 typedef struct qmm_plan qmm_plan;
 QMM_API int qmm_plan_compile(const char* stablehlo_text, size_t length, qmm_plan** plan);
 QMM_API void qmm_plan_destroy(qmm_plan* plan);
 QMM_API int qmm_plan_num_steps(const qmm_plan* plan);
+QMM_API int qmm_plan_num_fused_steps(const qmm_plan* plan); /* steps that are fused matmul kernels */
 QMM_API int qmm_plan_num_args(const qmm_plan* plan);
 QMM_API int qmm_plan_num_results(const qmm_plan* plan);
 QMM_API size_t qmm_plan_workspace_bytes(const qmm_plan* plan);

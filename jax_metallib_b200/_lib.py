@@ -61,6 +61,7 @@ SIGNATURES = {
     "qmm_plan_compile": (c_int, [c_char_p, c_size_t, ctypes.POINTER(c_void_p)]),
     "qmm_plan_destroy": (None, [c_void_p]),
     "qmm_plan_num_steps": (c_int, [c_void_p]),
+    "qmm_plan_num_fused_steps": (c_int, [c_void_p]),
     "qmm_plan_num_args": (c_int, [c_void_p]),
     "qmm_plan_num_results": (c_int, [c_void_p]),
     "qmm_plan_workspace_bytes": (c_size_t, [c_void_p]),

@@ -285,6 +285,14 @@ __device__ __forceinline__ void multimem_red_release_add_u32(uint32_t* mc_addr, 
 __device__ __forceinline__ void red_release_sys_add_u32(uint32_t* addr, uint32_t v) {
   asm volatile("red.release.sys.global.add.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
 }
+__device__ __forceinline__ uint32_t ld_acquire_gpu_u32(const uint32_t* addr) {
+  uint32_t v;
+  asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_gpu_u32(uint32_t* addr, uint32_t v) {
+  asm volatile("st.release.gpu.global.u32 [%0], %1;" ::"l"(addr), "r"(v) : "memory");
+}
 __device__ __forceinline__ uint32_t ld_acquire_sys_u32(const uint32_t* addr) {
   uint32_t v;
   asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(addr) : "memory");

@@ -11,21 +11,32 @@
 //   P1  x @ (convert(W:i8) * broadcast(scale))            -> qmm_w8a32 / qmm_w8a16
 //   P2  dot_general(A:i8, B:i8):i32 [-> convert * row * col] -> qmm_i8i8_i32
 //   P3  x @ reshape((convert(unpack4(Wq)) - bcast(z)) * bcast(s)) -> qmm_w4a16_g128
-// Each match becomes one kernel launch.  Anything left over is a compile error
-// that names the op (the reference's convention, api/pjrt_client.cc:211-220):
-// there is no fallback executor.  Every decision is recorded as a JSON line
-// (`QMM_PLAN_JSON:`), like the reference's JAX_METALLIB_TRACE_PLAN output, so
-// tests can assert that a chain was fused.
+// Each match becomes one kernel launch.  Ops that no match absorbs run as
+// standalone GPU kernels (generic_ops.cu) if they belong to the small supported
+// set (convert, multiply, subtract, add, and, shift_right_logical,
+// broadcast_in_dim, reshape, transpose, slice, concatenate, constant, plain
+// dot / dot_general), so that a dequantisation chain spelled in a way the
+// matcher does not know still computes correctly, op by op; anything else is a
+// compile error that names the op (the reference's convention,
+// api/pjrt_client.cc:211-220).  Nothing ever runs on the CPU.  Dense constants
+// (weights closed over by the jitted function) are lifted into extra arguments
+// that the plan owns.  Every decision is recorded as a JSON line
+// (`QMM_PLAN_JSON:`: "fused" with the kernel, "not_fused" with the op and, for a
+// dot, the reason), like the reference's JAX_METALLIB_TRACE_PLAN output, so
+// tests can assert that a chain was fused and fail on one that was not.
 #include <stdarg.h>
 #include <stdlib.h>
 #include <string.h>
 
+#include <algorithm>
 #include <map>
+#include <mutex>
 #include <set>
 #include <string>
 #include <vector>
 
 #include "../common.cuh"
+#include "../generic_ops.h"
 
 namespace qmm {
 namespace hlo {
@@ -56,6 +67,8 @@ struct Module {
   std::vector<std::string> returns;
   std::map<std::string, int> def;   // SSA name -> op index
   std::map<std::string, int> argi;  // SSA name -> argument index
+  int num_real_args = 0;            // arguments of @main; dense constants follow them as extra arguments
+  std::vector<std::vector<uint8_t>> const_data;  // contents of the lifted constants, in argument order
   std::string name = "main";        // module symbol (jit_<function> in what jax prints)
   int num_replicas = 1, num_partitions = 1;  // mhlo.num_replicas / mhlo.num_partitions of the module
   std::string error;
@@ -147,6 +160,82 @@ static std::vector<int64_t> int_list_after(const std::string& s, const std::stri
   return v;
 }
 
+static int dtype_of_elem_early(const std::string& e) {
+  if (e == "f32") return QMM_F32;
+  if (e == "f16") return QMM_F16;
+  if (e == "bf16") return QMM_BF16;
+  if (e == "i8" || e == "si8") return QMM_S8;
+  if (e == "ui8") return QMM_U8;
+  if (e == "i32" || e == "si32") return QMM_S32;
+  if (e == "ui4") return QMM_U4;
+  if (e == "ui32") return QMM_U32;
+  return -1;
+}
+
+static void append_scalar(std::vector<uint8_t>& out, int dtype, double v) {
+  auto put = [&](const void* p, size_t n) { out.insert(out.end(), (const uint8_t*)p, (const uint8_t*)p + n); };
+  switch (dtype) {
+    case QMM_F32: { float f = (float)v; put(&f, 4); break; }
+    case QMM_BF16: {
+      float f = (float)v;
+      uint32_t u;
+      memcpy(&u, &f, 4);
+      uint32_t r = (u + 0x7FFFu + ((u >> 16) & 1u)) >> 16;  // round to nearest even (finite values)
+      if ((u & 0x7FFFFFFFu) > 0x7F800000u) r = ((u >> 16) & 0x8000u) | 0x7FC0u;
+      uint16_t h = (uint16_t)r;
+      put(&h, 2);
+      break;
+    }
+    case QMM_S8: { int8_t x = (int8_t)(long long)v; put(&x, 1); break; }
+    case QMM_U8: { uint8_t x = (uint8_t)(long long)v; put(&x, 1); break; }
+    case QMM_S32: { int32_t x = (int32_t)(long long)v; put(&x, 4); break; }
+    case QMM_U32: { uint32_t x = (uint32_t)(long long)v; put(&x, 4); break; }
+    default: break;
+  }
+}
+
+// The value of a stablehlo.constant: "dense<...>".  Returns 0 = splat (one value), 1 = dense
+// (bytes filled, element count checked), -1 = not readable.
+static int parse_dense(const std::string& body, const TType& t, std::vector<uint8_t>& bytes, std::string& err) {
+  size_t a = body.find("dense<");
+  if (a == std::string::npos) { err = "constant without a dense<...> value"; return -1; }
+  size_t b = body.rfind('>');
+  if (b == std::string::npos || b <= a + 6) { err = "malformed dense<...>"; return -1; }
+  std::string val = trim(body.substr(a + 6, b - a - 6));
+  if (val.empty()) { err = "empty dense<...>"; return -1; }
+  const int dt = dtype_of_elem_early(t.elem);
+  const int64_t count = t.count();
+  if (val[0] == '"') {  // dense<"0x...">: the raw bytes of the tensor
+    if (val.size() < 4 || val[1] != '0' || (val[2] != 'x' && val[2] != 'X') || val.back() != '"') {
+      err = "unreadable hexadecimal constant";
+      return -1;
+    }
+    const std::string hex = val.substr(3, val.size() - 4);
+    if (hex.size() % 2) { err = "odd number of hexadecimal digits"; return -1; }
+    for (size_t i = 0; i < hex.size(); i += 2) bytes.push_back((uint8_t)strtoul(hex.substr(i, 2).c_str(), nullptr, 16));
+    const size_t bits = gen::dtype_bits(dt);
+    if (dt < 0 || bytes.size() != (size_t)count * bits / 8) { err = "hexadecimal constant of the wrong size"; return -1; }
+    return 1;
+  }
+  if (val[0] != '[') return 0;  // a splat: is_splat_const and the fill step read it from the body
+  if (dt < 0 || dt == QMM_U4 || dt == QMM_F16) { err = "dense constant of element type " + t.elem + " is not supported"; return -1; }
+  int64_t n = 0;
+  for (size_t i = 0; i < val.size();) {
+    const char c = val[i];
+    if (c == '[' || c == ']' || c == ',' || c == ' ') { ++i; continue; }
+    if (val.compare(i, 4, "true") == 0) { append_scalar(bytes, dt, 1); i += 4; ++n; continue; }
+    if (val.compare(i, 5, "false") == 0) { append_scalar(bytes, dt, 0); i += 5; ++n; continue; }
+    char* end = nullptr;
+    const double v = strtod(val.c_str() + i, &end);
+    if (end == val.c_str() + i) { err = "unreadable number in dense constant"; return -1; }
+    append_scalar(bytes, dt, v);
+    i = end - val.c_str();
+    ++n;
+  }
+  if (n != count) { err = "dense constant has " + std::to_string(n) + " values, its type " + std::to_string(count); return -1; }
+  return 1;
+}
+
 static bool parse_module(const char* text, size_t len, Module& m) {
   std::string all(text, len);
   std::vector<std::string> lines;
@@ -216,6 +305,7 @@ static bool parse_module(const char* text, size_t len, Module& m) {
         m.arg_names.push_back(name);
         m.arg_types.push_back(t);
       }
+      m.num_real_args = static_cast<int>(m.arg_names.size());
       continue;
     }
     if (!in_main) continue;
@@ -288,6 +378,24 @@ static bool parse_module(const char* text, size_t len, Module& m) {
       m.error = "line " + std::to_string(lineno) + ": cannot read result type of " + op.name;
       return false;
     }
+    if (op.name == "stablehlo.constant") {
+      std::vector<uint8_t> bytes;
+      std::string err;
+      const int kind = parse_dense(op.body, op.out_type, bytes, err);
+      if (kind < 0) {
+        m.error = "line " + std::to_string(lineno) + ": " + err;
+        return false;
+      }
+      if (kind == 1) {
+        // a dense constant (a weight closed over by the function): treated from here on as one
+        // more argument of @main whose buffer the plan owns
+        m.argi[op.result] = static_cast<int>(m.arg_names.size());
+        m.arg_names.push_back(op.result);
+        m.arg_types.push_back(op.out_type);
+        m.const_data.push_back(std::move(bytes));
+        continue;
+      }
+    }
     m.def[op.result] = static_cast<int>(m.ops.size());
     m.ops.push_back(op);
   }
@@ -301,23 +409,43 @@ static bool parse_module(const char* text, size_t len, Module& m) {
 // ---------------------------------------------------------------------------
 // plan
 // ---------------------------------------------------------------------------
-enum StepKind { kW8A32 = 0, kW8A16 = 1, kI8Dot = 2, kW4A16 = 3 };
+enum StepKind { kW8A32 = 0, kW8A16 = 1, kI8Dot = 2, kW4A16 = 3, kGeneric = 4 };
+enum GenericOp { gConvert = 0, gBinary, gGather, gConcat, gFill, gDot, gCopy };
 
+// Operands and results of a step are value slots: [0, A) the arguments of @main (lifted constants
+// included), [A, A + R) its results, above that temporaries inside the plan's workspace.
 struct Step {
   StepKind kind;
   int64_t M = 0, N = 0, K = 0;
-  int x = -1, w = -1, scale = -1, zeros = -1, row = -1, col = -1;  // argument indices
-  int out = -1, acc_out = -1;                                       // result indices (-1 = not returned)
+  int x = -1, w = -1, scale = -1, zeros = -1, row = -1, col = -1;
+  int out = -1, acc_out = -1;  // -1 = not produced
   int a_unsigned = 0, b_unsigned = 0, zeros_packed = 0;
   int anchor_line = 0;
+  int anchor_op = 0;  // index of the op the step stands for (steps run in this order)
   int fused_ops = 0;
+  // standalone ops
+  int gop = 0, bop = 0, in_dt = 0, out_dt = 0, b_transposed = 0;
+  std::vector<int> ins;
+  long long count = 0;
+  std::vector<long long> in_dims, out_dims, src_of, start, stride;  // gather
+  long long outer = 1, inner = 1, out_len = 0;                        // concatenate
+  std::vector<long long> part_len;
+  double fval = 0;
+  long long ival = 0;
+  size_t bytes = 0;  // copy
 };
 
 struct Plan {
   Module mod;
   std::vector<Step> steps;
   std::string trace;  // JSON lines
-  size_t workspace = 0;
+  size_t scratch = 0;    // kernel scratch (the int4 decode kernel's), at the start of the workspace
+  size_t workspace = 0;  // scratch + temporaries
+  std::map<std::string, int> slot;     // SSA value -> slot
+  std::vector<size_t> temp_offset;     // per temporary, from the start of the workspace
+  // device copies of the lifted constants, per device ordinal (created on first execution there)
+  std::mutex mu;
+  std::map<int, std::vector<void*>> const_dev;
 };
 
 // A value seen as "argument A with its dimensions placed on some dimensions of
@@ -484,15 +612,43 @@ static bool match_unpack4(const Module& m, const std::string& v, int* warg, std:
 
 static int build_plan(Plan& plan) {
   Module& m = plan.mod;
-  std::set<int> consumed;  // ops absorbed into a step
+  const int A = (int)m.arg_names.size(), R = (int)m.returns.size();
+  std::set<int> consumed;  // ops absorbed into a fused step
   // users of every value, to make sure absorbed intermediates do not escape
   std::map<std::string, std::vector<int>> users;
   for (size_t i = 0; i < m.ops.size(); ++i)
     for (auto& o : m.ops[i].operands) users[o].push_back((int)i);
 
-  for (size_t di = 0; di < m.ops.size(); ++di) {
+  // slot of a value: argument, result (its first position in the return list) or a new temporary
+  auto type_of = [&](const std::string& v) -> const TType* {
+    auto a = m.argi.find(v);
+    if (a != m.argi.end()) return &m.arg_types[a->second];
+    auto d = m.def.find(v);
+    return d == m.def.end() ? nullptr : &m.ops[d->second].out_type;
+  };
+  std::vector<size_t> temp_bytes;
+  auto slot_of = [&](const std::string& v) -> int {
+    auto it = plan.slot.find(v);
+    if (it != plan.slot.end()) return it->second;
+    int sl;
+    auto a = m.argi.find(v);
+    const int r = result_index(m, v);
+    if (a != m.argi.end()) sl = a->second;
+    else if (r >= 0) sl = A + r;
+    else {
+      const TType* t = type_of(v);
+      const size_t bits = t ? gen::dtype_bits(dtype_of_elem_early(t->elem)) : 0;
+      sl = A + R + (int)temp_bytes.size();
+      temp_bytes.push_back(t ? ((size_t)t->count() * bits / 8 + 255) / 256 * 256 : 0);
+    }
+    plan.slot[v] = sl;
+    return sl;
+  };
+
+  // ---- one dot: try the fused patterns.  QMM_ERR_UNSUPPORTED = "not a pattern this backend fuses"
+  // (the dot then runs unfused); any other error is final.
+  auto match = [&](size_t di, Step& st, std::vector<int>& used) -> int {
     const Op& dot = m.ops[di];
-    if (dot.name != "stablehlo.dot_general" && dot.name != "stablehlo.dot") continue;
     if (dot.operands.size() != 2 || dot.in_types.size() != 2)
       return set_error(QMM_ERR_PARSE, "line %d: malformed %s", dot.line, dot.name.c_str());
     const TType &lt = dot.in_types[0], &rt = dot.in_types[1], &ot = dot.out_type;
@@ -522,10 +678,9 @@ static int build_plan(Plan& plan) {
     for (size_t i = 0; i + 1 < lt.dims.size(); ++i) M *= lt.dims[i];
     if (lt.dims.back() != K)
       return set_error(QMM_ERR_PARSE, "line %d: contracting sizes differ", dot.line);
-    Step st;
     st.M = M; st.N = N; st.K = K;
     st.anchor_line = dot.line;
-    std::vector<int> used;
+    st.anchor_op = (int)di;
     used.push_back((int)di);
 
     auto lhs_arg = m.argi.find(dot.operands[0]);
@@ -542,7 +697,6 @@ static int build_plan(Plan& plan) {
       st.w = rhs_arg->second;
       st.a_unsigned = lt.elem == "ui8";
       st.b_unsigned = rt.elem == "ui8";
-      st.acc_out = result_index(m, dot.result);
       // optional rescale chain: convert -> multiply(row) -> multiply(col), either order
       std::string cur = dot.result;
       int got_row = -1, got_col = -1;
@@ -581,19 +735,25 @@ static int build_plan(Plan& plan) {
         // only by f32 rounding of one product and is accepted as the same fused step
         st.row = got_row;
         st.col = got_col;
-        st.out = result_index(m, last);
+        st.out = slot_of(last);
         for (int o : chain) used.push_back(o);
       }
-      if (st.acc_out < 0 && st.out < 0)
-        return set_error(QMM_ERR_UNSUPPORTED, "line %d: the integer dot's result is not returned", dot.line);
-    } else if (is_float(lt.elem) && lhs_arg != m.argi.end()) {
-      st.x = lhs_arg->second;
+      {
+        // the int32 accumulator itself is needed when it is returned or read by an op outside the chain
+        std::set<int> in_chain(used.begin(), used.end());
+        bool need_acc = result_index(m, dot.result) >= 0 || st.out < 0;
+        for (int u : users[dot.result])
+          if (!in_chain.count(u)) need_acc = true;
+        if (need_acc) st.acc_out = slot_of(dot.result);
+      }
+    } else if (is_float(lt.elem)) {
+      st.x = slot_of(dot.operands[0]);
       // rhs chain
       int ri;
       const Op* r = def_of(m, dot.operands[1], &ri);
       if (!r)
         return set_error(QMM_ERR_UNSUPPORTED,
-                         "line %d: dot_general on plain float arguments is not on the quantized-matmul path",
+                         "line %d: plain float dot_general (no dequantisation chain feeds it)",
                          dot.line);
       const Op* top = r;
       if (top->name == "stablehlo.reshape" && top->in_types[0].dims.size() == 3) {
@@ -674,7 +834,7 @@ static int build_plan(Plan& plan) {
         st.scale = sv.arg;
         st.zeros = zv.arg;
         st.zeros_packed = zt.elem == "ui4";  // 4-bit buffers hold two values per byte, low nibble first
-        st.out = result_index(m, dot.result);
+        st.out = slot_of(dot.result);
       } else if (top->name == "stablehlo.multiply") {
         // ---- P1: convert(W:i8) * broadcast(scale) ----
         used.push_back(ri);
@@ -702,45 +862,83 @@ static int build_plan(Plan& plan) {
         if (st_t.elem != "f32" || st_t.dims.size() != 1 || st_t.dims[0] != N)
           return set_error(QMM_ERR_UNSUPPORTED, "line %d: the per-channel scale must be an f32 [N] argument",
                            top->line);
+        std::string outv = dot.result;
         if (lt.elem == "f32" && ot.elem == "f32") st.kind = kW8A32;
         else if (lt.elem == "bf16" && ot.elem == "bf16") st.kind = kW8A16;
-        else
+        else if (lt.elem == "bf16" && ot.elem == "f32" && users[dot.result].size() == 1 &&
+                 result_index(m, dot.result) < 0 && m.ops[users[dot.result][0]].name == "stablehlo.convert" &&
+                 m.ops[users[dot.result][0]].out_type.elem == "bf16") {
+          // bf16 operands, f32 result (preferred_element_type) rounded to bf16 by a convert: the
+          // kernel accumulates in f32 and rounds once, which is exactly this
+          st.kind = kW8A16;
+          used.push_back(users[dot.result][0]);
+          outv = m.ops[users[dot.result][0]].result;
+        } else
           return set_error(QMM_ERR_UNSUPPORTED, "line %d: %s activations with %s result are not covered",
                            dot.line, lt.elem.c_str(), ot.elem.c_str());
         st.w = warg;
         st.scale = sv.arg;
-        st.out = result_index(m, dot.result);
+        st.out = slot_of(outv);
       } else {
         return set_error(QMM_ERR_UNSUPPORTED,
                          "line %d: the rhs of the dot on line %d is produced by %s, which is not a dequantisation "
                          "chain this backend fuses", top->line, dot.line, top->name.c_str());
-      }
-      if (st.out < 0) {
-        auto u = users.find(dot.result);
-        if (u != users.end() && !u->second.empty())
-          return set_error(QMM_ERR_UNSUPPORTED,
-                           "line %d: %s consumes the result of the dot on line %d; ops after the matmul are not "
-                           "executed by this backend", m.ops[u->second[0]].line,
-                           m.ops[u->second[0]].name.c_str(), dot.line);
-        return set_error(QMM_ERR_UNSUPPORTED, "line %d: the dot's result must be a result of @main", dot.line);
       }
     } else {
       return set_error(QMM_ERR_UNSUPPORTED,
                        "line %d: dot_general with %s x %s operands is not on the quantized-matmul path", dot.line,
                        lt.elem.c_str(), rt.elem.c_str());
     }
-    // absorbed intermediates must not be used elsewhere
+    return QMM_OK;
+  };
+
+  for (size_t di = 0; di < m.ops.size(); ++di) {
+    const Op& dot = m.ops[di];
+    if (dot.name != "stablehlo.dot_general" && dot.name != "stablehlo.dot") continue;
+    Step st;
+    std::vector<int> used;
+    const std::map<std::string, int> slots_before = plan.slot;
+    const size_t temps_before = temp_bytes.size();
+    int rc = match(di, st, used);
     std::set<int> mine(used.begin(), used.end());
-    for (int o : mine) {
-      if (m.ops[o].name == "stablehlo.constant") continue;
-      const std::string& res = m.ops[o].result;
-      bool is_out = (o == (int)di) || result_index(m, res) >= 0;
-      for (int u : users[res])
-        if (!mine.count(u) && !is_out)
-          return set_error(QMM_ERR_UNSUPPORTED,
-                           "line %d: %s is fused into the dot on line %d but its value is also used on line %d",
-                           m.ops[o].line, m.ops[o].name.c_str(), dot.line, m.ops[u].line);
+    if (rc == QMM_OK) {
+      // absorbed intermediates must not be used elsewhere
+      for (int o : mine) {
+        if (m.ops[o].name == "stablehlo.constant") continue;
+        const std::string& res = m.ops[o].result;
+        const bool is_out = (st.out >= 0 && plan.slot.count(res) && plan.slot[res] == st.out) ||
+                            (st.acc_out >= 0 && plan.slot.count(res) && plan.slot[res] == st.acc_out);
+        if (is_out) continue;
+        bool escapes = result_index(m, res) >= 0;
+        for (int u : users[res])
+          if (!mine.count(u)) escapes = true;
+        if (escapes) {
+          rc = set_error(QMM_ERR_UNSUPPORTED, "line %d: %s would be fused into the dot on line %d but its value is "
+                         "also used elsewhere", m.ops[o].line, m.ops[o].name.c_str(), dot.line);
+          break;
+        }
+      }
     }
+    if (rc == QMM_OK) {
+      // an op claimed by an earlier fused step cannot be shared
+      for (int o : mine)
+        if (consumed.count(o) && m.ops[o].name != "stablehlo.constant")
+          rc = set_error(QMM_ERR_UNSUPPORTED, "line %d: %s already belongs to another fused matmul", m.ops[o].line,
+                         m.ops[o].name.c_str());
+    }
+    if (rc == QMM_ERR_UNSUPPORTED) {
+      // not fused: forget the slots the attempt created; the dot and its chain run op by op
+      plan.slot = slots_before;
+      temp_bytes.resize(temps_before);
+      char why[512];
+      qmm_last_error(why, sizeof(why));
+      std::string reason;
+      for (const char* c = why; *c; ++c) reason += (*c == '"' || *c == '\\') ? '\'' : *c;
+      tracef(plan.trace, "{\"event\":\"not_fused\",\"line\":%d,\"op\":\"%s\",\"reason\":\"%s\"}", dot.line,
+             dot.name.c_str(), reason.c_str());
+      continue;
+    }
+    if (rc != QMM_OK) return rc;
     st.fused_ops = (int)mine.size();
     for (int o : mine) consumed.insert(o);
     static const char* kind_name[] = {"qmm_w8a32_perchannel", "qmm_w8a16_perchannel", "qmm_i8i8_i32",
@@ -748,19 +946,226 @@ static int build_plan(Plan& plan) {
     tracef(plan.trace,
            "{\"event\":\"fused\",\"anchor_line\":%d,\"kernel\":\"%s\",\"M\":%lld,\"N\":%lld,\"K\":%lld,"
            "\"ops_fused\":%d,\"rescale\":%s}",
-           dot.line, kind_name[st.kind], (long long)M, (long long)N, (long long)K, st.fused_ops,
+           dot.line, kind_name[st.kind], (long long)st.M, (long long)st.N, (long long)st.K, st.fused_ops,
            (st.kind == kI8Dot && st.out >= 0) ? "true" : "false");
     plan.steps.push_back(st);
   }
+
+  // ---- everything the fused steps did not absorb: one standalone kernel per op
+  int fused_count = (int)plan.steps.size();
   for (size_t i = 0; i < m.ops.size(); ++i) {
     if (consumed.count((int)i)) continue;
-    tracef(plan.trace, "{\"event\":\"not_fused\",\"line\":%d,\"op\":\"%s\"}", m.ops[i].line, m.ops[i].name.c_str());
-    return set_error(QMM_ERR_UNSUPPORTED,
-                     "line %d: %s is not part of a quantized-matmul pattern this backend executes "
-                     "(supported: int8/int4 dequantisation chains feeding dot_general, int8 dot_general)",
-                     m.ops[i].line, m.ops[i].name.c_str());
+    const Op& op = m.ops[i];
+    // a splat constant that only fused steps looked at needs no buffer
+    if (op.name == "stablehlo.constant") {
+      bool needed = result_index(m, op.result) >= 0;
+      for (int u : users[op.result])
+        if (!consumed.count(u)) needed = true;
+      if (!needed) continue;
+    }
+    Step st;
+    st.kind = kGeneric;
+    st.anchor_line = op.line;
+    st.anchor_op = (int)i;
+    const TType& ot = op.out_type;
+    st.out_dt = dtype_of_elem_early(ot.elem);
+    if (st.out_dt < 0)
+      return set_error(QMM_ERR_UNSUPPORTED, "line %d: %s produces element type %s, which this backend has no buffers for",
+                       op.line, op.name.c_str(), ot.elem.c_str());
+    st.count = ot.count();
+    for (auto& v : op.operands) {
+      if (!type_of(v)) return set_error(QMM_ERR_PARSE, "line %d: %s reads the undefined value %s", op.line, op.name.c_str(), v.c_str());
+      st.ins.push_back(slot_of(v));
+    }
+    st.in_dt = op.in_types.empty() ? st.out_dt : dtype_of_elem_early(op.in_types[0].elem);
+    if (st.in_dt < 0)
+      return set_error(QMM_ERR_UNSUPPORTED, "line %d: %s reads element type %s, which this backend has no buffers for",
+                       op.line, op.name.c_str(), op.in_types[0].elem.c_str());
+    st.out = slot_of(op.result);
+    const std::string& n = op.name;
+    auto need_operands = [&](size_t k) { return op.operands.size() == k && op.in_types.size() >= k; };
+    if (n == "stablehlo.convert" && need_operands(1)) {
+      st.gop = gConvert;
+    } else if ((n == "stablehlo.multiply" || n == "stablehlo.subtract" || n == "stablehlo.add" || n == "stablehlo.and" ||
+                n == "stablehlo.shift_right_logical") && need_operands(2)) {
+      st.gop = gBinary;
+      st.bop = n == "stablehlo.multiply" ? gen::kMul : n == "stablehlo.subtract" ? gen::kSub
+               : n == "stablehlo.add" ? gen::kAdd : n == "stablehlo.and" ? gen::kAnd : gen::kShrLogical;
+      if (op.in_types[0].count() != st.count || op.in_types[1].count() != st.count)
+        return set_error(QMM_ERR_UNSUPPORTED, "line %d: %s with operands of different shapes", op.line, n.c_str());
+    } else if (n == "stablehlo.reshape" && need_operands(1)) {
+      st.gop = gCopy;  // row-major data does not move
+      st.bytes = (size_t)st.count * gen::dtype_bits(st.out_dt) / 8;
+    } else if ((n == "stablehlo.broadcast_in_dim" || n == "stablehlo.transpose" || n == "stablehlo.slice") &&
+               need_operands(1)) {
+      st.gop = gGather;
+      const TType& it = op.in_types[0];
+      if (it.dims.size() > (size_t)gen::kMaxRank || ot.dims.size() > (size_t)gen::kMaxRank)
+        return set_error(QMM_ERR_UNSUPPORTED, "line %d: %s on tensors of rank > %d", op.line, n.c_str(), gen::kMaxRank);
+      st.in_dims.assign(it.dims.begin(), it.dims.end());
+      st.out_dims.assign(ot.dims.begin(), ot.dims.end());
+      st.start.assign(it.dims.size(), 0);
+      st.stride.assign(it.dims.size(), 1);
+      st.src_of.assign(it.dims.size(), 0);
+      if (n == "stablehlo.broadcast_in_dim") {
+        std::vector<int64_t> dims = int_list_after(op.body, "dims");
+        if (dims.size() != it.dims.size()) return set_error(QMM_ERR_PARSE, "line %d: malformed broadcast_in_dim", op.line);
+        for (size_t k = 0; k < dims.size(); ++k) {
+          if (dims[k] < 0 || dims[k] >= (int64_t)ot.dims.size() || (it.dims[k] != 1 && it.dims[k] != ot.dims[dims[k]]))
+            return set_error(QMM_ERR_PARSE, "line %d: broadcast_in_dim dimensions do not fit", op.line);
+          st.src_of[k] = dims[k];
+        }
+      } else if (n == "stablehlo.transpose") {
+        std::vector<int64_t> perm = int_list_after(op.body, "dims");
+        if (perm.empty()) perm = int_list_after(op.body, "permutation");
+        if (perm.size() != it.dims.size()) return set_error(QMM_ERR_PARSE, "line %d: malformed transpose", op.line);
+        for (size_t o = 0; o < perm.size(); ++o) {  // result dimension o is operand dimension perm[o]
+          if (perm[o] < 0 || perm[o] >= (int64_t)it.dims.size() || it.dims[perm[o]] != ot.dims[o])
+            return set_error(QMM_ERR_PARSE, "line %d: transpose permutation does not fit", op.line);
+          st.src_of[perm[o]] = (long long)o;
+        }
+        // a size-1 operand dimension reads coordinate 0, which is the only one it has
+      } else {
+        // slice: "[0:4, 2:10:2]" in the pretty form, start_indices / limit_indices / strides otherwise
+        std::vector<int64_t> start = int_list_after(op.body, "start_indices"), stride = int_list_after(op.body, "strides");
+        if (start.empty()) {
+          size_t a = op.body.find('['), b = op.body.find(']');
+          if (a == std::string::npos || b == std::string::npos)
+            return set_error(QMM_ERR_PARSE, "line %d: malformed slice", op.line);
+          for (auto& part : split_top(op.body.substr(a + 1, b - a - 1))) {
+            std::vector<long long> f;
+            size_t p0 = 0;
+            while (true) {
+              size_t c = part.find(':', p0);
+              f.push_back(atoll(part.substr(p0, c == std::string::npos ? std::string::npos : c - p0).c_str()));
+              if (c == std::string::npos) break;
+              p0 = c + 1;
+            }
+            start.push_back(f[0]);
+            stride.push_back(f.size() > 2 ? f[2] : 1);
+          }
+        }
+        if (stride.empty()) stride.assign(start.size(), 1);
+        if (start.size() != it.dims.size() || stride.size() != it.dims.size() || ot.dims.size() != it.dims.size())
+          return set_error(QMM_ERR_PARSE, "line %d: malformed slice", op.line);
+        for (size_t k = 0; k < start.size(); ++k) {
+          if (start[k] < 0 || stride[k] < 1 || (ot.dims[k] > 0 && start[k] + (ot.dims[k] - 1) * stride[k] >= it.dims[k]))
+            return set_error(QMM_ERR_PARSE, "line %d: slice out of range", op.line);
+          st.src_of[k] = (long long)k;
+          st.start[k] = start[k];
+          st.stride[k] = stride[k];
+        }
+        // the gather kernel reads coordinate 0 of size-1 operand dimensions: give those their start
+        for (size_t k = 0; k < start.size(); ++k)
+          if (it.dims[k] == 1 && start[k] != 0) return set_error(QMM_ERR_PARSE, "line %d: slice out of range", op.line);
+      }
+    } else if (n == "stablehlo.concatenate" && !op.operands.empty() && op.in_types.size() == op.operands.size()) {
+      st.gop = gConcat;
+      size_t p0 = op.body.find("dim");
+      size_t e0 = p0 == std::string::npos ? std::string::npos : op.body.find('=', p0);
+      if (e0 == std::string::npos) return set_error(QMM_ERR_PARSE, "line %d: concatenate without a dimension", op.line);
+      const long long dim = atoll(op.body.c_str() + e0 + 1);
+      if (dim < 0 || dim >= (long long)ot.dims.size()) return set_error(QMM_ERR_PARSE, "line %d: bad concatenate dimension", op.line);
+      st.outer = st.inner = 1;
+      for (long long k = 0; k < dim; ++k) st.outer *= ot.dims[k];
+      for (size_t k = dim + 1; k < ot.dims.size(); ++k) st.inner *= ot.dims[k];
+      st.out_len = ot.dims[dim];
+      long long total = 0;
+      for (auto& t : op.in_types) {
+        if (t.dims.size() != ot.dims.size()) return set_error(QMM_ERR_PARSE, "line %d: concatenate ranks differ", op.line);
+        st.part_len.push_back(t.dims[dim]);
+        total += t.dims[dim];
+      }
+      if (total != st.out_len) return set_error(QMM_ERR_PARSE, "line %d: concatenate sizes do not add up", op.line);
+    } else if (n == "stablehlo.constant") {
+      st.gop = gFill;
+      size_t a = op.body.find("dense<"), b = op.body.rfind('>');
+      std::string val = (a == std::string::npos || b == std::string::npos) ? "" : trim(op.body.substr(a + 6, b - a - 6));
+      if (val == "true") val = "1";
+      if (val == "false") val = "0";
+      st.fval = atof(val.c_str());
+      st.ival = atoll(val.c_str());
+    } else if ((n == "stablehlo.dot_general" || n == "stablehlo.dot") && need_operands(2)) {
+      st.gop = gDot;
+      const TType &lt = op.in_types[0], &rt = op.in_types[1];
+      std::vector<int64_t> lc, rc, lb;
+      if (n == "stablehlo.dot_general") {
+        size_t e = 0;
+        lb = int_list_after(op.body, "batching_dims");
+        lc = int_list_after(op.body, "contracting_dims", 0, &e);
+        if (!lc.empty()) rc = int_list_after(op.body, "x", e);
+        if (lc.empty()) {
+          lc = int_list_after(op.body, "lhs_contracting_dimensions");
+          rc = int_list_after(op.body, "rhs_contracting_dimensions");
+          lb = int_list_after(op.body, "lhs_batching_dimensions");
+        }
+      } else {
+        lc = {(int64_t)lt.dims.size() - 1};
+        rc = {0};
+      }
+      if (!lb.empty() || lc.size() != 1 || rc.size() != 1 || rt.dims.size() != 2 || lt.dims.empty() ||
+          lc[0] != (int64_t)lt.dims.size() - 1 || (rc[0] != 0 && rc[0] != 1))
+        return set_error(QMM_ERR_UNSUPPORTED,
+                         "line %d: %s with these dimension numbers is not supported (need [...,K] x [K,N] or "
+                         "[...,K] x [N,K], no batch dimensions)", op.line, n.c_str());
+      st.b_transposed = rc[0] == 1;
+      st.K = rt.dims[rc[0]];
+      st.N = rt.dims[1 - rc[0]];
+      st.M = 1;
+      for (size_t k = 0; k + 1 < lt.dims.size(); ++k) st.M *= lt.dims[k];
+      if (lt.dims.back() != st.K) return set_error(QMM_ERR_PARSE, "line %d: contracting sizes differ", op.line);
+      if (dtype_of_elem_early(rt.elem) != st.in_dt)
+        return set_error(QMM_ERR_UNSUPPORTED, "line %d: %s with operands of different element types", op.line, n.c_str());
+    } else {
+      tracef(plan.trace, "{\"event\":\"unsupported\",\"line\":%d,\"op\":\"%s\"}", op.line, n.c_str());
+      return set_error(QMM_ERR_UNSUPPORTED,
+                       "line %d: %s is not an op this backend executes (fused: int8/int4 dequantisation chains feeding "
+                       "dot_general, int8 dot_general; standalone: convert, multiply, subtract, add, and, "
+                       "shift_right_logical, broadcast_in_dim, reshape, transpose, slice, concatenate, constant, dot)",
+                       op.line, n.c_str());
+    }
+    if (n != "stablehlo.dot_general" && n != "stablehlo.dot")  // the dot's own line was written with its reason
+      tracef(plan.trace, "{\"event\":\"not_fused\",\"line\":%d,\"op\":\"%s\"}", op.line, n.c_str());
+    plan.steps.push_back(st);
   }
-  if (plan.steps.empty()) return set_error(QMM_ERR_UNSUPPORTED, "the module contains no dot_general");
+  if (plan.steps.empty()) return set_error(QMM_ERR_UNSUPPORTED, "the module computes nothing");
+  std::stable_sort(plan.steps.begin(), plan.steps.end(),
+                   [](const Step& a, const Step& b) { return a.anchor_op < b.anchor_op; });
+
+  // every temporary a step reads must be written by an earlier step
+  {
+    std::set<int> written;
+    for (int a = 0; a < A; ++a) written.insert(a);
+    for (const Step& st : plan.steps) {
+      std::vector<int> reads = st.ins;
+      for (int v : {st.x, st.w, st.scale, st.zeros, st.row, st.col})
+        if (v >= 0) reads.push_back(v);
+      for (int v : reads)
+        if (!written.count(v))
+          return set_error(QMM_ERR_UNSUPPORTED, "line %d: a value this step reads is not produced by any executed op",
+                           st.anchor_line);
+      if (st.out >= 0) written.insert(st.out);
+      if (st.acc_out >= 0) written.insert(st.acc_out);
+    }
+    // results: produced by a step, or a pass-through of an argument / a value returned twice -> copy
+    for (int r = 0; r < R; ++r) {
+      const std::string& v = m.returns[r];
+      const int src = plan.slot.count(v) ? plan.slot[v] : slot_of(v);
+      if (src == A + r && written.count(src)) continue;
+      if (!written.count(src))
+        return set_error(QMM_ERR_UNSUPPORTED, "result %d (%s) is not produced by any executed op", r, v.c_str());
+      const TType* t = type_of(v);
+      Step cp;
+      cp.kind = kGeneric;
+      cp.gop = gCopy;
+      cp.anchor_op = (int)m.ops.size() + r;
+      cp.ins = {src};
+      cp.out = A + r;
+      cp.bytes = (size_t)t->count() * gen::dtype_bits(dtype_of_elem_early(t->elem)) / 8;
+      plan.steps.push_back(cp);
+    }
+  }
+
   for (auto& s : plan.steps)
     if (s.kind == kW4A16) {
       size_t w = qmm_w4a16_g128_workspace_bytes(s.M, s.N, s.K);
@@ -770,10 +1175,17 @@ static int build_plan(Plan& plan) {
                          "line %d: int4 matmul with M=%lld N=%lld K=%lld is outside the kernels' range (N and K "
                          "must be multiples of 128)",
                          s.anchor_line, (long long)s.M, (long long)s.N, (long long)s.K);
-      if (w > plan.workspace) plan.workspace = w;
+      if (w > plan.scratch) plan.scratch = w;
     }
-  tracef(plan.trace, "{\"event\":\"plan\",\"steps\":%d,\"workspace_bytes\":%zu}", (int)plan.steps.size(),
-         plan.workspace);
+  plan.scratch = (plan.scratch + 255) / 256 * 256;
+  size_t off = plan.scratch;
+  for (size_t b : temp_bytes) {
+    plan.temp_offset.push_back(off);
+    off += b;
+  }
+  plan.workspace = off;
+  tracef(plan.trace, "{\"event\":\"plan\",\"steps\":%d,\"fused\":%d,\"workspace_bytes\":%zu}", (int)plan.steps.size(),
+         fused_count, plan.workspace);
   return QMM_OK;
 }
 
@@ -806,10 +1218,23 @@ int qmm_plan_compile(const char* text, size_t len, qmm_plan** out) {
   return QMM_OK;
 }
 
-void qmm_plan_destroy(qmm_plan* plan) { delete plan; }
+void qmm_plan_destroy(qmm_plan* plan) {
+  if (!plan) return;
+  for (auto& kv : plan->p.const_dev) {
+    cudaSetDevice(kv.first);
+    for (void* p : kv.second) cudaFree(p);
+  }
+  delete plan;
+}
 
 int qmm_plan_num_steps(const qmm_plan* plan) { return plan ? (int)plan->p.steps.size() : 0; }
-int qmm_plan_num_args(const qmm_plan* plan) { return plan ? (int)plan->p.mod.arg_names.size() : 0; }
+int qmm_plan_num_args(const qmm_plan* plan) { return plan ? plan->p.mod.num_real_args : 0; }
+int qmm_plan_num_fused_steps(const qmm_plan* plan) {
+  int n = 0;
+  if (plan)
+    for (const auto& s : plan->p.steps) n += s.kind != qmm::hlo::kGeneric;
+  return n;
+}
 int qmm_plan_num_results(const qmm_plan* plan) { return plan ? (int)plan->p.mod.returns.size() : 0; }
 size_t qmm_plan_workspace_bytes(const qmm_plan* plan) { return plan ? plan->p.workspace : 0; }
 
@@ -839,7 +1264,7 @@ static int type_info(const qmm::hlo::TType& t, int* dtype, int64_t* dims, int* r
 
 int qmm_plan_arg_info(const qmm_plan* plan, int index, int* dtype, int64_t* dims, int* rank) {
   using namespace qmm;
-  QMM_REQUIRE(plan && index >= 0 && index < (int)plan->p.mod.arg_types.size(), QMM_ERR_INVALID_ARGUMENT,
+  QMM_REQUIRE(plan && index >= 0 && index < plan->p.mod.num_real_args, QMM_ERR_INVALID_ARGUMENT,
               "qmm_plan_arg_info: bad plan or index %d", index);
   return type_info(plan->p.mod.arg_types[index], dtype, dims, rank);
 }
@@ -864,7 +1289,8 @@ int qmm_plan_num_partitions(const qmm_plan* plan) { return plan ? plan->p.mod.nu
 double qmm_plan_flops(const qmm_plan* plan) {
   double f = 0;
   if (plan)
-    for (const auto& s : plan->p.steps) f += 2.0 * (double)s.M * (double)s.N * (double)s.K;
+    for (const auto& s : plan->p.steps)
+      if (s.kind != qmm::hlo::kGeneric || s.gop == qmm::hlo::gDot) f += 2.0 * (double)s.M * (double)s.N * (double)s.K;
   return f;
 }
 
@@ -879,51 +1305,116 @@ size_t qmm_plan_trace(const qmm_plan* plan, char* buf, size_t cap) {
   return t.size();
 }
 
-int qmm_plan_execute(const qmm_plan* plan, const void* const* args, int num_args, void* const* results,
+// Device copies of the lifted constants for the current device (made on the first execution there).
+static int constants_on_device(qmm_plan* plan, std::vector<void*>** out) {
+  using namespace qmm;
+  int dev = 0;
+  QMM_CUDA_TRY(cudaGetDevice(&dev));
+  std::lock_guard<std::mutex> lock(plan->p.mu);
+  auto it = plan->p.const_dev.find(dev);
+  if (it == plan->p.const_dev.end()) {
+    std::vector<void*> ptrs;
+    for (const auto& bytes : plan->p.mod.const_data) {
+      void* p = nullptr;
+      QMM_CUDA_TRY(cudaMalloc(&p, bytes.empty() ? 256 : bytes.size()));
+      if (!bytes.empty()) QMM_CUDA_TRY(cudaMemcpy(p, bytes.data(), bytes.size(), cudaMemcpyHostToDevice));
+      ptrs.push_back(p);
+    }
+    it = plan->p.const_dev.emplace(dev, std::move(ptrs)).first;
+  }
+  *out = &it->second;
+  return QMM_OK;
+}
+
+int qmm_plan_execute(const qmm_plan* cplan, const void* const* args, int num_args, void* const* results,
                      int num_results, void* workspace, size_t workspace_bytes, void* stream) {
   using namespace qmm;
-  QMM_REQUIRE(plan && args && results, QMM_ERR_INVALID_ARGUMENT, "qmm_plan_execute: null argument");
-  QMM_REQUIRE(num_args == (int)plan->p.mod.arg_names.size() && num_results == (int)plan->p.mod.returns.size(),
-              QMM_ERR_INVALID_ARGUMENT, "qmm_plan_execute: expected %d arguments and %d results, got %d and %d",
-              (int)plan->p.mod.arg_names.size(), (int)plan->p.mod.returns.size(), num_args, num_results);
+  qmm_plan* plan = const_cast<qmm_plan*>(cplan);  // only the cache of constant buffers changes
+  QMM_REQUIRE(plan && (args || num_args == 0) && results, QMM_ERR_INVALID_ARGUMENT, "qmm_plan_execute: null argument");
+  const hlo::Module& m = plan->p.mod;
+  const int A = (int)m.arg_names.size(), R = (int)m.returns.size();
+  QMM_REQUIRE(num_args == m.num_real_args && num_results == R, QMM_ERR_INVALID_ARGUMENT,
+              "qmm_plan_execute: expected %d arguments and %d results, got %d and %d", m.num_real_args, R, num_args,
+              num_results);
   QMM_REQUIRE(plan->p.workspace == 0 || (workspace && workspace_bytes >= plan->p.workspace), QMM_ERR_WORKSPACE,
               "qmm_plan_execute: %zu bytes of workspace required", plan->p.workspace);
-  // Steps read only arguments of @main and write distinct results, so they do not depend on one
-  // another: a weight-only GEMM step that follows only GEMM steps of this call is launched as
-  // independent of them (it fills the SMs their last round leaves idle).  The first step is always
-  // ordered behind everything queued before the call.
+  QMM_REQUIRE(plan->p.workspace == 0 || aligned(workspace, 256), QMM_ERR_WORKSPACE,
+              "qmm_plan_execute: the workspace must be 256-byte aligned");
+  std::vector<void*>* consts = nullptr;
+  if (!m.const_data.empty())
+    if (int rc = constants_on_device(plan, &consts)) return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  auto ptr = [&](int slot) -> void* {
+    if (slot < 0) return nullptr;
+    if (slot < m.num_real_args) return const_cast<void*>(args[slot]);
+    if (slot < A) return (*consts)[slot - m.num_real_args];
+    if (slot < A + R) return results[slot - A];
+    return static_cast<uint8_t*>(workspace) + plan->p.temp_offset[slot - A - R];
+  };
+  // Fused steps read arguments and temporaries and write distinct buffers.  A weight-only GEMM step
+  // that follows only GEMM steps of this call, none of which produced one of its operands, is
+  // launched as independent of them (it fills the SMs their last round leaves idle).  The first
+  // step is always ordered behind everything queued before the call.
   bool only_gemms_so_far = true;
   bool first = true;
+  std::set<int> written_by_call;
   for (const hlo::Step& s : plan->p.steps) {
     int rc = QMM_OK;
-    void* out = s.out >= 0 ? results[s.out] : nullptr;
-    const bool independent = !first && only_gemms_so_far;
+    void* out = ptr(s.out);
+    bool independent = !first && only_gemms_so_far;
+    for (int v : {s.x, s.w, s.scale})
+      if (v >= 0 && written_by_call.count(v)) independent = false;
     first = false;
     if (s.kind != hlo::kW8A16 && s.kind != hlo::kI8Dot) only_gemms_so_far = false;
+    if (s.out >= 0) written_by_call.insert(s.out);
+    if (s.acc_out >= 0) written_by_call.insert(s.acc_out);
     switch (s.kind) {
       case hlo::kW8A32:
-        rc = qmm_w8a32_perchannel((const float*)args[s.x], (const int8_t*)args[s.w], (const float*)args[s.scale],
+        rc = qmm_w8a32_perchannel((const float*)ptr(s.x), (const int8_t*)ptr(s.w), (const float*)ptr(s.scale),
                                   (float*)out, s.M, s.N, s.K, stream);
         break;
-      case hlo::kW8A16:
-      {
+      case hlo::kW8A16: {
         qmm_gemm_ext ext = {};
         ext.struct_size = sizeof(ext);
         ext.flags = independent ? QMM_GEMM_INDEPENDENT : 0u;
-        rc = qmm_w8a16_perchannel_ex((const uint16_t*)args[s.x], (const int8_t*)args[s.w], (const float*)args[s.scale],
+        rc = qmm_w8a16_perchannel_ex((const uint16_t*)ptr(s.x), (const int8_t*)ptr(s.w), (const float*)ptr(s.scale),
                                      (uint16_t*)out, s.M, s.N, s.K, s.N, &ext, stream);
         break;
       }
       case hlo::kI8Dot:
-        rc = qmm_i8i8_i32(args[s.x], args[s.w], s.acc_out >= 0 ? (int32_t*)results[s.acc_out] : nullptr,
-                          s.row >= 0 ? (const float*)args[s.row] : nullptr,
-                          s.col >= 0 ? (const float*)args[s.col] : nullptr, (float*)out, s.M, s.N, s.K,
-                          s.a_unsigned, s.b_unsigned, stream);
+        rc = qmm_i8i8_i32(ptr(s.x), ptr(s.w), (int32_t*)ptr(s.acc_out), (const float*)ptr(s.row),
+                          (const float*)ptr(s.col), (float*)out, s.M, s.N, s.K, s.a_unsigned, s.b_unsigned, stream);
         break;
       case hlo::kW4A16:
-        rc = qmm_w4a16_g128((const uint16_t*)args[s.x], (const uint8_t*)args[s.w], (const uint16_t*)args[s.scale],
-                            (const uint8_t*)args[s.zeros], s.zeros_packed, (uint16_t*)out, s.M, s.N, s.K, 128,
-                            workspace, workspace_bytes, 0u, stream);
+        rc = qmm_w4a16_g128((const uint16_t*)ptr(s.x), (const uint8_t*)ptr(s.w), (const uint16_t*)ptr(s.scale),
+                            (const uint8_t*)ptr(s.zeros), s.zeros_packed, (uint16_t*)out, s.M, s.N, s.K, 128,
+                            workspace, plan->p.scratch, 0u, stream);
+        break;
+      case hlo::kGeneric:
+        switch (s.gop) {
+          case hlo::gConvert: rc = gen::convert(ptr(s.ins[0]), s.in_dt, out, s.out_dt, s.count, st); break;
+          case hlo::gBinary: rc = gen::binary(s.bop, ptr(s.ins[0]), ptr(s.ins[1]), out, s.out_dt, s.count, st); break;
+          case hlo::gGather:
+            rc = gen::gather(ptr(s.ins[0]), out, s.out_dt, s.in_dims.data(), (int)s.in_dims.size(), s.out_dims.data(),
+                             (int)s.out_dims.size(), s.src_of.data(), s.start.data(), s.stride.data(), st);
+            break;
+          case hlo::gConcat: {
+            long long off = 0;
+            for (size_t k = 0; k < s.ins.size() && rc == QMM_OK; ++k) {
+              rc = gen::concat_part(ptr(s.ins[k]), out, s.out_dt, s.outer, s.part_len[k], s.out_len, off, s.inner, st);
+              off += s.part_len[k];
+            }
+            break;
+          }
+          case hlo::gFill: rc = gen::fill(out, s.out_dt, s.fval, s.ival, s.count, st); break;
+          case hlo::gDot:
+            rc = gen::dot(ptr(s.ins[0]), ptr(s.ins[1]), out, s.in_dt, s.out_dt, s.M, s.N, s.K, s.b_transposed, st);
+            break;
+          case hlo::gCopy:
+            if (s.bytes && out != ptr(s.ins[0]))
+              QMM_CUDA_TRY(cudaMemcpyAsync(out, ptr(s.ins[0]), s.bytes, cudaMemcpyDeviceToDevice, st));
+            break;
+        }
         break;
     }
     if (rc != QMM_OK) return rc;

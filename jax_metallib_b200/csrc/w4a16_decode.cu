@@ -65,17 +65,19 @@ struct Smem {
   static constexpr int kS = kColsPerBlock * 2;             // 512
   static constexpr int kZ = kColsPerBlock;                 // 256 (128 used when packed)
   static constexpr int kF = 128;                           // per-row power-of-two factors (MT*8 floats)
+  static constexpr int kXS = 128;                          // per-row sums of the scaled activations (MT*8 floats)
   static constexpr int kX = MT * 8 * kXRowBytes;           // also the byte count of the TMA box
   static constexpr int kOffS = kW;
   static constexpr int kOffZ = kOffS + kS;
   static constexpr int kOffF = kOffZ + kZ;
+  static constexpr int kOffXS = kOffF + kF;
   static constexpr int kOffX = 17408;                      // multiple of 256 (the swizzle uses address bits 5-7)
   static constexpr int kStage = ((kOffX + kX + 1023) / 1024) * 1024;
   static constexpr int kMinBlocks = (MT <= 2) ? 2 : 1;     // resident CTAs per SM
   static constexpr int kStages = (MT <= 2) ? 5 : 8;
   static constexpr int kBarBytes = 1024;
   static constexpr int kTotal = kStages * kStage + kBarBytes + 1024;  // + alignment slack
-  static_assert(kOffF + kF <= kOffX, "stage layout overlaps");
+  static_assert(kOffXS + kXS <= kOffX, "stage layout overlaps");
 };
 
 __device__ __forceinline__ void bulk_copy_g2s(void* smem_dst, const void* gsrc, uint32_t bytes,
@@ -138,7 +140,7 @@ __global__ void __launch_bounds__(kThreads, Smem<MT>::kMinBlocks)
 w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap xmap,
                     const uint16_t* __restrict__ scales, const uint8_t* __restrict__ zeros,
                     uint16_t* __restrict__ y, float* __restrict__ ws_partial,
-                    int* __restrict__ ws_counter, int M, int N, int K, int G, int U, int max_slots,
+                    int* __restrict__ ws_flags, int M, int N, int K, int G, int U, int max_slots,
                     int static_weights, int* status
                     ) {
   using L = Smem<MT>;
@@ -239,6 +241,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
         if (!dev::mbar_wait_relaxed_warp(&xraw[s_conv], ph_conv, status, 4)) break;
         uint8_t* st = smem + s_conv * L::kStage;
         float* fac = reinterpret_cast<float*>(st + L::kOffF);
+        float* xsum_row = reinterpret_cast<float*>(st + L::kOffXS);
         uint4 v[kPasses];
 #pragma unroll
         for (int p = 0; p < kPasses; ++p) {
@@ -262,15 +265,19 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
           const bool scaled = (e8 >= 16u) && (e8 < 255u);
           const float mul = scaled ? __uint_as_float((262u - e8) << 23) : 1.0f;
           const float inv = scaled ? __uint_as_float((e8 - 8u) << 23) : 1.0f;
-          const float mul_odd = mul * 0.0625f;
-          const uint32_t w0 = pack_f16x2(__uint_as_float(v[p].x << 16) * mul,
-                                         __uint_as_float(v[p].x & 0xFFFF0000u) * mul_odd);
-          const uint32_t w1 = pack_f16x2(__uint_as_float(v[p].y << 16) * mul,
-                                         __uint_as_float(v[p].y & 0xFFFF0000u) * mul_odd);
-          const uint32_t w2 = pack_f16x2(__uint_as_float(v[p].z << 16) * mul,
-                                         __uint_as_float(v[p].z & 0xFFFF0000u) * mul_odd);
-          const uint32_t w3 = pack_f16x2(__uint_as_float(v[p].w << 16) * mul,
-                                         __uint_as_float(v[p].w & 0xFFFF0000u) * mul_odd);
+          const float e0 = __uint_as_float(v[p].x << 16) * mul, o0 = __uint_as_float(v[p].x & 0xFFFF0000u) * mul;
+          const float e1 = __uint_as_float(v[p].y << 16) * mul, o1 = __uint_as_float(v[p].y & 0xFFFF0000u) * mul;
+          const float e2 = __uint_as_float(v[p].z << 16) * mul, o2 = __uint_as_float(v[p].z & 0xFFFF0000u) * mul;
+          const float e3 = __uint_as_float(v[p].w << 16) * mul, o3 = __uint_as_float(v[p].w & 0xFFFF0000u) * mul;
+          // sum of the row's 128 scaled activations: what the zero point multiplies, once per
+          // (row, group) here instead of once per consumer warp on the tensor cores
+          float xs = ((e0 + o0) + (e1 + o1)) + ((e2 + o2) + (e3 + o3));
+#pragma unroll
+          for (int off = 8; off >= 1; off >>= 1) xs += __shfl_xor_sync(0xFFFFFFFFu, xs, off);
+          const uint32_t w0 = pack_f16x2(e0, o0 * 0.0625f);
+          const uint32_t w1 = pack_f16x2(e1, o1 * 0.0625f);
+          const uint32_t w2 = pack_f16x2(e2, o2 * 0.0625f);
+          const uint32_t w3 = pack_f16x2(e3, o3 * 0.0625f);
           // every 4 consecutive k go from (0,1,2,3) to (0,2,1,3): the order the
           // MMA fragments of the consumers read them in
           uint4 o;
@@ -280,7 +287,10 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
           o.w = __byte_perm(w2, w3, 0x7632);
           const int chunk = (lane & 15) ^ ((row & 3) << 1);
           *reinterpret_cast<uint4*>(st + L::kOffX + row * kXRowBytes + chunk * 16) = o;
-          if ((lane & 15) == 0) fac[row] = inv;
+          if ((lane & 15) == 0) {
+            fac[row] = inv;
+            xsum_row[row] = xs;
+          }
         }
         __syncwarp();
         if (lane == 0) dev::mbar_arrive(&full[s_conv]);
@@ -310,17 +320,36 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
 #pragma unroll
         for (int i = 0; i < 4; ++i) yacc[j][mt][i] = 0.f;
 
-    // Hand this warp's 32 columns of the finished column block over.  CTAs that
-    // share the block each write a partial tile; every warp counts arrivals on
-    // its own counter, and the warp that arrives last adds the partial tiles of
-    // its columns in slot order (so the result does not depend on arrival
-    // order) and writes bf16.  No CTA-wide rendezvous is involved.
-    auto flush = [&](int c) {
-      const int first = cta_of_unit(static_cast<long long>(c) * 2 * G, P, 2 * U);
-      const int last = cta_of_unit(static_cast<long long>(c) * 2 * G + 2 * G - 1, P, 2 * U);
-      const int nslots = last - first + 1;
+    // Hand this warp's 32 columns of a finished column block over.  The CTAs that share a block
+    // hold consecutive k-ranges of it; the one with the first range (slot 0) reaches the block at
+    // the end of its own work, the others at the start of theirs.  So the others store their
+    // partial tile and raise a flag (release) and go on; slot 0 keeps its partial in registers,
+    // checks the flags (acquire; they were raised long before, and the loads for the last block
+    // are issued before its last unit is multiplied), adds the partial tiles in slot order (the
+    // result does not depend on timing) and writes bf16.  Flags are cleared by their reader, so
+    // the workspace header is left zeroed.  The wait is bounded like every other wait here; it
+    // relies on all CTAs of the grid being resident, which the launch guarantees on an otherwise
+    // idle device (grid = resident CTAs per SM x SMs).
+    auto flag_of = [&](int c, int cta) { return ws_flags + (static_cast<size_t>(c) + cta) * kConsumerWarps + warp; };
+    auto slots_of = [&](int c, int& first) {
+      first = cta_of_unit(static_cast<long long>(c) * 2 * G, P, 2 * U);
+      return cta_of_unit(static_cast<long long>(c) * 2 * G + 2 * G - 1, P, 2 * U) - first + 1;
+    };
+    uint32_t early_flags = 0;   // bit i: flag of slot 1 + i of the final block seen raised (lane i's view)
+    auto poll_flags = [&](int c, int first, int nslots, int base) -> uint32_t {
+      // lanes look at slots base + 1 + lane; returns the ballot of raised flags
+      const int sl = base + 1 + lane;
+      uint32_t v = 0;
+      if (sl < nslots) v = dev::ld_acquire_gpu_u32(reinterpret_cast<const uint32_t*>(flag_of(c, first + sl)));
+      return __ballot_sync(0xFFFFFFFFu, sl >= nslots || v != 0);
+    };
+    auto flush = [&](int c, bool have_early) -> bool {
+      int first;
+      const int nslots = slots_of(c, first);
       const int col0 = c * kColsPerBlock;
-      if (nslots == 1) {
+      const int slot = static_cast<int>(blockIdx.x) - first;
+      if (slot != 0) {
+        float* part = ws_partial + (static_cast<size_t>(c) * max_slots + slot) * (MT * 8) * kColsPerBlock;
 #pragma unroll
         for (int j = 0; j < 2; ++j)
 #pragma unroll
@@ -328,15 +357,57 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
               const int m = mt * 8 + 2 * t4 + r;
-              const int col = col0 + lc + 16 * j;
-              if (m < M && col < N)
-                *reinterpret_cast<uint32_t*>(y + static_cast<size_t>(m) * N + col) =
-                    dev::pack_bf16x2(yacc[j][mt][r], yacc[j][mt][2 + r]);
+              if (m < M)
+                __stcg(reinterpret_cast<float2*>(part + m * kColsPerBlock + lc + 16 * j),
+                       make_float2(yacc[j][mt][r], yacc[j][mt][2 + r]));
             }
-        return;
+        __syncwarp();
+        if (lane == 0) dev::st_release_gpu_u32(reinterpret_cast<uint32_t*>(flag_of(c, blockIdx.x)), 1u);
+        return true;
       }
-      const int slot = static_cast<int>(blockIdx.x) - first;
-      float* part = ws_partial + (static_cast<size_t>(c) * max_slots + slot) * (MT * 8) * kColsPerBlock;
+      if (nslots > 1) {
+        // every other slot's partial tile of this warp's columns must be there
+        for (int base = 0; base < nslots - 1; base += 32) {
+          uint32_t seen = (have_early && base == 0) ? early_flags : 0u;
+          if (seen != 0xFFFFFFFFu) {
+            const uint64_t t0 = dev::globaltimer_ns();
+            while ((seen = poll_flags(c, first, nslots, base)) != 0xFFFFFFFFu) {
+              if (dev::globaltimer_ns() - t0 > dev::kWaitLimitNs) {
+                if (lane == 0 && status) atomicExch(status, (3 << 16) | QMM_ERR_TIMEOUT);
+                return false;
+              }
+              __nanosleep(100);
+            }
+          }
+        }
+        __syncwarp();
+        const float* base_part = ws_partial + static_cast<size_t>(c) * max_slots * (MT * 8) * kColsPerBlock;
+        for (int sl = 1; sl < nslots; ++sl) {  // ascending k: a fixed summation order
+          const float* part = base_part + static_cast<size_t>(sl) * (MT * 8) * kColsPerBlock;
+          float2 v[2][MT][2];
+#pragma unroll
+          for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+              for (int r = 0; r < 2; ++r) {
+                const int m = mt * 8 + 2 * t4 + r;
+                v[j][mt][r] = (m < M) ? __ldcg(reinterpret_cast<const float2*>(part + m * kColsPerBlock + lc + 16 * j))
+                                      : make_float2(0.f, 0.f);
+              }
+#pragma unroll
+          for (int j = 0; j < 2; ++j)
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+              for (int r = 0; r < 2; ++r) {
+                yacc[j][mt][r] += v[j][mt][r].x;
+                yacc[j][mt][2 + r] += v[j][mt][r].y;
+              }
+        }
+        // the flags have been consumed: leave them cleared for the next launch
+        for (int sl = 1 + lane; sl < nslots; sl += 32) *flag_of(c, first + sl) = 0;
+      }
 #pragma unroll
       for (int j = 0; j < 2; ++j)
 #pragma unroll
@@ -344,50 +415,20 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
 #pragma unroll
           for (int r = 0; r < 2; ++r) {
             const int m = mt * 8 + 2 * t4 + r;
-            if (m < M)
-              __stcg(reinterpret_cast<float2*>(part + m * kColsPerBlock + lc + 16 * j),
-                     make_float2(yacc[j][mt][r], yacc[j][mt][2 + r]));
+            const int col = col0 + lc + 16 * j;
+            if (m < M && col < N)
+              *reinterpret_cast<uint32_t*>(y + static_cast<size_t>(m) * N + col) =
+                  dev::pack_bf16x2(yacc[j][mt][r], yacc[j][mt][2 + r]);
           }
-      __syncwarp();
-      int is_last = 0;
-      if (lane == 0) {
-        __threadfence();  // the warp's partial tile is visible before its arrival is
-        is_last = (atomicAdd(&ws_counter[c * kConsumerWarps + warp], 1) + 1 == nslots);
-        if (is_last) __threadfence();
-      }
-      is_last = __shfl_sync(0xFFFFFFFFu, is_last, 0);
-      if (!is_last) return;
-      const float* base = ws_partial + static_cast<size_t>(c) * max_slots * (MT * 8) * kColsPerBlock;
-      const int wcol = warp * 32 + lane;  // one column per lane
-      // four rows x four slots of loads in flight; slots are always added in
-      // ascending order, so the rounding does not depend on who arrived last
-      for (int m0 = 0; m0 < M; m0 += 4) {
-        float a[4] = {0.f, 0.f, 0.f, 0.f};
-        for (int sl0 = 0; sl0 < nslots; sl0 += 4) {
-          float v[4][4];
-#pragma unroll
-          for (int ds = 0; ds < 4; ++ds)
-#pragma unroll
-            for (int r = 0; r < 4; ++r)
-              v[ds][r] = (sl0 + ds < nslots && m0 + r < M)
-                             ? __ldcg(base + (static_cast<size_t>(sl0 + ds) * (MT * 8) + m0 + r) * kColsPerBlock + wcol)
-                             : 0.f;
-#pragma unroll
-          for (int ds = 0; ds < 4; ++ds)
-#pragma unroll
-            for (int r = 0; r < 4; ++r) a[r] += v[ds][r];
-        }
-#pragma unroll
-        for (int r = 0; r < 4; ++r) {
-          const float b = __shfl_down_sync(0xFFFFFFFFu, a[r], 1);
-          if (m0 + r < M && !(lane & 1) && col0 + wcol < N)
-            *reinterpret_cast<uint32_t*>(y + static_cast<size_t>(m0 + r) * N + col0 + wcol) =
-                dev::pack_bf16x2(a[r], b);
-        }
-      }
-      __syncwarp();
-      if (lane == 0) ws_counter[c * kConsumerWarps + warp] = 0;
+      return true;
     };
+    // the block this CTA finishes last, if it is that block's slot 0 with partners
+    int final_c = -1, final_first = 0, final_nslots = 1;
+    if (n_units > 0) {
+      final_c = (u_end - 1) / G;
+      final_nslots = slots_of(final_c, final_first);
+      if (final_first != static_cast<int>(blockIdx.x) || final_nslots <= 1) final_c = -1;
+    }
 
     int c = (n_units > 0) ? u_begin / G : 0;
     int g = (n_units > 0) ? u_begin - c * G : 0;
@@ -426,15 +467,16 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
       }
 
       float acc[2][MT][4];
-      float xsum[MT][4];  // [0], [1]: sum over the group of this thread's two activation rows (x 2^-24)
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           acc[0][mt][i] = 0.f;
           acc[1][mt][i] = 0.f;
-          xsum[mt][i] = 0.f;
         }
+      // before the last unit is multiplied, look at the flags its hand-over will need: the
+      // round trip hides under the multiplication
+      if (it == n_units - 1 && final_c >= 0) early_flags = poll_flags(final_c, final_first, final_nslots, 0);
       const uint32_t xb = st_addr + x_off;
 
       const int hl = half_lo(it), hh = half_hi(it);
@@ -462,26 +504,23 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt)
             mma_f16_16816(acc[1][mt], r[0], r[2], r[1], r[3], xf[mt][0], xf[mt][1]);
-          // a weight operand of all ones gives the sum of the slab's activations, which is what
-          // the zero point multiplies
-#pragma unroll
-          for (int mt = 0; mt < MT; ++mt)
-            mma_f16_16816(xsum[mt], 0x00010001u, 0x00010001u, 0x00100010u, 0x00100010u, xf[mt][0], xf[mt][1]);
         }
       }
       // group epilogue: per pair this thread holds columns (c, c+1) for rows
       // (2t, 2t+1) of each 8-row tile
       const float* fac = reinterpret_cast<const float*>(st + L::kOffF);
+      const float* xsr = reinterpret_cast<const float*>(st + L::kOffXS);
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
         const float2 f = *reinterpret_cast<const float2*>(fac + mt * 8 + 2 * t4);
+        const float2 xs = *reinterpret_cast<const float2*>(xsr + mt * 8 + 2 * t4);  // rows 2t, 2t+1
 #pragma unroll
         for (int j = 0; j < 2; ++j) {
-          // sum_k (q - z) x = acc - z * sum_k x, both in units of 2^-24
-          const float v0 = fmaf(-zf[j][0], xsum[mt][0], acc[j][mt][0]) * 16777216.f;
-          const float v1 = fmaf(-zf[j][0], xsum[mt][1], acc[j][mt][1]) * 16777216.f;
-          const float v2 = fmaf(-zf[j][1], xsum[mt][0], acc[j][mt][2]) * 16777216.f;
-          const float v3 = fmaf(-zf[j][1], xsum[mt][1], acc[j][mt][3]) * 16777216.f;
+          // sum_k (q - z) x = acc * 2^24 - z * sum_k x (the weights went in as q * 2^-24)
+          const float v0 = fmaf(acc[j][mt][0], 16777216.f, -zf[j][0] * xs.x);
+          const float v1 = fmaf(acc[j][mt][1], 16777216.f, -zf[j][0] * xs.y);
+          const float v2 = fmaf(acc[j][mt][2], 16777216.f, -zf[j][1] * xs.x);
+          const float v3 = fmaf(acc[j][mt][3], 16777216.f, -zf[j][1] * xs.y);
           yacc[j][mt][0] = fmaf(sc[j][0] * f.x, v0, yacc[j][mt][0]);
           yacc[j][mt][1] = fmaf(sc[j][0] * f.y, v1, yacc[j][mt][1]);
           yacc[j][mt][2] = fmaf(sc[j][1] * f.x, v2, yacc[j][mt][2]);
@@ -494,7 +533,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
       if (++g == G) {
         // the column block is complete as far as this CTA is concerned
         g = 0;
-        flush(c);
+        if (!flush(c, false)) { ok = false; break; }  // a block that ends inside the range: never this CTA's final one with partners
         ++c;
 #pragma unroll
         for (int j = 0; j < 2; ++j)
@@ -504,7 +543,7 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
             for (int i = 0; i < 4; ++i) yacc[j][mt][i] = 0.f;
       }
     }
-    if (ok && n_units > 0 && g != 0) flush(c);
+    if (ok && n_units > 0 && g != 0) flush(c, c == final_c);
   }
 }
 
@@ -551,12 +590,16 @@ static int slots_for(int G, int U, int P) {
   // a column block of G units is shared by at most ceil(G*P/U) + 1 CTAs
   return static_cast<int>((static_cast<long long>(G) * P + U - 1) / U) + 1;
 }
-// One arrival counter per (column block, consumer warp).  The counters occupy a
-// fixed-size header of the workspace so that calls with different shapes can
-// share one workspace: only this header has to be zero between calls, and every
+// One flag per (column block, CTA that holds a part of it, consumer warp), at index
+// (block + CTA) * 8 + warp: consecutive (CTA, block) pairs differ in exactly one of the two, so the
+// sum is unique per pair.  The flags occupy a fixed-size header of the workspace so that calls with
+// different shapes can share one workspace: only this header has to be zero between calls, and every
 // call leaves it zero.
 constexpr int kMaxColBlocks = 2048;
-static size_t counter_bytes(int /*C*/) { return static_cast<size_t>(kMaxColBlocks) * kConsumerWarps * sizeof(int); }
+constexpr int kMaxCtas = 2048;
+static size_t counter_bytes(int /*C*/) {
+  return static_cast<size_t>(kMaxColBlocks + kMaxCtas) * kConsumerWarps * sizeof(int);
+}
 static int rows_padded(int M) { return M <= 8 ? 8 : (M <= 16 ? 16 : 32); }
 static int col_blocks(int64_t N) { return static_cast<int>((N + kColsPerBlock - 1) / kColsPerBlock); }
 
@@ -568,6 +611,7 @@ static int run(const char* name, const uint16_t* x, const uint8_t* wq, const uin
   const int C = col_blocks(N);
   const int U = G * C;
   const int P = grid_size(U, static_cast<int>(M));
+  QMM_REQUIRE(P <= kMaxCtas, QMM_ERR_UNSUPPORTED, "%s: a grid of %d CTAs exceeds the workspace header", name, P);
   const int slots = slots_for(G, U, P);
   const size_t counters = counter_bytes(C);
   int* ws_counter = static_cast<int*>(workspace);
@@ -587,7 +631,6 @@ static int run(const char* name, const uint16_t* x, const uint8_t* wq, const uin
     return rc;
   const int m = static_cast<int>(M), n = static_cast<int>(N), k = static_cast<int>(K);
   const int sw = (flags & QMM_W4_STATIC_WEIGHTS) ? 1 : 0;
-  (void)name;
 #define QMM_W4_LAUNCH(MT)                                                                         \
   (zeros_packed ? launch<MT, true>(wmap, xmap, scales, zeros, y, ws_partial, ws_counter, m, n, k, \
                                    G, U, P, slots, sw, status, st)                                \

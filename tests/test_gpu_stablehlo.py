@@ -64,3 +64,68 @@ def test_config5_module(cuda):
     out = torch.empty((4096, 1024), dtype=torch.bfloat16, device=cuda)
     exe([dev(c["x_bits"].view(np.int16), cuda, torch.bfloat16), dev(c["w"], cuda), dev(c["scale"], cuda)], [out])
     assert O.max_rel_err(bf16_np(out), O.w8_perchannel_matmul(c["x"], c["w"], c["scale"])) <= 1e-2
+
+
+# ---------------------------------------------------------------- around the fused patterns
+def _run(name, cuda, host_args, out_specs, bf16_args=()):
+    exe = Executable(load(name))
+    args = [dev(a, cuda, torch.bfloat16) if i in bf16_args else dev(a, cuda) for i, a in enumerate(host_args)]
+    outs = [torch.full(shape, -7, dtype=dt, device=cuda) for shape, dt in out_specs]
+    exe(args, outs)
+    torch.cuda.synchronize()
+    return exe, outs
+
+
+def test_unfused_chain_computes_the_same_values_op_by_op(cuda):
+    rng = np.random.default_rng(21)
+    x = rng.standard_normal((32, 256)).astype(np.float32)
+    w = rng.integers(-127, 128, size=(256, 128)).astype(np.int8)
+    s = rng.uniform(0.005, 0.02, size=(128,)).astype(np.float32)
+    exe, (y, wd) = _run("unfused_escaping_intermediate.mlir", cuda, [x, w, s],
+                        [((32, 128), torch.float32), ((256, 128), torch.float32)])
+    assert [t["event"] for t in exe.trace()].count("fused") == 0
+    np.testing.assert_array_equal(wd.cpu().numpy(), O.w8_perchannel_dequant(w, s))  # convert and multiply are exact f32 ops
+    assert O.max_rel_err(y.cpu().numpy(), O.w8_perchannel_matmul(x, w, s)) <= 2e-3
+    # a [N, K] weight: dequantised, transposed, multiplied
+    x = rng.standard_normal((16, 256)).astype(np.float32)
+    wt = rng.integers(-127, 128, size=(128, 256)).astype(np.int8)
+    _, (y,) = _run("unfused_transposed_weight.mlir", cuda, [x, wt, s], [((16, 128), torch.float32)])
+    assert O.max_rel_err(y.cpu().numpy(), O.w8_perchannel_matmul(x, wt.T.copy(), s)) <= 2e-3
+    # the same contraction written as [M, K] x [N, K] in bf16
+    xb = synthetic.to_bf16_bits(x)
+    _, (y,) = _run("unfused_contract_rhs_dim1.mlir", cuda, [xb.view(np.int16), wt, s], [((16, 128), torch.bfloat16)],
+                   bf16_args=(0,))
+    ref = O.w8_perchannel_matmul(synthetic.bf16_bits_to_f32(xb), wt.T.copy(), s)
+    assert O.max_rel_err(bf16_np(y), ref) <= 1e-2
+
+
+def test_legacy_dot_constants_bias_and_trailing_convert(cuda):
+    rng = np.random.default_rng(22)
+    x = rng.standard_normal((32, 256)).astype(np.float32)
+    w = rng.integers(-127, 128, size=(256, 128)).astype(np.int8)
+    s = rng.uniform(0.005, 0.02, size=(128,)).astype(np.float32)
+    _, (y,) = _run("legacy_dot_w8a32.mlir", cuda, [x, w, s], [((32, 128), torch.float32)])
+    assert O.max_rel_err(y.cpu().numpy(), O.w8_perchannel_matmul(x, w, s)) <= 2e-3
+    # weight and scale are dense constants of the module, the bias is added by a standalone kernel
+    x = rng.integers(-4, 5, size=(8, 4)).astype(np.float32)
+    bias = np.array([1.0, -2.0, 0.5], np.float32)
+    wc = np.array([[1, -2, 3], [4, 5, -6], [-7, 8, 9], [10, -11, 12]], np.float32)
+    sc = np.array([0.5, 0.25, 2.0], np.float32)
+    _, (y,) = _run("const_weight_bias_add.mlir", cuda, [x, bias], [((8, 3), torch.float32)])
+    np.testing.assert_array_equal(y.cpu().numpy(), (x @ wc) * sc + bias)  # small integers: exact in f32
+    c = synthetic.config5_small(256, 512, 384)
+    _, (y,) = _run("cfg5_f32_accumulate_then_convert.mlir", cuda, [c["x_bits"].view(np.int16), c["w"], c["scale"]],
+                   [((256, 384), torch.bfloat16)], bf16_args=(0,))
+    assert O.max_rel_err(bf16_np(y), O.w8_perchannel_matmul(c["x"], c["w"], c["scale"])) <= 1e-2
+
+
+def test_int8_typed_dot_wraps_and_shape_ops(cuda):
+    rng = np.random.default_rng(0)  # tests/test_int_dot.py: an i8 result wraps mod 2^8 after an int32 accumulate
+    a = rng.integers(-300, 300, size=(5, 7), dtype=np.int64).astype(np.int8)
+    b = rng.integers(-300, 300, size=(7, 3), dtype=np.int64).astype(np.int8)
+    _, (y,) = _run("int8_result_wraps.mlir", cuda, [a, b], [((5, 3), torch.int8)])
+    np.testing.assert_array_equal(y.cpu().numpy(), (a.astype(np.int32) @ b.astype(np.int32)).astype(np.int8))
+    p = rng.integers(0, 1 << 20, size=(6, 8)).astype(np.int32)
+    q = rng.integers(0, 1 << 20, size=(6, 2)).astype(np.int32)
+    _, (y,) = _run("unfused_slice_concat.mlir", cuda, [p, q], [((6, 6), torch.int32)])
+    np.testing.assert_array_equal(y.cpu().numpy(), np.concatenate([p[:, 1:8:2], q], axis=1) >> 3)

@@ -72,7 +72,7 @@ def test_config5_bf16_activations():
 
 @pytest.mark.parametrize("name,needle", [
     ("reject_unfused_add.mlir", "stablehlo.tanh"),
-    ("reject_escaping_intermediate.mlir", "also used on line"),
+    ("reject_unsupported_op_after_unfused_chain.mlir", "stablehlo.negate"),
 ])
 def test_unsupported_programs_fail_at_compile_time_naming_the_op(name, needle):
     with pytest.raises(_lib.QmmError) as e:
@@ -94,13 +94,66 @@ def test_malformed_and_foreign_programs():
     return %0 : tensor<8x4xf32>
   }
 }"""
+    exe = Executable(text)  # runs, but as a standalone dot: the trace says so and why
+    assert fused(exe) == [] and lib_fused_steps(exe) == 0
+    (nf,) = [t for t in exe.trace() if t["event"] == "not_fused"]
+    assert nf["op"] == "stablehlo.dot_general" and "plain float" in nf["reason"]
+    # group size other than 128: no kernel fuses it, so the chain runs op by op and the trace names the reason
+    exe = Executable(load("cfg3_w4a16.mlir").replace("32x128x14336", "64x64x14336").replace("32x14336", "64x14336"))
+    assert lib_fused_steps(exe) == 0
+    assert "group 128" in [t for t in exe.trace() if t.get("reason")][0]["reason"]
+
+
+def lib_fused_steps(exe):
+    return _lib.load().qmm_plan_num_fused_steps(exe._h)
+
+
+def not_fused_ops(exe):
+    return [t["op"] for t in exe.trace() if t["event"] == "not_fused"]
+
+
+def test_a_chain_the_matcher_declines_runs_op_by_op_and_says_so():
+    # the dequantised weight is also returned: fusing would lose it, so every op runs on its own
+    exe = Executable(load("unfused_escaping_intermediate.mlir"))
+    assert fused(exe) == [] and lib_fused_steps(exe) == 0 and exe.num_steps == 4
+    assert not_fused_ops(exe) == ["stablehlo.dot_general", "stablehlo.convert", "stablehlo.broadcast_in_dim",
+                                  "stablehlo.multiply"]
+    reason = [t for t in exe.trace() if t["event"] == "not_fused" and "reason" in t][0]["reason"]
+    assert "also used elsewhere" in reason
+    assert exe.workspace_bytes >= 2 * 256 * 128 * 4  # the convert and broadcast results are temporaries
+    # a [N, K] weight behind a transpose, and a dot that contracts the rhs on dimension 1
+    exe = Executable(load("unfused_transposed_weight.mlir"))
+    assert lib_fused_steps(exe) == 0 and "stablehlo.transpose" in not_fused_ops(exe)
+    exe = Executable(load("unfused_contract_rhs_dim1.mlir"))
+    assert lib_fused_steps(exe) == 0 and "stablehlo.dot_general" in not_fused_ops(exe)
+
+
+def test_legacy_dot_trailing_convert_and_constants_fuse():
+    exe = Executable(load("legacy_dot_w8a32.mlir"))
+    (f,) = fused(exe)
+    assert f["kernel"] == "qmm_w8a32_perchannel" and (f["M"], f["N"], f["K"]) == (32, 128, 256)
+    exe = Executable(load("cfg5_f32_accumulate_then_convert.mlir"))
+    (f,) = fused(exe)
+    assert f["kernel"] == "qmm_w8a16_perchannel" and f["ops_fused"] == 6 and exe.num_steps == 1
+    # weights and scales closed over as dense constants are arguments the plan owns; the bias add runs after
+    exe = Executable(load("const_weight_bias_add.mlir"))
+    (f,) = fused(exe)
+    assert f["kernel"] == "qmm_w8a32_perchannel" and exe.num_args == 2 and exe.num_steps == 3
+    assert not_fused_ops(exe) == ["stablehlo.broadcast_in_dim", "stablehlo.add"]
+    exe = Executable(load("int8_result_wraps.mlir"))
+    assert fused(exe) == [] and exe.num_steps == 1  # an i8-typed result: the standalone integer dot wraps it
+    exe = Executable(load("unfused_slice_concat.mlir"))
+    assert exe.num_steps == 5 and lib_fused_steps(exe) == 0
+
+
+def test_constant_parsing_errors():
+    bad = load("const_weight_bias_add.mlir").replace("[10, -11, 12]]", "[10, -11]]")
     with pytest.raises(_lib.QmmError) as e:
-        Executable(text)
-    assert e.value.status_name == "QMM_ERR_UNSUPPORTED" and "plain float" in str(e.value)
-    # group size other than 128
-    with pytest.raises(_lib.QmmError) as e:
-        Executable(load("cfg3_w4a16.mlir").replace("32x128x14336", "64x64x14336").replace("32x14336", "64x14336"))
-    assert "group 128" in str(e.value)
+        Executable(bad)
+    assert e.value.status_name == "QMM_ERR_PARSE" and "values" in str(e.value)
+    hexed = load("const_weight_bias_add.mlir").replace(
+        "dense<[[1, -2, 3], [4, 5, -6], [-7, 8, 9], [10, -11, 12]]>", 'dense<"0x01FE030405FAF908090AF50C">')
+    assert Executable(hexed).num_args == 2
 
 
 def test_a_layer_of_four_linears_is_four_fused_steps_with_introspection():
