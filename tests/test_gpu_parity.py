@@ -140,8 +140,8 @@ def test_w4a16_workspace_is_left_clean_and_results_repeat(cuda):
     need = _lib.load().qmm_w4a16_g128_workspace_bytes(4, 14336, 4096)
     ws = torch.zeros(need, dtype=torch.uint8, device=cuda)
     y1 = ops.w4a16_g128(*args, workspace=ws).clone()
-    flags = ws[: (2048 + 2048) * 8 * 4].view(torch.int32)  # the header: one flag per (block + CTA, warp)
-    assert int(flags.abs().sum()) == 0  # every flag was cleared by the warp that consumed it
+    counters = ws[: 2048 * 8 * 4].view(torch.int32)  # the header: one arrival counter per (column block, warp)
+    assert int(counters.abs().sum()) == 0
     y2 = ops.w4a16_g128(*args, workspace=ws)
     assert torch.equal(y1, y2)  # fixed summation order: bitwise repeatable
 
@@ -150,9 +150,10 @@ def test_w4a16_rejects_what_it_does_not_cover(cuda):
     c = synthetic.config3(1, 256, 128)
     x = dev(c["x_bits"].view(np.int16), cuda, torch.bfloat16)
     wq, s, z = dev(c["wq"], cuda), dev(c["s_bits"].view(np.int16), cuda, torch.bfloat16), dev(c["z"], cuda)
-    with pytest.raises(_lib.QmmError) as e:
-        ops.w4a16_g128(x, wq, s, z, group=64)
-    assert e.value.status_name == "QMM_ERR_UNSUPPORTED"
+    lib = _lib.load()
+    st = lib.qmm_w4a16_g128(x.data_ptr(), wq.data_ptr(), s.data_ptr(), z.data_ptr(), 0, x.data_ptr(), 1, 128, 256, 64,
+                            None, 0, 0, None)  # a group size the kernels do not cover
+    assert lib.qmm_status_name(st) == b"QMM_ERR_UNSUPPORTED"
     with pytest.raises(_lib.QmmError) as e:
         ops.w4a16_g128(x, wq, s, z, workspace=torch.zeros(256, dtype=torch.uint8, device=cuda)[:16])
     assert e.value.status_name == "QMM_ERR_WORKSPACE"
