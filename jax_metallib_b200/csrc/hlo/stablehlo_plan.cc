@@ -610,6 +610,75 @@ static bool match_unpack4(const Module& m, const std::string& v, int* warg, std:
   return true;
 }
 
+// ---------------------------------------------------------------------------
+// Explicit route: stablehlo.custom_call @qmm_b200.qmm with a JSON backend_config.
+// A guaranteed-fused entry that does not depend on the matcher recognising a jnp spelling; the
+// mechanism follows the reference's native-kernel custom call (src/jax_plugins/silicon/
+// _native_metal.py:34-60,179-196, dispatched in src/pjrt_plugin/ops/control_flow_ops.mm:1194-1222),
+// and its conventions for the descriptor (runtime/custom_metal_kernel.mm:129-193): versioned JSON,
+// exact-key validation, a size limit.
+//   {"version":1,"op":"w8a32_perchannel"}          operands (x f32, w i8, scale f32)      -> f32
+//   {"version":1,"op":"w8a16_perchannel"}          operands (x bf16, w i8, scale f32)     -> bf16
+//   {"version":1,"op":"i8i8_i32"}                  operands (a, b) -> i32, or (a, b, row, col) -> f32
+//   {"version":1,"op":"w4a16_g128","zeros_packed":true|false}
+//                                                  operands (x bf16, wq u8, scales bf16, zeros) -> bf16
+// ---------------------------------------------------------------------------
+constexpr const char* kCustomCallTarget = "qmm_b200.qmm";
+
+// A flat JSON object of string / integer / boolean values.  Returns false with `err` set.
+static bool parse_flat_json(const std::string& j, std::map<std::string, std::string>& out, std::string& err) {
+  size_t i = 0;
+  auto ws = [&] { while (i < j.size() && (j[i] == ' ' || j[i] == '\t' || j[i] == '\n')) ++i; };
+  auto str = [&](std::string& v) -> bool {
+    if (i >= j.size() || j[i] != '"') return false;
+    ++i;
+    v.clear();
+    while (i < j.size() && j[i] != '"') {
+      if (j[i] == '\\') return false;  // no escapes inside this descriptor's strings
+      v += j[i++];
+    }
+    if (i >= j.size()) return false;
+    ++i;
+    return true;
+  };
+  ws();
+  if (i >= j.size() || j[i] != '{') { err = "backend_config must be a JSON object"; return false; }
+  ++i;
+  ws();
+  if (i < j.size() && j[i] == '}') return true;
+  while (true) {
+    std::string k, v;
+    ws();
+    if (!str(k)) { err = "invalid backend_config JSON: expected a key"; return false; }
+    ws();
+    if (i >= j.size() || j[i] != ':') { err = "invalid backend_config JSON: expected ':'"; return false; }
+    ++i;
+    ws();
+    if (i < j.size() && j[i] == '"') {
+      if (!str(v)) { err = "invalid backend_config JSON: bad string"; return false; }
+      v = "s:" + v;
+    } else {
+      size_t b = i;
+      while (i < j.size() && j[i] != ',' && j[i] != '}' && j[i] != ' ') ++i;
+      v = j.substr(b, i - b);
+      if (v != "true" && v != "false" && (v.empty() || v.find_first_not_of("-0123456789") != std::string::npos)) {
+        err = "invalid backend_config JSON: value of '" + k + "' must be a string, an integer or a boolean";
+        return false;
+      }
+    }
+    if (out.count(k)) { err = "backend_config repeats the key '" + k + "'"; return false; }
+    out[k] = v;
+    ws();
+    if (i < j.size() && j[i] == ',') { ++i; continue; }
+    if (i < j.size() && j[i] == '}') { ++i; break; }
+    err = "invalid backend_config JSON: expected ',' or '}'";
+    return false;
+  }
+  ws();
+  if (i != j.size()) { err = "invalid backend_config JSON: trailing characters"; return false; }
+  return true;
+}
+
 static int build_plan(Plan& plan) {
   Module& m = plan.mod;
   const int A = (int)m.arg_names.size(), R = (int)m.returns.size();
@@ -891,6 +960,121 @@ static int build_plan(Plan& plan) {
     }
     return QMM_OK;
   };
+
+  // ---- explicit custom calls
+  for (size_t ci = 0; ci < m.ops.size(); ++ci) {
+    const Op& op = m.ops[ci];
+    if (op.name != "stablehlo.custom_call") continue;
+    size_t at = op.body.find('@');
+    size_t par = at == std::string::npos ? std::string::npos : op.body.find('(', at);
+    const std::string target = par == std::string::npos ? "" : trim(op.body.substr(at + 1, par - at - 1));
+    if (target != kCustomCallTarget)
+      return set_error(QMM_ERR_UNSUPPORTED, "line %d: custom_call target '%s' is not one this backend executes (only @%s)",
+                       op.line, target.c_str(), kCustomCallTarget);
+    size_t bc = op.body.find("backend_config");
+    size_t q0 = bc == std::string::npos ? std::string::npos : op.body.find('"', bc);
+    if (q0 == std::string::npos) return set_error(QMM_ERR_PARSE, "line %d: custom_call without a backend_config string", op.line);
+    std::string json;
+    size_t q = q0 + 1;
+    for (; q < op.body.size() && op.body[q] != '"'; ++q) {
+      if (op.body[q] == '\\' && q + 1 < op.body.size()) json += op.body[++q];  // \" inside the MLIR string attribute
+      else json += op.body[q];
+    }
+    if (q >= op.body.size()) return set_error(QMM_ERR_PARSE, "line %d: unterminated backend_config", op.line);
+    if (json.size() > 4096) return set_error(QMM_ERR_INVALID_ARGUMENT, "line %d: backend_config larger than 4096 bytes", op.line);
+    std::map<std::string, std::string> cfg;
+    std::string jerr;
+    if (!parse_flat_json(json, cfg, jerr)) return set_error(QMM_ERR_INVALID_ARGUMENT, "line %d: %s", op.line, jerr.c_str());
+    if (!cfg.count("version") || !cfg.count("op"))
+      return set_error(QMM_ERR_INVALID_ARGUMENT, "line %d: backend_config needs the keys \"version\" and \"op\"", op.line);
+    if (cfg["version"] != "1")
+      return set_error(QMM_ERR_INVALID_ARGUMENT, "line %d: unsupported backend_config version (expected 1)", op.line);
+    const std::string kind = cfg["op"].compare(0, 2, "s:") == 0 ? cfg["op"].substr(2) : "";
+    for (auto& kv : cfg) {
+      const bool known = kv.first == "version" || kv.first == "op" || (kind == "w4a16_g128" && kv.first == "zeros_packed");
+      if (!known)
+        return set_error(QMM_ERR_INVALID_ARGUMENT, "line %d: backend_config has the unknown key \"%s\"", op.line, kv.first.c_str());
+    }
+    Step st;
+    st.anchor_line = op.line;
+    st.anchor_op = (int)ci;
+    const size_t no = op.operands.size();
+    auto elem = [&](size_t k) { return k < op.in_types.size() ? op.in_types[k].elem : std::string(); };
+    auto dims = [&](size_t k) -> const std::vector<int64_t>& { return op.in_types[k].dims; };
+    const TType& ot = op.out_type;
+    auto bad = [&](const char* what) {
+      return set_error(QMM_ERR_INVALID_ARGUMENT, "line %d: custom_call @%s op \"%s\": %s", op.line, kCustomCallTarget,
+                       kind.c_str(), what);
+    };
+    if (op.in_types.size() != no || no < 2 || dims(0).size() != 2 || dims(1).size() != 2 || ot.dims.size() != 2)
+      return bad("operands and result must be rank-2 tensors with a full type signature");
+    st.M = dims(0)[0];
+    st.N = ot.dims[1];
+    if (kind == "w8a32_perchannel" || kind == "w8a16_perchannel") {
+      const bool f32 = kind == "w8a32_perchannel";
+      if (no != 3 || elem(0) != (f32 ? "f32" : "bf16") || elem(1) != "i8" || elem(2) != "f32" || ot.elem != elem(0))
+        return bad("expects (x, w: i8, scale: f32) with x and the result f32 (w8a32) or bf16 (w8a16)");
+      st.K = dims(0)[1];
+      if (dims(1)[0] != st.K || dims(1)[1] != st.N || dims(2) != std::vector<int64_t>{st.N} || ot.dims[0] != st.M)
+        return bad("shapes must be x [M,K], w [K,N], scale [N] -> [M,N]");
+      st.kind = f32 ? kW8A32 : kW8A16;
+      st.x = slot_of(op.operands[0]);
+      st.w = slot_of(op.operands[1]);
+      st.scale = slot_of(op.operands[2]);
+      st.out = slot_of(op.result);
+    } else if (kind == "i8i8_i32") {
+      const bool ints = (elem(0) == "i8" || elem(0) == "ui8") && (elem(1) == "i8" || elem(1) == "ui8");
+      st.K = dims(0)[1];
+      if (!ints || dims(1)[0] != st.K || dims(1)[1] != st.N || ot.dims[0] != st.M) return bad("expects a [M,K] and b [K,N] of i8 / ui8");
+      st.kind = kI8Dot;
+      st.x = slot_of(op.operands[0]);
+      st.w = slot_of(op.operands[1]);
+      st.a_unsigned = elem(0) == "ui8";
+      st.b_unsigned = elem(1) == "ui8";
+      if (no == 2 && ot.elem == "i32") {
+        st.acc_out = slot_of(op.result);
+      } else if (no == 4 && ot.elem == "f32" && elem(2) == "f32" && elem(3) == "f32" &&
+                 dims(2) == std::vector<int64_t>{st.M} && dims(3) == std::vector<int64_t>{st.N}) {
+        st.row = slot_of(op.operands[2]);
+        st.col = slot_of(op.operands[3]);
+        st.out = slot_of(op.result);
+      } else {
+        return bad("expects (a, b) -> i32 or (a, b, row: f32 [M], col: f32 [N]) -> f32");
+      }
+    } else if (kind == "w4a16_g128") {
+      st.K = dims(0)[1];
+      if (no != 4 || elem(0) != "bf16" || (elem(1) != "ui8" && elem(1) != "i8") || elem(2) != "bf16" || ot.elem != "bf16")
+        return bad("expects (x: bf16, wq: ui8, scales: bf16, zeros) -> bf16");
+      const bool packed_type = elem(3) == "ui4";
+      const bool packed_cfg = cfg.count("zeros_packed") && cfg["zeros_packed"] == "true";
+      if (cfg.count("zeros_packed") && cfg["zeros_packed"] != "true" && cfg["zeros_packed"] != "false")
+        return bad("\"zeros_packed\" must be true or false");
+      st.zeros_packed = packed_type || packed_cfg;
+      const int64_t G = st.K / 128;
+      const std::vector<int64_t> zshape = (st.zeros_packed && !packed_type) ? std::vector<int64_t>{G, st.N / 2}
+                                                                             : std::vector<int64_t>{G, st.N};
+      if (st.K % 128 || dims(1)[0] * 2 != st.K || dims(1)[1] != st.N || dims(2) != std::vector<int64_t>{G, st.N} ||
+          dims(3) != zshape || ot.dims[0] != st.M || (elem(3) != "ui4" && elem(3) != "ui8" && elem(3) != "i8"))
+        return bad("shapes must be x [M,K], wq [K/2,N], scales [K/128,N], zeros [K/128,N] (ui4, or ui8; [K/128,N/2] "
+                   "bytes with zeros_packed) -> [M,N]");
+      st.kind = kW4A16;
+      st.x = slot_of(op.operands[0]);
+      st.w = slot_of(op.operands[1]);
+      st.scale = slot_of(op.operands[2]);
+      st.zeros = slot_of(op.operands[3]);
+      st.out = slot_of(op.result);
+    } else {
+      return set_error(QMM_ERR_INVALID_ARGUMENT,
+                       "line %d: backend_config \"op\" must be one of w8a32_perchannel, w8a16_perchannel, i8i8_i32, "
+                       "w4a16_g128", op.line);
+    }
+    st.fused_ops = 1;
+    consumed.insert((int)ci);
+    static const char* kind_name[] = {"qmm_w8a32_perchannel", "qmm_w8a16_perchannel", "qmm_i8i8_i32", "qmm_w4a16_g128"};
+    tracef(plan.trace, "{\"event\":\"custom_call\",\"anchor_line\":%d,\"kernel\":\"%s\",\"M\":%lld,\"N\":%lld,\"K\":%lld}",
+           op.line, kind_name[st.kind], (long long)st.M, (long long)st.N, (long long)st.K);
+    plan.steps.push_back(st);
+  }
 
   for (size_t di = 0; di < m.ops.size(); ++di) {
     const Op& dot = m.ops[di];

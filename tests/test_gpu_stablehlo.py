@@ -129,3 +129,28 @@ def test_int8_typed_dot_wraps_and_shape_ops(cuda):
     q = rng.integers(0, 1 << 20, size=(6, 2)).astype(np.int32)
     _, (y,) = _run("unfused_slice_concat.mlir", cuda, [p, q], [((6, 6), torch.int32)])
     np.testing.assert_array_equal(y.cpu().numpy(), np.concatenate([p[:, 1:8:2], q], axis=1) >> 3)
+
+
+def test_custom_call_route_runs_the_named_kernels(cuda):
+    from jax_metallib_b200 import custom_call as cc
+
+    c = synthetic.config5_small(256, 512, 384)
+    text = cc.module_text(["tensor<256x512xbf16>", "tensor<512x384xi8>", "tensor<384xf32>"], "tensor<256x384xbf16>",
+                          cc.backend_config("w8a16_perchannel"))
+    exe = Executable(text)
+    out = torch.empty((256, 384), dtype=torch.bfloat16, device=cuda)
+    exe([dev(c["x_bits"].view(np.int16), cuda, torch.bfloat16), dev(c["w"], cuda), dev(c["scale"], cuda)], [out])
+    assert O.max_rel_err(bf16_np(out), O.w8_perchannel_matmul(c["x"], c["w"], c["scale"])) <= 1e-2
+    c = synthetic.config2(128, 256, 384)
+    text = cc.module_text(["tensor<128x256xi8>", "tensor<256x384xi8>", "tensor<128xf32>", "tensor<384xf32>"],
+                          "tensor<128x384xf32>", cc.backend_config("i8i8_i32"))
+    out = torch.empty((128, 384), dtype=torch.float32, device=cuda)
+    Executable(text)([dev(c["a"], cuda), dev(c["b"], cuda), dev(c["row"], cuda), dev(c["col"], cuda)], [out])
+    np.testing.assert_array_equal(out.cpu().numpy(), O.i8_dot_rescale(O.i8_dot_i32(c["a"], c["b"]), c["row"], c["col"]))
+    c = synthetic.config3(4, 1024, 512)
+    text = cc.module_text(["tensor<4x1024xbf16>", "tensor<512x512xui8>", "tensor<8x512xbf16>", "tensor<8x256xui8>"],
+                          "tensor<4x512xbf16>", cc.backend_config("w4a16_g128", zeros_packed=True))
+    out = torch.empty((4, 512), dtype=torch.bfloat16, device=cuda)
+    Executable(text)([dev(c["x_bits"].view(np.int16), cuda, torch.bfloat16), dev(c["wq"], cuda),
+                      dev(c["s_bits"].view(np.int16), cuda, torch.bfloat16), dev(c["z_packed"], cuda)], [out])
+    assert O.max_rel_err(bf16_np(out), O.w4a16_matmul(c["x"], c["wq"], c["s"], c["z"])) <= 1e-2

@@ -178,3 +178,59 @@ def test_a_layer_of_four_linears_is_four_fused_steps_with_introspection():
     assert lib.qmm_plan_name(exe._h) == b"jit_layer"
     assert lib.qmm_plan_num_replicas(exe._h) == 1 and lib.qmm_plan_num_partitions(exe._h) == 1
     assert lib.qmm_plan_flops(exe._h) == 2.0 * 256 * (512 * (640 + 512 + 3584) + 1792 * 512)
+
+
+# ---- the explicit custom_call route ---------------------------------------------------------------
+def test_custom_call_route_builds_the_named_kernel():
+    from jax_metallib_b200 import custom_call as cc
+
+    text = cc.module_text(["tensor<256x512xbf16>", "tensor<512x384xi8>", "tensor<384xf32>"], "tensor<256x384xbf16>",
+                          cc.backend_config("w8a16_perchannel"))
+    exe = Executable(text)
+    assert exe.num_steps == 1 and lib_fused_steps(exe) == 1 and fused(exe) == []
+    (t,) = [t for t in exe.trace() if t["event"] == "custom_call"]
+    assert t["kernel"] == "qmm_w8a16_perchannel" and (t["M"], t["N"], t["K"]) == (256, 384, 512)
+    text = cc.module_text(["tensor<4x4096xbf16>", "tensor<2048x14336xui8>", "tensor<32x14336xbf16>", "tensor<32x14336xui4>"],
+                          "tensor<4x14336xbf16>", cc.backend_config("w4a16_g128"))
+    exe = Executable(text)
+    assert exe.workspace_bytes >= _lib.load().qmm_w4a16_g128_workspace_bytes(4, 14336, 4096)
+    text = cc.module_text(["tensor<4x4096xbf16>", "tensor<2048x14336xui8>", "tensor<32x14336xbf16>", "tensor<32x7168xui8>"],
+                          "tensor<4x14336xbf16>", cc.backend_config("w4a16_g128", zeros_packed=True))
+    assert Executable(text).num_steps == 1
+    text = cc.module_text(["tensor<64x128xi8>", "tensor<128x256xui8>", "tensor<64xf32>", "tensor<256xf32>"],
+                          "tensor<64x256xf32>", cc.backend_config("i8i8_i32"))
+    assert [t["kernel"] for t in Executable(text).trace() if t["event"] == "custom_call"] == ["qmm_i8i8_i32"]
+
+
+def test_custom_call_descriptor_is_validated_key_by_key():
+    from jax_metallib_b200 import custom_call as cc
+
+    types = (["tensor<32x64xf32>", "tensor<64x16xi8>", "tensor<16xf32>"], "tensor<32x16xf32>")
+
+    def compile_with(config, target=None):
+        text = cc.module_text(*types, config)
+        if target:
+            text = text.replace("@" + cc.TARGET, "@" + target)
+        return Executable(text)
+
+    assert compile_with(cc.backend_config("w8a32_perchannel")).num_steps == 1
+    for config, needle in [
+        ('{"version":2,"op":"w8a32_perchannel"}', "version"),
+        ('{"version":1}', "needs the keys"),
+        ('{"version":1,"op":"w8a32_perchannel","grid":4}', "unknown key"),
+        ('{"version":1,"op":"gemm"}', "must be one of"),
+        ('{"version":1,"op":"w8a32_perchannel","op":"x"}', "repeats"),
+        ('[1]', "JSON object"),
+        ('{"version":1,"op":"w8a16_perchannel"}', "expects"),  # operand types do not fit the named kernel
+        ('{"version":1,"op":"w8a32_perchannel","pad":"' + "x" * 5000 + '"}', "4096"),
+    ]:
+        with pytest.raises(_lib.QmmError) as e:
+            compile_with(config)
+        assert needle in str(e.value), (config[:60], str(e.value))
+    with pytest.raises(_lib.QmmError) as e:
+        compile_with(cc.backend_config("w8a32_perchannel"), target="somebody.else")
+    assert "somebody.else" in str(e.value) and e.value.status_name == "QMM_ERR_UNSUPPORTED"
+    with pytest.raises(ValueError):
+        cc.backend_config("w8a32_perchannel", zeros_packed=True)
+    with pytest.raises(ValueError):
+        cc.backend_config("dense")
