@@ -611,6 +611,8 @@ def run_detail(torch, ops, synthetic, lib, device, peaks, items=None):
 
     if want("int4_decode"):
         _detail_int4_decode(torch, ops, synthetic, lib, device, hbm, graph_time, detail)
+    if want("int4_prefill"):
+        _detail_int4_prefill(torch, ops, synthetic, device, peaks, detail)
     if want("int8_dot"):
         _detail_int8_dot(torch, synthetic, lib, device, peaks, graph_time, detail)
     if items is not None and "int4_decode_sweep" in items:  # not part of the default run
@@ -648,6 +650,37 @@ def _detail_int4_decode(torch, ops, synthetic, lib, device, hbm, graph_time, det
             "us": us, "bytes": nbytes, "GB/s": gbs, "frac_of_measured_hbm": gbs / hbm, "frac_of_8TBs": gbs / 8000.0,
             "us_warm_l2_single_copy": us_warm,
             "note": f"{copies} rotating weight copies (cold L2), zero points packed 4-bit, CUDA-graph replay"}
+    del wqs
+
+
+def _detail_int4_prefill(torch, ops, synthetic, device, peaks, detail):
+    # int4 g128 weight-only matmul at prefill sizes: the tcgen05 GEMM with in-kernel nibble dequantisation
+    K, N, G = 4096, 14336, 32
+    gen = synthetic.torch_generator(device, 3, 50)
+    copies = 6  # 6 x 29 MB of packed weights; the activations (33 MB at M = 4096) add to the L2 pressure
+    wqs = [torch.randint(0, 256, (K // 2, N), dtype=torch.uint8, device=device, generator=gen) for _ in range(copies)]
+    sc = synthetic.device_uniform((G, N), 0.002, 0.01, device, gen, torch.bfloat16)
+    zp = torch.randint(0, 256, (G, N // 2), dtype=torch.uint8, device=device, generator=gen)
+    for M in (512, 4096):
+        x = synthetic.device_normal((M, K), device, gen, torch.bfloat16)
+        y = torch.empty((M, N), dtype=torch.bfloat16, device=device)
+        for i in range(3):
+            ops.w4a16_g128(x, wqs[i % copies], sc, zp, zeros_packed=True, out=y)
+        torch.cuda.synchronize()
+        reps = 24
+        e0 = torch.cuda.Event(enable_timing=True)
+        e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(reps):
+            ops.w4a16_g128(x, wqs[i % copies], sc, zp, zeros_packed=True, out=y)
+        e1.record()
+        e1.synchronize()
+        us = e0.elapsed_time(e1) * 1e3 / reps
+        tf = 2.0 * M * K * N / (us * 1e-6) / 1e12
+        detail[f"int4_g128_prefill_M{M}"] = {
+            "us": us, "TFLOP/s": tf, "frac_of_measured_bf16_burst": tf / peaks["bf16_tflops"],
+            "note": "w8a16_kernel<4>: tcgen05 kind::f16 after in-kernel nibble dequantisation; back-to-back launches "
+                    "(dependent, so they do not overlap), rotating weight copies"}
     del wqs
 
 
@@ -873,7 +906,7 @@ def main():
     ap.add_argument("--detail-only", action="store_true",
                     help="run only the per-workload detail (small case for profiling) and print it as JSON")
     ap.add_argument("--detail-items", default="",
-                    help="comma-separated subset of int4_decode,int8_dot,llama_decode,operator_api,small_f32 (and int4_decode_sweep, "
+                    help="comma-separated subset of int4_decode,int4_prefill,int8_dot,llama_decode,operator_api,small_f32 (and int4_decode_sweep, "
                          "which is not part of the default run)")
     args = ap.parse_args()
     if args.impl == "reference":

@@ -146,6 +146,10 @@ struct qmm_rt_device {
   qmm_rt_client* client = nullptr;
   int id = 0;        // global id == local hardware id (one process)
   int ordinal = 0;   // CUDA device ordinal
+  // Streams (and with them the device's CUDA context) are created when the device is first used,
+  // so a client on a box with eight GPUs touches only the GPUs it is given work for.
+  std::mutex stream_mu;
+  bool streams_ready = false;
   cudaStream_t exec = nullptr, d2h = nullptr;
   std::string kind, debug, text;
   std::unique_ptr<qmm_rt_memory> memory;
@@ -237,6 +241,17 @@ int after_stream(qmm_rt_client* c, cudaStream_t stream, std::function<void()> fn
   return QMM_OK;
 }
 
+int device_ready(qmm_rt_device* d) {
+  QMM_REQUIRE(d != nullptr, QMM_ERR_INVALID_ARGUMENT, "null device");
+  std::lock_guard<std::mutex> lock(d->stream_mu);
+  if (d->streams_ready) return QMM_OK;
+  QMM_CUDA_TRY(cudaSetDevice(d->ordinal));
+  QMM_CUDA_TRY(cudaStreamCreateWithFlags(&d->exec, cudaStreamNonBlocking));
+  QMM_CUDA_TRY(cudaStreamCreateWithFlags(&d->d2h, cudaStreamNonBlocking));
+  d->streams_ready = true;
+  return QMM_OK;
+}
+
 int element_count(const int64_t* dims, int rank, int64_t* count) {
   int64_t n = 1;
   for (int i = 0; i < rank; ++i) {
@@ -272,6 +287,7 @@ int new_buffer(qmm_rt_client* c, qmm_rt_device* dev, int dtype, const int64_t* d
   size_t bytes = 0;
   if (int rc = tensor_bytes(dtype, dims, rank, &bytes)) return rc;
   QMM_REQUIRE(dev != nullptr && dev->client == c, QMM_ERR_INVALID_ARGUMENT, "the device does not belong to this client");
+  if (int rc = device_ready(dev)) return rc;
   QMM_CUDA_TRY(cudaSetDevice(dev->ordinal));
   // a zero-element shape still gets an address of its own (a placeholder allocation)
   const size_t alloc = bytes ? bytes : 256;
@@ -408,8 +424,6 @@ int qmm_rt_client_create(qmm_rt_client** out) {
   cudaRuntimeGetVersion(&rt);
   cudaDriverGetVersion(&drv);
   c->platform_version = std::string(qmm_version()) + "; CUDA runtime " + std::to_string(rt) + ", driver " + std::to_string(drv);
-  int prev = 0;
-  cudaGetDevice(&prev);
   for (int i = 0; i < n; ++i) {
     auto d = std::unique_ptr<qmm_rt_device>(new qmm_rt_device());
     d->client = c.get();
@@ -417,9 +431,6 @@ int qmm_rt_client_create(qmm_rt_client** out) {
     d->ordinal = i;
     cudaDeviceProp prop;
     QMM_CUDA_TRY(cudaGetDeviceProperties(&prop, i));
-    QMM_CUDA_TRY(cudaSetDevice(i));
-    QMM_CUDA_TRY(cudaStreamCreateWithFlags(&d->exec, cudaStreamNonBlocking));
-    QMM_CUDA_TRY(cudaStreamCreateWithFlags(&d->d2h, cudaStreamNonBlocking));
     d->kind = prop.name;
     d->bytes_limit = static_cast<int64_t>(prop.totalGlobalMem);
     d->debug = "QmmDevice(id=" + std::to_string(i) + ", kind=" + d->kind + ", sm_" + std::to_string(prop.major) +
@@ -432,7 +443,6 @@ int qmm_rt_client_create(qmm_rt_client** out) {
     d->memory->text = "device_memory:" + std::to_string(i);
     c->devices.push_back(std::move(d));
   }
-  cudaSetDevice(prev);
   qmm_rt_client* raw = c.get();
   c->worker = std::thread([raw] { raw->run(); });
   *out = c.release();
@@ -444,6 +454,7 @@ int qmm_rt_client_destroy(qmm_rt_client* c) {
   // everything queued on the client's streams completes first, so no host function is left
   // that could post to the completion thread after it has gone
   for (auto& d : c->devices) {
+    if (!d->streams_ready) continue;
     cudaSetDevice(d->ordinal);
     cudaStreamSynchronize(d->exec);
     cudaStreamSynchronize(d->d2h);
@@ -455,6 +466,7 @@ int qmm_rt_client_destroy(qmm_rt_client* c) {
   c->qcv.notify_all();
   if (c->worker.joinable()) c->worker.join();
   for (auto& d : c->devices) {
+    if (!d->streams_ready) continue;
     cudaSetDevice(d->ordinal);
     cudaStreamDestroy(d->exec);
     cudaStreamDestroy(d->d2h);
@@ -705,6 +717,7 @@ int qmm_rt_buffer_view_of_device_memory(qmm_rt_client* c, void* device_ptr, int 
   QMM_REQUIRE(device_ptr != nullptr || bytes == 0, QMM_ERR_INVALID_ARGUMENT, "null device pointer");
   qmm_rt_device* dev = pick_device(c, device);
   QMM_REQUIRE(dev != nullptr && dev->client == c, QMM_ERR_INVALID_ARGUMENT, "the device does not belong to this client");
+  if (int rc = device_ready(dev)) return rc;
   auto* b = new qmm_rt_buffer();
   b->client = c;
   b->device = dev;
@@ -912,7 +925,7 @@ int qmm_rt_executable_destroy(qmm_rt_executable* e) {
   for (auto& kv : e->workspace) {
     cudaSetDevice(kv.first);
     qmm_rt_device* d = qmm_rt_client_device(e->client, kv.first);
-    if (d) cudaStreamSynchronize(d->exec);  // a launch may still use it
+    if (d && d->streams_ready) cudaStreamSynchronize(d->exec);  // a launch may still use it
     cudaFree(kv.second);
   }
   qmm_plan_destroy(e->plan);
@@ -1036,6 +1049,7 @@ int qmm_rt_executable_execute(qmm_rt_executable* e, qmm_rt_buffer* const* const*
                   "argument %d does not have the element type and shape the program was compiled for", a);
     }
     QMM_REQUIRE(dev != nullptr, QMM_ERR_INVALID_ARGUMENT, "no device for list %d", d);
+    if (int rc = device_ready(dev)) return rc;
     QMM_CUDA_TRY(cudaSetDevice(dev->ordinal));
     for (int a = 0; a < num_args; ++a) {
       qmm_rt_buffer* b = argument_lists[d][a];
