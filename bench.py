@@ -275,6 +275,10 @@ def build_weights(torch, synthetic, device, rank, world, layers):
 # (K, N), from the ncu captures summarised in profiles/w8a16_kernel_dram_traffic.md.  Shapes that
 # were not captured are scaled by FLOPs from the nearest captured shape of the same K and said so.
 MEASURED_TRAFFIC = {
+    (8192, 10240): 417.29e6, (8192, 8192): 339.71e6, (8192, 57344): 2020.91e6, (28672, 8192): 1304.28e6,  # full width
+    (8192, 5120): 231.95e6, (8192, 4096): 199.90e6, (8192, 28672): 1065.67e6, (28672, 4096): 794.24e6,    # N / 2
+    (8192, 2560): 115.98e6, (8192, 2048): 85.28e6, (8192, 14336): 545.10e6, (28672, 2048): 295.03e6,      # N / 4
+    (8192, 1280): 164.82e6, (8192, 1024): 77.20e6, (8192, 7168): 295.67e6, (28672, 1024): 266.00e6,       # N / 8
 }
 
 
@@ -368,10 +372,11 @@ def run_gpu(args):
     result_host = torch.empty((world, M_TOKENS, shapes["down"][1] // world), dtype=torch.bfloat16).pin_memory()
     launches = [0]
 
-    def step():
+    def step(ex=None):
         # Every launch reads activations and weights that nothing on the stream writes, and writes a
         # slot whose previous use lies eight launches back: the launches are independent of their
         # predecessors, so each may fill the SMs that the last round of the one before leaves idle.
+        ex = ex or exchange[0]
         for li, layer in enumerate(weights):
             for name, k, n, ns, act, w, s in layer:
                 ex.linear(name, li & 1, acts[act], w, s, independent=True)
@@ -382,6 +387,34 @@ def run_gpu(args):
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
+
+    exchange = [ex]
+    tuned = None
+    if world > 1 and args.exchange == "auto" and ex.mode == "fused":
+        # Two ways to fill the gathered buffers are available here (multimem stores in the GEMM's
+        # epilogue; copy-engine peer copies).  Which one is faster depends on N: time two steps of each
+        # before the measurement and keep the faster one, the same choice on every rank.
+        alt = tp.GatherExchange(shapes, device, depth=2, mode="copy")
+        times = {}
+        for cand in (ex, alt):
+            step(cand)
+            barrier()
+            c0 = torch.cuda.Event(enable_timing=True)
+            c1 = torch.cuda.Event(enable_timing=True)
+            c0.record()
+            step(cand)
+            step(cand)
+            c1.record()
+            barrier()
+            t = torch.tensor([c0.elapsed_time(c1) / 2], dtype=torch.float64, device=device)
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            times[cand.mode] = float(t.item())
+        tuned = {"ms_per_step": times, "chosen": min(times, key=times.get)}
+        if tuned["chosen"] == "copy":
+            ex, alt = alt, ex
+        exchange[0] = ex
+        del alt
+        torch.cuda.empty_cache()
 
     # ---- resident-input timing -------------------------------------------------
     for _ in range(args.warmup):
@@ -539,7 +572,7 @@ def run_gpu(args):
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": workload_config(world, layers),
-            "exchange": {"mode": ex.mode, "detail": par},
+            "exchange": {"mode": ex.mode, "detail": par, "chosen_by_timing": tuned},
             "checked": checked,
             "check": {"rows": n_rows, "linears": 4, "max_rel_err": worst_err, "tolerance": 1e-2,
                       "what": "last layer's four gathered outputs, four rows of every 256-row tile, all columns, "
