@@ -423,6 +423,8 @@ struct Step {
   int anchor_line = 0;
   int anchor_op = 0;  // index of the op the step stands for (steps run in this order)
   int fused_ops = 0;
+  // how the fused kernel's arithmetic relates to the program as written: "as_written", or what differs
+  const char* numerics = "as_written";
   // standalone ops
   int gop = 0, bop = 0, in_dt = 0, out_dt = 0, b_transposed = 0;
   std::vector<int> ins;
@@ -790,8 +792,12 @@ static int build_plan(Plan& plan) {
           if (!view_of(m, other, v) || v.dim_of.size() != 2) break;
           const TType& at = m.arg_types[v.arg];
           if (at.elem != "f32" || at.dims.size() != 1) break;
-          if (v.dim_of[0] == 0 && v.dim_of[1] == -1 && at.dims[0] == M && got_row < 0) got_row = v.arg;
-          else if (v.dim_of[0] == -1 && v.dim_of[1] == 0 && at.dims[0] == N && got_col < 0) got_col = v.arg;
+          if (v.dim_of[0] == 0 && v.dim_of[1] == -1 && at.dims[0] == M && got_row < 0) {
+            got_row = v.arg;
+          } else if (v.dim_of[0] == -1 && v.dim_of[1] == 0 && at.dims[0] == N && got_col < 0) {
+            got_col = v.arg;
+            if (got_row < 0) st.numerics = "rescale_reordered: the kernel multiplies by the row scale first";
+          }
           else break;
           chain.push_back(mu);
           for (int o : v.ops) chain.push_back(o);
@@ -899,6 +905,8 @@ static int build_plan(Plan& plan) {
                            "line %d: the int4 kernel covers group 128 with bf16 activations and result "
                            "(got group %lld, %s -> %s)", dot.line, (long long)gs, lt.elem.c_str(), ot.elem.c_str());
         st.kind = kW4A16;
+        st.numerics = M <= 32 ? "f32_group_sums: (q - z) * s applied per 128-k group to f32 sums, not rounded to bf16 per weight"
+                              : "as_written";
         st.w = warg;
         st.scale = sv.arg;
         st.zeros = zv.arg;
@@ -945,6 +953,9 @@ static int build_plan(Plan& plan) {
         } else
           return set_error(QMM_ERR_UNSUPPORTED, "line %d: %s activations with %s result are not covered",
                            dot.line, lt.elem.c_str(), ot.elem.c_str());
+        if (lt.elem == "bf16")
+          st.numerics = "f32_scale_in_epilogue: the scale stays f32 and multiplies the f32 accumulator once; the program "
+                        "rounds the scale and every w * s product to bf16";
         st.w = warg;
         st.scale = sv.arg;
         st.out = slot_of(outv);
@@ -1129,9 +1140,9 @@ static int build_plan(Plan& plan) {
                                       "qmm_w4a16_g128"};
     tracef(plan.trace,
            "{\"event\":\"fused\",\"anchor_line\":%d,\"kernel\":\"%s\",\"M\":%lld,\"N\":%lld,\"K\":%lld,"
-           "\"ops_fused\":%d,\"rescale\":%s}",
+           "\"ops_fused\":%d,\"rescale\":%s,\"numerics\":\"%s\"}",
            dot.line, kind_name[st.kind], (long long)st.M, (long long)st.N, (long long)st.K, st.fused_ops,
-           (st.kind == kI8Dot && st.out >= 0) ? "true" : "false");
+           (st.kind == kI8Dot && st.out >= 0) ? "true" : "false", st.numerics);
     plan.steps.push_back(st);
   }
 

@@ -68,6 +68,12 @@ def test_config3_int4_chain():
 def test_config5_bf16_activations():
     (f,) = fused(Executable(load("cfg5_w8a16.mlir")))
     assert f["kernel"] == "qmm_w8a16_perchannel" and (f["M"], f["N"], f["K"]) == (4096, 1024, 8192)
+    # the trace says where the fused arithmetic departs from the program as written
+    assert f["numerics"].startswith("f32_scale_in_epilogue")
+    (f,) = fused(Executable(load("cfg1_w8a32.mlir")))
+    assert f["numerics"] == "as_written"
+    (f,) = fused(Executable(load("cfg3_w4a16.mlir")))
+    assert f["numerics"].startswith("f32_group_sums")
 
 
 @pytest.mark.parametrize("name,needle", [
