@@ -69,6 +69,11 @@ struct Module {
   std::map<std::string, int> argi;  // SSA name -> argument index
   int num_real_args = 0;            // arguments of @main; dense constants follow them as extra arguments
   std::vector<std::vector<uint8_t>> const_data;  // contents of the lifted constants, in argument order
+  // Contiguous slices (and reshapes) of arguments are further extra arguments that alias their source:
+  // (slot of the source, byte offset).  They follow the constants.  No data moves (the reference's
+  // input-slice views, src/pjrt_plugin/core/mps_executable.mm:7509-7603).
+  std::vector<std::pair<int, size_t>> views;
+  std::set<int> view_ops;  // the ops these views stand for
   std::string name = "main";        // module symbol (jit_<function> in what jax prints)
   int num_replicas = 1, num_partitions = 1;  // mhlo.num_replicas / mhlo.num_partitions of the module
   std::string error;
@@ -236,22 +241,393 @@ static int parse_dense(const std::string& body, const TType& t, std::vector<uint
   return 1;
 }
 
+// ---------------------------------------------------------------------------
+// Counted stablehlo.while loops are unrolled on the text, before the module is parsed, the way the
+// reference unrolls them at parse time (src/pjrt_plugin/core/stablehlo_parser.mm:116-519: counted
+// loops of a bounded trip count are replaced by their bodies, and dynamic_slice indices that depend
+// only on the induction variable become static slices), so that a model written as a lax.scan over
+// stacked per-layer weights reaches the matcher as straight-line code with one static slice per
+// layer.  A loop is unrolled when every value its condition depends on folds to a constant: integer
+// scalars are folded through constant, compare, add, subtract, multiply, select, convert, minimum,
+// maximum, clamp, and, or.  The trip count is capped (kMaxUnrollTrips, like the reference's 16,
+// raisable to 64).  Anything else about a while loop is an error naming the line.
+// ---------------------------------------------------------------------------
+struct SrcLine {
+  std::string text;
+  int line;
+};
+constexpr int kMaxUnrollTrips = 64;
+
+static bool is_name_char(char c) { return isalnum((unsigned char)c) || c == '_' || c == '#'; }
+
+// every %token of `s`, replaced through `sub` (longest names first is not needed: tokens are whole)
+static std::string substitute(const std::string& s, const std::map<std::string, std::string>& sub) {
+  std::string out;
+  for (size_t i = 0; i < s.size();) {
+    if (s[i] == '"') {  // string attributes are left alone
+      size_t e = s.find('"', i + 1);
+      e = e == std::string::npos ? s.size() : e + 1;
+      out += s.substr(i, e - i);
+      i = e;
+      continue;
+    }
+    if (s[i] != '%') { out += s[i++]; continue; }
+    size_t e = i + 1;
+    while (e < s.size() && is_name_char(s[e])) ++e;
+    const std::string tok = s.substr(i, e - i);
+    auto it = sub.find(tok);
+    out += it == sub.end() ? tok : it->second;
+    i = e;
+  }
+  return out;
+}
+
+static bool scalar_int_type(const std::string& t) {
+  return t == "tensor<i32>" || t == "tensor<i64>" || t == "tensor<i1>" || t == "tensor<ui32>" || t == "tensor<i8>" ||
+         t == "tensor<ui8>" || t == "tensor<i16>";
+}
+
+struct Unroller {
+  std::string err;
+  int uid = 0;
+
+  // Emits `in` into `out`, unrolling whiles; `known` = scalar integer values by SSA name; `sub` = renames.
+  bool run(const std::vector<SrcLine>& in, std::vector<SrcLine>& out, std::map<std::string, long long>& known,
+           std::map<std::string, std::string>& sub, int depth) {
+    if (depth > 4) return fail(in.empty() ? 0 : in[0].line, "while loops nested too deeply");
+    for (size_t i = 0; i < in.size(); ++i) {
+      std::string l = substitute(trim(in[i].text), sub);
+      size_t loc = l.find(" loc(");
+      if (loc != std::string::npos) l = trim(l.substr(0, loc));
+      const int ln = in[i].line;
+      if (l.find("stablehlo.while") == std::string::npos || l.empty() || l[0] != '%') {
+        if (!fold_or_emit(l, ln, out, known)) return false;
+        continue;
+      }
+      // ---- %r:n = stablehlo.while(%iterArg = %init, ...) : types
+      size_t eq = l.find(" = ");
+      std::string res = trim(l.substr(0, eq));
+      int nres = 1;
+      size_t colon = res.find(':');
+      if (colon != std::string::npos) {
+        nres = atoi(res.c_str() + colon + 1);
+        res = res.substr(0, colon);
+      }
+      size_t a = l.find('(', eq), b = l.find(')', a);
+      if (a == std::string::npos || b == std::string::npos) return fail(ln, "malformed stablehlo.while");
+      std::vector<std::string> iter_names, init;
+      for (auto& pr : split_top(l.substr(a + 1, b - a - 1))) {
+        size_t e2 = pr.find('=');
+        if (e2 == std::string::npos) return fail(ln, "malformed stablehlo.while operand list");
+        iter_names.push_back(trim(pr.substr(0, e2)));
+        init.push_back(trim(pr.substr(e2 + 1)));
+      }
+      if ((int)iter_names.size() != nres) return fail(ln, "stablehlo.while: result count does not match its operands");
+      size_t tc = l.find(" : ", b);
+      std::vector<std::string> types = tc == std::string::npos ? std::vector<std::string>() : split_top(l.substr(tc + 3));
+      if ((int)types.size() != nres) return fail(ln, "stablehlo.while: one type per loop-carried value expected");
+      // ---- regions
+      std::vector<SrcLine> cond, body;
+      size_t j = i + 1;
+      auto is_open = [&](const std::string& t, const char* what) { return trim(t) == what; };
+      if (j >= in.size() || !is_open(in[j].text, "cond {")) return fail(ln, "stablehlo.while: expected 'cond {'");
+      ++j;
+      int nest = 0;
+      for (; j < in.size(); ++j) {
+        const std::string t = trim(in[j].text);
+        if (nest == 0 && t == "} do {") break;
+        if (!t.empty() && t.back() == '{') ++nest;
+        if (!t.empty() && t[0] == '}') --nest;
+        cond.push_back(in[j]);
+      }
+      if (j >= in.size()) return fail(ln, "stablehlo.while: expected '} do {'");
+      ++j;
+      nest = 0;
+      for (; j < in.size(); ++j) {
+        const std::string t = trim(in[j].text);
+        if (nest == 0 && t == "}") break;
+        if (!t.empty() && t.back() == '{') ++nest;
+        if (!t.empty() && t[0] == '}') --nest;
+        body.push_back(in[j]);
+      }
+      if (j >= in.size()) return fail(ln, "stablehlo.while: unterminated body");
+      i = j;  // continue after the closing brace
+      // ---- iterate
+      std::vector<std::string> cur = init;  // SSA names (outer scope or renamed), or "" when only a constant is carried
+      std::vector<bool> has_const(nres, false);
+      std::vector<long long> cval(nres, 0);
+      for (int k = 0; k < nres; ++k) {
+        auto kn = known.find(init[k]);
+        if (kn != known.end() && scalar_int_type(types[k])) {
+          has_const[k] = true;
+          cval[k] = kn->second;
+        }
+      }
+      const int my = uid++;
+      int trip = 0;
+      while (true) {
+        auto bind = [&](std::map<std::string, long long>& kn, std::map<std::string, std::string>& sb) {
+          for (int k = 0; k < nres; ++k) {
+            if (has_const[k]) kn[iter_names[k]] = cval[k];
+            else kn.erase(iter_names[k]);
+            sb[iter_names[k]] = cur[k];
+          }
+        };
+        // condition: must fold to a constant
+        {
+          std::map<std::string, long long> kn = known;
+          std::map<std::string, std::string> sb = sub;
+          bind(kn, sb);
+          // iteration-carried constants are referred to by the iter-arg names inside the regions
+          for (int k = 0; k < nres; ++k)
+            if (has_const[k]) sb.erase(iter_names[k]);
+          std::vector<SrcLine> scratch;
+          long long cv = 0;
+          if (!eval_region(cond, kn, sb, scratch, depth, nullptr, &cv, true))
+            return err.empty() ? fail(ln, "the condition of this while loop does not fold to a constant: only counted loops are unrolled") : false;
+          if (!cv) break;
+        }
+        if (++trip > kMaxUnrollTrips) return fail(ln, "while loop with more than 64 trips is not unrolled");
+        // body
+        std::map<std::string, long long> kn = known;
+        std::map<std::string, std::string> sb = sub;
+        bind(kn, sb);
+        for (int k = 0; k < nres; ++k)
+          if (has_const[k]) sb.erase(iter_names[k]);
+        // results defined inside the body get names unique to this trip
+        for (auto& bl : body) {
+          const std::string t = trim(bl.text);
+          size_t e2 = t.find(" = ");
+          if (t.empty() || t[0] != '%' || e2 == std::string::npos) continue;
+          std::string r = trim(t.substr(0, e2));
+          size_t c2 = r.find(':');
+          if (c2 != std::string::npos) r = r.substr(0, c2);
+          sb[r] = r + "_w" + std::to_string(my) + "_" + std::to_string(trip);
+        }
+        std::vector<std::string> yielded;
+        if (!eval_region(body, kn, sb, out, depth, &yielded, nullptr, false)) return err.empty() ? fail(ln, "malformed while body") : false;
+        if ((int)yielded.size() != nres) return fail(ln, "stablehlo.while: the body returns a different number of values");
+        for (int k = 0; k < nres; ++k) {
+          auto kv = kn.find(yielded[k]);
+          if (kv != kn.end() && scalar_int_type(types[k])) {
+            has_const[k] = true;
+            cval[k] = kv->second;
+            cur[k] = yielded[k];
+          } else {
+            has_const[k] = false;
+            cur[k] = yielded[k];
+          }
+        }
+      }
+      // ---- results of the loop
+      for (int k = 0; k < nres; ++k) {
+        const std::string name = nres == 1 && colon == std::string::npos ? res : res + "#" + std::to_string(k);
+        if (has_const[k]) {
+          // a carried constant (the counter): give later users a constant op to read
+          const std::string cname = res + "_w" + std::to_string(my) + "_c" + std::to_string(k);
+          out.push_back({cname + " = stablehlo.constant dense<" + std::to_string(cval[k]) + "> : " + types[k], ln});
+          known[cname] = cval[k];
+          sub[name] = cname;
+        } else {
+          sub[name] = cur[k];
+        }
+      }
+    }
+    return true;
+  }
+
+  bool fail(int line, const std::string& what) {
+    err = "line " + std::to_string(line) + ": " + what;
+    return false;
+  }
+
+  // Runs the lines of a region.  Scalar integer ops whose operands are known are folded away; a
+  // dynamic_slice with known indices becomes a slice; nested whiles are unrolled.  `yielded` receives the
+  // operands of the terminating stablehlo.return; for a condition `*cond_value` receives its folded value.
+  bool eval_region(const std::vector<SrcLine>& region, std::map<std::string, long long>& known,
+                   std::map<std::string, std::string>& sub, std::vector<SrcLine>& out, int depth,
+                   std::vector<std::string>* yielded, long long* cond_value, bool is_cond) {
+    std::vector<SrcLine> ops;
+    std::string ret;
+    int ret_line = 0;
+    for (auto& l : region) {
+      const std::string t = trim(l.text);
+      if (t.compare(0, 16, "stablehlo.return") == 0 || t.compare(0, 6, "return") == 0) {
+        ret = t;
+        ret_line = l.line;
+        break;
+      }
+      ops.push_back(l);
+    }
+    std::vector<SrcLine> emitted;
+    if (!run(ops, emitted, known, sub, depth + 1)) return false;
+    if (is_cond) {
+      for (auto& e : emitted)  // constants are kept as statements; anything else means the condition did not fold
+        if (e.text.find("= stablehlo.constant ") == std::string::npos) return false;
+    } else {
+      out.insert(out.end(), emitted.begin(), emitted.end());
+    }
+    if (ret.empty()) return fail(region.empty() ? 0 : region[0].line, "region without stablehlo.return");
+    size_t sp = ret.find(' ');
+    std::string rest = sp == std::string::npos ? "" : ret.substr(sp + 1);
+    size_t c = last_top_colon(rest);
+    std::vector<std::string> vals = split_top(substitute(c == std::string::npos ? rest : rest.substr(0, c), sub));
+    if (is_cond) {
+      if (vals.size() != 1) return fail(ret_line, "a while condition returns one value");
+      auto kv = known.find(vals[0]);
+      if (kv == known.end()) return false;
+      *cond_value = kv->second;
+    } else if (yielded) {
+      *yielded = vals;
+    }
+    return true;
+  }
+
+  // One non-while statement (already renamed): fold it if it is scalar integer arithmetic on known
+  // values, rewrite dynamic_slice, otherwise pass it through.
+  bool fold_or_emit(const std::string& l, int ln, std::vector<SrcLine>& out, std::map<std::string, long long>& known) {
+    size_t eq = l.find(" = ");
+    if (l.empty() || l[0] != '%' || eq == std::string::npos) {
+      out.push_back({l, ln});
+      return true;
+    }
+    const std::string res = trim(l.substr(0, eq));
+    std::string rest = trim(l.substr(eq + 3));
+    size_t c = last_top_colon(rest);
+    if (c == std::string::npos) {
+      out.push_back({l, ln});
+      return true;
+    }
+    std::string head = trim(rest.substr(0, c)), sig = trim(rest.substr(c + 1));
+    size_t sp = head.find_first_of(" (");
+    std::string name = sp == std::string::npos ? head : head.substr(0, sp);
+    std::string body = sp == std::string::npos ? "" : head.substr(sp);
+    std::vector<std::string> operands;
+    for (size_t i = 0; i < body.size(); ++i) {
+      if (body[i] != '%') continue;
+      size_t e = i + 1;
+      while (e < body.size() && is_name_char(body[e])) ++e;
+      operands.push_back(body.substr(i, e - i));
+      i = e - 1;
+    }
+    std::string out_type = sig;
+    size_t arrow = sig.find("->");
+    if (arrow != std::string::npos) {
+      out_type = trim(sig.substr(arrow + 2));
+    } else {
+      std::vector<std::string> ts = split_top(sig);  // "select" prints the predicate's type and the result's
+      if (!ts.empty()) out_type = ts.back();
+    }
+    auto val = [&](size_t k, long long& v) {
+      if (k >= operands.size()) return false;
+      auto it = known.find(operands[k]);
+      if (it == known.end()) return false;
+      v = it->second;
+      return true;
+    };
+    if (name == "stablehlo.constant" && scalar_int_type(out_type)) {
+      size_t a = body.find("dense<"), b = body.rfind('>');
+      if (a != std::string::npos && b != std::string::npos) {
+        std::string v = trim(body.substr(a + 6, b - a - 6));
+        if (v == "true") v = "1";
+        if (v == "false") v = "0";
+        if (!v.empty() && v.find_first_not_of("-0123456789") == std::string::npos) known[res] = atoll(v.c_str());
+      }
+      out.push_back({l, ln});  // kept: a later tensor op may read it
+      return true;
+    }
+    if (scalar_int_type(out_type)) {
+      long long x = 0, y = 0, z = 0;
+      bool folded = false;
+      long long r = 0;
+      if (name == "stablehlo.compare" && val(0, x) && val(1, y)) {
+        const std::string dir = body;
+        folded = true;
+        if (dir.find(" LT") != std::string::npos) r = x < y;
+        else if (dir.find(" LE") != std::string::npos) r = x <= y;
+        else if (dir.find(" GT") != std::string::npos) r = x > y;
+        else if (dir.find(" GE") != std::string::npos) r = x >= y;
+        else if (dir.find(" EQ") != std::string::npos) r = x == y;
+        else if (dir.find(" NE") != std::string::npos) r = x != y;
+        else folded = false;
+      } else if ((name == "stablehlo.add" || name == "stablehlo.subtract" || name == "stablehlo.multiply" ||
+                  name == "stablehlo.minimum" || name == "stablehlo.maximum" || name == "stablehlo.and" ||
+                  name == "stablehlo.or") && val(0, x) && val(1, y)) {
+        folded = true;
+        r = name == "stablehlo.add" ? x + y : name == "stablehlo.subtract" ? x - y : name == "stablehlo.multiply" ? x * y
+            : name == "stablehlo.minimum" ? std::min(x, y) : name == "stablehlo.maximum" ? std::max(x, y)
+            : name == "stablehlo.and" ? (x & y) : (x | y);
+      } else if (name == "stablehlo.select" && val(0, x) && val(1, y) && val(2, z)) {
+        folded = true;
+        r = x ? y : z;
+      } else if (name == "stablehlo.clamp" && val(0, x) && val(1, y) && val(2, z)) {
+        folded = true;
+        r = std::min(std::max(y, x), z);
+      } else if (name == "stablehlo.convert" && val(0, x)) {
+        folded = true;
+        r = x;
+      }
+      if (folded) {
+        known[res] = r;
+        return true;
+      }
+    }
+    if (name == "stablehlo.dynamic_slice" && operands.size() >= 2) {
+      std::vector<int64_t> sizes = int_list_after(body, "sizes");
+      if (sizes.empty()) sizes = int_list_after(body, "slice_sizes");
+      size_t p0 = sig.find('('), p1 = sig.find(')');
+      std::vector<std::string> in_types = (p0 == std::string::npos || p1 == std::string::npos)
+                                              ? std::vector<std::string>() : split_top(sig.substr(p0 + 1, p1 - p0 - 1));
+      TType src = in_types.empty() ? TType() : parse_type(in_types[0]);
+      bool all = src.ok && sizes.size() == src.dims.size() && operands.size() == src.dims.size() + 1;
+      std::vector<long long> start(sizes.size(), 0);
+      for (size_t k = 0; all && k < sizes.size(); ++k) {
+        long long v;
+        if (!val(k + 1, v)) all = false;
+        else start[k] = std::min<long long>(std::max<long long>(v, 0), src.dims[k] - sizes[k]);  // clamped, as the op is defined
+      }
+      if (!all) return fail(ln, "dynamic_slice whose indices do not fold to constants is not supported");
+      std::string lim;
+      for (size_t k = 0; k < sizes.size(); ++k)
+        lim += (k ? ", " : "") + std::to_string(start[k]) + ":" + std::to_string(start[k] + sizes[k]);
+      out.push_back({res + " = stablehlo.slice " + operands[0] + " [" + lim + "] : (" + in_types[0] + ") -> " + out_type, ln});
+      return true;
+    }
+    out.push_back({l, ln});
+    return true;
+  }
+};
+
 static bool parse_module(const char* text, size_t len, Module& m) {
   std::string all(text, len);
-  std::vector<std::string> lines;
+  std::vector<SrcLine> lines;
   {
     size_t p = 0;
+    int n = 0;
     while (p <= all.size()) {
       size_t e = all.find('\n', p);
       if (e == std::string::npos) e = all.size();
-      lines.push_back(all.substr(p, e - p));
+      lines.push_back({all.substr(p, e - p), ++n});
       p = e + 1;
     }
   }
+  if (all.find("stablehlo.while") != std::string::npos) {
+    // counted loops are replaced by their bodies before anything else looks at the program
+    Unroller u;
+    std::vector<SrcLine> flat;
+    std::map<std::string, long long> known;
+    std::map<std::string, std::string> sub;
+    if (!u.run(lines, flat, known, sub, 0)) {
+      m.error = u.err.empty() ? "could not unroll a stablehlo.while loop" : u.err;
+      return false;
+    }
+    lines.swap(flat);
+  }
   bool in_main = false, seen_main = false;
   int lineno = 0;
-  for (auto& raw : lines) {
-    ++lineno;
+  for (auto& src : lines) {
+    lineno = src.line;
+    const std::string& raw = src.text;
     std::string l = trim(raw);
     size_t loc = l.find(" loc(");
     if (loc != std::string::npos) l = trim(l.substr(0, loc));
@@ -612,6 +988,71 @@ static bool match_unpack4(const Module& m, const std::string& v, int* warg, std:
   return true;
 }
 
+// Slices of an argument that select one contiguous block (unit strides; full extent in every
+// dimension after the first partial one, extent 1 before it) and reshapes of arguments become
+// arguments themselves that point into their source: a scan over stacked [layers, K, N] weights then
+// hands the matcher one [K, N] "argument" per layer without copying anything.
+static void lift_argument_views(Module& m) {
+  for (size_t i = 0; i < m.ops.size(); ++i) {
+    const Op& op = m.ops[i];
+    if (op.operands.size() != 1 || op.in_types.empty()) continue;
+    auto src = m.argi.find(op.operands[0]);
+    if (src == m.argi.end()) continue;
+    const TType& it = op.in_types[0];
+    const TType& ot = op.out_type;
+    const size_t bits = gen::dtype_bits(dtype_of_elem_early(it.elem));
+    if (bits < 8 || it.elem != ot.elem) continue;
+    size_t offset = 0;
+    if (op.name == "stablehlo.reshape") {
+      // only reshapes of a slice view (dropping its unit dimensions); reshapes of plain arguments stay
+      // ops, which the matchers read through
+      if (it.count() != ot.count() || src->second < m.num_real_args + (int)m.const_data.size()) continue;
+    } else if (op.name == "stablehlo.slice") {
+      size_t a = op.body.find('['), b = op.body.find(']');
+      if (a == std::string::npos || b == std::string::npos) continue;
+      std::vector<std::string> parts = split_top(op.body.substr(a + 1, b - a - 1));
+      if (parts.size() != it.dims.size() || ot.dims.size() != it.dims.size()) continue;
+      bool ok = true;
+      int64_t stride = 1;
+      std::vector<int64_t> start(parts.size());
+      for (size_t d = 0; d < parts.size(); ++d) {
+        size_t c1 = parts[d].find(':');
+        if (c1 == std::string::npos) { ok = false; break; }
+        size_t c2 = parts[d].find(':', c1 + 1);
+        start[d] = atoll(parts[d].c_str());
+        const int64_t limit = atoll(parts[d].c_str() + c1 + 1);
+        const int64_t step = c2 == std::string::npos ? 1 : atoll(parts[d].c_str() + c2 + 1);
+        if (step != 1 || limit - start[d] != ot.dims[d] || start[d] < 0 || limit > it.dims[d]) { ok = false; break; }
+      }
+      if (!ok) continue;
+      // contiguity: before the first dimension with extent > 1 everything has extent 1; after it, full extent
+      size_t first_wide = 0;
+      while (first_wide < parts.size() && ot.dims[first_wide] == 1) ++first_wide;
+      for (size_t d = first_wide + 1; d < parts.size(); ++d)
+        if (ot.dims[d] != it.dims[d]) ok = false;
+      if (!ok) continue;
+      for (int d = (int)parts.size() - 1; d >= 0; --d) {
+        offset += (size_t)(start[d] * stride) * bits / 8;
+        stride *= it.dims[d];
+      }
+    } else {
+      continue;
+    }
+    // the source may itself be a view: offsets add up on the original argument
+    int base = src->second;
+    const int first_view = m.num_real_args + (int)m.const_data.size();
+    if (base >= first_view) {
+      offset += m.views[base - first_view].second;
+      base = m.views[base - first_view].first;
+    }
+    m.argi[op.result] = (int)m.arg_names.size();
+    m.arg_names.push_back(op.result);
+    m.arg_types.push_back(ot);
+    m.views.push_back({base, offset});
+    m.view_ops.insert((int)i);
+  }
+}
+
 // ---------------------------------------------------------------------------
 // Explicit route: stablehlo.custom_call @qmm_b200.qmm with a JSON backend_config.
 // A guaranteed-fused entry that does not depend on the matcher recognising a jnp spelling; the
@@ -684,7 +1125,7 @@ static bool parse_flat_json(const std::string& j, std::map<std::string, std::str
 static int build_plan(Plan& plan) {
   Module& m = plan.mod;
   const int A = (int)m.arg_names.size(), R = (int)m.returns.size();
-  std::set<int> consumed;  // ops absorbed into a fused step
+  std::set<int> consumed = m.view_ops;  // ops absorbed into a fused step (views of arguments move no data)
   // users of every value, to make sure absorbed intermediates do not escape
   std::map<std::string, std::vector<int>> users;
   for (size_t i = 0; i < m.ops.size(); ++i)
@@ -1403,6 +1844,7 @@ int qmm_plan_compile(const char* text, size_t len, qmm_plan** out) {
     delete plan;
     return rc;
   }
+  hlo::lift_argument_views(plan->p.mod);
   int rc = hlo::build_plan(plan->p);
   if (getenv("QMM_TRACE_PLAN")) fputs(plan->p.trace.c_str(), stderr);
   if (rc != QMM_OK) {
@@ -1542,7 +1984,13 @@ int qmm_plan_execute(const qmm_plan* cplan, const void* const* args, int num_arg
   auto ptr = [&](int slot) -> void* {
     if (slot < 0) return nullptr;
     if (slot < m.num_real_args) return const_cast<void*>(args[slot]);
-    if (slot < A) return (*consts)[slot - m.num_real_args];
+    const int first_view = m.num_real_args + (int)m.const_data.size();
+    if (slot < first_view) return (*consts)[slot - m.num_real_args];
+    if (slot < A) {
+      const auto& v = m.views[slot - first_view];
+      void* base = v.first < m.num_real_args ? const_cast<void*>(args[v.first]) : (*consts)[v.first - m.num_real_args];
+      return static_cast<uint8_t*>(base) + v.second;
+    }
     if (slot < A + R) return results[slot - A];
     return static_cast<uint8_t*>(workspace) + plan->p.temp_offset[slot - A - R];
   };

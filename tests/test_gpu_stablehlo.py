@@ -154,3 +154,17 @@ def test_custom_call_route_runs_the_named_kernels(cuda):
     Executable(text)([dev(c["x_bits"].view(np.int16), cuda, torch.bfloat16), dev(c["wq"], cuda),
                       dev(c["s_bits"].view(np.int16), cuda, torch.bfloat16), dev(c["z_packed"], cuda)], [out])
     assert O.max_rel_err(bf16_np(out), O.w4a16_matmul(c["x"], c["wq"], c["s"], c["z"])) <= 1e-2
+
+
+def test_scan_over_two_layers_runs_on_views_of_the_stacked_weights(cuda):
+    exe = Executable(load("scan_two_layers_w8a16.mlir"))
+    rng = np.random.default_rng(31)
+    xb = synthetic.to_bf16_bits(rng.standard_normal((256, 512)).astype(np.float32))
+    w = rng.integers(-127, 128, size=(2, 512, 512)).astype(np.int8)
+    s = rng.uniform(0.001, 0.004, size=(2, 512)).astype(np.float32)
+    out = torch.empty((256, 512), dtype=torch.bfloat16, device=cuda)
+    exe([dev(xb.view(np.int16), cuda, torch.bfloat16), dev(w, cuda), dev(s, cuda)], [out])
+    torch.cuda.synchronize()
+    h = O.round_to_bf16(O.w8_perchannel_matmul(synthetic.bf16_bits_to_f32(xb), w[0], s[0]))  # layer 0's bf16 output
+    ref = O.w8_perchannel_matmul(h, w[1], s[1])
+    assert O.max_rel_err(bf16_np(out), ref) <= 1e-2

@@ -240,3 +240,34 @@ def test_custom_call_descriptor_is_validated_key_by_key():
         cc.backend_config("w8a32_perchannel", zeros_packed=True)
     with pytest.raises(ValueError):
         cc.backend_config("dense")
+
+
+# ---- counted while loops and views of stacked arguments ------------------------------------------
+def test_scan_over_stacked_weights_is_unrolled_into_fused_steps_on_views():
+    text = load("scan_two_layers_w8a16.mlir")
+    exe = Executable(text)
+    assert (exe.num_args, exe.num_results, exe.num_steps) == (3, 1, 2)
+    fs = fused(exe)
+    assert [f["kernel"] for f in fs] == ["qmm_w8a16_perchannel"] * 2 and not_fused_ops(exe) == []
+    assert exe.workspace_bytes == 256 * 512 * 2  # only the activation carried between the two layers
+    # more layers: the trip count comes from the loop's bound
+    more = text.replace("tensor<2x512x512xi8>", "tensor<5x512x512xi8>").replace("tensor<2x512xf32>", "tensor<5x512xf32>") \
+        .replace("%c_1 = stablehlo.constant dense<2> : tensor<i32>\n      %1 = stablehlo.compare  LT, %iterArg, %c_1",
+                 "%c_1 = stablehlo.constant dense<5> : tensor<i32>\n      %1 = stablehlo.compare  LT, %iterArg, %c_1")
+    assert Executable(more).num_steps == 5
+
+
+def test_loops_that_are_not_counted_are_refused():
+    text = load("scan_two_layers_w8a16.mlir")
+    # the bound is an argument of the program: nothing to fold
+    dyn = text.replace("%arg2: tensor<2x512xf32>)", "%arg2: tensor<2x512xf32>, %arg3: tensor<i32>)") \
+        .replace("%1 = stablehlo.compare  LT, %iterArg, %c_1,  SIGNED : (tensor<i32>, tensor<i32>) -> tensor<i1>\n      stablehlo.return",
+                 "%1 = stablehlo.compare  LT, %iterArg, %arg3,  SIGNED : (tensor<i32>, tensor<i32>) -> tensor<i1>\n      stablehlo.return")
+    with pytest.raises(_lib.QmmError) as e:
+        Executable(dyn)
+    assert e.value.status_name == "QMM_ERR_PARSE" and "counted" in str(e.value)
+    long = text.replace("dense<2> : tensor<i32>\n      %1 = stablehlo.compare  LT, %iterArg, %c_1",
+                        "dense<1000> : tensor<i32>\n      %1 = stablehlo.compare  LT, %iterArg, %c_1")
+    with pytest.raises(_lib.QmmError) as e:
+        Executable(long)
+    assert "64 trips" in str(e.value)
