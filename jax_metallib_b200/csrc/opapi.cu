@@ -288,6 +288,253 @@ qgemm_vec_kernel(const T* __restrict__ x, T* __restrict__ y, VDec dec, int M, in
     }
 }
 
+// ---------------------------------------------------------------------------
+// Tensor-core route for the affine formats at decode sizes (f16 activations, M <= 16, group_size a
+// multiple of the 64 (4-bit) or 32 (8-bit) k that a quad of threads covers per step).  The CUDA-core
+// kernels above spend about nine lane instructions per weight, several times what the memory
+// system needs to keep up; here a weight costs a fraction of one:
+//   sum_k x[m,k] * (s * q[n,k] + b) = s * sum_k x q + b * sum_k x        per (n, group)
+// so the packed words go to mma.sync.m16n8k16 as they are.  A shift and an AND leave two codes of a
+// word in the low bits of the two halves of a register, where each reads as the f16 subnormal
+// q * 2^-24 (exact for q < 1024); the factor 2^24 is folded into the group's scale.  The 16 rows of
+// the MMA's first operand are 16 output columns (a thread holds two of them), its 16 k-slots are
+// four codes of one packed word per thread of a quad, and the activations are staged in shared
+// memory once per CTA in exactly that slot order, so a thread's fragments are one 8-byte load per
+// weight row and 16-byte shared loads of activations.  A CTA has eight warps: four 16-column tiles
+// times two halves of K, combined through shared memory.  sum_k x per (row, group) is computed once
+// per CTA.  Products are exact (f16 x f16 in f32), accumulation is f32; the scale and bias are
+// applied per group instead of per weight, which moves the result by f32 rounding only.
+// ---------------------------------------------------------------------------
+namespace tcq {
+constexpr int kThreads = 256;
+constexpr int kTileCols = 16;
+constexpr int kTilesPerCta = 4;
+constexpr int kDepth = 8;  // steps of weights in flight per thread (8 bytes per row and step)
+constexpr int kMaxSmem = 200 * 1024;
+
+__device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                         uint32_t b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+      : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+template <int BITS>
+struct Fmt {
+  static constexpr int kPerWord = 32 / BITS;       // codes per 32-bit word
+  static constexpr int kSpan = 8 * kPerWord;       // k per step of a quad: 4 threads x 2 words
+  // staged activation rows are padded so that the two rows of a quarter-warp's 16-byte loads fall
+  // into different banks: a quad reads 4 x 16 bytes 32 apart (4-bit) or 64 contiguous bytes (8-bit)
+  static constexpr int kRowPad = BITS == 4 ? 16 : 64;
+};
+
+// bytes of dynamic shared memory: staged activations, sums per (row, group), the hand-over of the
+// second K half
+template <int BITS>
+inline size_t smem_bytes(int MT, int K, int G) {
+  return static_cast<size_t>(MT) * 8 * (static_cast<size_t>(K) * 2 + Fmt<BITS>::kRowPad) +
+         static_cast<size_t>(MT) * 8 * G * 4 + static_cast<size_t>(kTilesPerCta) * 32 * MT * 4 * 4;
+}
+
+template <int BITS, int MT>
+__global__ void __launch_bounds__(kThreads)
+affine_tc_kernel(const __half* __restrict__ x, const uint32_t* __restrict__ w, const float* __restrict__ scales,
+                 const float* __restrict__ biases, __half* __restrict__ y, int M, int N, int K, int gs) {
+  using F = Fmt<BITS>;
+  extern __shared__ __align__(16) uint8_t smem[];
+  const int G = K / gs;
+  const int row_bytes = K * 2 + F::kRowPad;
+  uint8_t* xs = smem;
+  float* xsum = reinterpret_cast<float*>(smem + static_cast<size_t>(MT) * 8 * row_bytes);
+  float* hand = xsum + MT * 8 * G;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+
+  // ---- stage the activations in MMA slot order.  Per 8 k (16 bytes):
+  //   4-bit (one word):  (x0,x4) (x1,x5) (x2,x6) (x3,x7)
+  //   8-bit (two words): (x0,x2) (x1,x3) (x4,x6) (x5,x7)
+  const int chunks = K / 8;
+  for (int i = tid; i < MT * 8 * chunks; i += kThreads) {
+    const int m = i / chunks, c8 = i - m * chunks;
+    uint4 v = make_uint4(0, 0, 0, 0);
+    if (m < M) v = __ldg(reinterpret_cast<const uint4*>(x + static_cast<size_t>(m) * K + c8 * 8));
+    const uint32_t h0 = v.x, h1 = v.y, h2 = v.z, h3 = v.w;  // (x0,x1) (x2,x3) (x4,x5) (x6,x7)
+    uint4 o;
+    if (BITS == 4) {
+      o.x = __byte_perm(h0, h2, 0x5410);
+      o.y = __byte_perm(h0, h2, 0x7632);
+      o.z = __byte_perm(h1, h3, 0x5410);
+      o.w = __byte_perm(h1, h3, 0x7632);
+    } else {
+      o.x = __byte_perm(h0, h1, 0x5410);
+      o.y = __byte_perm(h0, h1, 0x7632);
+      o.z = __byte_perm(h2, h3, 0x5410);
+      o.w = __byte_perm(h2, h3, 0x7632);
+    }
+    *reinterpret_cast<uint4*>(xs + static_cast<size_t>(m) * row_bytes + c8 * 16) = o;
+  }
+  for (int i = tid; i < MT * 8 * G; i += kThreads) {  // one thread per (row, group): a fixed summation order
+    const int m = i / G, g = i - m * G;
+    float acc = 0.f;
+    if (m < M)
+      for (int k = 0; k < gs; k += 8) {
+        const uint4 v = __ldg(reinterpret_cast<const uint4*>(x + static_cast<size_t>(m) * K + g * gs + k));
+        const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 f = __half22float2(h[j]);
+          acc += f.x + f.y;
+        }
+      }
+    xsum[m * G + g] = acc;
+  }
+  __syncthreads();
+
+  const int tile = warp & 3, khalf = warp >> 2;
+  const int n0 = (blockIdx.x * kTilesPerCta + tile) * kTileCols;
+  const int g8 = lane >> 2, t4 = lane & 3;
+  float yacc[MT][4];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) yacc[mt][i] = 0.f;
+
+  if (n0 < N) {  // whole warp; N is a multiple of 16, so the tile is complete
+    const int g_begin = khalf == 0 ? 0 : (G + 1) / 2, g_end = khalf == 0 ? (G + 1) / 2 : G;
+    const int steps_per_group = gs / F::kSpan;
+    const int total = (g_end - g_begin) * steps_per_group;
+    const int words_per_row = K / F::kPerWord;
+    const int word_begin = g_begin * (gs / F::kPerWord) + 2 * t4;  // this thread's first word within a row
+    const uint32_t* w0 = w + static_cast<size_t>(n0 + g8) * words_per_row + word_begin;
+    const uint32_t* w1 = w0 + static_cast<size_t>(8) * words_per_row;
+    const float* s0 = scales + static_cast<size_t>(n0 + g8) * G, *s1 = s0 + static_cast<size_t>(8) * G;
+    const float* b0p = biases + static_cast<size_t>(n0 + g8) * G, *b1p = b0p + static_cast<size_t>(8) * G;
+    // a word's activations: 16 staged bytes (4-bit) or 8 (8-bit)
+    const uint8_t* xrow = xs + static_cast<size_t>(g8) * row_bytes + static_cast<size_t>(word_begin) * (2 * F::kPerWord);
+    constexpr int kStepXBytes = 8 * 2 * F::kPerWord;  // staged bytes a step of 8 words advances
+    uint2 qa[kDepth], qb[kDepth];  // steps in flight: two words of row g8, two of row g8 + 8
+#pragma unroll
+    for (int i = 0; i < kDepth; ++i)
+      if (i < total) {
+        qa[i] = __ldcs(reinterpret_cast<const uint2*>(w0 + i * 8));
+        qb[i] = __ldcs(reinterpret_cast<const uint2*>(w1 + i * 8));
+      }
+    float d[MT][4];
+    int in_group = 0, g = g_begin;
+    for (int base = 0; base < total; base += kDepth) {
+#pragma unroll
+      for (int i = 0; i < kDepth; ++i) {
+        const int sp = base + i;
+        if (sp >= total) break;
+        if (in_group == 0) {
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+            for (int j = 0; j < 4; ++j) d[mt][j] = 0.f;
+        }
+        const uint2 a = qa[i], b = qb[i];
+        if (sp + kDepth < total) {  // refill the slot
+          qa[i] = __ldcs(reinterpret_cast<const uint2*>(w0 + (sp + kDepth) * 8));
+          qb[i] = __ldcs(reinterpret_cast<const uint2*>(w1 + (sp + kDepth) * 8));
+        }
+        if (BITS == 4) {
+          constexpr uint32_t kNib = 0x000F000Fu;
+#pragma unroll
+          for (int wi = 0; wi < 2; ++wi) {
+            const uint32_t lo = wi ? a.y : a.x, hi = wi ? b.y : b.x;
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+              const uint4 xq = *reinterpret_cast<const uint4*>(xrow + static_cast<size_t>(mt) * 8 * row_bytes +
+                                                               static_cast<size_t>(sp) * kStepXBytes + wi * 16);
+              mma16816(d[mt], lo & kNib, hi & kNib, (lo >> 4) & kNib, (hi >> 4) & kNib, xq.x, xq.y);
+              mma16816(d[mt], (lo >> 8) & kNib, (hi >> 8) & kNib, (lo >> 12) & kNib, (hi >> 12) & kNib, xq.z, xq.w);
+            }
+          }
+        } else {
+          constexpr uint32_t kByte = 0x00FF00FFu;
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            const uint4 xq = *reinterpret_cast<const uint4*>(xrow + static_cast<size_t>(mt) * 8 * row_bytes +
+                                                             static_cast<size_t>(sp) * kStepXBytes);
+            mma16816(d[mt], a.x & kByte, b.x & kByte, (a.x >> 8) & kByte, (b.x >> 8) & kByte, xq.x, xq.y);
+            mma16816(d[mt], a.y & kByte, b.y & kByte, (a.y >> 8) & kByte, (b.y >> 8) & kByte, xq.z, xq.w);
+          }
+        }
+        if (++in_group == steps_per_group) {
+          in_group = 0;
+          const float sc0 = __ldg(s0 + g) * 16777216.f, sc1 = __ldg(s1 + g) * 16777216.f;
+          const float bi0 = __ldg(b0p + g), bi1 = __ldg(b1p + g);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            const float xs0 = xsum[(mt * 8 + 2 * t4) * G + g], xs1 = xsum[(mt * 8 + 2 * t4 + 1) * G + g];
+            yacc[mt][0] = fmaf(bi0, xs0, fmaf(sc0, d[mt][0], yacc[mt][0]));
+            yacc[mt][1] = fmaf(bi0, xs1, fmaf(sc0, d[mt][1], yacc[mt][1]));
+            yacc[mt][2] = fmaf(bi1, xs0, fmaf(sc1, d[mt][2], yacc[mt][2]));
+            yacc[mt][3] = fmaf(bi1, xs1, fmaf(sc1, d[mt][3], yacc[mt][3]));
+          }
+          ++g;
+        }
+      }
+    }
+  }
+  // ---- the second K half hands its sums to the first, which stores
+  float* slot = hand + (tile * 32 + lane) * MT * 4;
+  if (khalf == 1) {
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) slot[mt * 4 + i] = yacc[mt][i];
+  }
+  __syncthreads();
+  if (khalf == 0 && n0 < N) {
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int n = n0 + g8 + ((i >> 1) << 3), m = mt * 8 + 2 * t4 + (i & 1);
+        if (m < M) y[static_cast<size_t>(m) * N + n] = __float2half_rn(yacc[mt][i] + slot[mt * 4 + i]);
+      }
+    }
+  }
+}
+
+template <int BITS, int MT>
+static int launch_one(const void* x, const void* w, const float* scales, const float* biases, void* y, int64_t M,
+                      int64_t N, int64_t K, int64_t gs, void* stream) {
+  static std::atomic<uint64_t> configured{0};
+  auto kernel = affine_tc_kernel<BITS, MT>;
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), kMaxSmem, configured)) return rc;
+  const size_t smem = smem_bytes<BITS>(MT, static_cast<int>(K), static_cast<int>(K / gs));
+  const unsigned grid = static_cast<unsigned>((N + kTileCols * kTilesPerCta - 1) / (kTileCols * kTilesPerCta));
+  kernel<<<grid, kThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __half*>(x), static_cast<const uint32_t*>(w), scales, biases, static_cast<__half*>(y),
+      static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), static_cast<int>(gs));
+  QMM_CHECK_LAUNCH(BITS == 4 ? "affine_qgemm_4bit_f16 (tensor cores)" : "affine_qgemm_8bit_f16 (tensor cores)");
+  return QMM_OK;
+}
+
+static int launch(int bits, const void* x, const void* w, const float* scales, const float* biases, void* y, int64_t M,
+                  int64_t N, int64_t K, int64_t gs, void* stream) {
+  if (bits == 4)
+    return M <= 8 ? launch_one<4, 1>(x, w, scales, biases, y, M, N, K, gs, stream)
+                  : launch_one<4, 2>(x, w, scales, biases, y, M, N, K, gs, stream);
+  return M <= 8 ? launch_one<8, 1>(x, w, scales, biases, y, M, N, K, gs, stream)
+                : launch_one<8, 2>(x, w, scales, biases, y, M, N, K, gs, stream);
+}
+
+// shapes the tensor-core route covers
+static bool covers(int64_t M, int64_t N, int64_t K, int bits, int64_t gs, int dtype, const void* x, const void* w) {
+  if ((bits != 4 && bits != 8) || dtype != QMM_F16 || M < 1 || M > 16 || N % 16 != 0) return false;
+  const int span = bits == 4 ? Fmt<4>::kSpan : Fmt<8>::kSpan;
+  if (gs % span != 0 || K % gs != 0 || K > (1 << 20)) return false;
+  if (!aligned(x, 16) || !aligned(w, 8)) return false;
+  const int MT = M <= 8 ? 1 : 2;
+  const size_t smem = bits == 4 ? smem_bytes<4>(MT, static_cast<int>(K), static_cast<int>(K / gs))
+                                : smem_bytes<8>(MT, static_cast<int>(K), static_cast<int>(K / gs));
+  return smem <= static_cast<size_t>(kMaxSmem);
+}
+}  // namespace tcq
+
 template <typename T, typename VDec>
 static int launch_vec(const void* x, void* y, VDec dec, int64_t M, int64_t N, int64_t K, void* stream,
                       const char* name) {
@@ -340,6 +587,9 @@ int qmm_affine_matmul(const void* x, const void* w_packed, const float* scales, 
               "qmm_affine_matmul: x must be 16-byte and w_packed 8-byte aligned");
   const int k = static_cast<int>(K), gs = static_cast<int>(group_size);
   if (M == 0 || N == 0) return QMM_OK;
+  // decode-sized f16 problems: the tensor-core kernel
+  if (tcq::covers(M, N, K, bits, group_size, dtype, x, w_packed))
+    return tcq::launch(bits, x, w_packed, scales, biases, y, M, N, K, group_size, stream);
   // rows of 16-byte words: the vectorised kernel
   if (aligned(w_packed, 16) && K % (bits == 4 ? 32 : 16) == 0) {
     if (bits == 4) {

@@ -93,3 +93,42 @@ def test_affine_large_k_and_rows(cuda):
         out = Q.affine_quantized_matmul(x, p, s, b, bits=bits, group_size=128, K=K)
         ref = O.affine_qmm(x, p, s, b, bits=bits, group_size=128, K=K)
         assert O.max_rel_err(out, ref) <= 1e-5
+
+
+@pytest.mark.parametrize("M", [1, 5, 8, 9, 16])
+@pytest.mark.parametrize("bits,gs,K,N", [(4, 64, 4096, 208), (4, 128, 4096, 4096), (4, 64, 192, 16), (4, 256, 1024, 80),
+                                         (4, 64, 64, 32), (8, 32, 4096, 208), (8, 64, 4096, 4096), (8, 32, 96, 16),
+                                         (8, 128, 1024, 80), (8, 32, 32, 32)])
+def test_affine_f16_decode_sizes(cuda, M, bits, gs, K, N):
+    """f16 activations with at most 16 rows and groups of a multiple of 64 (4-bit) or 32 (8-bit) take
+    the tensor-core kernel (codes fed to the MMA as f16 subnormals, scale and bias applied per group);
+    same result as the dequantise-then-multiply arithmetic of the reference's fused kernels up to f32
+    summation order."""
+    rng = np.random.default_rng(M * 1000 + K + N + bits)
+    x = rng.standard_normal((M, K)).astype(np.float16)
+    w = rng.standard_normal((N, K)).astype(np.float32) * 0.05
+    p, s, b = Q.affine_quantize(w, bits=bits, group_size=gs)
+    out = Q.affine_quantized_matmul(x, p, s, b, bits=bits, group_size=gs, K=K)
+    assert out.dtype == np.float16 and out.shape == (M, N)
+    ref = O.affine_qmm(x.astype(np.float32), p, s, b, bits=bits, group_size=gs, K=K)
+    # one f16 rounding of the result (2^-11 relative) on top of f32 accumulation
+    np.testing.assert_allclose(out.astype(np.float32), ref, rtol=1e-3, atol=1e-3 * float(np.abs(ref).max()))
+    # f32 activations take the general kernel: the two routes agree
+    wide = Q.affine_quantized_matmul(x.astype(np.float32), p, s, b, bits=bits, group_size=gs, K=K)
+    np.testing.assert_allclose(out.astype(np.float32), wide, rtol=1e-3, atol=1e-3 * float(np.abs(ref).max()))
+
+
+@pytest.mark.parametrize("bits", [4, 8])
+def test_affine_f16_tiny_and_large_activations(cuda, bits):
+    """Activation magnitudes at both ends of f16: the subnormal trick scales no activation, so
+    neither underflow nor overflow is introduced."""
+    rng = np.random.default_rng(3)
+    K, N, gs = 512, 64, 64
+    w = rng.standard_normal((N, K)).astype(np.float32)
+    p, s, b = Q.affine_quantize(w, bits=bits, group_size=gs)
+    for scale in (2.0 ** -20, 1.0, 200.0):
+        x = (rng.standard_normal((3, K)) * scale).astype(np.float16)
+        out = Q.affine_quantized_matmul(x, p, s, b, bits=bits, group_size=gs, K=K).astype(np.float32)
+        ref = O.affine_qmm(x.astype(np.float32), p, s, b, bits=bits, group_size=gs, K=K)
+        assert np.isfinite(out).all()
+        np.testing.assert_allclose(out, ref, rtol=2e-3, atol=2e-3 * float(np.abs(ref).max()))
