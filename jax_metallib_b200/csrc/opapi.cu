@@ -13,6 +13,13 @@
 #include "common.cuh"
 
 namespace qmm {
+
+// the TMA-ring tensor-core kernel for the affine formats
+bool affine_ring_covers(int64_t M, int64_t N, int64_t K, int bits, int64_t gs, int dtype, const void* x, const void* w,
+                        const float* scales, const float* biases);
+int affine_ring_launch(int bits, const void* x, const void* w, const float* scales, const float* biases, void* y, int64_t M,
+                       int64_t N, int64_t K, int64_t gs, void* stream);
+
 namespace opapi {
 
 constexpr int kWarpsPerBlock = 4;
@@ -587,7 +594,9 @@ int qmm_affine_matmul(const void* x, const void* w_packed, const float* scales, 
               "qmm_affine_matmul: x must be 16-byte and w_packed 8-byte aligned");
   const int k = static_cast<int>(K), gs = static_cast<int>(group_size);
   if (M == 0 || N == 0) return QMM_OK;
-  // decode-sized f16 problems: the tensor-core kernel
+  // decode-sized f16 problems: the tensor-core kernels (TMA ring where the shape allows, else plain loads)
+  if (affine_ring_covers(M, N, K, bits, group_size, dtype, x, w_packed, scales, biases))
+    return affine_ring_launch(bits, x, w_packed, scales, biases, y, M, N, K, group_size, stream);
   if (tcq::covers(M, N, K, bits, group_size, dtype, x, w_packed))
     return tcq::launch(bits, x, w_packed, scales, biases, y, M, N, K, group_size, stream);
   // rows of 16-byte words: the vectorised kernel

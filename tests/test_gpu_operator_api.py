@@ -98,7 +98,11 @@ def test_affine_large_k_and_rows(cuda):
 @pytest.mark.parametrize("M", [1, 5, 8, 9, 16])
 @pytest.mark.parametrize("bits,gs,K,N", [(4, 64, 4096, 208), (4, 128, 4096, 4096), (4, 64, 192, 16), (4, 256, 1024, 80),
                                          (4, 64, 64, 32), (8, 32, 4096, 208), (8, 64, 4096, 4096), (8, 32, 96, 16),
-                                         (8, 128, 1024, 80), (8, 32, 32, 32)])
+                                         (8, 128, 1024, 80), (8, 32, 32, 32),
+                                         # shapes of the TMA-ring kernel: several tiles per CTA, K cut 2 to 16 ways,
+                                         # groups of 1, 2 and 4 steps, a last CTA with fewer tiles
+                                         (4, 64, 4096, 14336), (4, 128, 4096, 2368), (4, 256, 8192, 512), (4, 64, 1024, 2384),
+                                         (4, 64, 14336, 4096), (8, 32, 2048, 1024), (8, 64, 4096, 14336), (8, 128, 8192, 2400)])
 def test_affine_f16_decode_sizes(cuda, M, bits, gs, K, N):
     """f16 activations with at most 16 rows and groups of a multiple of 64 (4-bit) or 32 (8-bit) take
     the tensor-core kernel (codes fed to the MMA as f16 subnormals, scale and bias applied per group);
