@@ -776,8 +776,8 @@ def _detail_operator_api(torch, synthetic, lib, device, hbm, graph_time, detail)
         detail[f"operator_api_{name}_M{M}_{N}x{K}"] = {
             "us": us, "bytes": nbytes, "GB/s": nbytes / (us * 1e-6) / 1e9,
             "frac_of_measured_hbm": nbytes / (us * 1e-6) / 1e9 / hbm,
-            "note": ("affine_ring_kernel (mma.sync on packed codes, per-warp TMA rings)" if name.startswith("affine")
-                     else "qgemm_vec_kernel (CUDA cores)") + "; rotating weight copies (cold L2), CUDA-graph replay"}
+            "note": ("affine_ring_kernel" if name.startswith("affine") else "mx_ring_kernel") +
+                    " (mma.sync on the packed codes, per-warp TMA rings); rotating weight copies (cold L2), CUDA-graph replay"}
 
 
 def _detail_int8_dot(torch, synthetic, lib, device, peaks, graph_time, detail):

@@ -19,6 +19,9 @@ bool affine_ring_covers(int64_t M, int64_t N, int64_t K, int bits, int64_t gs, i
                         const float* scales, const float* biases);
 int affine_ring_launch(int bits, const void* x, const void* w, const float* scales, const float* biases, void* y, int64_t M,
                        int64_t N, int64_t K, int64_t gs, void* stream);
+bool mx_ring_covers(int64_t M, int64_t N, int64_t K, int mode, int dtype, const void* x, const void* w, const void* scales);
+int mx_ring_launch(int mode, const void* x, const void* w, const void* scales, void* y, int64_t M, int64_t N, int64_t K,
+                   void* stream);
 
 namespace opapi {
 
@@ -638,6 +641,9 @@ int qmm_mx_matmul(const void* x, const uint8_t* w_packed, const uint8_t* scales,
               "qmm_mx_matmul: x must be 16-byte and w_packed 8-byte aligned");
   const int k = static_cast<int>(K);
   if (M == 0 || N == 0) return QMM_OK;
+  static_assert(QMM_MXFP4 == 0 && QMM_MXFP8 == 1 && QMM_NVFP4 == 2, "mode numbering shared with the tensor-core kernel");
+  if (mx_ring_covers(M, N, K, mode, dtype, x, w_packed, scales))   // decode-sized f16 problems: the tensor-core kernel
+    return mx_ring_launch(mode, x, w_packed, scales, y, M, N, K, stream);
   if (aligned(w_packed, 16) && K % 32 == 0) {  // rows of 16-byte words: the vectorised kernel
     if (mode == QMM_MXFP4) {
       VMx<0> d{w_packed, scales, k};

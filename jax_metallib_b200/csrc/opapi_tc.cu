@@ -93,6 +93,74 @@ struct Fmt {
   static constexpr int kRowPad = BITS == 4 ? 16 : 64;
 };
 
+// Order of the eight activations of a 16-byte piece in shared memory: the k-slots of one MMA are four codes of one
+// packed word per thread of a quad, so a register of the second operand pairs the activations of two codes that
+// the first operand takes from one register.
+//   kOrderAffine4: (x0,x4) (x2,x6) | (x1,x5) (x3,x7)   one word of 4-bit codes; the second pair meets the codes at bits 4-7
+//   kOrderBytes:   (x0,x2) (x1,x3) | (x4,x6) (x5,x7)   two words of 8-bit codes
+//   kOrderNibbles: (x0,x4) (x1,x5) | (x2,x6) (x3,x7)   one word of 4-bit codes converted pair by pair
+enum { kOrderAffine4 = 0, kOrderBytes = 1, kOrderNibbles = 2 };
+
+// Stages x[M][K] (f16) into shared memory, 8 k (16 bytes) per thread and pass, every global load of a pass issued
+// before the first store.  With SUMS, also the sum of each (row, group) into xsum[group * stride + row]: fused into
+// the same pass by shuffles when a group is a power-of-two number of lanes (fused_sum), in a fixed order.
+template <int ORDER, bool SUMS>
+__device__ __forceinline__ void stage_activations(const __half* __restrict__ x, uint8_t* xs, int row_bytes, int M, int chunks,
+                                                  float* xsum, int stride, int lanes_per_group, bool fused_sum) {
+  const int tid = threadIdx.x, lane = tid & 31, threads = blockDim.x;
+  const int n_it = M * chunks;
+  int m = 0, c8 = tid;                                    // i = m * chunks + c8, advanced without a division
+  while (c8 >= chunks) { c8 -= chunks; ++m; }
+  for (int i0 = tid; i0 - tid < n_it; i0 += threads * 4) {   // whole warps stay in the loop for the shuffles
+    uint4 v[4];
+    int mm[4], cc[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int i = i0 + j * threads;
+      mm[j] = m;
+      cc[j] = c8;
+      v[j] = i < n_it ? __ldg(reinterpret_cast<const uint4*>(x) + i) : make_uint4(0, 0, 0, 0);
+      c8 += threads;
+      while (c8 >= chunks) { c8 -= chunks; ++m; }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int i = i0 + j * threads;
+      if (i - lane >= n_it) continue;                     // warp-uniform
+      const uint32_t h0 = v[j].x, h1 = v[j].y, h2 = v[j].z, h3 = v[j].w;   // (x0,x1) (x2,x3) (x4,x5) (x6,x7)
+      if (i < n_it) {
+        uint4 o;
+        if (ORDER == kOrderAffine4) {
+          o.x = __byte_perm(h0, h2, 0x5410);
+          o.y = __byte_perm(h1, h3, 0x5410);
+          o.z = __byte_perm(h0, h2, 0x7632);
+          o.w = __byte_perm(h1, h3, 0x7632);
+        } else if (ORDER == kOrderBytes) {
+          o.x = __byte_perm(h0, h1, 0x5410);
+          o.y = __byte_perm(h0, h1, 0x7632);
+          o.z = __byte_perm(h2, h3, 0x5410);
+          o.w = __byte_perm(h2, h3, 0x7632);
+        } else {
+          o.x = __byte_perm(h0, h2, 0x5410);
+          o.y = __byte_perm(h0, h2, 0x7632);
+          o.z = __byte_perm(h1, h3, 0x5410);
+          o.w = __byte_perm(h1, h3, 0x7632);
+        }
+        *reinterpret_cast<uint4*>(xs + mm[j] * row_bytes + cc[j] * 16) = o;
+      }
+      if (SUMS && fused_sum) {
+        const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&h0));
+        const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&h1));
+        const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&h2));
+        const float2 f3 = __half22float2(*reinterpret_cast<const __half2*>(&h3));
+        float p = ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
+        for (int o = 1; o < lanes_per_group; o <<= 1) p += __shfl_xor_sync(0xFFFFFFFFu, p, o);
+        if (i < n_it && (cc[j] & (lanes_per_group - 1)) == 0) xsum[(cc[j] / lanes_per_group) * stride + mm[j]] = p;
+      }
+    }
+  }
+}
+
 struct Plan {
   int tiles, ksplit, stages, warps;
   unsigned grid;
@@ -108,38 +176,51 @@ static size_t fixed_smem(int bits, int warps, int M, int MT, int K, int G) {
          static_cast<size_t>(warps) * 32 * MT * 4 * 4 + static_cast<size_t>(warps) * (8 + 1) * 8 + 1024;
 }
 
-// How to cut the problem; false when this kernel does not cover it.
+// Picks tiles per CTA, the K split and the ring depth: as many warps as a CTA may have, at most 8 K units per warp
+// (one box of scales), at least two boxes of weights per warp (a box is refilled while the next is read).  When the
+// staged activations leave too little room, fewer warps.  fixed(warps) = shared memory beside the rings.
+template <typename FixedFn>
+static bool choose(int64_t tiles_total, int U, int chunks_per_unit, FixedFn fixed, Plan* p) {
+  const int ksplit_min = (U + 7) / 8;
+  if (ksplit_min > kMaxWarps) return false;
+  const int sms = num_sms();
+  int tiles = static_cast<int>((tiles_total + sms - 1) / sms);
+  if (tiles * ksplit_min > kMaxWarps) tiles = kMaxWarps / ksplit_min;
+  int ksplit = kMaxWarps / tiles;
+  if (ksplit > U) ksplit = U;
+  for (;;) {
+    const int warps = tiles * ksplit;
+    const size_t fx = fixed(warps);
+    const int chunks_per_warp = ((U + ksplit - 1) / ksplit) * chunks_per_unit;
+    int stages = fx < static_cast<size_t>(kMaxSmem) ? static_cast<int>((kMaxSmem - fx) / (static_cast<size_t>(warps) * kBox)) : 0;
+    if (stages > 8) stages = 8;
+    if (stages > chunks_per_warp) stages = chunks_per_warp;
+    if (stages >= 2 || (stages == 1 && chunks_per_warp == 1)) {
+      p->tiles = tiles;
+      p->ksplit = ksplit;
+      p->warps = warps;
+      p->stages = stages;
+      p->grid = static_cast<unsigned>((tiles_total + tiles - 1) / tiles);
+      p->smem = fx + static_cast<size_t>(warps) * stages * kBox;
+      return true;
+    }
+    if (ksplit > ksplit_min) ksplit = (ksplit + ksplit_min) / 2;     // first give up the extra K parts, then tiles
+    else if (tiles > 1) tiles = (tiles + 1) / 2;
+    else return false;
+  }
+}
+
+// How to cut an affine problem; false when this kernel does not cover it.
 static bool plan(int bits, int64_t M, int64_t N, int64_t K, int64_t gs, Plan* p) {
   const int step_k = bits == 4 ? Fmt<4>::kStepK : Fmt<8>::kStepK;
   const int64_t spg = gs / step_k;                       // steps per group
   if (gs % step_k != 0 || (spg != 1 && spg != 2 && spg != 4)) return false;
   if (N % 16 != 0 || K % gs != 0 || K * bits / 8 < 128 || K > (1 << 17)) return false;
   const int64_t G = K / gs;
-  if (G % 4 != 0) return false;                          // K parts begin on 4 groups: 16 bytes of a scale row, one box of weights
-  const int U = static_cast<int>(G / 4);
-  const int ksplit_min = (U + 7) / 8;                    // at most 32 groups per warp: one box of scales
-  if (ksplit_min > kMaxWarps) return false;
-  const int64_t tiles_total = N / 16;
-  const int sms = num_sms();
-  int tiles = static_cast<int>((tiles_total + sms - 1) / sms);
-  if (tiles * ksplit_min > kMaxWarps) tiles = kMaxWarps / ksplit_min;
-  int ksplit = kMaxWarps / tiles;
-  if (ksplit > U) ksplit = U;
-  p->tiles = tiles;
-  p->ksplit = ksplit;
-  p->warps = tiles * ksplit;
-  p->grid = static_cast<unsigned>((tiles_total + tiles - 1) / tiles);
+  if (G % 4 != 0) return false;        // K parts begin on 4 groups: 16 bytes of a scale row, one box of weights
   const int MT = M <= 8 ? 1 : 2;
-  const size_t fixed = fixed_smem(bits, p->warps, static_cast<int>(M), MT, static_cast<int>(K), static_cast<int>(G));
-  if (fixed + static_cast<size_t>(p->warps) * 2 * kBox > static_cast<size_t>(kMaxSmem)) return false;
-  const int chunks_per_warp = static_cast<int>((((U + ksplit - 1) / ksplit) * 4 * spg + kStepsPerChunk - 1) / kStepsPerChunk);
-  int stages = static_cast<int>((kMaxSmem - fixed) / (static_cast<size_t>(p->warps) * kBox));
-  if (stages > 8) stages = 8;
-  if (stages > chunks_per_warp) stages = chunks_per_warp;
-  if (stages < 1) return false;
-  p->stages = stages;
-  p->smem = fixed + static_cast<size_t>(p->warps) * stages * kBox;
-  return true;
+  return choose(N / 16, static_cast<int>(G / 4), static_cast<int>(spg),
+                [&](int warps) { return fixed_smem(bits, warps, static_cast<int>(M), MT, static_cast<int>(K), static_cast<int>(G)); }, p);
 }
 
 template <int BITS, int MT, int SPG>
@@ -198,60 +279,12 @@ affine_ring_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
   }
   __syncwarp();
 
-  // ---- activations: 8 k (16 bytes) per thread and pass, stored in MMA slot order; sums per (row, group)
-  //   4-bit: (x0,x4) (x2,x6) | (x1,x5) (x3,x7)     one packed word; the second pair meets the codes at bits 4-7
-  //   8-bit: (x0,x2) (x1,x3) | (x4,x6) (x5,x7)     two packed words
+  // ---- activations in MMA slot order, sums per (row, group)
   const int chunks = K / 8;
   const int lanes_per_group = gs / 8;
   const bool fused_sum = lanes_per_group <= 32 && (lanes_per_group & (lanes_per_group - 1)) == 0;
-  {
-    const int n_it = M * chunks;
-    int m = 0, c8 = tid;                                    // i = m * chunks + c8, advanced without a division
-    while (c8 >= chunks) { c8 -= chunks; ++m; }
-    for (int i0 = tid; i0 - tid < n_it; i0 += threads * 4) {   // whole warps stay in the loop for the shuffles
-      uint4 v[4];
-      int mm[4], cc[4];
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int i = i0 + j * threads;
-        mm[j] = m;
-        cc[j] = c8;
-        v[j] = i < n_it ? __ldg(reinterpret_cast<const uint4*>(x) + i) : make_uint4(0, 0, 0, 0);
-        c8 += threads;
-        while (c8 >= chunks) { c8 -= chunks; ++m; }
-      }
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int i = i0 + j * threads;
-        if (i - lane >= n_it) continue;                     // warp-uniform
-        const uint32_t h0 = v[j].x, h1 = v[j].y, h2 = v[j].z, h3 = v[j].w;   // (x0,x1) (x2,x3) (x4,x5) (x6,x7)
-        if (i < n_it) {
-          uint4 o;
-          if (BITS == 4) {
-            o.x = __byte_perm(h0, h2, 0x5410);
-            o.y = __byte_perm(h1, h3, 0x5410);
-            o.z = __byte_perm(h0, h2, 0x7632);
-            o.w = __byte_perm(h1, h3, 0x7632);
-          } else {
-            o.x = __byte_perm(h0, h1, 0x5410);
-            o.y = __byte_perm(h0, h1, 0x7632);
-            o.z = __byte_perm(h2, h3, 0x5410);
-            o.w = __byte_perm(h2, h3, 0x7632);
-          }
-          *reinterpret_cast<uint4*>(xs + mm[j] * row_bytes + cc[j] * 16) = o;
-        }
-        if (fused_sum) {
-          const float2 f0 = __half22float2(*reinterpret_cast<const __half2*>(&h0));
-          const float2 f1 = __half22float2(*reinterpret_cast<const __half2*>(&h1));
-          const float2 f2 = __half22float2(*reinterpret_cast<const __half2*>(&h2));
-          const float2 f3 = __half22float2(*reinterpret_cast<const __half2*>(&h3));
-          float p = ((f0.x + f0.y) + (f1.x + f1.y)) + ((f2.x + f2.y) + (f3.x + f3.y));
-          for (int o = 1; o < lanes_per_group; o <<= 1) p += __shfl_xor_sync(0xFFFFFFFFu, p, o);
-          if (i < n_it && (cc[j] & (lanes_per_group - 1)) == 0) xsum[(cc[j] / lanes_per_group) * (MT * 8) + mm[j]] = p;
-        }
-      }
-    }
-  }
+  stage_activations<BITS == 4 ? kOrderAffine4 : kOrderBytes, true>(x, xs, row_bytes, M, chunks, xsum, MT * 8, lanes_per_group,
+                                                                  fused_sum);
   // rows m >= M only feed result columns that are never stored; keep them finite
   for (int i = tid; i < G * MT * 8; i += threads)
     if ((i % (MT * 8)) >= M) xsum[i] = 0.f;
@@ -441,6 +474,370 @@ static int launch_bits(const Plan& p, const CUtensorMap& wmap, const CUtensorMap
   return launch_one<BITS, 2, 4>(p, wmap, smap, bmap, x, y, M, N, K, gs, stream);
 }
 
+
+// ---------------------------------------------------------------------------
+// The MX formats (mxfp4, mxfp8: e8m0 scale per 32 k; nvfp4: e4m3 scale per 16 k) on the same skeleton.
+// An e2m1 code placed at bits 15 (sign) and 11..9 of a half reads as the f16 value v * 2^-14 (its
+// subnormal 0.5 lands on an f16 subnormal), an e4m3 byte placed at bits 15 and 13..7 as v * 2^-8; the
+// power of two multiplies the result once at the end.  mxfp4 and mxfp8 keep one accumulator per scale
+// group and apply the decoded e8m0 scale in f32.  nvfp4, whose groups are shorter than one MMA's k
+// range per thread, multiplies the converted weights by their scale in f16 before the MMA: the product
+// of a 2-bit and a 4-bit significand, scaled to stay between 2^-18 and 2^15, is exact.
+// ---------------------------------------------------------------------------
+enum { kMxfp4 = 0, kMxfp8 = 1, kNvfp4 = 2 };
+
+template <int MODE>
+struct MxFmt {
+  static constexpr int kBits = MODE == kMxfp8 ? 8 : 4;
+  static constexpr int kGroup = MODE == kNvfp4 ? 16 : 32;
+  static constexpr int kStepK = kStepBytes * 8 / kBits;             // 64 or 32
+  static constexpr int kScalesPerStep = kStepK / kGroup;            // mxfp4 2, mxfp8 1, nvfp4 4
+  static constexpr int kScalesPerChunk = kStepsPerChunk * kScalesPerStep;
+  static constexpr int kUnitSteps = 16 / kScalesPerStep;            // a K part begins on 16 scale bytes
+  static constexpr int kXStep = kStepK * 2;
+  // mxfp4 takes words t4 and t4 + 4 of a step (one scale group per MMA pair), so a quad reads 64 contiguous
+  // bytes of activations, as it does for 8-bit codes; nvfp4 takes words 2 t4 and 2 t4 + 1
+  static constexpr int kRowPad = MODE == kNvfp4 ? 16 : 64;
+  static constexpr int kOrder = MODE == kMxfp8 ? kOrderBytes : kOrderNibbles;
+};
+
+namespace dev {
+template <int OFF>
+__device__ __forceinline__ uint32_t lds32(uint32_t a) {
+  uint32_t v;
+  asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(a), "n"(OFF));
+  return v;
+}
+// eight e2m1 codes of a word -> four registers of two f16 each, codes (j, j + 4) in register j
+__device__ __forceinline__ void e2m1_to_f16x2(uint32_t w, uint32_t (&r)[4]) {
+  r[0] = ((w << 12) & 0x80008000u) | ((w << 9) & 0x0E000E00u);
+  r[1] = ((w << 8) & 0x80008000u) | ((w << 5) & 0x0E000E00u);
+  r[2] = ((w << 4) & 0x80008000u) | ((w << 1) & 0x0E000E00u);
+  r[3] = (w & 0x80008000u) | ((w >> 3) & 0x0E000E00u);
+}
+// four e4m3 bytes of a word -> bytes (0, 2) and bytes (1, 3) as two f16 each
+__device__ __forceinline__ void e4m3_to_f16x2(uint32_t w, uint32_t& even, uint32_t& odd) {
+  even = ((w << 8) & 0x80008000u) | ((w << 7) & 0x3F803F80u);
+  odd = (w & 0x80008000u) | ((w >> 1) & 0x3F803F80u);
+}
+// byte IDX of a word of e8m0 scales as f32; exact except for the codes 0 (2^-127) and 255 (NaN), which the caller
+// detects per word and decodes with e8m0_exact
+template <int IDX>
+__device__ __forceinline__ float e8m0_fast(uint32_t w) {
+  const uint32_t v = IDX == 0 ? (w << 23) : IDX == 1 ? (w << 15) : IDX == 2 ? (w << 7) : (w >> 1);
+  return __uint_as_float(v & 0x7F800000u);
+}
+__device__ __forceinline__ float e8m0_exact(uint32_t b) {
+  if (b == 0xFFu) return __uint_as_float(0x7FC00000u);
+  return __uint_as_float(b == 0 ? 0x00400000u : (b << 23));
+}
+__device__ __forceinline__ bool has_byte_00_or_ff(uint32_t w) { return (__vcmpeq4(w, 0u) | __vcmpeq4(w, 0xFFFFFFFFu)) != 0; }
+__device__ __forceinline__ bool has_e4m3_nan(uint32_t w) { return __vcmpeq4(w & 0x7F7F7F7Fu, 0x7F7F7F7Fu) != 0; }
+__device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+}  // namespace dev
+
+static size_t mx_fixed_smem(int mode, int warps, int M, int MT, int K) {
+  const int pad = mode == kNvfp4 ? 16 : 64;
+  return static_cast<size_t>(warps) * kBox + static_cast<size_t>(M) * (2 * K + pad) + static_cast<size_t>(warps) * 32 * MT * 4 * 4 +
+         static_cast<size_t>(warps) * (8 + 1) * 8 + 1024;
+}
+
+static bool mx_plan(int mode, int64_t M, int64_t N, int64_t K, Plan* p) {
+  const int group = mode == kNvfp4 ? 16 : 32, bits = mode == kMxfp8 ? 8 : 4;
+  if (N % 16 != 0 || K % (16 * group) != 0 || K * bits / 8 < 128 || K > (1 << 17)) return false;
+  const int MT = M <= 8 ? 1 : 2;
+  const int unit_chunks = (mode == kMxfp4 ? 8 : mode == kMxfp8 ? 16 : 4) / kStepsPerChunk;
+  return choose(N / 16, static_cast<int>(K / (16 * group)), unit_chunks,      // units of 16 scale bytes
+                [&](int warps) { return mx_fixed_smem(mode, warps, static_cast<int>(M), MT, static_cast<int>(K)); }, p);
+}
+
+template <int MODE, int MT>
+__global__ void __launch_bounds__(kMaxWarps * 32)
+mx_ring_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap smap,
+               const __half* __restrict__ x, __half* __restrict__ y, int M, int N, int K, int stages, int tiles, int ksplit,
+               int* status) {
+  using namespace dev;
+  using F = MxFmt<MODE>;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  const int threads = blockDim.x, warps = threads >> 5;
+  const int row_bytes = K * 2 + F::kRowPad;
+  uint8_t* ring = smem;
+  uint8_t* sbox = ring + warps * stages * kBox;
+  uint8_t* xs = sbox + warps * kBox;
+  float* hand = reinterpret_cast<float*>(xs + M * row_bytes);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(hand + warps * 32 * MT * 4);
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int tile = warp % tiles, ks = warp / tiles;
+  const int n0 = (blockIdx.x * tiles + tile) * 16;
+  const int g8 = lane >> 2, t4 = lane & 3;
+  const int rho = ((g8 & 3) << 1) | (g8 >> 2);
+  const bool active = n0 < N;
+  const int U = K / (16 * F::kGroup);
+  const int u_begin = (U * ks) / ksplit, u_end = (U * (ks + 1)) / ksplit;
+  const int total = active ? (u_end - u_begin) * F::kUnitSteps : 0;
+  const int nchunks = total / kStepsPerChunk;
+  const int seg_begin = u_begin * (16 * F::kGroup * F::kBits / 8);
+  uint8_t* my_ring = ring + warp * stages * kBox;
+  uint8_t* my_sbox = sbox + warp * kBox;
+  uint64_t* my_bar = bars + warp * (stages + 1);
+
+  if (lane == 0) {
+    for (int i = 0; i <= stages; ++i) mbar_init(my_bar + i, 1);
+    fence_mbar_init();
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  pdl_wait();
+  pdl_launch_dependents();
+  if (lane == 0 && active) {
+    mbar_expect_tx(my_bar + stages, kBox);
+    tma_load_2d(my_sbox, &smap, my_bar + stages, u_begin * 16, n0);
+    for (int c = 0; c < stages && c < nchunks; ++c) {
+      mbar_expect_tx(my_bar + c, kBox);
+      tma_load_2d(my_ring + c * kBox, &wmap, my_bar + c, seg_begin + c * 128, n0);
+    }
+  }
+  __syncwarp();
+  stage_activations<F::kOrder, false>(x, xs, row_bytes, M, K / 8, nullptr, 0, 1, false);
+  __syncthreads();
+
+  float ys[MT][4];
+#pragma unroll
+  for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) ys[mt][i] = 0.f;
+  uint32_t nan_lo = 0, nan_hi = 0;     // mxfp8: a NaN code seen in row rho / rho + 8
+  bool ok = true;
+  int consumed = 0, requested = stages < nchunks ? stages : nchunks;
+  if (active) {
+    // this thread's bytes of step 0 within a box (row rho; the 16-byte chunks of a row are XOR-swizzled by rho):
+    // 8 bytes at 8 t4 (nvfp4, mxfp8: words 2 t4, 2 t4 + 1) or 4 bytes at 4 t4 and 16 further (mxfp4: words t4, t4 + 4)
+    const uint32_t wthread = MODE == kMxfp4 ? rho * 128 + (rho << 4) + (t4 << 2)
+                                            : rho * 128 + (((t4 >> 1) ^ rho) << 4) + ((t4 & 1) << 3);
+    uint32_t xa[MT];
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+      const int row = min(mt * 8 + g8, M - 1);
+      xa[mt] = smem_u32(xs) + row * row_bytes + (u_begin * (16 * F::kGroup / 8) + (MODE == kNvfp4 ? 2 * t4 : t4)) * 16;
+    }
+    const uint32_t sa = smem_u32(my_sbox) + rho * 128;
+    ok = wait_box(my_bar + stages, 0, status, 72);
+    float d[MT][4];
+    if (MODE == kNvfp4) {
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) d[mt][i] = 0.f;
+    }
+    const uint32_t sel_t4 = (t4 << 12) | (4u << 8) | (t4 << 4) | 4u;   // scale byte t4 of a word into the high byte of both halves
+    int st = 0, prev_st = 0;
+    uint32_t phase = 0;
+    const uint32_t ring32 = smem_u32(my_ring);
+    for (int c = 0; c < nchunks && ok; ++c) {
+      ok = wait_box(my_bar + st, phase, status, 73);
+      if (!ok) break;
+      if (c >= 1 && requested < nchunks) {
+        if (lane == 0) {
+          mbar_expect_tx(my_bar + prev_st, kBox);
+          tma_load_2d(my_ring + prev_st * kBox, &wmap, my_bar + prev_st, seg_begin + requested * 128, n0);
+        }
+        ++requested;
+      }
+      // ---- this chunk's scale bytes of rows rho and rho + 8
+      uint32_t sl[4], sh[4];      // words of scale bytes (mxfp4: 2, mxfp8: 1, nvfp4: 4 used)
+      bool special;
+      if (MODE == kMxfp4) {
+        const uint32_t sq = sa + ((((c >> 1) ^ rho) & 7) << 4) + ((c & 1) << 3);
+        const uint2 a = lds64<0>(sq), b = lds64<1024>(sq);
+        sl[0] = a.x; sl[1] = a.y; sh[0] = b.x; sh[1] = b.y;
+        special = has_byte_00_or_ff(a.x) | has_byte_00_or_ff(a.y) | has_byte_00_or_ff(b.x) | has_byte_00_or_ff(b.y);
+      } else if (MODE == kMxfp8) {
+        const uint32_t sq = sa + ((((c >> 2) ^ rho) & 7) << 4) + ((c & 3) << 2);
+        sl[0] = lds32<0>(sq); sh[0] = lds32<1024>(sq);
+        special = has_byte_00_or_ff(sl[0]) | has_byte_00_or_ff(sh[0]);
+      } else {
+        const uint32_t sq = sa + (((c ^ rho) & 7) << 4);
+        const uint4 a = lds128<0>(sq), b = lds128<1024>(sq);
+        sl[0] = a.x; sl[1] = a.y; sl[2] = a.z; sl[3] = a.w;
+        sh[0] = b.x; sh[1] = b.y; sh[2] = b.z; sh[3] = b.w;
+        special = has_e4m3_nan(a.x) | has_e4m3_nan(a.y) | has_e4m3_nan(a.z) | has_e4m3_nan(a.w) | has_e4m3_nan(b.x) |
+                  has_e4m3_nan(b.y) | has_e4m3_nan(b.z) | has_e4m3_nan(b.w);
+      }
+      const uint32_t wbase = (ring32 + st * kBox) | wthread;
+#pragma unroll
+      for (int s4 = 0; s4 < kStepsPerChunk; ++s4) {
+        if (MODE == kMxfp4) {
+#pragma unroll
+          for (int wi = 0; wi < 2; ++wi) {
+            const uint32_t wa = wbase ^ ((2 * s4 + wi) << 4);
+            uint32_t lo[4], hi[4];
+            e2m1_to_f16x2(lds32<0>(wa), lo);
+            e2m1_to_f16x2(lds32<1024>(wa), hi);
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+              const uint4 xq = wi ? (s4 == 0 ? lds128<64>(xa[mt]) : s4 == 1 ? lds128<128 + 64>(xa[mt]) : s4 == 2 ? lds128<256 + 64>(xa[mt]) : lds128<384 + 64>(xa[mt]))
+                                  : (s4 == 0 ? lds128<0>(xa[mt]) : s4 == 1 ? lds128<128>(xa[mt]) : s4 == 2 ? lds128<256>(xa[mt]) : lds128<384>(xa[mt]));
+              mma16816_first(d[mt], lo[0], hi[0], lo[1], hi[1], xq.x, xq.y);
+              mma16816(d[mt], lo[2], hi[2], lo[3], hi[3], xq.z, xq.w);
+            }
+            // scale byte (s4 & 1) * 2 + wi of word s4 >> 1
+            const uint32_t wl = sl[s4 >> 1], wh = sh[s4 >> 1];
+            float fl, fh;
+            if ((s4 & 1) * 2 + wi == 0) { fl = e8m0_fast<0>(wl); fh = e8m0_fast<0>(wh); }
+            else if ((s4 & 1) * 2 + wi == 1) { fl = e8m0_fast<1>(wl); fh = e8m0_fast<1>(wh); }
+            else if ((s4 & 1) * 2 + wi == 2) { fl = e8m0_fast<2>(wl); fh = e8m0_fast<2>(wh); }
+            else { fl = e8m0_fast<3>(wl); fh = e8m0_fast<3>(wh); }
+            if (special) {
+              fl = e8m0_exact((wl >> (8 * ((s4 & 1) * 2 + wi))) & 0xFFu);
+              fh = e8m0_exact((wh >> (8 * ((s4 & 1) * 2 + wi))) & 0xFFu);
+            }
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+              ys[mt][0] = fmaf(fl, d[mt][0], ys[mt][0]);
+              ys[mt][1] = fmaf(fl, d[mt][1], ys[mt][1]);
+              ys[mt][2] = fmaf(fh, d[mt][2], ys[mt][2]);
+              ys[mt][3] = fmaf(fh, d[mt][3], ys[mt][3]);
+            }
+          }
+        } else if (MODE == kMxfp8) {
+          const uint32_t wa = wbase ^ (s4 << 5);
+          const uint2 a = lds64<0>(wa), b = lds64<1024>(wa);
+          uint32_t ae0, ao0, ae1, ao1, be0, bo0, be1, bo1;
+          e4m3_to_f16x2(a.x, ae0, ao0);
+          e4m3_to_f16x2(a.y, ae1, ao1);
+          e4m3_to_f16x2(b.x, be0, bo0);
+          e4m3_to_f16x2(b.y, be1, bo1);
+          nan_lo |= __vcmpeq4(a.x & 0x7F7F7F7Fu, 0x7F7F7F7Fu) | __vcmpeq4(a.y & 0x7F7F7F7Fu, 0x7F7F7F7Fu);
+          nan_hi |= __vcmpeq4(b.x & 0x7F7F7F7Fu, 0x7F7F7F7Fu) | __vcmpeq4(b.y & 0x7F7F7F7Fu, 0x7F7F7F7Fu);
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            const uint4 xq = s4 == 0 ? lds128<0>(xa[mt]) : s4 == 1 ? lds128<64>(xa[mt]) : s4 == 2 ? lds128<128>(xa[mt]) : lds128<192>(xa[mt]);
+            mma16816_first(d[mt], ae0, be0, ao0, bo0, xq.x, xq.y);
+            mma16816(d[mt], ae1, be1, ao1, bo1, xq.z, xq.w);
+          }
+          float fl, fh;
+          if (s4 == 0) { fl = e8m0_fast<0>(sl[0]); fh = e8m0_fast<0>(sh[0]); }
+          else if (s4 == 1) { fl = e8m0_fast<1>(sl[0]); fh = e8m0_fast<1>(sh[0]); }
+          else if (s4 == 2) { fl = e8m0_fast<2>(sl[0]); fh = e8m0_fast<2>(sh[0]); }
+          else { fl = e8m0_fast<3>(sl[0]); fh = e8m0_fast<3>(sh[0]); }
+          if (special) {
+            fl = e8m0_exact((sl[0] >> (8 * s4)) & 0xFFu);
+            fh = e8m0_exact((sh[0] >> (8 * s4)) & 0xFFu);
+          }
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            ys[mt][0] = fmaf(fl, d[mt][0], ys[mt][0]);
+            ys[mt][1] = fmaf(fl, d[mt][1], ys[mt][1]);
+            ys[mt][2] = fmaf(fh, d[mt][2], ys[mt][2]);
+            ys[mt][3] = fmaf(fh, d[mt][3], ys[mt][3]);
+          }
+        } else {
+          // nvfp4: this thread's two words of the step lie in the step's 16-k group t4
+          const uint32_t wa = wbase ^ (s4 << 5);
+          const uint2 a = lds64<0>(wa), b = lds64<1024>(wa);
+          uint32_t hl = __byte_perm(sl[s4], 0u, sel_t4), hh = __byte_perm(sh[s4], 0u, sel_t4);
+          uint32_t fl = (hl & 0x80008000u) | ((hl >> 1) & 0x3F803F80u), fh = (hh & 0x80008000u) | ((hh >> 1) & 0x3F803F80u);
+          fl = hmul2_u32(fl, 0x70007000u);     // x 2^13: f16 1.0 x 2^13 = 0x7000; see the exponent budget above
+          fh = hmul2_u32(fh, 0x70007000u);
+          if (special) {
+            if ((hl & 0x7F007F00u) == 0x7F007F00u) fl = 0x7E007E00u;
+            if ((hh & 0x7F007F00u) == 0x7F007F00u) fh = 0x7E007E00u;
+          }
+#pragma unroll
+          for (int wi = 0; wi < 2; ++wi) {
+            uint32_t lo[4], hi[4];
+            e2m1_to_f16x2(wi ? a.y : a.x, lo);
+            e2m1_to_f16x2(wi ? b.y : b.x, hi);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              lo[j] = hmul2_u32(lo[j], fl);
+              hi[j] = hmul2_u32(hi[j], fh);
+            }
+#pragma unroll
+            for (int mt = 0; mt < MT; ++mt) {
+              const uint4 xq = wi ? (s4 == 0 ? lds128<16>(xa[mt]) : s4 == 1 ? lds128<128 + 16>(xa[mt]) : s4 == 2 ? lds128<256 + 16>(xa[mt]) : lds128<384 + 16>(xa[mt]))
+                                  : (s4 == 0 ? lds128<0>(xa[mt]) : s4 == 1 ? lds128<128>(xa[mt]) : s4 == 2 ? lds128<256>(xa[mt]) : lds128<384>(xa[mt]));
+              mma16816(d[mt], lo[0], hi[0], lo[1], hi[1], xq.x, xq.y);
+              mma16816(d[mt], lo[2], hi[2], lo[3], hi[3], xq.z, xq.w);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) xa[mt] += kStepsPerChunk * F::kXStep;
+      __syncwarp();
+      ++consumed;
+      prev_st = st;
+      if (++st == stages) { st = 0; phase ^= 1; }
+    }
+    if (!ok) {
+      for (int c = consumed + 1; c < requested; ++c) {
+        if (++st == stages) { st = 0; phase ^= 1; }
+        mbar_wait_relaxed_warp(my_bar + st, phase, nullptr, 0);
+      }
+    }
+    if (MODE == kNvfp4) {
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) ys[mt][i] = d[mt][i];
+    }
+    if (MODE == kMxfp8) {
+      // a NaN code anywhere in a weight row makes that output column NaN for every activation row; the four threads
+      // of a quad hold the same two weight rows
+      nan_lo |= __shfl_xor_sync(0xFFFFFFFFu, nan_lo, 1);
+      nan_lo |= __shfl_xor_sync(0xFFFFFFFFu, nan_lo, 2);
+      nan_hi |= __shfl_xor_sync(0xFFFFFFFFu, nan_hi, 1);
+      nan_hi |= __shfl_xor_sync(0xFFFFFFFFu, nan_hi, 2);
+      const float qnan = __uint_as_float(0x7FC00000u);
+#pragma unroll
+      for (int mt = 0; mt < MT; ++mt) {
+        if (nan_lo) ys[mt][0] = ys[mt][1] = qnan;
+        if (nan_hi) ys[mt][2] = ys[mt][3] = qnan;
+      }
+    }
+  }
+  // the power of two that the code placement left out: e2m1 2^14, e4m3 2^8; nvfp4: 2^14 for the codes, 2^8 for
+  // the scales, less the 2^13 the scales were multiplied by
+  constexpr float kFinal = MODE == kMxfp4 ? 16384.f : MODE == kMxfp8 ? 256.f : 512.f;
+  float* slot = hand + (warp * 32 + lane) * MT * 4;
+  if (ks != 0 && active) {
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) slot[mt * 4 + i] = ys[mt][i] * kFinal;
+  }
+  __syncthreads();
+  if (ks == 0 && active) {
+#pragma unroll
+    for (int mt = 0; mt < MT; ++mt) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float v = ys[mt][i] * kFinal;
+        for (int o = 1; o < ksplit; ++o) v += hand[((o * tiles + tile) * 32 + lane) * MT * 4 + mt * 4 + i];
+        const int n = n0 + rho + ((i >> 1) << 3), m = mt * 8 + 2 * t4 + (i & 1);
+        if (m < M) y[static_cast<size_t>(m) * N + n] = __float2half_rn(v);
+      }
+    }
+  }
+}
+
+template <int MODE, int MT>
+static int mx_launch_one(const Plan& p, const CUtensorMap& wmap, const CUtensorMap& smap, const void* x, void* y, int M, int N,
+                         int K, cudaStream_t stream) {
+  static std::atomic<uint64_t> configured{0};
+  auto kernel = mx_ring_kernel<MODE, MT>;
+  if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(kernel), kMaxSmem, configured)) return rc;
+  cudaError_t e = launch_pdl(kernel, dim3(p.grid), dim3(p.warps * 32), p.smem, stream, wmap, smap, static_cast<const __half*>(x),
+                             static_cast<__half*>(y), M, N, K, p.stages, p.tiles, p.ksplit, device_status_word());
+  if (e != cudaSuccess) return set_error(QMM_ERR_CUDA, "mx_qgemm_f16 (TMA ring): launch failed: %s", cudaGetErrorString(e));
+  return QMM_OK;
+}
+
 }  // namespace opapi_tc
 
 // True when the TMA-ring kernel covers the call (f16 activations, 1 <= M <= 16, groups of 1, 2 or 4 steps
@@ -478,6 +875,42 @@ int affine_ring_launch(int bits, const void* x, const void* w, const float* scal
   cudaStream_t st = static_cast<cudaStream_t>(stream);
   return bits == 4 ? launch_bits<4>(p, wmap, smap, bmap, x, y, (int)M, (int)N, (int)K, (int)gs, st)
                    : launch_bits<8>(p, wmap, smap, bmap, x, y, (int)M, (int)N, (int)K, (int)gs, st);
+}
+
+// The same for the MX modes (0 mxfp4, 1 mxfp8, 2 nvfp4): f16 activations, 1 <= M <= 16, K a multiple of 16 scale
+// groups, 16-byte aligned operands.
+bool mx_ring_covers(int64_t M, int64_t N, int64_t K, int mode, int dtype, const void* x, const void* w, const void* scales) {
+  using namespace opapi_tc;
+  if (mode < 0 || mode > 2 || dtype != QMM_F16 || M < 1 || M > 16) return false;
+  if (!aligned(x, 16) || !aligned(w, 16) || !aligned(scales, 16)) return false;
+  Plan p;
+  return mx_plan(mode, M, N, K, &p);
+}
+
+int mx_ring_launch(int mode, const void* x, const void* w, const void* scales, void* y, int64_t M, int64_t N, int64_t K,
+                   void* stream) {
+  using namespace opapi_tc;
+  Plan p;
+  QMM_REQUIRE(mx_plan(mode, M, N, K, &p), QMM_ERR_UNSUPPORTED, "mx_ring_launch: shape not covered");
+  if (int st = read_device_status())
+    return set_error(QMM_ERR_TIMEOUT, "qmm_mx_matmul: an earlier kernel gave up a wait (status 0x%x); "
+                     "call qmm_clear_device_status() after handling it", st);
+  CUtensorMap wmap, smap;
+  const int bits = mode == kMxfp8 ? 8 : 4, group = mode == kNvfp4 ? 16 : 32;
+  const uint64_t row_bytes = static_cast<uint64_t>(K) * bits / 8, srow = static_cast<uint64_t>(K / group);
+  if (int rc = make_tensor_map_2d(&wmap, w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, static_cast<uint64_t>(N), row_bytes, row_bytes, 16,
+                                  128, CU_TENSOR_MAP_SWIZZLE_128B))
+    return rc;
+  if (int rc = make_tensor_map_2d(&smap, scales, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, static_cast<uint64_t>(N), srow, srow, 16, 128,
+                                  CU_TENSOR_MAP_SWIZZLE_128B))
+    return rc;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  const int m = static_cast<int>(M), n = static_cast<int>(N), k = static_cast<int>(K);
+  if (mode == kMxfp4)
+    return M <= 8 ? mx_launch_one<kMxfp4, 1>(p, wmap, smap, x, y, m, n, k, st) : mx_launch_one<kMxfp4, 2>(p, wmap, smap, x, y, m, n, k, st);
+  if (mode == kMxfp8)
+    return M <= 8 ? mx_launch_one<kMxfp8, 1>(p, wmap, smap, x, y, m, n, k, st) : mx_launch_one<kMxfp8, 2>(p, wmap, smap, x, y, m, n, k, st);
+  return M <= 8 ? mx_launch_one<kNvfp4, 1>(p, wmap, smap, x, y, m, n, k, st) : mx_launch_one<kNvfp4, 2>(p, wmap, smap, x, y, m, n, k, st);
 }
 
 }  // namespace qmm

@@ -136,3 +136,60 @@ def test_affine_f16_tiny_and_large_activations(cuda, bits):
         ref = O.affine_qmm(x.astype(np.float32), p, s, b, bits=bits, group_size=gs, K=K)
         assert np.isfinite(out).all()
         np.testing.assert_allclose(out, ref, rtol=2e-3, atol=2e-3 * float(np.abs(ref).max()))
+
+
+@pytest.mark.parametrize("M", [1, 5, 8, 9, 16])
+@pytest.mark.parametrize("mode,K,N", [("mxfp4", 4096, 14336), ("mxfp4", 512, 16), ("mxfp4", 8192, 2384), ("mxfp4", 1024, 208),
+                                      ("mxfp8", 4096, 14336), ("mxfp8", 512, 16), ("mxfp8", 8192, 2384), ("mxfp8", 1536, 208),
+                                      ("nvfp4", 4096, 14336), ("nvfp4", 256, 16), ("nvfp4", 8192, 2384), ("nvfp4", 768, 208)])
+def test_mx_f16_decode_sizes(cuda, M, mode, K, N):
+    """f16 activations with at most 16 rows and K a multiple of 16 scale groups take the tensor-core kernel
+    (codes placed in f16 as they are, power-of-two factor applied once); same result as the
+    dequantise-then-multiply arithmetic of the reference's fused kernels up to f32 summation order."""
+    rng = np.random.default_rng(M * 1000 + K + N)
+    x = rng.standard_normal((M, K)).astype(np.float16)
+    w = (rng.standard_normal((N, K)) * np.exp(rng.standard_normal((N, 1)))).astype(np.float32) * 0.05
+    p, s = Q.mx_quantize(w, mode=mode)
+    out = Q.quantized_matmul(x, p, s, mode=mode, K=K)
+    assert out.dtype == np.float16 and out.shape == (M, N)
+    ref = O.mx_qmm(x.astype(np.float32), p, s, mode=mode, K=K)
+    np.testing.assert_allclose(out.astype(np.float32), ref, rtol=1e-3, atol=1e-3 * float(np.abs(ref).max()))
+    wide = Q.quantized_matmul(x.astype(np.float32), p, s, mode=mode, K=K)    # f32 activations: the general kernel
+    np.testing.assert_allclose(out.astype(np.float32), wide, rtol=1e-3, atol=1e-3 * float(np.abs(ref).max()))
+
+
+@pytest.mark.parametrize("mode", ["mxfp4", "mxfp8", "nvfp4"])
+def test_mx_f16_special_codes(cuda, mode):
+    """NaN element codes (e4m3 0x7F / 0xFF), NaN scale codes (e8m0 0xFF, e4m3 0x7F) and the e8m0 code 0
+    (2^-127) on the tensor-core route: NaN reaches exactly the output columns of the weight rows that
+    hold one, for every activation row; everything else is unchanged."""
+    rng = np.random.default_rng(11)
+    K, N, M = 1024, 64, 3
+    group = 16 if mode == "nvfp4" else 32
+    x = rng.standard_normal((M, K)).astype(np.float16)
+    w = rng.standard_normal((N, K)).astype(np.float32) * 0.1
+    p, s = Q.mx_quantize(w, mode=mode)
+    p, s = p.copy(), s.copy()
+    nan_rows = set()
+    if mode == "mxfp8":
+        p[5, 700] = 0x7F
+        p[40, 3] = 0xFF
+        nan_rows |= {5, 40}
+    if mode == "nvfp4":
+        s[9, 17] = 0x7F
+        s[33, K // group - 1] = 0xFF
+        nan_rows |= {9, 33}
+    else:
+        s[12, 5] = 0xFF
+        nan_rows |= {12}
+        s[20, 7] = 0          # 2^-127: the group contributes (next to) nothing
+    out = Q.quantized_matmul(x, p, s, mode=mode, K=K).astype(np.float32)
+    ref = O.mx_qmm(x.astype(np.float32), p, s, mode=mode, K=K)
+    for n in range(N):
+        if n in nan_rows:
+            assert np.isnan(out[:, n]).all(), n
+            assert np.isnan(ref[:, n]).all(), n
+        else:
+            assert np.isfinite(out[:, n]).all(), n
+    keep = [n for n in range(N) if n not in nan_rows]
+    np.testing.assert_allclose(out[:, keep], ref[:, keep], rtol=1e-3, atol=1e-3 * float(np.abs(ref[:, keep]).max()))
