@@ -10,6 +10,10 @@
 // warp reduces with shuffles.  Arithmetic follows the reference kernels:
 // weight = scale * q + bias (affine) or scale * element (MX) in f32, product
 // and accumulation in f32, one final cast; NaN codes propagate.
+//
+// These CUDA-core kernels take any M and f32 or f16 activations.  Decode-sized
+// f16 problems (M <= 16) go to the tensor-core kernels instead: the TMA-ring
+// kernels of opapi_tc.cu where the shape allows, else affine_tc_kernel below.
 #include "common.cuh"
 
 namespace qmm {
