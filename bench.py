@@ -648,6 +648,8 @@ def run_detail(torch, ops, synthetic, lib, device, peaks, items=None):
         _detail_int4_prefill(torch, ops, synthetic, device, peaks, detail)
     if want("int8_dot"):
         _detail_int8_dot(torch, synthetic, lib, device, peaks, graph_time, detail)
+    if items is not None and "operator_api_sweep" in items:  # not part of the default run
+        _detail_operator_api_sweep(torch, synthetic, lib, device, graph_time, detail)
     if items is not None and "int4_decode_sweep" in items:  # not part of the default run
         _detail_int4_sweep(torch, ops, synthetic, lib, device, graph_time, detail)
     if want("llama_decode"):
@@ -736,6 +738,32 @@ def _detail_int4_sweep(torch, ops, synthetic, lib, device, graph_time, detail):
         rows.append({"K": K, "N": N, "MB": nbytes / 1e6, "us": us, "TB/s": nbytes / us / 1e6})
         del wqs
     detail["int4_g128_decode_M1_size_sweep"] = rows
+
+
+def _detail_operator_api_sweep(torch, synthetic, lib, device, graph_time, detail):
+    # affine 4-bit g64, f16, M = 4 over a range of sizes: time = fixed cost + bytes / streaming rate
+    gen = synthetic.torch_generator(device, 6, 9)
+    st = lambda: torch.cuda.current_stream().cuda_stream  # noqa: E731
+    rows = []
+    M, gs = 4, 64
+    for K, N in [(4096, 2368), (4096, 14336), (4096, 28672), (8192, 28672), (8192, 57344)]:
+        wbytes = N * K // 2
+        copies = max(2, min(10, (300 << 20) // wbytes))
+        x = synthetic.device_normal((M, K), device, gen, torch.float16)
+        y = torch.empty((M, N), dtype=torch.float16, device=device)
+        ws = [torch.randint(0, 256, (wbytes,), dtype=torch.uint8, device=device, generator=gen) for _ in range(copies)]
+        sc = synthetic.device_uniform((N, K // gs), 0.002, 0.01, device, gen)
+        bi = synthetic.device_uniform((N, K // gs), -0.05, 0.05, device, gen)
+
+        def run(i):
+            assert lib.qmm_affine_matmul(x.data_ptr(), ws[i % copies].data_ptr(), sc.data_ptr(), bi.data_ptr(),
+                                         y.data_ptr(), M, N, K, 4, gs, 1, st()) == 0
+
+        us = graph_time(run, copies * 2)
+        nbytes = wbytes + 2 * N * (K // gs) * 4
+        rows.append({"K": K, "N": N, "MB": nbytes / 1e6, "us": us, "TB/s": nbytes / us / 1e6})
+        del ws
+    detail["operator_api_affine_4bit_g64_M4_size_sweep"] = rows
 
 
 def _detail_operator_api(torch, synthetic, lib, device, hbm, graph_time, detail):
@@ -940,7 +968,7 @@ def main():
     ap.add_argument("--detail-only", action="store_true",
                     help="run only the per-workload detail (small case for profiling) and print it as JSON")
     ap.add_argument("--detail-items", default="",
-                    help="comma-separated subset of int4_decode,int4_prefill,int8_dot,llama_decode,operator_api,small_f32 (and int4_decode_sweep, "
+                    help="comma-separated subset of int4_decode,int4_prefill,int8_dot,llama_decode,operator_api,small_f32 (and int4_decode_sweep, operator_api_sweep, "
                          "which is not part of the default run)")
     args = ap.parse_args()
     if args.impl == "reference":

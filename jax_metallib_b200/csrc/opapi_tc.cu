@@ -21,6 +21,8 @@
 // Per 64 weights of a row the main loop issues 1 shared load of weights, 2 of activations (4-bit), 10
 // logic instructions, 2 MMAs and, per group, 12 FMAs; that is what bounds it, not the MMA rate.
 #include <atomic>
+#include <type_traits>
+#include <utility>
 
 #include "common.cuh"
 
@@ -36,6 +38,17 @@ constexpr int kMaxSmem = 227 * 1024;
 
 namespace dev {
 using namespace qmm::dev;
+
+// A loop whose index is a compile-time constant in the body (shared-memory offsets fold into the load
+// instructions, the choice of MMA form and of scale component is made at compile time): f(integral_constant<0>) ...
+template <typename Fn, int... Is>
+__device__ __forceinline__ void static_for_impl(Fn& f, std::integer_sequence<int, Is...>) {
+  (f(std::integral_constant<int, Is>{}), ...);
+}
+template <int N, typename Fn>
+__device__ __forceinline__ void static_for(Fn&& f) {
+  static_for_impl(f, std::make_integer_sequence<int, N>{});
+}
 
 __device__ __forceinline__ void mma16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
                                          uint32_t b1) {
@@ -104,9 +117,13 @@ enum { kOrderAffine4 = 0, kOrderBytes = 1, kOrderNibbles = 2 };
 // Stages x[M][K] (f16) into shared memory, 8 k (16 bytes) per thread and pass, every global load of a pass issued
 // before the first store.  With SUMS, also the sum of each (row, group) into xsum[group * stride + row]: fused into
 // the same pass by shuffles when a group is a power-of-two number of lanes (fused_sum), in a fixed order.
-template <int ORDER, bool SUMS>
+//
+// after_first_loads() runs once, after the first pass's loads have been issued and before anything waits for them:
+// the caller requests its TMA boxes there, so that the small activation loads are not queued behind them.
+template <int ORDER, bool SUMS, typename Fn>
 __device__ __forceinline__ void stage_activations(const __half* __restrict__ x, uint8_t* xs, int row_bytes, int M, int chunks,
-                                                  float* xsum, int stride, int lanes_per_group, bool fused_sum) {
+                                                  float* xsum, int stride, int lanes_per_group, bool fused_sum,
+                                                  Fn after_first_loads) {
   const int tid = threadIdx.x, lane = tid & 31, threads = blockDim.x;
   const int n_it = M * chunks;
   int m = 0, c8 = tid;                                    // i = m * chunks + c8, advanced without a division
@@ -123,6 +140,7 @@ __device__ __forceinline__ void stage_activations(const __half* __restrict__ x, 
       c8 += threads;
       while (c8 >= chunks) { c8 -= chunks; ++m; }
     }
+    if (i0 == tid) after_first_loads();
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
       const int i = i0 + j * threads;
@@ -224,7 +242,7 @@ static bool plan(int bits, int64_t M, int64_t N, int64_t K, int64_t gs, Plan* p)
 }
 
 template <int BITS, int MT, int SPG>
-__global__ void __launch_bounds__(kMaxWarps * 32)
+__global__ void __launch_bounds__(kMaxWarps * 32, 1)
 affine_ring_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap smap,
                    const __grid_constant__ CUtensorMap bmap, const __half* __restrict__ x, __half* __restrict__ y, int M,
                    int N, int K, int gs, int stages, int tiles, int ksplit, int* status) {
@@ -260,14 +278,18 @@ affine_ring_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
   uint64_t* my_bar = bars + warp * (stages + 1);             // [stages] = the scale and bias boxes
 
   if (lane == 0) {
+    tma_prefetch_desc(&wmap);
+    tma_prefetch_desc(&smap);
+    tma_prefetch_desc(&bmap);
     for (int i = 0; i <= stages; ++i) mbar_init(my_bar + i, 1);
     fence_mbar_init();
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
+  __syncwarp();
   pdl_wait();                 // everything below may read what the previous kernel wrote
   pdl_launch_dependents();
-  if (lane == 0) {
-    if (active) {
+  auto request_boxes = [&]() {
+    if (lane == 0 && active) {
       mbar_expect_tx(my_bar + stages, 2 * kBox);
       tma_load_2d(my_sbox, &smap, my_bar + stages, g_begin, n0);
       tma_load_2d(my_sbox + kBox, &bmap, my_bar + stages, g_begin, n0);
@@ -276,15 +298,14 @@ affine_ring_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
         tma_load_2d(my_ring + c * kBox, &wmap, my_bar + c, seg_begin + c * 128, n0);
       }
     }
-  }
-  __syncwarp();
+  };
 
   // ---- activations in MMA slot order, sums per (row, group)
   const int chunks = K / 8;
   const int lanes_per_group = gs / 8;
   const bool fused_sum = lanes_per_group <= 32 && (lanes_per_group & (lanes_per_group - 1)) == 0;
   stage_activations<BITS == 4 ? kOrderAffine4 : kOrderBytes, true>(x, xs, row_bytes, M, chunks, xsum, MT * 8, lanes_per_group,
-                                                                  fused_sum);
+                                                                  fused_sum, request_boxes);
   // rows m >= M only feed result columns that are never stored; keep them finite
   for (int i = tid; i < G * MT * 8; i += threads)
     if ((i % (MT * 8)) >= M) xsum[i] = 0.f;
@@ -348,21 +369,20 @@ affine_ring_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
       const uint32_t sq = sa + ((((gq >> 2) ^ rho) & 7) << 4);
       const float4 s_lo = lds128f(sq), s_hi = lds128f(sq + 1024), b_lo = lds128f(sq + kBox), b_hi = lds128f(sq + kBox + 1024);
       const uint32_t wbase = (ring32 + st * kBox) | wthread;
-#pragma unroll
-      for (int s4 = 0; s4 < kStepsPerChunk; ++s4) {
+      static_for<kStepsPerChunk>([&](auto s4c) {
+        constexpr int s4 = decltype(s4c)::value;
         const uint32_t wa = wbase ^ (s4 << 5);
         const uint2 a = lds64<0>(wa), b = lds64<1024>(wa);
-        const bool first = s4 % SPG == 0;
-        if (BITS == 4) {
-#pragma unroll
-          for (int wi = 0; wi < 2; ++wi) {
+        constexpr bool first = s4 % SPG == 0;
+        if constexpr (BITS == 4) {
+          static_for<2>([&](auto wic) {
+            constexpr int wi = decltype(wic)::value;
             const uint32_t lo = wi ? a.y : a.x, hi = wi ? b.y : b.x;
             const uint32_t lo8 = lo >> 8, hi8 = hi >> 8;
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
-              const uint4 xq = wi ? (s4 == 0 ? lds128<16>(xa[mt]) : s4 == 1 ? lds128<128 + 16>(xa[mt]) : s4 == 2 ? lds128<256 + 16>(xa[mt]) : lds128<384 + 16>(xa[mt]))
-                                  : (s4 == 0 ? lds128<0>(xa[mt]) : s4 == 1 ? lds128<128>(xa[mt]) : s4 == 2 ? lds128<256>(xa[mt]) : lds128<384>(xa[mt]));
-              if (wi == 0 && first) {
+              const uint4 xq = lds128<s4 * 128 + wi * 16>(xa[mt]);
+              if constexpr (wi == 0 && first) {
                 mma16816_first(d1[mt], lo & kLo4, hi & kLo4, lo8 & kLo4, hi8 & kLo4, xq.x, xq.y);
                 mma16816_first(d16[mt], lo & kHi4, hi & kHi4, lo8 & kHi4, hi8 & kHi4, xq.z, xq.w);
               } else {
@@ -370,25 +390,25 @@ affine_ring_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
                 mma16816(d16[mt], lo & kHi4, hi & kHi4, lo8 & kHi4, hi8 & kHi4, xq.z, xq.w);
               }
             }
-          }
+          });
         } else {
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
-            const uint4 xq = s4 == 0 ? lds128<0>(xa[mt]) : s4 == 1 ? lds128<64>(xa[mt]) : s4 == 2 ? lds128<128>(xa[mt]) : lds128<192>(xa[mt]);
-            if (first) mma16816_first(d1[mt], a.x & kByte, b.x & kByte, (a.x >> 8) & kByte, (b.x >> 8) & kByte, xq.x, xq.y);
+            const uint4 xq = lds128<s4 * 64>(xa[mt]);
+            if constexpr (first) mma16816_first(d1[mt], a.x & kByte, b.x & kByte, (a.x >> 8) & kByte, (b.x >> 8) & kByte, xq.x, xq.y);
             else mma16816(d1[mt], a.x & kByte, b.x & kByte, (a.x >> 8) & kByte, (b.x >> 8) & kByte, xq.x, xq.y);
             mma16816(d1[mt], a.y & kByte, b.y & kByte, (a.y >> 8) & kByte, (b.y >> 8) & kByte, xq.z, xq.w);
           }
         }
-        if (s4 % SPG == SPG - 1) {      // a group ends
-          const int j = (GPC == 4) ? s4 : ((gq & 3) + s4 / SPG);   // component of the 4-group chunk; static when GPC == 4
+        if constexpr (s4 % SPG == SPG - 1) {      // a group ends
+          // component of the 4-group chunk of scales: static when a chunk of steps holds 4 groups
+          const int j = (GPC == 4) ? s4 : ((gq & 3) + s4 / SPG);
           const float sl = sel4(s_lo, j & 3), sh = sel4(s_hi, j & 3), bl = sel4(b_lo, j & 3), bh = sel4(b_hi, j & 3);
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
-            const float2 xv = s4 / SPG == 0 ? lds64f<0>(xsa + mt * 32) : s4 / SPG == 1 ? lds64f<MT * 32>(xsa + mt * 32)
-                              : s4 / SPG == 2 ? lds64f<2 * MT * 32>(xsa + mt * 32) : lds64f<3 * MT * 32>(xsa + mt * 32);
+            const float2 xv = lds64f<(s4 / SPG) * MT * 32>(xsa + mt * 32);
             float t0 = d1[mt][0], t1 = d1[mt][1], t2 = d1[mt][2], t3 = d1[mt][3];
-            if (BITS == 4) {
+            if constexpr (BITS == 4) {
               t0 = fmaf(d16[mt][0], 0.0625f, t0);
               t1 = fmaf(d16[mt][1], 0.0625f, t1);
               t2 = fmaf(d16[mt][2], 0.0625f, t2);
@@ -404,7 +424,7 @@ affine_ring_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
             yb[mt][3] = fmaf(bh, xv.y, yb[mt][3]);
           }
         }
-      }
+      });
       gq += GPC;
       xsa += GPC * MT * 32;
 #pragma unroll
@@ -556,7 +576,7 @@ static bool mx_plan(int mode, int64_t M, int64_t N, int64_t K, Plan* p) {
 }
 
 template <int MODE, int MT>
-__global__ void __launch_bounds__(kMaxWarps * 32)
+__global__ void __launch_bounds__(kMaxWarps * 32, 1)
 mx_ring_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap smap,
                const __half* __restrict__ x, __half* __restrict__ y, int M, int N, int K, int stages, int tiles, int ksplit,
                int* status) {
@@ -587,22 +607,25 @@ mx_ring_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
   uint64_t* my_bar = bars + warp * (stages + 1);
 
   if (lane == 0) {
+    tma_prefetch_desc(&wmap);
+    tma_prefetch_desc(&smap);
     for (int i = 0; i <= stages; ++i) mbar_init(my_bar + i, 1);
     fence_mbar_init();
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
+  __syncwarp();
   pdl_wait();
   pdl_launch_dependents();
-  if (lane == 0 && active) {
-    mbar_expect_tx(my_bar + stages, kBox);
-    tma_load_2d(my_sbox, &smap, my_bar + stages, u_begin * 16, n0);
-    for (int c = 0; c < stages && c < nchunks; ++c) {
-      mbar_expect_tx(my_bar + c, kBox);
-      tma_load_2d(my_ring + c * kBox, &wmap, my_bar + c, seg_begin + c * 128, n0);
+  stage_activations<F::kOrder, false>(x, xs, row_bytes, M, K / 8, nullptr, 0, 1, false, [&]() {
+    if (lane == 0 && active) {
+      mbar_expect_tx(my_bar + stages, kBox);
+      tma_load_2d(my_sbox, &smap, my_bar + stages, u_begin * 16, n0);
+      for (int c = 0; c < stages && c < nchunks; ++c) {
+        mbar_expect_tx(my_bar + c, kBox);
+        tma_load_2d(my_ring + c * kBox, &wmap, my_bar + c, seg_begin + c * 128, n0);
+      }
     }
-  }
-  __syncwarp();
-  stage_activations<F::kOrder, false>(x, xs, row_bytes, M, K / 8, nullptr, 0, 1, false);
+  });
   __syncthreads();
 
   float ys[MT][4];
@@ -668,32 +691,28 @@ mx_ring_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
                   has_e4m3_nan(b.y) | has_e4m3_nan(b.z) | has_e4m3_nan(b.w);
       }
       const uint32_t wbase = (ring32 + st * kBox) | wthread;
-#pragma unroll
-      for (int s4 = 0; s4 < kStepsPerChunk; ++s4) {
-        if (MODE == kMxfp4) {
-#pragma unroll
-          for (int wi = 0; wi < 2; ++wi) {
+      static_for<kStepsPerChunk>([&](auto s4c) {
+        constexpr int s4 = decltype(s4c)::value;
+        if constexpr (MODE == kMxfp4) {
+          static_for<2>([&](auto wic) {
+            constexpr int wi = decltype(wic)::value;
             const uint32_t wa = wbase ^ ((2 * s4 + wi) << 4);
             uint32_t lo[4], hi[4];
             e2m1_to_f16x2(lds32<0>(wa), lo);
             e2m1_to_f16x2(lds32<1024>(wa), hi);
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
-              const uint4 xq = wi ? (s4 == 0 ? lds128<64>(xa[mt]) : s4 == 1 ? lds128<128 + 64>(xa[mt]) : s4 == 2 ? lds128<256 + 64>(xa[mt]) : lds128<384 + 64>(xa[mt]))
-                                  : (s4 == 0 ? lds128<0>(xa[mt]) : s4 == 1 ? lds128<128>(xa[mt]) : s4 == 2 ? lds128<256>(xa[mt]) : lds128<384>(xa[mt]));
+              const uint4 xq = lds128<s4 * 128 + wi * 64>(xa[mt]);
               mma16816_first(d[mt], lo[0], hi[0], lo[1], hi[1], xq.x, xq.y);
               mma16816(d[mt], lo[2], hi[2], lo[3], hi[3], xq.z, xq.w);
             }
             // scale byte (s4 & 1) * 2 + wi of word s4 >> 1
+            constexpr int idx = (s4 & 1) * 2 + wi;
             const uint32_t wl = sl[s4 >> 1], wh = sh[s4 >> 1];
-            float fl, fh;
-            if ((s4 & 1) * 2 + wi == 0) { fl = e8m0_fast<0>(wl); fh = e8m0_fast<0>(wh); }
-            else if ((s4 & 1) * 2 + wi == 1) { fl = e8m0_fast<1>(wl); fh = e8m0_fast<1>(wh); }
-            else if ((s4 & 1) * 2 + wi == 2) { fl = e8m0_fast<2>(wl); fh = e8m0_fast<2>(wh); }
-            else { fl = e8m0_fast<3>(wl); fh = e8m0_fast<3>(wh); }
+            float fl = e8m0_fast<idx>(wl), fh = e8m0_fast<idx>(wh);
             if (special) {
-              fl = e8m0_exact((wl >> (8 * ((s4 & 1) * 2 + wi))) & 0xFFu);
-              fh = e8m0_exact((wh >> (8 * ((s4 & 1) * 2 + wi))) & 0xFFu);
+              fl = e8m0_exact((wl >> (8 * idx)) & 0xFFu);
+              fh = e8m0_exact((wh >> (8 * idx)) & 0xFFu);
             }
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
@@ -702,8 +721,8 @@ mx_ring_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
               ys[mt][2] = fmaf(fh, d[mt][2], ys[mt][2]);
               ys[mt][3] = fmaf(fh, d[mt][3], ys[mt][3]);
             }
-          }
-        } else if (MODE == kMxfp8) {
+          });
+        } else if constexpr (MODE == kMxfp8) {
           const uint32_t wa = wbase ^ (s4 << 5);
           const uint2 a = lds64<0>(wa), b = lds64<1024>(wa);
           uint32_t ae0, ao0, ae1, ao1, be0, bo0, be1, bo1;
@@ -715,15 +734,11 @@ mx_ring_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
           nan_hi |= __vcmpeq4(b.x & 0x7F7F7F7Fu, 0x7F7F7F7Fu) | __vcmpeq4(b.y & 0x7F7F7F7Fu, 0x7F7F7F7Fu);
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
-            const uint4 xq = s4 == 0 ? lds128<0>(xa[mt]) : s4 == 1 ? lds128<64>(xa[mt]) : s4 == 2 ? lds128<128>(xa[mt]) : lds128<192>(xa[mt]);
+            const uint4 xq = lds128<s4 * 64>(xa[mt]);
             mma16816_first(d[mt], ae0, be0, ao0, bo0, xq.x, xq.y);
             mma16816(d[mt], ae1, be1, ao1, bo1, xq.z, xq.w);
           }
-          float fl, fh;
-          if (s4 == 0) { fl = e8m0_fast<0>(sl[0]); fh = e8m0_fast<0>(sh[0]); }
-          else if (s4 == 1) { fl = e8m0_fast<1>(sl[0]); fh = e8m0_fast<1>(sh[0]); }
-          else if (s4 == 2) { fl = e8m0_fast<2>(sl[0]); fh = e8m0_fast<2>(sh[0]); }
-          else { fl = e8m0_fast<3>(sl[0]); fh = e8m0_fast<3>(sh[0]); }
+          float fl = e8m0_fast<s4>(sl[0]), fh = e8m0_fast<s4>(sh[0]);
           if (special) {
             fl = e8m0_exact((sl[0] >> (8 * s4)) & 0xFFu);
             fh = e8m0_exact((sh[0] >> (8 * s4)) & 0xFFu);
@@ -741,14 +756,14 @@ mx_ring_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
           const uint2 a = lds64<0>(wa), b = lds64<1024>(wa);
           uint32_t hl = __byte_perm(sl[s4], 0u, sel_t4), hh = __byte_perm(sh[s4], 0u, sel_t4);
           uint32_t fl = (hl & 0x80008000u) | ((hl >> 1) & 0x3F803F80u), fh = (hh & 0x80008000u) | ((hh >> 1) & 0x3F803F80u);
-          fl = hmul2_u32(fl, 0x70007000u);     // x 2^13: f16 1.0 x 2^13 = 0x7000; see the exponent budget above
+          fl = hmul2_u32(fl, 0x70007000u);     // x 2^13 (f16 0x7000); see the exponent budget above
           fh = hmul2_u32(fh, 0x70007000u);
           if (special) {
             if ((hl & 0x7F007F00u) == 0x7F007F00u) fl = 0x7E007E00u;
             if ((hh & 0x7F007F00u) == 0x7F007F00u) fh = 0x7E007E00u;
           }
-#pragma unroll
-          for (int wi = 0; wi < 2; ++wi) {
+          static_for<2>([&](auto wic) {
+            constexpr int wi = decltype(wic)::value;
             uint32_t lo[4], hi[4];
             e2m1_to_f16x2(wi ? a.y : a.x, lo);
             e2m1_to_f16x2(wi ? b.y : b.x, hi);
@@ -759,14 +774,13 @@ mx_ring_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
             }
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
-              const uint4 xq = wi ? (s4 == 0 ? lds128<16>(xa[mt]) : s4 == 1 ? lds128<128 + 16>(xa[mt]) : s4 == 2 ? lds128<256 + 16>(xa[mt]) : lds128<384 + 16>(xa[mt]))
-                                  : (s4 == 0 ? lds128<0>(xa[mt]) : s4 == 1 ? lds128<128>(xa[mt]) : s4 == 2 ? lds128<256>(xa[mt]) : lds128<384>(xa[mt]));
+              const uint4 xq = lds128<s4 * 128 + wi * 16>(xa[mt]);
               mma16816(d[mt], lo[0], hi[0], lo[1], hi[1], xq.x, xq.y);
               mma16816(d[mt], lo[2], hi[2], lo[3], hi[3], xq.z, xq.w);
             }
-          }
+          });
         }
-      }
+      });
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) xa[mt] += kStepsPerChunk * F::kXStep;
       __syncwarp();
