@@ -391,12 +391,13 @@ def run_gpu(args):
     exchange = [ex]
     tuned = None
     if world > 1 and args.exchange == "auto" and ex.mode == "fused":
-        # Two ways to fill the gathered buffers are available here (multimem stores in the GEMM's
-        # epilogue; copy-engine peer copies).  Which one is faster depends on N: time two steps of each
-        # before the measurement and keep the faster one, the same choice on every rank.
-        alt = tp.GatherExchange(shapes, device, depth=2, mode="copy")
+        # Three ways to fill the gathered buffers are available here: multimem stores in the GEMM's
+        # epilogue (fused), a small multicast copy kernel per finished block on a side stream (mcast),
+        # copy-engine peer copies (copy).  Which one is fastest depends on N: time two steps of each
+        # before the measurement and keep the fastest, the same choice on every rank.
         times = {}
-        for cand in (ex, alt):
+        for mode in ("fused", "mcast", "copy"):
+            cand = ex if mode == "fused" else tp.GatherExchange(shapes, device, depth=2, mode=mode, reserve_ctas=NCCL_CTAS)
             step(cand)
             barrier()
             c0 = torch.cuda.Event(enable_timing=True)
@@ -408,12 +409,15 @@ def run_gpu(args):
             barrier()
             t = torch.tensor([c0.elapsed_time(c1) / 2], dtype=torch.float64, device=device)
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            times[cand.mode] = float(t.item())
+            times[mode] = float(t.item())
+            if mode != "fused":
+                cand.close()
+                del cand
         tuned = {"ms_per_step": times, "chosen": min(times, key=times.get)}
-        if tuned["chosen"] == "copy":
-            ex, alt = alt, ex
+        if tuned["chosen"] != "fused":
+            ex.close()
+            ex = tp.GatherExchange(shapes, device, depth=2, mode=tuned["chosen"], reserve_ctas=NCCL_CTAS)
         exchange[0] = ex
-        del alt
         torch.cuda.empty_cache()
 
     # ---- resident-input timing -------------------------------------------------
@@ -559,6 +563,11 @@ def run_gpu(args):
                    "multimem.st to an NVSwitch multicast address, which places it in block r of every rank's "
                    "[P, M, N/P] buffer (no separate all-gather); per-launch completion signals, bounded wait "
                    "for all of them at the end of a step")
+        elif ex.mode == "mcast":
+            par = ("weights column-sharded along N; every finished [M, N/P] block is copied to the NVSwitch multicast "
+                   "address of the gathered [P, M, N/P] buffer by a 16-CTA kernel on a side stream (multimem.st, "
+                   "512-byte runs), overlapped with the next GEMMs, which leave those SMs free; per-launch completion "
+                   "signals, bounded wait for all of them at the end of a step")
         elif ex.mode == "copy":
             par = ("weights column-sharded along N; outputs gathered into [P, M, N/P] by copy-engine peer copies "
                    "of each finished [M, N/P] block into every peer's symmetric buffer, overlapped on side "
@@ -959,7 +968,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--layers", type=int, default=N_LAYERS, help="layers in the pass (the workload names 80)")
-    ap.add_argument("--exchange", default="auto", choices=["auto", "fused", "copy", "collective"],
+    ap.add_argument("--exchange", default="auto", choices=["auto", "fused", "mcast", "copy", "collective"],
                     help="how the outputs are gathered at N > 1 (auto: fused multimem stores when the symmetric "
                          "allocation has a multicast address, else peer copies, else the NCCL all-gather)")
     ap.add_argument("--shard-of", type=int, default=1, choices=[1, 2, 4, 8],

@@ -167,6 +167,21 @@ QMM_API int qmm_w8a16_perchannel_ex(const uint16_t* x_bf16, const int8_t* w, con
  * the wait. */
 QMM_API int qmm_wait_signals(const uint32_t* words, int count, uint32_t expected, uint64_t timeout_ns,
                              void* stream);
+/* The all-gather of a finished block as a kernel of its own: copies `bytes`
+ * (a multiple of 16; both pointers 16-byte aligned) from local memory to a
+ * multicast (NVSwitch multimem) address, 16 bytes per thread and fully
+ * coalesced, so that every GPU bound to the multicast object receives the
+ * block at that offset; then adds 1 to done_signal (a multicast address) with
+ * release semantics at system scope, as qmm_w8a16_perchannel_ex does.
+ * arrive_counter is a local uint32, zero before its first use and left zero.
+ * max_ctas bounds the grid (0 = 16): the copy is meant to run beside a GEMM
+ * that leaves those SMs free (qmm_set_cta_limit).  Replaces the same
+ * reference handler as QMM_GEMM_STORE_MULTIMEM
+ * (src/pjrt_plugin/ops/collective_ops.mm:88-229) where link efficiency
+ * matters more than the SMs the copy occupies: the GEMM epilogue's stores
+ * reach the switch as 64-byte runs, these as 512-byte runs. */
+QMM_API int qmm_multicast_copy(const void* src, void* dst_multicast, size_t bytes, uint32_t* done_signal,
+                               uint32_t* arrive_counter, int max_ctas, void* stream);
 
 /* ---------------------------------------------------------------------------
  * int8 x int8 -> int32 dot with optional fused f32 rescale.

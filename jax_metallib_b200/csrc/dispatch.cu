@@ -69,6 +69,32 @@ __global__ void wait_words_kernel(const uint32_t* words, int count, uint32_t exp
   if (status) atomicExch(status, (60 << 16) | QMM_ERR_TIMEOUT);
 }
 
+// Local block -> multicast address, 16 bytes per thread, four loads in flight per thread; the last CTA to finish
+// publishes the completion count on every rank (tag of the bounded wait that reads it: 60).
+__global__ void __launch_bounds__(512)
+multicast_copy_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst_mc, size_t n16, uint32_t* signal_mc,
+                      uint32_t* arrive) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  for (; i + 3 * stride < n16; i += 4 * stride) {
+    uint4 v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = src[i + j * stride];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) dev::multimem_st_v4_b32(dst_mc + i + j * stride, v[j]);
+  }
+  for (; i < n16; i += stride) dev::multimem_st_v4_b32(dst_mc + i, src[i]);
+  dev::fence_sys();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned prev = atomicInc(arrive, gridDim.x - 1);
+    if (prev == gridDim.x - 1) {
+      dev::fence_sys();
+      dev::multimem_red_release_add_u32(signal_mc, 1u);
+    }
+  }
+}
+
 }  // namespace simple
 
 // QMM_FORCE_SIMPLE=1 routes every shape to the CUDA-core kernels (a cross-check of the tensor-core
@@ -184,6 +210,26 @@ int qmm_wait_signals(const uint32_t* words, int count, uint32_t expected, uint64
   simple::wait_words_kernel<<<(count + 127) / 128, 128, 0, static_cast<cudaStream_t>(stream)>>>(
       words, count, expected, timeout_ns, device_status_word());
   QMM_CHECK_LAUNCH("wait_words_kernel");
+  return QMM_OK;
+}
+
+int qmm_multicast_copy(const void* src, void* dst_multicast, size_t bytes, uint32_t* done_signal, uint32_t* arrive_counter,
+                       int max_ctas, void* stream) {
+  using namespace qmm;
+  QMM_REQUIRE(src && dst_multicast && done_signal && arrive_counter, QMM_ERR_INVALID_ARGUMENT,
+              "qmm_multicast_copy: null pointer");
+  QMM_REQUIRE(bytes % 16 == 0 && aligned(src, 16) && aligned(dst_multicast, 16) && aligned(done_signal, 4) &&
+                  aligned(arrive_counter, 4),
+              QMM_ERR_INVALID_ARGUMENT, "qmm_multicast_copy: bytes and pointers must be multiples of 16");
+  QMM_REQUIRE(max_ctas >= 0 && max_ctas <= 1024, QMM_ERR_INVALID_ARGUMENT, "qmm_multicast_copy: bad max_ctas");
+  if (bytes == 0) return QMM_OK;
+  const size_t n16 = bytes / 16;
+  int ctas = max_ctas == 0 ? 16 : max_ctas;
+  const size_t need = (n16 + 511) / 512;
+  if (static_cast<size_t>(ctas) > need) ctas = static_cast<int>(need);
+  simple::multicast_copy_kernel<<<ctas, 512, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const uint4*>(src), static_cast<uint4*>(dst_multicast), n16, done_signal, arrive_counter);
+  QMM_CHECK_LAUNCH("multicast_copy_kernel");
   return QMM_OK;
 }
 

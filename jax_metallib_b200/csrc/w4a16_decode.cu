@@ -37,6 +37,8 @@
 // that the weights are static, their first loads are issued before that wait.
 #include <cstdlib>
 #include <mutex>
+#include <type_traits>
+#include <utility>
 
 #include "common.cuh"
 
@@ -95,9 +97,11 @@ __device__ __forceinline__ void ldmatrix_x4_trans(uint32_t addr, uint32_t (&r)[4
                : "r"(addr));
 }
 
+// not volatile: a pure function of its operands, so that the compiler may interleave the MMAs of a slab with the
+// conversion of the next one
 __device__ __forceinline__ void mma_f16_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                               uint32_t a3, uint32_t b0, uint32_t b1) {
-  asm volatile(
+  asm(
       "mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
       "{%8, %9}, {%0, %1, %2, %3};"
       : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
@@ -116,6 +120,16 @@ __device__ __forceinline__ void grid_launch_dependents() {
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
+
+// f(integral_constant<0>) ... f(integral_constant<N-1>): a loop whose index is a compile-time constant in the body
+template <typename Fn, int... Is>
+__device__ __forceinline__ void static_for_impl(Fn& f, std::integer_sequence<int, Is...>) {
+  (f(std::integral_constant<int, Is>{}), ...);
+}
+template <int N, typename Fn>
+__device__ __forceinline__ void static_for(Fn&& f) {
+  static_for_impl(f, std::make_integer_sequence<int, N>{});
+}
 
 // CTA that owns unit u when U units are dealt to P CTAs as [i*U/P, (i+1)*U/P).
 __device__ __forceinline__ int cta_of_unit(long long u, int P, int U) {
@@ -452,15 +466,17 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
       const uint32_t xb = st_addr + x_off;
 
       const int hl = half_lo(it), hh = half_hi(it);
-#pragma unroll
-      for (int h = 0; h < 2; ++h) {
-        if (h < hl || h >= hh) continue;  // the other half of a boundary unit belongs to a neighbour CTA
+      // both loops run over compile-time indices, so that the slab's XOR into the activation address and the
+      // choice of ldmatrix register are constants of each copy of the body
+      static_for<2>([&](auto hc) {
+        constexpr int h = decltype(hc)::value;
+        if (h < hl || h >= hh) return;  // the other half of a boundary unit belongs to a neighbour CTA
         uint32_t wa[4], wb[4];
         ldmatrix_x4_trans(st_addr + ld_off0 + h * 4096, wa);
         ldmatrix_x4_trans(st_addr + ld_off1 + h * 4096, wb);
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          const int slab = 4 * h + q;
+        static_for<4>([&](auto qc) {
+          constexpr int q = decltype(qc)::value;
+          constexpr int slab = 4 * h + q;
           uint32_t xf[MT][2];
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt)
@@ -476,8 +492,8 @@ w4a16_decode_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_const
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt)
             mma_f16_16816(acc[1][mt], r[0], r[2], r[1], r[3], xf[mt][0], xf[mt][1]);
-        }
-      }
+        });
+      });
       // group epilogue: per pair this thread holds columns (c, c+1) for rows
       // (2t, 2t+1) of each 8-row tile
       const float* fac = reinterpret_cast<const float*>(st + L::kOffF);

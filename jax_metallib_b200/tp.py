@@ -171,35 +171,40 @@ class GatherExchange:
         self._peer_views = {}
         self._set_cta_limit = False
         self.why_not_fused = ""
-        if mode not in ("auto", "fused", "copy", "collective", "local"):
+        if mode not in ("auto", "fused", "mcast", "copy", "collective", "local"):
             raise ValueError(f"unknown exchange mode {mode!r}")
         if self.world == 1:
             mode = "local"
         elif self.device.type != "cuda":
-            if mode in ("fused", "copy"):
+            if mode in ("fused", "mcast", "copy"):
                 raise ValueError("symmetric-memory exchange modes need CUDA devices")
             mode = "collective"
         self._buf = None
-        if mode in ("auto", "fused", "copy"):
+        if mode in ("auto", "fused", "mcast", "copy"):
             mode = self._setup_symmetric(mode)
         if self._buf is None:
             self._buf = torch.zeros(self._total, dtype=torch.uint8, device=self.device)
         self.mode = mode
-        if mode in ("copy", "collective"):
+        if mode in ("copy", "collective", "mcast"):
             self._comm = torch.cuda.Stream(device=self.device) if self.device.type == "cuda" else None
         if mode == "copy":
             self._peer_streams = {p: torch.cuda.Stream(device=self.device) for p in range(self.world) if p != self.rank}
             self._sync_word = torch.zeros(1, dtype=torch.int32, device=self.device)
-        if mode == "collective" and self.device.type == "cuda":
+        self._copy_ctas = 0
+        if mode == "mcast":
+            reserve_ctas = min(reserve_ctas, 16)
+            self._copy_ctas = reserve_ctas
+        if mode in ("collective", "mcast") and self.device.type == "cuda":
             # the persistent GEMM keeps one CTA per SM resident; leave the all-gather kernel its own SMs
             from . import _lib
 
             sms = torch.cuda.get_device_properties(self.device).multi_processor_count
             _lib.check(_lib.load().qmm_set_cta_limit(max(1, sms - reserve_ctas)))
             self._set_cta_limit = True
+        if mode == "collective" and self.device.type == "cuda":
             self._shards = {n: torch.empty((m, nn // self.world), dtype=dtype, device=self.device)
                             for n, (m, nn) in self.shapes.items()}
-        if mode == "fused":
+        if mode in ("fused", "mcast"):
             self._arrive = torch.zeros(len(self._counts), dtype=torch.int32, device=self.device)
         self._signals = self._buf[self._sig_off:self._sig_off + 4 * depth * len(self.names) * self.world].view(torch.int32)
 
@@ -222,7 +227,7 @@ class GatherExchange:
         dist.all_reduce(flags, op=dist.ReduceOp.MIN, group=self.group)
         ok, mc = int(flags[0].item()), int(flags[1].item())
         if not ok:
-            if mode in ("fused", "copy"):
+            if mode in ("fused", "mcast", "copy"):
                 raise RuntimeError(f"exchange mode {mode!r} needs symmetric memory ({self.why_not_fused})")
             return "collective"
         buf.zero_()
@@ -233,11 +238,11 @@ class GatherExchange:
             return "copy"
         if not mc:
             self.why_not_fused = self.why_not_fused or "no NVSwitch multicast address for the symmetric allocation"
-            if mode == "fused":
-                raise RuntimeError(f"exchange mode 'fused' unavailable: {self.why_not_fused}")
+            if mode in ("fused", "mcast"):
+                raise RuntimeError(f"exchange mode {mode!r} unavailable: {self.why_not_fused}")
             return "copy"
         self._mc_ptr = mc_ptr
-        return "fused"
+        return "mcast" if mode == "mcast" else "fused"
 
     def close(self) -> None:
         """Give back what the exchange changed process-wide (the CTA limit of ``collective`` mode)."""
@@ -311,6 +316,28 @@ class GatherExchange:
             _lib.check(lib.qmm_w8a16_perchannel_ex(x.data_ptr(), w_shard.data_ptr(), scale_shard.data_ptr(),
                                                    mine.data_ptr(), m, ns, k, ns, ctypes.byref(ext), stream.cuda_stream))
             return out
+        if self.mode == "mcast":
+            # the GEMM stores its block locally; a small kernel on the side stream then copies it to the
+            # multicast address in 512-byte runs and publishes the completion count on every rank
+            prev = self._pending.pop((slot, name), None)
+            if prev is not None:
+                stream.wait_event(prev)   # the previous copy out of this block has read it
+            ext = _lib.GemmExt(flags)
+            _lib.check(lib.qmm_w8a16_perchannel_ex(x.data_ptr(), w_shard.data_ptr(), scale_shard.data_ptr(),
+                                                   mine.data_ptr(), m, ns, k, ns, ctypes.byref(ext), stream.cuda_stream))
+            ready = torch.cuda.Event()
+            ready.record(stream)
+            self._comm.wait_event(ready)
+            idx = (slot * len(self.names) + self.names.index(name))
+            _lib.check(lib.qmm_multicast_copy(mine.data_ptr(), self._mc_ptr + b.offset + self.rank * b.block_bytes,
+                                              b.block_bytes,
+                                              self._mc_ptr + self._sig_off + 4 * (idx * self.world + self.rank),
+                                              self._arrive.data_ptr() + 4 * idx, self._copy_ctas,
+                                              self._comm.cuda_stream))
+            done = torch.cuda.Event()
+            done.record(self._comm)
+            self._pending[(slot, name)] = done
+            return out
         # copy / collective: the exchange of this slot's previous use must have finished
         prev = self._pending.pop((slot, name), None)
         if prev is not None:
@@ -349,10 +376,12 @@ class GatherExchange:
         if self.mode == "local" or self.device.type != "cuda":
             return
         stream = torch.cuda.current_stream(self.device)
-        if self.mode == "fused":
+        if self.mode in ("fused", "mcast"):
             from . import _lib
 
             lib = _lib.load()
+            if self.mode == "mcast":
+                stream.wait_stream(self._comm)
             for (slot, name), count in self._counts.items():
                 if count:
                     words = self.signal_words(name, slot)
