@@ -39,6 +39,9 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
+# SMs left to the multicast copy kernel of --exchange mcast: a rank's own egress is 1/P of the gathered
+# bytes (6.9 GB per step at P = 8), so a few CTAs keep up; the links are loaded by what arrives.
+MCAST_CTAS = 8
 # SMs left to the all-gather kernel when the exchange is an NCCL collective (--exchange collective).
 # Measured at N = 2 (40 layers): NCCL's own choice with no SMs reserved 1786 TFLOP/s (its CTAs queue
 # behind the resident GEMM CTAs and delay the next launch), 8 reserved 1660 (the gather becomes the
@@ -368,7 +371,10 @@ def run_gpu(args):
     # gathered outputs [P, M, N/P] per linear kind, two slots each (layer parity): the exchange of a
     # layer may run under the whole of the next layer
     shapes = {name: (M_TOKENS, n // (shard_world if world == 1 else 1)) for name, k, n, act in layer_shapes()}
-    ex = tp.GatherExchange(shapes, device, depth=2, mode=args.exchange, reserve_ctas=NCCL_CTAS)
+    def reserve(mode):
+        return args.copy_ctas if mode in ("mcast", "peer") else NCCL_CTAS
+
+    ex = tp.GatherExchange(shapes, device, depth=2, mode=args.exchange, reserve_ctas=reserve(args.exchange))
     result_host = torch.empty((world, M_TOKENS, shapes["down"][1] // world), dtype=torch.bfloat16).pin_memory()
     launches = [0]
 
@@ -396,8 +402,8 @@ def run_gpu(args):
         # copy-engine peer copies (copy).  Which one is fastest depends on N: time two steps of each
         # before the measurement and keep the fastest, the same choice on every rank.
         times = {}
-        for mode in ("fused", "mcast", "copy"):
-            cand = ex if mode == "fused" else tp.GatherExchange(shapes, device, depth=2, mode=mode, reserve_ctas=NCCL_CTAS)
+        for mode in ("fused", "mcast", "peer", "copy"):
+            cand = ex if mode == "fused" else tp.GatherExchange(shapes, device, depth=2, mode=mode, reserve_ctas=reserve(mode))
             step(cand)
             barrier()
             c0 = torch.cuda.Event(enable_timing=True)
@@ -416,7 +422,7 @@ def run_gpu(args):
         tuned = {"ms_per_step": times, "chosen": min(times, key=times.get)}
         if tuned["chosen"] != "fused":
             ex.close()
-            ex = tp.GatherExchange(shapes, device, depth=2, mode=tuned["chosen"], reserve_ctas=NCCL_CTAS)
+            ex = tp.GatherExchange(shapes, device, depth=2, mode=tuned["chosen"], reserve_ctas=reserve(tuned["chosen"]))
         exchange[0] = ex
         torch.cuda.empty_cache()
 
@@ -565,9 +571,14 @@ def run_gpu(args):
                    "for all of them at the end of a step")
         elif ex.mode == "mcast":
             par = ("weights column-sharded along N; every finished [M, N/P] block is copied to the NVSwitch multicast "
-                   "address of the gathered [P, M, N/P] buffer by a 16-CTA kernel on a side stream (multimem.st, "
+                   "address of the gathered [P, M, N/P] buffer by a small kernel (--copy-ctas CTAs) on a side stream (multimem.st, "
                    "512-byte runs), overlapped with the next GEMMs, which leave those SMs free; per-launch completion "
                    "signals, bounded wait for all of them at the end of a step")
+        elif ex.mode == "peer":
+            par = ("weights column-sharded along N; every finished [M, N/P] block is stored into every peer's gathered "
+                   "[P, M, N/P] buffer over NVLink by a small kernel (--copy-ctas CTAs) on a side stream, overlapped "
+                   "with the next GEMMs, which leave those SMs free; per-launch completion signals, bounded wait for "
+                   "all of them at the end of a step")
         elif ex.mode == "copy":
             par = ("weights column-sharded along N; outputs gathered into [P, M, N/P] by copy-engine peer copies "
                    "of each finished [M, N/P] block into every peer's symmetric buffer, overlapped on side "
@@ -968,7 +979,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--layers", type=int, default=N_LAYERS, help="layers in the pass (the workload names 80)")
-    ap.add_argument("--exchange", default="auto", choices=["auto", "fused", "mcast", "copy", "collective"],
+    ap.add_argument("--copy-ctas", type=int, default=MCAST_CTAS,
+                    help="SMs left to the multicast copy kernel of --exchange mcast (the GEMM keeps the rest)")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "fused", "mcast", "peer", "copy", "collective"],
                     help="how the outputs are gathered at N > 1 (auto: fused multimem stores when the symmetric "
                          "allocation has a multicast address, else peer copies, else the NCCL all-gather)")
     ap.add_argument("--shard-of", type=int, default=1, choices=[1, 2, 4, 8],

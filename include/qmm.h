@@ -182,6 +182,19 @@ QMM_API int qmm_wait_signals(const uint32_t* words, int count, uint32_t expected
  * reach the switch as 64-byte runs, these as 512-byte runs. */
 QMM_API int qmm_multicast_copy(const void* src, void* dst_multicast, size_t bytes, uint32_t* done_signal,
                                uint32_t* arrive_counter, int max_ctas, void* stream);
+/* The same all-gather step with plain peer stores instead of a multicast
+ * address: every 16 bytes read from src are stored to dst_peers[0..n_peers-1]
+ * (the block's address in each peer GPU's buffer; peer-mapped pointers, at most
+ * QMM_MAX_PEERS), then signal_peers[i] (the word of this rank in peer i's
+ * buffer) and local_signal are each incremented by 1 with release semantics at
+ * system scope.  A multicast store also delivers the block to the sender's own
+ * buffer, 1/P of the arriving bytes; when the links are the bound (P = 8 on
+ * NVLink 5: 55 GB of gathered outputs per step of the headline workload
+ * against 66 ms of GEMM) leaving that out is worth more than the P-1 stores
+ * per load cost.  max_ctas bounds the grid (0 = 16). */
+#define QMM_MAX_PEERS 15
+QMM_API int qmm_peer_copy(const void* src, void* const* dst_peers, uint32_t* const* signal_peers, int n_peers,
+                          size_t bytes, uint32_t* local_signal, uint32_t* arrive_counter, int max_ctas, void* stream);
 
 /* ---------------------------------------------------------------------------
  * int8 x int8 -> int32 dot with optional fused f32 rescale.

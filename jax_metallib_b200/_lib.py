@@ -34,6 +34,7 @@ SIGNATURES = {
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int64, c_void_p, c_void_p]),
     "qmm_wait_signals": (c_int, [c_void_p, c_int, ctypes.c_uint32, ctypes.c_uint64, c_void_p]),
     "qmm_multicast_copy": (c_int, [c_void_p, c_void_p, ctypes.c_size_t, c_void_p, c_void_p, c_int, c_void_p]),
+    "qmm_peer_copy": (c_int, [c_void_p, c_void_p, c_void_p, c_int, ctypes.c_size_t, c_void_p, c_void_p, c_int, c_void_p]),
     "qmm_i8i8_i32": (
         c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int64, c_int64, c_int64, c_int, c_int,
                 c_void_p]),

@@ -95,6 +95,41 @@ multicast_copy_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst_mc,
   }
 }
 
+struct PeerList {
+  uint4* dst[QMM_MAX_PEERS];
+  uint32_t* signal[QMM_MAX_PEERS];
+  int n;
+};
+// Local block -> the same block of every peer's buffer by plain stores over NVLink (no copy to this GPU).
+__global__ void __launch_bounds__(512)
+peer_copy_kernel(const uint4* __restrict__ src, PeerList peers, size_t n16, uint32_t* local_signal, uint32_t* arrive) {
+  const size_t stride = static_cast<size_t>(gridDim.x) * blockDim.x;
+  size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+  for (; i + 3 * stride < n16; i += 4 * stride) {
+    uint4 v[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) v[j] = src[i + j * stride];
+    for (int p = 0; p < peers.n; ++p) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) __stcg(peers.dst[p] + i + j * stride, v[j]);
+    }
+  }
+  for (; i < n16; i += stride) {
+    const uint4 v = src[i];
+    for (int p = 0; p < peers.n; ++p) __stcg(peers.dst[p] + i, v);
+  }
+  dev::fence_sys();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned prev = atomicInc(arrive, gridDim.x - 1);
+    if (prev == gridDim.x - 1) {
+      dev::fence_sys();
+      for (int p = 0; p < peers.n; ++p) dev::red_release_sys_add_u32(peers.signal[p], 1u);
+      dev::red_release_sys_add_u32(local_signal, 1u);
+    }
+  }
+}
+
 }  // namespace simple
 
 // QMM_FORCE_SIMPLE=1 routes every shape to the CUDA-core kernels (a cross-check of the tensor-core
@@ -230,6 +265,35 @@ int qmm_multicast_copy(const void* src, void* dst_multicast, size_t bytes, uint3
   simple::multicast_copy_kernel<<<ctas, 512, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const uint4*>(src), static_cast<uint4*>(dst_multicast), n16, done_signal, arrive_counter);
   QMM_CHECK_LAUNCH("multicast_copy_kernel");
+  return QMM_OK;
+}
+
+int qmm_peer_copy(const void* src, void* const* dst_peers, uint32_t* const* signal_peers, int n_peers, size_t bytes,
+                  uint32_t* local_signal, uint32_t* arrive_counter, int max_ctas, void* stream) {
+  using namespace qmm;
+  QMM_REQUIRE(src && dst_peers && signal_peers && local_signal && arrive_counter, QMM_ERR_INVALID_ARGUMENT,
+              "qmm_peer_copy: null pointer");
+  QMM_REQUIRE(n_peers >= 1 && n_peers <= QMM_MAX_PEERS, QMM_ERR_INVALID_ARGUMENT, "qmm_peer_copy: 1 to %d peers",
+              QMM_MAX_PEERS);
+  QMM_REQUIRE(bytes % 16 == 0 && aligned(src, 16) && aligned(local_signal, 4) && aligned(arrive_counter, 4),
+              QMM_ERR_INVALID_ARGUMENT, "qmm_peer_copy: bytes and pointers must be multiples of 16");
+  QMM_REQUIRE(max_ctas >= 0 && max_ctas <= 1024, QMM_ERR_INVALID_ARGUMENT, "qmm_peer_copy: bad max_ctas");
+  simple::PeerList peers;
+  peers.n = n_peers;
+  for (int p = 0; p < n_peers; ++p) {
+    QMM_REQUIRE(dst_peers[p] && signal_peers[p] && aligned(dst_peers[p], 16) && aligned(signal_peers[p], 4),
+                QMM_ERR_INVALID_ARGUMENT, "qmm_peer_copy: peer %d: null or misaligned pointer", p);
+    peers.dst[p] = static_cast<uint4*>(dst_peers[p]);
+    peers.signal[p] = signal_peers[p];
+  }
+  if (bytes == 0) return QMM_OK;
+  const size_t n16 = bytes / 16;
+  int ctas = max_ctas == 0 ? 16 : max_ctas;
+  const size_t need = (n16 + 511) / 512;
+  if (static_cast<size_t>(ctas) > need) ctas = static_cast<int>(need);
+  simple::peer_copy_kernel<<<ctas, 512, 0, static_cast<cudaStream_t>(stream)>>>(static_cast<const uint4*>(src), peers, n16,
+                                                                              local_signal, arrive_counter);
+  QMM_CHECK_LAUNCH("peer_copy_kernel");
   return QMM_OK;
 }
 

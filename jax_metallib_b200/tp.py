@@ -171,30 +171,30 @@ class GatherExchange:
         self._peer_views = {}
         self._set_cta_limit = False
         self.why_not_fused = ""
-        if mode not in ("auto", "fused", "mcast", "copy", "collective", "local"):
+        if mode not in ("auto", "fused", "mcast", "peer", "copy", "collective", "local"):
             raise ValueError(f"unknown exchange mode {mode!r}")
         if self.world == 1:
             mode = "local"
         elif self.device.type != "cuda":
-            if mode in ("fused", "mcast", "copy"):
+            if mode in ("fused", "mcast", "peer", "copy"):
                 raise ValueError("symmetric-memory exchange modes need CUDA devices")
             mode = "collective"
         self._buf = None
-        if mode in ("auto", "fused", "mcast", "copy"):
+        if mode in ("auto", "fused", "mcast", "peer", "copy"):
             mode = self._setup_symmetric(mode)
         if self._buf is None:
             self._buf = torch.zeros(self._total, dtype=torch.uint8, device=self.device)
         self.mode = mode
-        if mode in ("copy", "collective", "mcast"):
+        if mode in ("copy", "collective", "mcast", "peer"):
             self._comm = torch.cuda.Stream(device=self.device) if self.device.type == "cuda" else None
         if mode == "copy":
             self._peer_streams = {p: torch.cuda.Stream(device=self.device) for p in range(self.world) if p != self.rank}
             self._sync_word = torch.zeros(1, dtype=torch.int32, device=self.device)
         self._copy_ctas = 0
-        if mode == "mcast":
-            reserve_ctas = min(reserve_ctas, 16)
+        if mode in ("mcast", "peer"):
+            reserve_ctas = max(1, min(reserve_ctas, 32))
             self._copy_ctas = reserve_ctas
-        if mode in ("collective", "mcast") and self.device.type == "cuda":
+        if mode in ("collective", "mcast", "peer") and self.device.type == "cuda":
             # the persistent GEMM keeps one CTA per SM resident; leave the all-gather kernel its own SMs
             from . import _lib
 
@@ -204,8 +204,9 @@ class GatherExchange:
         if mode == "collective" and self.device.type == "cuda":
             self._shards = {n: torch.empty((m, nn // self.world), dtype=dtype, device=self.device)
                             for n, (m, nn) in self.shapes.items()}
-        if mode in ("fused", "mcast"):
+        if mode in ("fused", "mcast", "peer"):
             self._arrive = torch.zeros(len(self._counts), dtype=torch.int32, device=self.device)
+        self._peer_args = {}
         self._signals = self._buf[self._sig_off:self._sig_off + 4 * depth * len(self.names) * self.world].view(torch.int32)
 
     # -- set-up ---------------------------------------------------------------
@@ -227,15 +228,15 @@ class GatherExchange:
         dist.all_reduce(flags, op=dist.ReduceOp.MIN, group=self.group)
         ok, mc = int(flags[0].item()), int(flags[1].item())
         if not ok:
-            if mode in ("fused", "mcast", "copy"):
+            if mode in ("fused", "mcast", "peer", "copy"):
                 raise RuntimeError(f"exchange mode {mode!r} needs symmetric memory ({self.why_not_fused})")
             return "collective"
         buf.zero_()
         self._buf, self._hdl = buf, hdl
         torch.cuda.synchronize(self.device)
         dist.barrier(group=self.group)  # every rank's signal words are zero before anyone signals
-        if mode == "copy":
-            return "copy"
+        if mode in ("copy", "peer"):
+            return mode
         if not mc:
             self.why_not_fused = self.why_not_fused or "no NVSwitch multicast address for the symmetric allocation"
             if mode in ("fused", "mcast"):
@@ -316,6 +317,37 @@ class GatherExchange:
             _lib.check(lib.qmm_w8a16_perchannel_ex(x.data_ptr(), w_shard.data_ptr(), scale_shard.data_ptr(),
                                                    mine.data_ptr(), m, ns, k, ns, ctypes.byref(ext), stream.cuda_stream))
             return out
+        if self.mode == "peer":
+            # the GEMM stores its block locally; a small kernel on the side stream then stores it into every
+            # peer's buffer over NVLink and bumps this rank's word in every buffer
+            prev = self._pending.pop((slot, name), None)
+            if prev is not None:
+                stream.wait_event(prev)
+            ext = _lib.GemmExt(flags)
+            _lib.check(lib.qmm_w8a16_perchannel_ex(x.data_ptr(), w_shard.data_ptr(), scale_shard.data_ptr(),
+                                                   mine.data_ptr(), m, ns, k, ns, ctypes.byref(ext), stream.cuda_stream))
+            ready = torch.cuda.Event()
+            ready.record(stream)
+            self._comm.wait_event(ready)
+            idx = (slot * len(self.names) + self.names.index(name))
+            args = self._peer_args.get((slot, name))
+            if args is None:
+                peers = [p for p in range(self.world) if p != self.rank]
+                dst = (ctypes.c_void_p * len(peers))()
+                sig = (ctypes.c_void_p * len(peers))()
+                for i, p in enumerate(peers):
+                    base = self._hdl.get_buffer(p, (self._total,), torch.uint8, 0).data_ptr()
+                    dst[i] = base + b.offset + self.rank * b.block_bytes
+                    sig[i] = base + self._sig_off + 4 * (idx * self.world + self.rank)
+                args = (dst, sig, len(peers))
+                self._peer_args[(slot, name)] = args
+            _lib.check(lib.qmm_peer_copy(mine.data_ptr(), args[0], args[1], args[2], b.block_bytes,
+                                         self._signals.data_ptr() + 4 * (idx * self.world + self.rank),
+                                         self._arrive.data_ptr() + 4 * idx, self._copy_ctas, self._comm.cuda_stream))
+            done = torch.cuda.Event()
+            done.record(self._comm)
+            self._pending[(slot, name)] = done
+            return out
         if self.mode == "mcast":
             # the GEMM stores its block locally; a small kernel on the side stream then copies it to the
             # multicast address in 512-byte runs and publishes the completion count on every rank
@@ -376,11 +408,11 @@ class GatherExchange:
         if self.mode == "local" or self.device.type != "cuda":
             return
         stream = torch.cuda.current_stream(self.device)
-        if self.mode in ("fused", "mcast"):
+        if self.mode in ("fused", "mcast", "peer"):
             from . import _lib
 
             lib = _lib.load()
-            if self.mode == "mcast":
+            if self.mode != "fused":
                 stream.wait_stream(self._comm)
             for (slot, name), count in self._counts.items():
                 if count:

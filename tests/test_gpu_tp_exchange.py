@@ -38,7 +38,7 @@ def _worker(rank, world, port, result_dir):
         x_h = synthetic.bf16_bits_to_f32(synthetic.to_bf16_bits(rng.standard_normal((M, K)).astype(np.float32)))
         x = torch.from_numpy(x_h).to(device).to(torch.bfloat16)
         modes_seen = []
-        for mode in ("auto", "mcast", "copy", "collective"):
+        for mode in ("auto", "mcast", "peer", "copy", "collective"):
             try:
                 ex = tp.GatherExchange(shapes, device, depth=2, mode=mode)
             except RuntimeError:
@@ -64,7 +64,7 @@ def _worker(rank, world, port, result_dir):
                     err = O.max_rel_err(got, ref)
                     assert err <= 1e-2, (mode, ex.mode, name, use, err)
                     dist.barrier()  # nobody overwrites a slot a peer is still reading
-            if ex.mode in ("fused", "mcast"):
+            if ex.mode in ("fused", "mcast", "peer"):
                 assert int(ex.signal_words("a", 0)[0]) == 2 and int(ex.signal_words("a", 1)[1]) == 1
             ex.close()
             del ex
