@@ -14,7 +14,7 @@ columns, which is also what ``ncclAllGather`` builds); :func:`gathered_to_logica
 turns it into the logical ``[M, N]`` result.
 
 :class:`GatherExchange` owns the gathered buffers of a set of linears and fills
-them in one of three ways:
+them in one of five ways:
 
 ``fused``       the buffers live in symmetric memory bound to an NVSwitch multicast
                 object and the GEMM's epilogue stores with ``multimem.st``: one store
@@ -23,6 +23,14 @@ them in one of three ways:
                 GEMM launches.  Each launch ends by incrementing a per-(slot, linear,
                 rank) signal word on every rank (release, system scope), which a
                 consumer waits for with a bounded wait.
+``mcast``       the GEMM writes its block locally; a small kernel on a side stream
+                (``qmm_multicast_copy``, a few CTAs that the GEMM leaves free) copies the
+                finished block to the multicast address in 512-byte runs and publishes
+                the same signal word.  The GEMM epilogue's stores reach the switch as
+                64-byte runs; where the links are the bound this uses them better.
+``peer``        the same with plain peer stores (``qmm_peer_copy``): P-1 stores per load,
+                but nothing is sent to the sender's own buffer, 1/P of what a multicast
+                store delivers.
 ``copy``        symmetric memory without multicast: the GEMM writes its block locally
                 and copy-engine peer copies on side streams put it into every peer's
                 buffer.
