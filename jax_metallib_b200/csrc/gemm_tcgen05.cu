@@ -53,6 +53,12 @@ constexpr int kEpiWarpsI = 8;
 // Warp roles: 0 TMA, 1 MMA issue for row block 0, 2-9 epilogue, 10 MMA issue for row block 1.
 constexpr int kSecondMmaWarp = 2 + kEpiWarpsI;
 constexpr int kThreads = (kSecondMmaWarp + 1) * 32;
+// One 32 x 32 chunk of 4-byte results per epilogue warp, 128-byte swizzled, for the TMA stores of a CTA's last
+// item.  It lies in the first stage of the operand ring, which is idle by then; shared memory of its own would
+// take the CTA past 196 KB, into the SM's largest shared-memory split, for 32 KB that the ring already has.
+constexpr int kOutStage = 32 * 128;
+constexpr int kOutBase = 0;
+static_assert(kEpiWarpsI * kOutStage <= kStageBytes, "the result chunks must fit in one stage of the ring");
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*barriers*/ + 1024 /*alignment*/;
 static_assert(BK == 128, "the issue loop is written out for four 32-byte k-steps");
 
@@ -80,9 +86,10 @@ __device__ __forceinline__ bool get_work(int i, int tiles_m2, int tiles_n, int h
 
 __global__ void __launch_bounds__(kThreads, 1)
 i8gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap bmap,
+              const __grid_constant__ CUtensorMap accmap, const __grid_constant__ CUtensorMap outmap,
               int32_t* __restrict__ acc_out, float* __restrict__ f_out,
               const float* __restrict__ row_scale, const float* __restrict__ col_scale, int M, int N,
-              int K, uint32_t idesc, int halves, int* status) {
+              int K, uint32_t idesc, int halves, int staged_store, int* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~static_cast<uintptr_t>(1023));
@@ -181,44 +188,97 @@ i8gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ 
     // ------------------------------ epilogue -------------------------------
     const int q = warp & 3;         // TMEM lane quarter this warp may access
     const int j = (warp - 2) >> 2;  // accumulator (row block) of this warp
+    const uint64_t store_policy = dev::policy_evict_first();
     int items = 0;
     Work w;
     for (int i = 0; get_work(i, tiles_m2, tiles_n, halves, M, w); ++i) {
       if (w.nh == 0) continue;
       if (!dev::mbar_wait_relaxed_warp(tfull, items & 1, status, 14)) break;
       dev::tc_fence_after();
-      const int row = (w.tm2 * 2 + j) * BMB + q * 32 + lane;
+      // A lane holds one row of a 32 x 32 chunk.  Stored straight from registers, a warp's 16-byte stores
+      // would touch 32 different 128-byte lines per instruction; instead the chunk goes to shared memory
+      // (row r at r * 128, 16-byte piece p at p ^ (r & 7): conflict-free) and one TMA store writes it out,
+      // clipped to the tensor's bounds.
+      // results of the CTA's last item leave through shared memory and TMA stores (the ring is idle: every load
+      // has been consumed once the accumulators are complete); earlier items overlap their plain stores with the
+      // loads of the next item, which the producer has already started into the ring
+      Work w_next;
+      const bool staged = staged_store && !get_work(i + 1, tiles_m2, tiles_n, halves, M, w_next);
+      const int row0 = (w.tm2 * 2 + j) * BMB + q * 32;
+      const int row = row0 + lane;
       const bool mine = (j >= w.h0) && (j < w.h0 + w.nh) && row < M;
       const float rs = (f_out && mine) ? __ldg(row_scale + row) : 0.f;
-      if (j >= w.h0 && j < w.h0 + w.nh) {
+      uint8_t* stage = smem + kOutBase + (warp - 2) * kOutStage;
+      uint8_t* my_row = stage + lane * 128;
+      if (j >= w.h0 && j < w.h0 + w.nh && row0 < M) {
 #pragma unroll 1
         for (int ch = 0; ch < BN / 32; ++ch) {
+          const int col0 = w.tn * BN + ch * 32;
+          if (col0 >= N) break;
           uint32_t r[32];
           dev::tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(q * 32) << 16) + j * BN + ch * 32, r);
           dev::tc_wait_ld();
-          const int col0 = w.tn * BN + ch * 32;
-          if (mine) {
-            if (acc_out) {
-              int32_t* dst = acc_out + static_cast<size_t>(row) * N + col0;
+          if (!staged) {
+            // straight from registers: 16-byte stores of 32 different rows per instruction
+            if (mine) {
+              if (acc_out) {
+                int32_t* dst = acc_out + static_cast<size_t>(row) * N + col0;
 #pragma unroll
-              for (int i4 = 0; i4 < 8; ++i4)
-                if (col0 + 4 * i4 < N)
-                  *reinterpret_cast<uint4*>(dst + 4 * i4) =
-                      make_uint4(r[4 * i4], r[4 * i4 + 1], r[4 * i4 + 2], r[4 * i4 + 3]);
+                for (int i4 = 0; i4 < 8; ++i4)
+                  if (col0 + 4 * i4 < N)
+                    *reinterpret_cast<uint4*>(dst + 4 * i4) = make_uint4(r[4 * i4], r[4 * i4 + 1], r[4 * i4 + 2], r[4 * i4 + 3]);
+              }
+              if (f_out) {
+                float* dst = f_out + static_cast<size_t>(row) * N + col0;
+#pragma unroll
+                for (int i4 = 0; i4 < 8; ++i4)
+                  if (col0 + 4 * i4 < N) {
+                    const float4 cs = __ldg(reinterpret_cast<const float4*>(col_scale + col0 + 4 * i4));
+                    float4 o;
+                    o.x = static_cast<float>(static_cast<int32_t>(r[4 * i4])) * rs * cs.x;
+                    o.y = static_cast<float>(static_cast<int32_t>(r[4 * i4 + 1])) * rs * cs.y;
+                    o.z = static_cast<float>(static_cast<int32_t>(r[4 * i4 + 2])) * rs * cs.z;
+                    o.w = static_cast<float>(static_cast<int32_t>(r[4 * i4 + 3])) * rs * cs.w;
+                    *reinterpret_cast<float4*>(dst + 4 * i4) = o;
+                  }
+              }
             }
-            if (f_out) {
-              float* dst = f_out + static_cast<size_t>(row) * N + col0;
+            continue;
+          }
+          if (acc_out) {
+            if (lane == 0) dev::tma_store_wait_read();   // the previous store has read the buffer
+            __syncwarp();
 #pragma unroll
-              for (int i4 = 0; i4 < 8; ++i4)
-                if (col0 + 4 * i4 < N) {
-                  const float4 cs = __ldg(reinterpret_cast<const float4*>(col_scale + col0 + 4 * i4));
-                  float4 o;
-                  o.x = static_cast<float>(static_cast<int32_t>(r[4 * i4])) * rs * cs.x;
-                  o.y = static_cast<float>(static_cast<int32_t>(r[4 * i4 + 1])) * rs * cs.y;
-                  o.z = static_cast<float>(static_cast<int32_t>(r[4 * i4 + 2])) * rs * cs.z;
-                  o.w = static_cast<float>(static_cast<int32_t>(r[4 * i4 + 3])) * rs * cs.w;
-                  *reinterpret_cast<float4*>(dst + 4 * i4) = o;
-                }
+            for (int i4 = 0; i4 < 8; ++i4)
+              *reinterpret_cast<uint4*>(my_row + ((i4 ^ (lane & 7)) << 4)) =
+                  make_uint4(r[4 * i4], r[4 * i4 + 1], r[4 * i4 + 2], r[4 * i4 + 3]);
+            dev::fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+              dev::tma_store_2d_hint(&accmap, stage, col0, row0, store_policy);
+              dev::tma_store_commit();
+            }
+          }
+          if (f_out) {
+            float4 o[8];
+#pragma unroll
+            for (int i4 = 0; i4 < 8; ++i4) {
+              float4 cs = make_float4(0.f, 0.f, 0.f, 0.f);
+              if (col0 + 4 * i4 < N) cs = __ldg(reinterpret_cast<const float4*>(col_scale + col0 + 4 * i4));
+              o[i4].x = static_cast<float>(static_cast<int32_t>(r[4 * i4])) * rs * cs.x;
+              o[i4].y = static_cast<float>(static_cast<int32_t>(r[4 * i4 + 1])) * rs * cs.y;
+              o[i4].z = static_cast<float>(static_cast<int32_t>(r[4 * i4 + 2])) * rs * cs.z;
+              o[i4].w = static_cast<float>(static_cast<int32_t>(r[4 * i4 + 3])) * rs * cs.w;
+            }
+            if (lane == 0) dev::tma_store_wait_read();
+            __syncwarp();
+#pragma unroll
+            for (int i4 = 0; i4 < 8; ++i4) *reinterpret_cast<float4*>(my_row + ((i4 ^ (lane & 7)) << 4)) = o[i4];
+            dev::fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+              dev::tma_store_2d_hint(&outmap, stage, col0, row0, store_policy);
+              dev::tma_store_commit();
             }
           }
         }
@@ -228,6 +288,7 @@ i8gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ 
       if (lane == 0) dev::mbar_arrive(tempty);
       ++items;
     }
+    if (lane == 0) dev::tma_store_wait_read();   // no store still reads this CTA's shared memory
   }
   dev::tc_fence_before();
   __syncthreads();
@@ -764,6 +825,16 @@ int i8gemm_tcgen05(const void* a, const void* b, int32_t* acc, const float* row_
   if (int rc = make_tensor_map_2d(&bmap, b, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, (uint64_t)K,
                                   (uint64_t)N, (uint64_t)N, BK, 128, CU_TENSOR_MAP_SWIZZLE_128B))
     return rc;
+  // results leave through TMA stores of 32 x 32 chunks (128 bytes of a row per chunk)
+  CUtensorMap accmap = amap, outmap = amap;   // placeholders where an output is absent (never used by the kernel)
+  if (acc)
+    if (int rc = make_tensor_map_2d(&accmap, acc, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, (uint64_t)M, (uint64_t)N,
+                                    (uint64_t)N * 4, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
+  if (out)
+    if (int rc = make_tensor_map_2d(&outmap, out, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, (uint64_t)M, (uint64_t)N,
+                                    (uint64_t)N * 4, 32, 32, CU_TENSOR_MAP_SWIZZLE_128B))
+      return rc;
   static std::atomic<uint64_t> configured{0};  // per device
   if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(i8gemm_kernel), kSmemBytes, configured)) return rc;
   const uint32_t idesc = dev::make_idesc(/*c=s32*/ 2, a_unsigned ? 0 : 1, b_unsigned ? 0 : 1,
@@ -773,8 +844,10 @@ int i8gemm_tcgen05(const void* a, const void* b, int32_t* acc, const float* row_
   const int halves = (tiles * 2 <= ctas) ? 1 : 0;  // few tiles: one row block per CTA
   const int items = tiles * (halves ? 2 : 1);
   const int grid = items < ctas ? items : ctas;
-  i8gemm_kernel<<<grid, kThreads, kSmemBytes, stream>>>(amap, bmap, acc, out, row_scale, col_scale,
-                                                        (int)M, (int)N, (int)K, idesc, halves,
+  static std::atomic<int> staged_cache{INT32_MIN};
+  const int staged = env_int_once("QMM_I8_STAGED_STORE", 1, staged_cache);   // 0: results stored straight from registers
+  i8gemm_kernel<<<grid, kThreads, kSmemBytes, stream>>>(amap, bmap, accmap, outmap, acc, out, row_scale, col_scale,
+                                                        (int)M, (int)N, (int)K, idesc, halves, staged,
                                                         device_status_word());
   QMM_CHECK_LAUNCH("i8gemm_kernel");
   return QMM_OK;
