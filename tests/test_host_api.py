@@ -46,6 +46,28 @@ def test_error_reporting_without_a_gpu():
     assert e.value.status_name == "QMM_ERR_UNSUPPORTED"
 
 
+def test_gather_copy_entry_points_validate_before_any_cuda_call():
+    """qmm_multicast_copy / qmm_peer_copy: null, misaligned and out-of-range arguments are refused
+    with QMM_ERR_INVALID_ARGUMENT (no launch is attempted, so this runs without a GPU)."""
+    lib = _lib.load()
+    buf = (ctypes.c_uint8 * 256)()
+    base = ctypes.addressof(buf)
+    base += (-base) % 16
+    assert lib.qmm_multicast_copy(None, base, 64, base, base, 0, None) == 1
+    assert lib.qmm_multicast_copy(base, base + 16, 40, base + 32, base + 36, 0, None) == 1      # bytes not a multiple of 16
+    assert lib.qmm_multicast_copy(base + 4, base + 16, 64, base + 32, base + 36, 0, None) == 1  # misaligned source
+    assert lib.qmm_multicast_copy(base, base + 16, 64, base + 32, base + 36, -1, None) == 1
+    assert lib.qmm_multicast_copy(base, base + 16, 0, base + 32, base + 36, 0, None) == 0       # nothing to copy
+    dst = (ctypes.c_void_p * 2)(base + 64, base + 128)
+    sig = (ctypes.c_void_p * 2)(base + 192, base + 196)
+    assert lib.qmm_peer_copy(base, dst, sig, 0, 64, base + 200, base + 204, 0, None) == 1        # no peers
+    assert lib.qmm_peer_copy(base, dst, sig, 16, 64, base + 200, base + 204, 0, None) == 1       # more than QMM_MAX_PEERS
+    bad = (ctypes.c_void_p * 2)(base + 64, None)
+    assert lib.qmm_peer_copy(base, bad, sig, 2, 64, base + 200, base + 204, 0, None) == 1
+    assert "peer 1" in _lib.last_error()
+    assert lib.qmm_peer_copy(base, dst, sig, 2, 0, base + 200, base + 204, 0, None) == 0
+
+
 def test_codecs_match_reference_fixtures(golden):
     p = golden["codec_probe"]
     np.testing.assert_array_equal(Q._fp4_e2m1_quantize(p), golden["e2m1_encode_probe"])
