@@ -111,8 +111,8 @@ struct Fmt {
 // the first operand takes from one register.
 //   kOrderAffine4: (x0,x4) (x2,x6) | (x1,x5) (x3,x7)   one word of 4-bit codes; the second pair meets the codes at bits 4-7
 //   kOrderBytes:   (x0,x2) (x1,x3) | (x4,x6) (x5,x7)   two words of 8-bit codes
-//   kOrderNibbles: (x0,x4) (x1,x5) | (x2,x6) (x3,x7)   one word of 4-bit codes converted pair by pair
-enum { kOrderAffine4 = 0, kOrderBytes = 1, kOrderNibbles = 2 };
+//   kOrderNatural: (x0,x1) (x2,x3) | (x4,x5) (x6,x7)   codes converted by the hardware, two neighbours per instruction
+enum { kOrderAffine4 = 0, kOrderBytes = 1, kOrderNatural = 2 };
 
 // Stages x[M][K] (f16) into shared memory, 8 k (16 bytes) per thread and pass, every global load of a pass issued
 // before the first store.  With SUMS, also the sum of each (row, group) into xsum[group * stride + row]: fused into
@@ -159,10 +159,7 @@ __device__ __forceinline__ void stage_activations(const __half* __restrict__ x, 
           o.z = __byte_perm(h2, h3, 0x5410);
           o.w = __byte_perm(h2, h3, 0x7632);
         } else {
-          o.x = __byte_perm(h0, h2, 0x5410);
-          o.y = __byte_perm(h0, h2, 0x7632);
-          o.z = __byte_perm(h1, h3, 0x5410);
-          o.w = __byte_perm(h1, h3, 0x7632);
+          o = v[j];
         }
         *reinterpret_cast<uint4*>(xs + mm[j] * row_bytes + cc[j] * 16) = o;
       }
@@ -497,12 +494,12 @@ static int launch_bits(const Plan& p, const CUtensorMap& wmap, const CUtensorMap
 
 // ---------------------------------------------------------------------------
 // The MX formats (mxfp4, mxfp8: e8m0 scale per 32 k; nvfp4: e4m3 scale per 16 k) on the same skeleton.
-// An e2m1 code placed at bits 15 (sign) and 11..9 of a half reads as the f16 value v * 2^-14 (its
-// subnormal 0.5 lands on an f16 subnormal), an e4m3 byte placed at bits 15 and 13..7 as v * 2^-8; the
-// power of two multiplies the result once at the end.  mxfp4 and mxfp8 keep one accumulator per scale
-// group and apply the decoded e8m0 scale in f32.  nvfp4, whose groups are shorter than one MMA's k
-// range per thread, multiplies the converted weights by their scale in f16 before the MMA: the product
-// of a 2-bit and a 4-bit significand, scaled to stay between 2^-18 and 2^15, is exact.
+// The codes are converted by cvt.rn.f16x2.e2m1x2 / .e4m3x2: one instruction per two neighbouring codes, true
+// values (all exact in f16), NaN codes become NaN and reach exactly the output columns of their weight rows
+// through the MMA.  The activations are therefore staged in their natural order.  mxfp4 and mxfp8 keep one
+// accumulator per scale group and apply the decoded e8m0 scale in f32.  nvfp4, whose groups are shorter than
+// one MMA's k range per thread, multiplies the converted weights by their scale in f16 before the MMA: the
+// product of a 2-bit and a 4-bit significand between 2^-10 and 2688 is exact.
 // ---------------------------------------------------------------------------
 enum { kMxfp4 = 0, kMxfp8 = 1, kNvfp4 = 2 };
 
@@ -518,7 +515,7 @@ struct MxFmt {
   // mxfp4 takes words t4 and t4 + 4 of a step (one scale group per MMA pair), so a quad reads 64 contiguous
   // bytes of activations, as it does for 8-bit codes; nvfp4 takes words 2 t4 and 2 t4 + 1
   static constexpr int kRowPad = MODE == kNvfp4 ? 16 : 64;
-  static constexpr int kOrder = MODE == kMxfp8 ? kOrderBytes : kOrderNibbles;
+  static constexpr int kOrder = kOrderNatural;
 };
 
 namespace dev {
@@ -528,17 +525,20 @@ __device__ __forceinline__ uint32_t lds32(uint32_t a) {
   asm volatile("ld.shared.u32 %0, [%1+%2];" : "=r"(v) : "r"(a), "n"(OFF));
   return v;
 }
-// eight e2m1 codes of a word -> four registers of two f16 each, codes (j, j + 4) in register j
+// eight e2m1 codes of a word -> four registers of two f16 each: register j holds codes (2j, 2j + 1), true values
 __device__ __forceinline__ void e2m1_to_f16x2(uint32_t w, uint32_t (&r)[4]) {
-  r[0] = ((w << 12) & 0x80008000u) | ((w << 9) & 0x0E000E00u);
-  r[1] = ((w << 8) & 0x80008000u) | ((w << 5) & 0x0E000E00u);
-  r[2] = ((w << 4) & 0x80008000u) | ((w << 1) & 0x0E000E00u);
-  r[3] = (w & 0x80008000u) | ((w >> 3) & 0x0E000E00u);
+  asm("{\n\t.reg .b8 b0, b1, b2, b3;\n\tmov.b32 {b0, b1, b2, b3}, %4;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %0, b0;\n\tcvt.rn.f16x2.e2m1x2 %1, b1;\n\t"
+      "cvt.rn.f16x2.e2m1x2 %2, b2;\n\tcvt.rn.f16x2.e2m1x2 %3, b3;\n\t}"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3])
+      : "r"(w));
 }
-// four e4m3 bytes of a word -> bytes (0, 2) and bytes (1, 3) as two f16 each
-__device__ __forceinline__ void e4m3_to_f16x2(uint32_t w, uint32_t& even, uint32_t& odd) {
-  even = ((w << 8) & 0x80008000u) | ((w << 7) & 0x3F803F80u);
-  odd = (w & 0x80008000u) | ((w >> 1) & 0x3F803F80u);
+// four e4m3 bytes of a word -> bytes (0, 1) and bytes (2, 3) as two f16 each, true values, NaN codes -> NaN
+__device__ __forceinline__ void e4m3_to_f16x2(uint32_t w, uint32_t& p01, uint32_t& p23) {
+  asm("{\n\t.reg .b16 h0, h1;\n\tmov.b32 {h0, h1}, %2;\n\t"
+      "cvt.rn.f16x2.e4m3x2 %0, h0;\n\tcvt.rn.f16x2.e4m3x2 %1, h1;\n\t}"
+      : "=r"(p01), "=r"(p23)
+      : "r"(w));
 }
 // byte IDX of a word of e8m0 scales as f32; exact except for the codes 0 (2^-127) and 255 (NaN), which the caller
 // detects per word and decodes with e8m0_exact
@@ -552,7 +552,6 @@ __device__ __forceinline__ float e8m0_exact(uint32_t b) {
   return __uint_as_float(b == 0 ? 0x00400000u : (b << 23));
 }
 __device__ __forceinline__ bool has_byte_00_or_ff(uint32_t w) { return (__vcmpeq4(w, 0u) | __vcmpeq4(w, 0xFFFFFFFFu)) != 0; }
-__device__ __forceinline__ bool has_e4m3_nan(uint32_t w) { return __vcmpeq4(w & 0x7F7F7F7Fu, 0x7F7F7F7Fu) != 0; }
 __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
   uint32_t r;
   asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
@@ -633,7 +632,6 @@ mx_ring_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
   for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
     for (int i = 0; i < 4; ++i) ys[mt][i] = 0.f;
-  uint32_t nan_lo = 0, nan_hi = 0;     // mxfp8: a NaN code seen in row rho / rho + 8
   bool ok = true;
   int consumed = 0, requested = stages < nchunks ? stages : nchunks;
   if (active) {
@@ -656,7 +654,7 @@ mx_ring_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
 #pragma unroll
         for (int i = 0; i < 4; ++i) d[mt][i] = 0.f;
     }
-    const uint32_t sel_t4 = (t4 << 12) | (4u << 8) | (t4 << 4) | 4u;   // scale byte t4 of a word into the high byte of both halves
+    const uint32_t sel_t4 = 0x4400u | (t4 << 4) | t4;   // scale byte t4 of a word, twice, into the low half
     int st = 0, prev_st = 0;
     uint32_t phase = 0;
     const uint32_t ring32 = smem_u32(my_ring);
@@ -687,8 +685,7 @@ mx_ring_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
         const uint4 a = lds128<0>(sq), b = lds128<1024>(sq);
         sl[0] = a.x; sl[1] = a.y; sl[2] = a.z; sl[3] = a.w;
         sh[0] = b.x; sh[1] = b.y; sh[2] = b.z; sh[3] = b.w;
-        special = has_e4m3_nan(a.x) | has_e4m3_nan(a.y) | has_e4m3_nan(a.z) | has_e4m3_nan(a.w) | has_e4m3_nan(b.x) |
-                  has_e4m3_nan(b.y) | has_e4m3_nan(b.z) | has_e4m3_nan(b.w);
+        special = false;   // a NaN scale code converts to a NaN scale
       }
       const uint32_t wbase = (ring32 + st * kBox) | wthread;
       static_for<kStepsPerChunk>([&](auto s4c) {
@@ -725,13 +722,12 @@ mx_ring_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
         } else if constexpr (MODE == kMxfp8) {
           const uint32_t wa = wbase ^ (s4 << 5);
           const uint2 a = lds64<0>(wa), b = lds64<1024>(wa);
+          // two registers per word and row: bytes (0, 1) and bytes (2, 3)
           uint32_t ae0, ao0, ae1, ao1, be0, bo0, be1, bo1;
           e4m3_to_f16x2(a.x, ae0, ao0);
           e4m3_to_f16x2(a.y, ae1, ao1);
           e4m3_to_f16x2(b.x, be0, bo0);
           e4m3_to_f16x2(b.y, be1, bo1);
-          nan_lo |= __vcmpeq4(a.x & 0x7F7F7F7Fu, 0x7F7F7F7Fu) | __vcmpeq4(a.y & 0x7F7F7F7Fu, 0x7F7F7F7Fu);
-          nan_hi |= __vcmpeq4(b.x & 0x7F7F7F7Fu, 0x7F7F7F7Fu) | __vcmpeq4(b.y & 0x7F7F7F7Fu, 0x7F7F7F7Fu);
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
             const uint4 xq = lds128<s4 * 64>(xa[mt]);
@@ -754,14 +750,10 @@ mx_ring_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
           // nvfp4: this thread's two words of the step lie in the step's 16-k group t4
           const uint32_t wa = wbase ^ (s4 << 5);
           const uint2 a = lds64<0>(wa), b = lds64<1024>(wa);
-          uint32_t hl = __byte_perm(sl[s4], 0u, sel_t4), hh = __byte_perm(sh[s4], 0u, sel_t4);
-          uint32_t fl = (hl & 0x80008000u) | ((hl >> 1) & 0x3F803F80u), fh = (hh & 0x80008000u) | ((hh >> 1) & 0x3F803F80u);
-          fl = hmul2_u32(fl, 0x70007000u);     // x 2^13 (f16 0x7000); see the exponent budget above
-          fh = hmul2_u32(fh, 0x70007000u);
-          if (special) {
-            if ((hl & 0x7F007F00u) == 0x7F007F00u) fl = 0x7E007E00u;
-            if ((hh & 0x7F007F00u) == 0x7F007F00u) fh = 0x7E007E00u;
-          }
+          // scale byte t4 of the word twice in the low half, converted to (s, s); a NaN code converts to NaN
+          uint32_t fl, fh, unused;
+          e4m3_to_f16x2(__byte_perm(sl[s4], 0u, sel_t4), fl, unused);
+          e4m3_to_f16x2(__byte_perm(sh[s4], 0u, sel_t4), fh, unused);
           static_for<2>([&](auto wic) {
             constexpr int wi = decltype(wic)::value;
             uint32_t lo[4], hi[4];
@@ -800,30 +792,13 @@ mx_ring_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
 #pragma unroll
         for (int i = 0; i < 4; ++i) ys[mt][i] = d[mt][i];
     }
-    if (MODE == kMxfp8) {
-      // a NaN code anywhere in a weight row makes that output column NaN for every activation row; the four threads
-      // of a quad hold the same two weight rows
-      nan_lo |= __shfl_xor_sync(0xFFFFFFFFu, nan_lo, 1);
-      nan_lo |= __shfl_xor_sync(0xFFFFFFFFu, nan_lo, 2);
-      nan_hi |= __shfl_xor_sync(0xFFFFFFFFu, nan_hi, 1);
-      nan_hi |= __shfl_xor_sync(0xFFFFFFFFu, nan_hi, 2);
-      const float qnan = __uint_as_float(0x7FC00000u);
-#pragma unroll
-      for (int mt = 0; mt < MT; ++mt) {
-        if (nan_lo) ys[mt][0] = ys[mt][1] = qnan;
-        if (nan_hi) ys[mt][2] = ys[mt][3] = qnan;
-      }
-    }
   }
-  // the power of two that the code placement left out: e2m1 2^14, e4m3 2^8; nvfp4: 2^14 for the codes, 2^8 for
-  // the scales, less the 2^13 the scales were multiplied by
-  constexpr float kFinal = MODE == kMxfp4 ? 16384.f : MODE == kMxfp8 ? 256.f : 512.f;
   float* slot = hand + (warp * 32 + lane) * MT * 4;
   if (ks != 0 && active) {
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) slot[mt * 4 + i] = ys[mt][i] * kFinal;
+      for (int i = 0; i < 4; ++i) slot[mt * 4 + i] = ys[mt][i];
   }
   __syncthreads();
   if (ks == 0 && active) {
@@ -831,7 +806,7 @@ mx_ring_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     for (int mt = 0; mt < MT; ++mt) {
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        float v = ys[mt][i] * kFinal;
+        float v = ys[mt][i];
         for (int o = 1; o < ksplit; ++o) v += hand[((o * tiles + tile) * 32 + lane) * MT * 4 + mt * 4 + i];
         const int n = n0 + rho + ((i >> 1) << 3), m = mt * 8 + 2 * t4 + (i & 1);
         if (m < M) y[static_cast<size_t>(m) * N + n] = __float2half_rn(v);
