@@ -296,7 +296,17 @@ QMM_API int qmm_w4a16_g128_static_scratch(const uint16_t* x_bf16, const uint8_t*
  * qmm_mx_matmul replaces quantized_matmul / _quantized_matmul_gpu and the
  * mx_qgemm_{mxfp4,mxfp8,nvfp4}_{f32,f16} kernels (quantized.py:528-753,
  * :995-1074): E2M1 / E4M3 elements, E8M0 (group 32) or E4M3 (group 16) scales,
- * NaN codes (E4M3 0x7F/0xFF, E8M0 0xFF) propagate. */
+ * NaN codes (E4M3 0x7F/0xFF, E8M0 0xFF) propagate.
+ *
+ * Both choose a kernel by shape.  With f16 activations and M <= 16 (decode) the
+ * packed codes go to the tensor cores from per-warp TMA rings when x, w_packed,
+ * scales (and biases) are 16-byte aligned, N is a multiple of 16 and, affine:
+ * group_size is 64 / 128 / 256 (4-bit) or 32 / 64 / 128 (8-bit) with a multiple
+ * of 4 groups per row; MX: K is a multiple of 512 (mxfp4, mxfp8) or 256
+ * (nvfp4).  Other shapes, M > 16 and f32 activations run on CUDA-core kernels
+ * with the same arithmetic (scale * q + bias or scale * element in f32, f32
+ * accumulation, one cast).  The tensor-core kernels apply the scale per group
+ * instead of per weight: same result up to f32 rounding of the sums. */
 QMM_API int qmm_affine_matmul(const void* x, const void* w_packed, const float* scales,
                               const float* biases, void* y, int64_t M, int64_t N, int64_t K,
                               int bits, int64_t group_size, int dtype, void* stream);
