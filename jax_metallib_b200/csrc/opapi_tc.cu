@@ -496,7 +496,7 @@ static int launch_bits(const Plan& p, const CUtensorMap& wmap, const CUtensorMap
 // The MX formats (mxfp4, mxfp8: e8m0 scale per 32 k; nvfp4: e4m3 scale per 16 k) on the same skeleton.
 // The codes are converted by cvt.rn.f16x2.e2m1x2 / .e4m3x2: one instruction per two neighbouring codes, true
 // values (all exact in f16), NaN codes become NaN and reach exactly the output columns of their weight rows
-// through the MMA.  The activations are therefore staged in their natural order.  mxfp4 and mxfp8 keep one
+// through the MMA; e8m0 scales by cvt.rn.bf16x2.ue8m0x2 (code 0 = 2^-127, code 255 = NaN).  The activations are therefore staged in their natural order.  mxfp4 and mxfp8 keep one
 // accumulator per scale group and apply the decoded e8m0 scale in f32.  nvfp4, whose groups are shorter than
 // one MMA's k range per thread, multiplies the converted weights by their scale in f16 before the MMA: the
 // product of a 2-bit and a 4-bit significand between 2^-10 and 2688 is exact.
@@ -540,18 +540,18 @@ __device__ __forceinline__ void e4m3_to_f16x2(uint32_t w, uint32_t& p01, uint32_
       : "=r"(p01), "=r"(p23)
       : "r"(w));
 }
-// byte IDX of a word of e8m0 scales as f32; exact except for the codes 0 (2^-127) and 255 (NaN), which the caller
-// detects per word and decodes with e8m0_exact
-template <int IDX>
-__device__ __forceinline__ float e8m0_fast(uint32_t w) {
-  const uint32_t v = IDX == 0 ? (w << 23) : IDX == 1 ? (w << 15) : IDX == 2 ? (w << 7) : (w >> 1);
-  return __uint_as_float(v & 0x7F800000u);
+// four e8m0 scale codes of a word -> bytes (0, 1) and bytes (2, 3) as two bf16 each: 2^(code - 127), exact
+// (code 0 is the bf16 subnormal 2^-127, code 255 is NaN); a bf16 is the upper half of the f32 of the same value
+__device__ __forceinline__ void e8m0_to_bf16x2(uint32_t w, uint32_t& p01, uint32_t& p23) {
+  asm("{\n\t.reg .b16 h0, h1;\n\tmov.b32 {h0, h1}, %2;\n\t"
+      "cvt.rn.bf16x2.ue8m0x2 %0, h0;\n\tcvt.rn.bf16x2.ue8m0x2 %1, h1;\n\t}"
+      : "=r"(p01), "=r"(p23)
+      : "r"(w));
 }
-__device__ __forceinline__ float e8m0_exact(uint32_t b) {
-  if (b == 0xFFu) return __uint_as_float(0x7FC00000u);
-  return __uint_as_float(b == 0 ? 0x00400000u : (b << 23));
+template <int HALF>
+__device__ __forceinline__ float bf16_half_as_f32(uint32_t p) {
+  return __uint_as_float(HALF ? (p & 0xFFFF0000u) : (p << 16));
 }
-__device__ __forceinline__ bool has_byte_00_or_ff(uint32_t w) { return (__vcmpeq4(w, 0u) | __vcmpeq4(w, 0xFFFFFFFFu)) != 0; }
 __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
   uint32_t r;
   asm("mul.rn.f16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
@@ -669,23 +669,25 @@ mx_ring_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
         ++requested;
       }
       // ---- this chunk's scale bytes of rows rho and rho + 8
-      uint32_t sl[4], sh[4];      // words of scale bytes (mxfp4: 2, mxfp8: 1, nvfp4: 4 used)
-      bool special;
+      // mxfp4, mxfp8: the chunk's e8m0 scales as bf16 pairs (register j = scales 2j, 2j + 1 of the chunk);
+      // nvfp4: the words of e4m3 scale bytes
+      uint32_t sl[4], sh[4];
       if (MODE == kMxfp4) {
         const uint32_t sq = sa + ((((c >> 1) ^ rho) & 7) << 4) + ((c & 1) << 3);
         const uint2 a = lds64<0>(sq), b = lds64<1024>(sq);
-        sl[0] = a.x; sl[1] = a.y; sh[0] = b.x; sh[1] = b.y;
-        special = has_byte_00_or_ff(a.x) | has_byte_00_or_ff(a.y) | has_byte_00_or_ff(b.x) | has_byte_00_or_ff(b.y);
+        e8m0_to_bf16x2(a.x, sl[0], sl[1]);
+        e8m0_to_bf16x2(a.y, sl[2], sl[3]);
+        e8m0_to_bf16x2(b.x, sh[0], sh[1]);
+        e8m0_to_bf16x2(b.y, sh[2], sh[3]);
       } else if (MODE == kMxfp8) {
         const uint32_t sq = sa + ((((c >> 2) ^ rho) & 7) << 4) + ((c & 3) << 2);
-        sl[0] = lds32<0>(sq); sh[0] = lds32<1024>(sq);
-        special = has_byte_00_or_ff(sl[0]) | has_byte_00_or_ff(sh[0]);
+        e8m0_to_bf16x2(lds32<0>(sq), sl[0], sl[1]);
+        e8m0_to_bf16x2(lds32<1024>(sq), sh[0], sh[1]);
       } else {
         const uint32_t sq = sa + (((c ^ rho) & 7) << 4);
         const uint4 a = lds128<0>(sq), b = lds128<1024>(sq);
         sl[0] = a.x; sl[1] = a.y; sl[2] = a.z; sl[3] = a.w;
         sh[0] = b.x; sh[1] = b.y; sh[2] = b.z; sh[3] = b.w;
-        special = false;   // a NaN scale code converts to a NaN scale
       }
       const uint32_t wbase = (ring32 + st * kBox) | wthread;
       static_for<kStepsPerChunk>([&](auto s4c) {
@@ -703,14 +705,8 @@ mx_ring_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
               mma16816_first(d[mt], lo[0], hi[0], lo[1], hi[1], xq.x, xq.y);
               mma16816(d[mt], lo[2], hi[2], lo[3], hi[3], xq.z, xq.w);
             }
-            // scale byte (s4 & 1) * 2 + wi of word s4 >> 1
-            constexpr int idx = (s4 & 1) * 2 + wi;
-            const uint32_t wl = sl[s4 >> 1], wh = sh[s4 >> 1];
-            float fl = e8m0_fast<idx>(wl), fh = e8m0_fast<idx>(wh);
-            if (special) {
-              fl = e8m0_exact((wl >> (8 * idx)) & 0xFFu);
-              fh = e8m0_exact((wh >> (8 * idx)) & 0xFFu);
-            }
+            // scale 2 s4 + wi of the chunk: register s4, half wi
+            const float fl = bf16_half_as_f32<wi>(sl[s4]), fh = bf16_half_as_f32<wi>(sh[s4]);
 #pragma unroll
             for (int mt = 0; mt < MT; ++mt) {
               ys[mt][0] = fmaf(fl, d[mt][0], ys[mt][0]);
@@ -734,11 +730,7 @@ mx_ring_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
             mma16816_first(d[mt], ae0, be0, ao0, bo0, xq.x, xq.y);
             mma16816(d[mt], ae1, be1, ao1, bo1, xq.z, xq.w);
           }
-          float fl = e8m0_fast<s4>(sl[0]), fh = e8m0_fast<s4>(sh[0]);
-          if (special) {
-            fl = e8m0_exact((sl[0] >> (8 * s4)) & 0xFFu);
-            fh = e8m0_exact((sh[0] >> (8 * s4)) & 0xFFu);
-          }
+          const float fl = bf16_half_as_f32<(s4 & 1)>(sl[s4 >> 1]), fh = bf16_half_as_f32<(s4 & 1)>(sh[s4 >> 1]);   // scale s4 of the chunk
 #pragma unroll
           for (int mt = 0; mt < MT; ++mt) {
             ys[mt][0] = fmaf(fl, d[mt][0], ys[mt][0]);
