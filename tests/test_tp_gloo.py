@@ -85,6 +85,20 @@ def _exchange_worker(rank, world, port, result_dir):
                 assert torch.equal(ex.logical(name, slot), _oracle_matmul(x, w, scale))
                 assert torch.equal(tp.gathered_view(out)[:, rank, :], _oracle_matmul(x, w[:, a:b], scale[a:b]))
         ex.finish()
+        # the symmetric-memory modes are refused on CPU ranks, unknown modes everywhere
+        for mode in ("fused", "mcast", "peer", "copy"):
+            try:
+                tp.GatherExchange(shapes, "cpu", depth=2, mode=mode)
+            except ValueError as exc:
+                assert "CUDA" in str(exc)
+            else:
+                raise AssertionError(f"mode {mode!r} accepted on CPU ranks")
+        try:
+            tp.GatherExchange(shapes, "cpu", depth=2, mode="ring")
+        except ValueError as exc:
+            assert "unknown exchange mode" in str(exc)
+        else:
+            raise AssertionError("unknown mode accepted")
         with open(os.path.join(result_dir, f"ok{rank}"), "w") as f:
             f.write("ok")
     finally:
