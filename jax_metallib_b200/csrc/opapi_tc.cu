@@ -35,6 +35,10 @@ constexpr int kStepBytes = 32;       // bytes of a weight row per step of a quad
 constexpr int kStepsPerChunk = 4;    // a box holds 4 steps
 constexpr int kGroupsPerBox = 32;    // scales / biases of 32 groups per row in one box
 constexpr int kMaxSmem = 227 * 1024;
+// boxes per warp's ring.  Deeper rings measured slower where shared memory allowed them (8-bit codes, M <= 2,
+// 14336 x 4096: 16.6 and 20.1 us with 8 boxes against 13.9 and 13.1 us with 4): every box requested at the start
+// delays the first one.
+constexpr int kMaxStages = 4;
 
 namespace dev {
 using namespace qmm::dev;
@@ -189,7 +193,7 @@ struct Plan {
 static size_t fixed_smem(int bits, int warps, int M, int MT, int K, int G) {
   const int pad = bits == 4 ? Fmt<4>::kRowPad : Fmt<8>::kRowPad;
   return static_cast<size_t>(warps) * 2 * kBox + static_cast<size_t>(M) * (2 * K + pad) + static_cast<size_t>(G) * MT * 8 * 4 +
-         static_cast<size_t>(warps) * 32 * MT * 4 * 4 + static_cast<size_t>(warps) * (8 + 1) * 8 + 1024;
+         static_cast<size_t>(warps) * 32 * MT * 4 * 4 + static_cast<size_t>(warps) * (kMaxStages + 1) * 8 + 1024;
 }
 
 // Picks tiles per CTA, the K split and the ring depth: as many warps as a CTA may have, at most 8 K units per warp
@@ -209,7 +213,7 @@ static bool choose(int64_t tiles_total, int U, int chunks_per_unit, FixedFn fixe
     const size_t fx = fixed(warps);
     const int chunks_per_warp = ((U + ksplit - 1) / ksplit) * chunks_per_unit;
     int stages = fx < static_cast<size_t>(kMaxSmem) ? static_cast<int>((kMaxSmem - fx) / (static_cast<size_t>(warps) * kBox)) : 0;
-    if (stages > 8) stages = 8;
+    if (stages > kMaxStages) stages = kMaxStages;
     if (stages > chunks_per_warp) stages = chunks_per_warp;
     if (stages >= 2 || (stages == 1 && chunks_per_warp == 1)) {
       p->tiles = tiles;
@@ -563,7 +567,7 @@ __device__ __forceinline__ uint32_t hmul2_u32(uint32_t a, uint32_t b) {
 static size_t mx_fixed_smem(int mode, int warps, int M, int MT, int K) {
   const int pad = mode == kNvfp4 ? 16 : 64;
   return static_cast<size_t>(warps) * kBox + static_cast<size_t>(M) * (2 * K + pad) + static_cast<size_t>(warps) * 32 * MT * 4 * 4 +
-         static_cast<size_t>(warps) * (8 + 1) * 8 + 1024;
+         static_cast<size_t>(warps) * (kMaxStages + 1) * 8 + 1024;
 }
 
 static bool mx_plan(int mode, int64_t M, int64_t N, int64_t K, Plan* p) {
